@@ -1,0 +1,547 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a: the dense forward / dgrad / wgrad work of
+// the reference's Dense layer (machine_learning/src/arch/layers/dense.rs:36-64) and the GEMM half
+// of its im2col convolution (arch/layers/conv/conv2d.rs:119-125), rebuilt for Blackwell.
+//
+//   warp 4 (one elected lane)  TMA producer: cp.async.bulk.tensor tiles -> 128B-swizzled smem ring
+//   warp 5 (one elected lane)  MMA issuer:   tcgen05.mma (kind::tf32 | kind::f16/bf16), f32
+//                                            accumulators in TMEM, double buffered (2 x BN columns)
+//   warps 0-3                  epilogue:     tcgen05.ld TMEM -> registers, bias / activation /
+//                                            activation-derivative / accumulate, stores (row-major
+//                                            and transposed, f32 and bf16)
+//
+// Operands may be K-major or (bf16 only) MN-major; the difference is confined to the TMA box
+// pattern and three descriptor fields computed on the host (see make_operand()).
+// All mbarrier waits are bounded; on a timeout the kernel records a code in *status, every role
+// leaves its loop, TMEM is freed and the kernel returns normally.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "act.cuh"
+#include "ono_kernels.h"
+#include "ptx.cuh"
+
+namespace ono {
+
+// Predicated, fully unrolled tail loop: keeps v[] in registers (no dynamic indexing).
+#define ONO_TAIL_LOOP(j) _Pragma("unroll") for (int j = 0; j < 32; ++j) if (j < ncols)
+
+struct OperandDev {
+  int mn_major;       // 0: K contiguous in global memory, 1: MN contiguous
+  int n_box;          // TMA boxes per stage
+  int box_mn;         // MN extent covered by one box
+  uint32_t box_stride_bytes;
+  uint32_t lbo_bytes, sbo_bytes, kstep_bytes;
+};
+
+struct GemmDev {
+  int M, N, K;
+  OperandDev a, b;
+  uint32_t idesc;
+  OnoEpilogue epi;
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int BN>
+struct TileCfg {
+  static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
+__device__ __forceinline__ void fail(const GemmDev& p, volatile int* abort_flag, int code) {
+  if (p.status) atomicCAS(p.status, 0, code);
+  *abort_flag = 1;
+}
+
+// Processes 32 consecutive columns [n0, n0+32) of row m held in v[].
+__device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[32], int m, int n0,
+                                               int M, int N) {
+  const bool row_ok = m < M;
+  const int ncols = min(32, N - n0);
+  const bool full = ncols == 32;
+  if (e.alpha != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+  }
+  if (e.bias) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += __ldg(e.bias + n0 + j);
+  }
+  const size_t row_off = (size_t)m * e.ld_out + n0;
+  if (row_ok && e.pre_f32) {
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(e.pre_f32 + row_off + j) =
+            make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+      ONO_TAIL_LOOP(j) e.pre_f32[row_off + j] = v[j];
+    }
+  }
+  if (row_ok && e.pre_bf16) {
+    __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(e.pre_bf16) + row_off;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 pk;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&t0);
+        pk.y = *reinterpret_cast<uint32_t*>(&t1);
+        pk.z = *reinterpret_cast<uint32_t*>(&t2);
+        pk.w = *reinterpret_cast<uint32_t*>(&t3);
+        *reinterpret_cast<uint4*>(pb + j) = pk;
+      }
+    } else {
+      ONO_TAIL_LOOP(j) pb[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+  if (e.act != ACT_NONE) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = act_fwd(e.act, e.act_param, v[j]);
+  }
+  if (e.dact != ACT_NONE && row_ok) {
+    const size_t aoff = (size_t)m * e.ld_aux + n0;
+    if (e.aux_f32) {
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 a = *reinterpret_cast<const float4*>(e.aux_f32 + aoff + j);
+          v[j] = act_bwd(e.dact, e.dact_param, e.relu_quirk, a.x, v[j]);
+          v[j + 1] = act_bwd(e.dact, e.dact_param, e.relu_quirk, a.y, v[j + 1]);
+          v[j + 2] = act_bwd(e.dact, e.dact_param, e.relu_quirk, a.z, v[j + 2]);
+          v[j + 3] = act_bwd(e.dact, e.dact_param, e.relu_quirk, a.w, v[j + 3]);
+        }
+      } else {
+        ONO_TAIL_LOOP(j)
+          v[j] = act_bwd(e.dact, e.dact_param, e.relu_quirk, e.aux_f32[aoff + j], v[j]);
+      }
+    } else if (e.aux_bf16) {
+      const __nv_bfloat16* ab = reinterpret_cast<const __nv_bfloat16*>(e.aux_bf16) + aoff;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk = *reinterpret_cast<const uint4*>(ab + j);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float2 f = __bfloat1622float2(h[q]);
+            v[j + 2 * q] = act_bwd(e.dact, e.dact_param, e.relu_quirk, f.x, v[j + 2 * q]);
+            v[j + 2 * q + 1] = act_bwd(e.dact, e.dact_param, e.relu_quirk, f.y, v[j + 2 * q + 1]);
+          }
+        }
+      } else {
+        ONO_TAIL_LOOP(j)
+          v[j] = act_bwd(e.dact, e.dact_param, e.relu_quirk, __bfloat162float(ab[j]), v[j]);
+      }
+    }
+  }
+  if (row_ok && e.out_f32) {
+    float* o = e.out_f32 + row_off;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (e.beta != 0.0f) {
+          float4 old = *reinterpret_cast<const float4*>(o + j);
+          r.x += e.beta * old.x; r.y += e.beta * old.y; r.z += e.beta * old.z; r.w += e.beta * old.w;
+          v[j] = r.x; v[j + 1] = r.y; v[j + 2] = r.z; v[j + 3] = r.w;
+        }
+        *reinterpret_cast<float4*>(o + j) = r;
+      }
+    } else {
+      ONO_TAIL_LOOP(j) {
+        if (e.beta != 0.0f) v[j] += e.beta * o[j];
+        o[j] = v[j];
+      }
+    }
+  }
+  if (row_ok && e.out_bf16) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(e.out_bf16) + row_off;
+    if (full) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 pk;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&t0);
+        pk.y = *reinterpret_cast<uint32_t*>(&t1);
+        pk.z = *reinterpret_cast<uint32_t*>(&t2);
+        pk.w = *reinterpret_cast<uint32_t*>(&t3);
+        *reinterpret_cast<uint4*>(o + j) = pk;
+      }
+    } else {
+      ONO_TAIL_LOOP(j) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  }
+  // Transposed copies: for a fixed column the 32 lanes of a warp hold 32 consecutive rows, so each
+  // store instruction writes one contiguous 128-byte (f32) or 64-byte (bf16) run.
+  if (row_ok && e.outT_f32) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) e.outT_f32[(size_t)(n0 + j) * e.ld_outT + m] = v[j];
+  }
+  if (row_ok && e.outT_bf16) {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(e.outT_bf16);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) o[(size_t)(n0 + j) * e.ld_outT + m] = __float2bfloat16_rn(v[j]);
+  }
+}
+
+template <int ESIZE, int BN>
+__global__ void __launch_bounds__(192, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmDev p) {
+  constexpr int BM = 128;
+  constexpr int BK = 128 / ESIZE;      // one 128-byte swizzle row of K per stage
+  constexpr int UMMA_K = 32 / ESIZE;   // 8 for tf32, 16 for bf16
+  constexpr int KSTEPS = BK / UMMA_K;  // 4
+  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = TileCfg<BN>::STAGES;
+  constexpr uint32_t TMEM_COLS = TileCfg<BN>::TMEM_COLS;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ __align__(8) uint64_t drain_bar;
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], 128);
+    }
+    mbar_init(&drain_bar, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 5) {
+    tmem_alloc(&tmem_base_smem, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int total_tiles = num_m * num_n;
+  const int KB = (p.K + BK - 1) / BK;
+  const uint64_t budget = p.timeout_ns;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---------------- TMA producer ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % num_m) * BM;
+        const int n0 = (tile / num_m) * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abortp, budget)) {
+            fail(p, abortp, ONO_ERR_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          for (int i = 0; i < p.a.n_box; ++i) {
+            const int mn = m0 + i * p.a.box_mn;
+            tma_load_2d(sa + i * p.a.box_stride_bytes, &tmA, &full_bar[stage],
+                        p.a.mn_major ? mn : k0, p.a.mn_major ? k0 : mn);
+          }
+          for (int i = 0; i < p.b.n_box; ++i) {
+            const int mn = n0 + i * p.b.box_mn;
+            tma_load_2d(sb + i * p.b.box_stride_bytes, &tmB, &full_bar[stage],
+                        p.b.mn_major ? mn : k0, p.b.mn_major ? k0 : mn);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Give copies already in flight time to land before the CTA retires its shared memory.
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // ---------------- MMA issuer ----------------
+      int stage = 0;
+      uint32_t phase = 0;
+      int t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        if (!mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1u, abortp, budget)) {
+          fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_EMPTY);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, budget)) {
+            fail(p, abortp, ONO_ERR_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + (size_t)stage * STAGE_BYTES);
+          const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < KSTEPS; ++k) {
+            const uint64_t adesc =
+                make_smem_desc_sw128(a_addr + k * p.a.kstep_bytes, p.a.lbo_bytes, p.a.sbo_bytes);
+            const uint64_t bdesc =
+                make_smem_desc_sw128(b_addr + k * p.b.kstep_bytes, p.b.lbo_bytes, p.b.sbo_bytes);
+            if (ESIZE == 4) umma_tf32(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+            else umma_f16(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+          }
+          umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tmem_full_bar[buf]);
+      }
+      // Make sure no MMA is still running before TMEM is released.
+      umma_commit(&drain_bar);
+      mbar_wait_bounded(&drain_bar, 0, abortp, ok ? budget : 1000000ull);
+    }
+  } else {
+    // ---------------- epilogue warps 0..3 (TMEM lanes 32*warp .. 32*warp+31) ----------------
+    int t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      const int m0 = (tile % num_m) * BM;
+      const int n0 = (tile / num_m) * BN;
+      const int buf = t & 1;
+      const uint32_t acc_phase = (t >> 1) & 1;
+      if (!mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget)) {
+        if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int m = m0 + warp * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int nc = n0 + c * 32;
+        if (nc >= p.N) break;  // uniform across the CTA
+        uint32_t r[32];
+        tmem_ld_x32(t_row + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        epilogue_chunk(p.epi, v, m, nc, p.M, p.N);
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty_bar[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+void set_error(const char* fmt, const char* a = "", long long b = 0, long long c = 0) {
+  snprintf(g_err, sizeof(g_err), fmt, a, b, c);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+// 2-D row-major global matrix [rows, cols] with leading dimension ld (elements); box = {box_cols
+// (innermost, 128 bytes), box_rows}; 128-byte swizzle.
+int encode_map_2d(CUtensorMap* map, const void* base, int esize, long long rows, long long cols,
+                  long long ld, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled unavailable%s", ""); return -2; }
+  if (((uintptr_t)base & 15) != 0) { set_error("TMA base not 16-byte aligned%s", ""); return -3; }
+  if ((ld * esize) % 16 != 0) { set_error("TMA row stride %s%lld bytes not a multiple of 16", "", ld * esize); return -3; }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * esize)};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%s%lld)", "", (long long)r); return -4; }
+  return 0;
+}
+
+// Fills the device-side operand description and encodes the operand's tensor map.
+static int make_operand(OperandDev* od, CUtensorMap* map, const void* ptr, int esize, int major,
+                        int MN, int K, int ld, int tile_mn) {
+  const int BK = 128 / esize;
+  if (major == ONO_K_MAJOR) {
+    od->mn_major = 0;
+    od->n_box = 1;
+    od->box_mn = tile_mn;
+    od->box_stride_bytes = 0;
+    od->lbo_bytes = 16;      // unused for a single swizzle atom along K
+    od->sbo_bytes = 1024;    // 8 rows x 128 bytes
+    od->kstep_bytes = 32;    // one UMMA_K slice inside the 128-byte row
+    return encode_map_2d(map, ptr, esize, MN, K, ld, BK, tile_mn);
+  }
+  if (esize != 2) { set_error("MN-major operands are supported for bf16 only%s", ""); return -5; }
+  const int chunk = 128 / esize;  // 64 elements of MN per 128-byte row
+  od->mn_major = 1;
+  od->n_box = tile_mn / chunk;
+  if (od->n_box < 1) { set_error("MN-major tile too narrow%s", ""); return -5; }
+  od->box_mn = chunk;
+  od->box_stride_bytes = (uint32_t)BK * 128u;  // BK rows of K, 128 bytes each
+  od->lbo_bytes = od->box_stride_bytes;        // between 64-wide MN atoms
+  od->sbo_bytes = 1024;                        // between groups of 8 K-rows
+  od->kstep_bytes = (32 / esize) * 128u;       // UMMA_K rows of K
+  return encode_map_2d(map, ptr, esize, K, MN, ld, chunk, BK);
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int ESIZE, int BN>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDev& p, int max_ctas,
+                  cudaStream_t stream) {
+  constexpr int STAGES = TileCfg<BN>::STAGES;
+  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN * 128) + 1024;
+  static bool attr_set = false;
+  auto kern = gemm_tcgen05_kernel<ESIZE, BN>;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return -6; }
+    attr_set = true;
+  }
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  int grid = max_ctas > 0 ? max_ctas : num_sms();
+  if (grid > tiles) grid = tiles;
+  kern<<<grid, 192, smem, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { set_error("gemm launch: %s", cudaGetErrorString(e)); return -7; }
+  return 0;
+}
+
+}  // namespace ono
+
+extern "C" const char* ono_last_error(void) { return ono::g_err; }
+extern "C" int ono_num_sms(void) { return ono::num_sms(); }
+
+extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
+  using namespace ono;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (!g || !g->A || !g->B || g->M <= 0 || g->N <= 0 || g->K <= 0) { set_error("bad gemm args%s", ""); return -1; }
+  const int esize = g->dtype == ONO_TF32 ? 4 : 2;
+  int bn = g->bn;
+  if (bn == 0) {
+    if (g->N <= 32) bn = 32;
+    else if (g->N <= 128) bn = 128;
+    else {
+      // Prefer 256-wide tiles unless they leave most SMs idle.
+      const long long t256 = (long long)((g->M + 127) / 128) * ((g->N + 255) / 256);
+      bn = t256 >= (long long)num_sms() * 3 / 4 ? 256 : 128;
+    }
+  }
+  if (bn != 32 && bn != 128 && bn != 256) { set_error("bn must be 32, 128 or 256%s", ""); return -1; }
+  if (g->b_major == ONO_MN_MAJOR && bn < 64) bn = 128;
+  const OnoEpilogue& e = g->epi;
+  if ((e.out_f32 || e.out_bf16 || e.pre_f32 || e.pre_bf16) && e.ld_out < g->N) { set_error("ld_out < N%s", ""); return -1; }
+  if ((e.outT_f32 || e.outT_bf16) && e.ld_outT < g->M) { set_error("ld_outT < M%s", ""); return -1; }
+  // The vectorised epilogue paths need 16-byte aligned rows.
+  if ((e.out_f32 || e.pre_f32) && (e.ld_out % 4 != 0)) { set_error("ld_out must be a multiple of 4 for f32 outputs%s", ""); return -1; }
+  if ((e.out_bf16 || e.pre_bf16) && (e.ld_out % 8 != 0)) { set_error("ld_out must be a multiple of 8 for bf16 outputs%s", ""); return -1; }
+  if (e.dact != ACT_NONE) {
+    if (!e.aux_f32 && !e.aux_bf16) { set_error("dact needs aux%s", ""); return -1; }
+    if (e.aux_f32 && e.ld_aux % 4 != 0) { set_error("ld_aux must be a multiple of 4%s", ""); return -1; }
+    if (e.aux_bf16 && e.ld_aux % 8 != 0) { set_error("ld_aux must be a multiple of 8%s", ""); return -1; }
+  }
+
+  GemmDev p;
+  memset(&p, 0, sizeof(p));
+  p.M = g->M; p.N = g->N; p.K = g->K;
+  p.epi = g->epi;
+  p.status = g->status;
+  p.timeout_ns = 2000000000ull;
+  CUtensorMap ta, tb;
+  int rc = make_operand(&p.a, &ta, g->A, esize, g->a_major, g->M, g->K, g->lda, 128);
+  if (rc) return rc;
+  rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, bn);
+  if (rc) return rc;
+  const uint32_t fmt = g->dtype == ONO_TF32 ? 2u : 1u;  // TF32 / BF16
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
+            ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+  if (esize == 4) {
+    if (bn == 32) return launch<4, 32>(ta, tb, p, g->max_ctas, stream);
+    if (bn == 128) return launch<4, 128>(ta, tb, p, g->max_ctas, stream);
+    return launch<4, 256>(ta, tb, p, g->max_ctas, stream);
+  }
+  if (bn == 32) return launch<2, 32>(ta, tb, p, g->max_ctas, stream);
+  if (bn == 128) return launch<2, 128>(ta, tb, p, g->max_ctas, stream);
+  return launch<2, 256>(ta, tb, p, g->max_ctas, stream);
+}

@@ -1,0 +1,97 @@
+"""Python entry to the tcgen05 GEMM (``csrc/kernels/gemm_tcgen05.cu``).
+
+``gemm(a, b, ...)`` computes ``D[M,N] = A[M,K] @ B[K,N]`` on the 5th-generation tensor cores with
+f32 accumulation in TMEM and a fused epilogue (bias, activation, activation derivative, row-major
+and transposed outputs in f32/bf16). Operands are described the way the hardware sees them:
+
+* ``a``: ``[M, K]`` (K contiguous, "K-major") or, with ``a_mn_major=True``, ``[K, M]``
+* ``b``: ``[N, K]`` (K contiguous)              or, with ``b_mn_major=True``, ``[K, N]``
+
+MN-major operands are bf16 only. f32 tensors run as tf32 tiles straight from the f32 storage.
+This mirrors the three GEMMs of the reference's Dense layer
+(machine_learning/src/arch/layers/dense.rs:36-64): forward ``X·W``, ``d·Wᵀ`` and ``Xᵀ·d``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+ACT = {"none": 0, None: 0, "relu": 1, "sigmoid": 2, "tanh": 3, "gelu": 4}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
+         out: torch.Tensor | None = None, out_t: torch.Tensor | None = None,
+         out_bf16: torch.Tensor | None = None, out_t_bf16: torch.Tensor | None = None,
+         pre: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+         act: str | None = None, act_param: float = 0.0,
+         aux: torch.Tensor | None = None, dact: str | None = None, dact_param: float = 0.0,
+         relu_quirk: bool = False, alpha: float = 1.0, beta: float = 0.0, bn: int = 0,
+         max_ctas: int = 0, status: torch.Tensor | None = None, stream=None) -> None:
+    """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride."""
+    if not a.is_cuda:
+        raise RuntimeError("ono gemm needs CUDA tensors (there is no CPU fallback on this path)")
+    lib = _lib.load()
+    if a.dtype != b.dtype or a.dtype not in (torch.float32, torch.bfloat16):
+        raise TypeError("a and b must both be float32 (tf32 tiles) or bfloat16")
+    for t in (a, b, out, out_t, out_bf16, out_t_bf16, pre, aux):
+        if t is not None and (t.dim() != 2 or t.stride(1) != 1):
+            raise ValueError("tensors must be 2-D with unit inner stride")
+    if a_mn_major:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn_major:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: {K} vs {Kb}")
+    g = _lib.OnoGemm()
+    g.A, g.B = a.data_ptr(), b.data_ptr()
+    g.M, g.N, g.K = M, N, K
+    g.lda, g.ldb = a.stride(0), b.stride(0)
+    g.dtype = 0 if a.dtype == torch.float32 else 1
+    g.a_major, g.b_major = int(a_mn_major), int(b_mn_major)
+    g.bn, g.max_ctas = bn, max_ctas
+    e = g.epi
+    ld_out = ld_out_t = 0
+    for t in (out, out_bf16, pre):
+        if t is not None:
+            if ld_out and t.stride(0) != ld_out:
+                raise ValueError("row-major outputs must share one leading dimension")
+            ld_out = t.stride(0)
+    for t in (out_t, out_t_bf16):
+        if t is not None:
+            if ld_out_t and t.stride(0) != ld_out_t:
+                raise ValueError("transposed outputs must share one leading dimension")
+            ld_out_t = t.stride(0)
+    if out is not None and out.dtype != torch.float32:
+        raise TypeError("out must be float32")
+    e.out_f32, e.outT_f32 = _ptr(out), _ptr(out_t)
+    e.out_bf16, e.outT_bf16 = _ptr(out_bf16), _ptr(out_t_bf16)
+    if pre is not None:
+        if pre.dtype == torch.float32:
+            e.pre_f32 = pre.data_ptr()
+        else:
+            e.pre_bf16 = pre.data_ptr()
+    e.bias = _ptr(bias)
+    if aux is not None:
+        if aux.dtype == torch.float32:
+            e.aux_f32 = aux.data_ptr()
+        else:
+            e.aux_bf16 = aux.data_ptr()
+        e.ld_aux = aux.stride(0)
+    e.ld_out, e.ld_outT = ld_out, ld_out_t
+    e.act, e.act_param = ACT[act], act_param
+    e.dact, e.dact_param = ACT[dact], dact_param
+    e.relu_quirk = int(relu_quirk)
+    e.alpha, e.beta = alpha, beta
+    g.status = _ptr(status)
+    _lib.check(lib.ono_gemm(C.byref(g), _lib.stream_ptr(stream)), "ono_gemm")

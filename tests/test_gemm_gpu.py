@@ -1,0 +1,93 @@
+"""Numerics of the tcgen05 GEMM against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, a_mn, b_mn):
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    return A.double() @ B.double()
+
+
+def _tol(dtype, K):
+    # tf32 keeps 10 mantissa bits (truncated), bf16 inputs are exact products accumulated in f32.
+    return (4e-3 if dtype == torch.float32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (32, 10, 784), (300, 200, 136), (512, 1024, 512),
+                                   (1024, 4096, 784), (129, 257, 72)])
+def test_gemm_k_major(dtype, shape):
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(0)
+    ld = lambda n: (n + 15) // 16 * 16
+    a = torch.randn(M, ld(K), device="cuda", dtype=dtype)[:, :K]
+    b = torch.randn(N, ld(K), device="cuda", dtype=dtype)[:, :K]
+    out = torch.zeros(M, ld(N), device="cuda")[:, :N]
+    out_t = torch.zeros(N, ld(M), device="cuda")[:, :M]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, b, out=out, out_t=out_t, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(a, b, False, False)
+    scale = ref.abs().max().item()
+    assert (out.double() - ref).abs().max().item() <= _tol(dtype, K) * scale
+    assert (out_t.double() - ref.t()).abs().max().item() <= _tol(dtype, K) * scale
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 320, 200), (512, 1024, 512)])
+def test_gemm_bf16_mn_major(a_mn, b_mn, shape):
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(1)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(M, N, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(a, b, a_mn, b_mn)
+    assert (out.double() - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_epilogue(dtype):
+    """bias + activation forward, then derivative-through-activation backward, bf16 copies, beta."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    torch.manual_seed(2)
+    M, N, K = 200, 272, 96
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(N, K, device="cuda", dtype=dtype) * 0.1
+    bias = torch.randn(N, device="cuda")
+    for act, param, fn in [("relu", 0.0, torch.relu), ("sigmoid", 1.5, lambda z: 1.5 * torch.sigmoid(z)),
+                           ("tanh", 2.0, lambda z: 2.0 * torch.tanh(z)),
+                           ("gelu", 0.0, torch.nn.functional.gelu)]:
+        out = torch.empty(M, N, device="cuda")
+        pre = torch.empty(M, N, device="cuda")
+        ob = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        otb = torch.empty(N, 208, device="cuda", dtype=torch.bfloat16)[:, :M]
+        gemm(a, b, out=out, pre=pre, out_bf16=ob, out_t_bf16=otb, bias=bias, act=act, act_param=param)
+        z = (a.float() @ b.float().t()) + bias
+        ref = fn(z)
+        tol = 3e-2
+        assert (pre - z).abs().max().item() < tol
+        assert (out - ref).abs().max().item() < tol
+        assert (ob.float() - ref).abs().max().item() < tol + 2e-2 * ref.abs().max().item()
+        assert (otb.float().t() - ref).abs().max().item() < tol + 2e-2 * ref.abs().max().item()
+        # backward: v = (a @ b^T) * act'(stored)
+        stored = (pre if act == "gelu" else out).clone()
+        zz = z.clone().requires_grad_(True)
+        fn(zz).backward(torch.ones_like(zz))
+        dref = (a.float() @ b.float().t()) * zz.grad
+        base = torch.ones(M, N, device="cuda")
+        dout = base.clone()
+        gemm(a, b, out=dout, aux=stored, dact=act, dact_param=param, beta=2.0)
+        assert (dout - (dref + 2.0)).abs().max().item() < 5e-2 * max(1.0, dref.abs().max().item())
