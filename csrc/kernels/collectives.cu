@@ -1,0 +1,452 @@
+// Gradient synchronisation kernels over NVLink peer memory / NVSwitch multicast, each fused with
+// the averaging and the optimizer step. See ono_kernels.h for the contract of each entry point and
+// the reference code they replace (worker_ring.rs, server_cluster.rs, blocking/shard.rs, barrier.rs,
+// non_blocking.rs, wild/shard.rs, stat_service.rs).
+//
+// Synchronisation between ranks uses epoch-stamped flag words in each rank's signal pad, written
+// with st.release.sys and polled with ld.acquire.sys. Every poll loop is bounded by a wall-clock
+// budget; on expiry the block records an error code and skips the rest of its work.
+// No TMA is used here; peer data moves with plain vector loads/stores or multimem instructions.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "ono_kernels.h"
+#include "ptx.cuh"
+
+namespace ono {
+void set_error(const char* fmt, const char* a, long long b, long long c);
+
+struct OptScal {
+  int kind;
+  float lr, mu, b1, b2, eps, gs, adam_step;
+};
+
+__device__ __forceinline__ float opt_apply(const OptScal& s, float p, float g, float& m, float& v) {
+  g *= s.gs;
+  if (s.kind == 0) return p - s.lr * g;
+  if (s.kind == 1) {
+    m = s.mu * m + g;
+    return p - s.lr * m;
+  }
+  m = s.b1 * m + (1.0f - s.b1) * g;
+  v = s.b2 * v + (1.0f - s.b2) * g * g;
+  return p - s.adam_step * m / (sqrtf(v) + s.eps);
+}
+
+__device__ __forceinline__ uint2 pack_bf16x4(float4 p) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+  uint2 pk;
+  pk.x = *reinterpret_cast<uint32_t*>(&lo);
+  pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  return pk;
+}
+
+// Barrier between block `blk` of every member rank. Thread t (< nranks) talks to rank t.
+__device__ __forceinline__ bool rank_barrier(unsigned int* const* flags, int nranks, int rank, int blk,
+                                             unsigned int members, uint32_t epoch, uint64_t budget) {
+  __syncthreads();
+  int ok = 1;
+  const int t = threadIdx.x;
+  if (t < nranks && ((members >> t) & 1u) && ((members >> rank) & 1u)) {
+    __threadfence_system();
+    st_release_sys(flags[t] + (size_t)blk * ONO_MAX_RANKS + rank, epoch);
+    ok = wait_flag_ge(flags[rank] + (size_t)blk * ONO_MAX_RANKS + t, epoch, budget) ? 1 : 0;
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Fused reduce-scatter + optimizer + all-gather (two-shot / one-shot / parameter server / NVLS)
+// ------------------------------------------------------------------------------------------------
+__device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
+  const OnoSyncLocal& L = a.loc[rank];
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) s_epoch = L.epoch[blk];
+  __syncthreads();
+  const uint32_t e0 = s_epoch;
+  const unsigned int members = a.live_mask ? *a.live_mask : a.member_mask;
+  const unsigned int workers = a.worker_mask & members;
+  const uint64_t budget = a.timeout_ns;
+
+  // Every member has finished producing its gradients (its kernel has started) before anyone reads.
+  bool ok = rank_barrier(a.flags, a.nranks, rank, blk, members, e0 + 1, budget);
+  if (!ok && threadIdx.x == 0 && L.status) atomicCAS(L.status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
+
+  OptScal s{a.kind, a.lr, a.mu, a.b1, a.b2, a.eps, a.divide ? 1.0f / (float)a.n_workers : 1.0f, 0.0f};
+  if (a.kind == 2 && L.adam_pows) s.adam_step = a.lr * sqrtf(1.0f - L.adam_pows[1]) / (1.0f - L.adam_pows[0]);
+
+  double sq = 0.0;
+  if (ok) {
+    const long long stride = (long long)a.nblocks * blockDim.x;
+    for (int ri = 0; ri < L.n_ranges; ++ri) {
+      const long long b4 = L.ranges[ri].begin >> 2;
+      const long long e4 = (L.ranges[ri].end + 3) >> 2;
+      for (long long i4 = b4 + (long long)blk * blockDim.x + threadIdx.x; i4 < e4; i4 += stride) {
+        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (a.algo == 1) {
+          g = multimem_ld_reduce_add_v4(reinterpret_cast<const float4*>(a.g_mc) + i4);
+        } else {
+          float4 part[ONO_MAX_RANKS];
+#pragma unroll
+          for (int q = 0; q < ONO_MAX_RANKS; ++q)
+            if (q < a.nranks && ((workers >> q) & 1u))
+              part[q] = ld_global_v4_volatile(reinterpret_cast<const float4*>(a.g[q]) + i4);
+#pragma unroll
+          for (int q = 0; q < ONO_MAX_RANKS; ++q)  // fixed rank order: run-to-run deterministic
+            if (q < a.nranks && ((workers >> q) & 1u)) {
+              g.x += part[q].x; g.y += part[q].y; g.z += part[q].z; g.w += part[q].w;
+            }
+        }
+        const long long si = (i4 << 2) - L.state_off;
+        float4 p = *(reinterpret_cast<const float4*>(L.p_master) + i4);
+        float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+        if (a.kind >= 1) m = *reinterpret_cast<const float4*>(L.m + si);
+        if (a.kind == 2) v = *reinterpret_cast<const float4*>(L.v + si);
+        p.x = opt_apply(s, p.x, g.x, m.x, v.x);
+        p.y = opt_apply(s, p.y, g.y, m.y, v.y);
+        p.z = opt_apply(s, p.z, g.z, m.z, v.z);
+        p.w = opt_apply(s, p.w, g.w, m.w, v.w);
+        if (L.sumsq) {
+          const float gx = g.x * s.gs, gy = g.y * s.gs, gz = g.z * s.gs, gw = g.w * s.gs;
+          sq += (double)(gx * gx + gy * gy) + (double)(gz * gz + gw * gw);
+        }
+        if (a.kind >= 1) *reinterpret_cast<float4*>(L.m + si) = m;
+        if (a.kind == 2) *reinterpret_cast<float4*>(L.v + si) = v;
+        *(reinterpret_cast<float4*>(L.p_master) + i4) = p;
+        if (a.algo == 1) {
+          if (a.p_mc_f32) multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, p);
+        } else {
+#pragma unroll
+          for (int q = 0; q < ONO_MAX_RANKS; ++q)
+            if (q < a.nranks && a.p_out_f32[q] && a.p_out_f32[q] != L.p_master)
+              *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = p;
+        }
+        const uint2 pb = pack_bf16x4(p);
+#pragma unroll
+        for (int q = 0; q < ONO_MAX_RANKS; ++q)
+          if (q < a.nranks && a.p_out_bf16[q])
+            *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
+        if (a.zero_grad && ((workers >> rank) & 1u))
+          *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  }
+  if (L.sumsq) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    if ((threadIdx.x & 31) == 0 && sq != 0.0) atomicAdd(L.sumsq, sq);
+  }
+  // Nobody leaves before every member has stopped reading gradients and writing parameters.
+  const bool ok2 = rank_barrier(a.flags, a.nranks, rank, blk, members, e0 + 2, budget);
+  if (!ok2 && ok && threadIdx.x == 0 && L.status) atomicCAS(L.status, 0, ONO_ERR_TIMEOUT_BARRIER);
+  if (threadIdx.x == 0) L.epoch[blk] = e0 + 2;
+}
+
+__global__ void __launch_bounds__(512) sync_kernel(const OnoSync a) { sync_body(a, a.rank, blockIdx.x); }
+__global__ void __launch_bounds__(512) sync_kernel_emulated(const OnoSync a) { sync_body(a, blockIdx.y, blockIdx.x); }
+
+// ------------------------------------------------------------------------------------------------
+// Asynchronous parameter server: worker-driven remote read-modify-write of the owners' shards.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512) ps_async_kernel(const OnoPsAsync a) {
+  const int blk = blockIdx.x;
+  OptScal s{a.kind, a.lr, a.mu, a.b1, a.b2, a.eps, a.divide ? 1.0f / (float)a.n_workers : 1.0f, 0.0f};
+  if (a.kind == 2 && a.adam_pows) s.adam_step = a.lr * sqrtf(1.0f - a.adam_pows[1]) / (1.0f - a.adam_pows[0]);
+  __shared__ int s_ok;
+  for (int owner = 0; owner < a.nranks; ++owner) {
+    for (int ri = 0; ri < a.n_ranges[owner]; ++ri) {
+      const OnoRange rg = a.ranges[owner][ri];
+      const long long b4 = rg.begin >> 2, e4 = (rg.end + 3) >> 2;
+      const long long per = (e4 - b4 + a.nblocks - 1) / a.nblocks;
+      const long long lo = b4 + per * blk, hi = min(e4, lo + per);
+      if (lo >= hi) continue;  // uniform per block
+      unsigned int* lock = a.locks[owner] ? a.locks[owner] + (size_t)ri * a.nblocks + blk : nullptr;
+      if (lock) {
+        if (threadIdx.x == 0) {
+          int got = 0;
+          const uint64_t t0 = globaltimer_ns();
+          while (true) {
+            if (atomicCAS_system(lock, 0u, 1u) == 0u) { got = 1; break; }
+            if (globaltimer_ns() - t0 > a.timeout_ns) break;
+            __nanosleep(200);
+          }
+          __threadfence_system();
+          s_ok = got;
+        }
+        __syncthreads();
+        if (!s_ok) {
+          if (threadIdx.x == 0 && a.status) atomicCAS(a.status, 0, ONO_ERR_TIMEOUT_BARRIER);
+          __syncthreads();
+          continue;
+        }
+      }
+      float* master = a.master[owner];
+      for (long long i4 = lo + threadIdx.x; i4 < hi; i4 += blockDim.x) {
+        const float4 g = *(reinterpret_cast<const float4*>(a.g) + i4);
+        const long long si = (i4 << 2) - a.state_off[owner];
+        float4 p = ld_global_v4_volatile(reinterpret_cast<const float4*>(master) + i4);
+        float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+        if (a.kind >= 1) m = ld_global_v4_volatile(reinterpret_cast<const float4*>(a.m[owner] + si));
+        if (a.kind == 2) v = ld_global_v4_volatile(reinterpret_cast<const float4*>(a.v[owner] + si));
+        p.x = opt_apply(s, p.x, g.x, m.x, v.x);
+        p.y = opt_apply(s, p.y, g.y, m.y, v.y);
+        p.z = opt_apply(s, p.z, g.z, m.z, v.z);
+        p.w = opt_apply(s, p.w, g.w, m.w, v.w);
+        *(reinterpret_cast<float4*>(master) + i4) = p;
+        if (a.kind >= 1) *reinterpret_cast<float4*>(a.m[owner] + si) = m;
+        if (a.kind == 2) *reinterpret_cast<float4*>(a.v[owner] + si) = v;
+        if (a.p_local_f32 && a.p_local_f32 != master) *(reinterpret_cast<float4*>(a.p_local_f32) + i4) = p;
+        if (a.p_local_bf16) *(reinterpret_cast<uint2*>(a.p_local_bf16) + i4) = pack_bf16x4(p);
+      }
+      if (lock) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          st_release_sys(lock, 0u);
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Ring all-reduce, pull formulation: at every step a rank reads one chunk from its predecessor's
+// window. Block b of each rank forms an independent pipeline with block b of its neighbours.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void chunk_bounds4(long long n4, int nranks, int c, long long& lo, long long& hi) {
+  // near-equal split: the first (n4 % nranks) chunks get one extra element (middlewares/mod.rs:15-59)
+  const long long base = n4 / nranks, rem = n4 % nranks;
+  lo = base * c + (c < rem ? c : rem);
+  hi = lo + base + (c < rem ? 1 : 0);
+}
+
+__global__ void __launch_bounds__(512) ring_kernel(const OnoRing a) {
+  const int N = a.nranks, r = a.rank, blk = blockIdx.x;
+  const int prev = (r + N - 1) % N, next = (r + 1) % N;
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_epoch = a.epoch[blk];
+  __syncthreads();
+  const uint32_t base = s_epoch;
+  uint32_t tick = base;  // value I have published to `next` so far
+  const long long n4 = (a.n + 3) >> 2;
+  float4* mine = reinterpret_cast<float4*>(a.acc[r]);
+  const float4* theirs = reinterpret_cast<const float4*>(a.acc[prev]);
+  unsigned int* fwd_flag_at_next = a.flags[next] + blk;             // my progress, seen by next
+  const unsigned int* fwd_flag_mine = a.flags[r] + blk;             // prev's progress, seen by me
+  unsigned int* back_flag_at_prev = a.flags[prev] + a.nblocks + blk;  // "I finished reading you"
+  const unsigned int* back_flag_mine = a.flags[r] + a.nblocks + blk;
+  bool ok = true;
+
+  auto publish = [&]() {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(fwd_flag_at_next, ++tick);
+    } else {
+      ++tick;
+    }
+  };
+  auto wait_prev = [&](uint32_t want) {
+    if (threadIdx.x == 0) s_ok = wait_flag_ge(fwd_flag_mine, want, a.timeout_ns) ? 1 : 0;
+    __syncthreads();
+    const bool good = s_ok != 0;
+    __syncthreads();
+    return good;
+  };
+  auto slice = [&](int c, long long& lo, long long& hi) {
+    long long clo, chi;
+    chunk_bounds4(n4, N, c, clo, chi);
+    const long long per = (chi - clo + a.nblocks - 1) / a.nblocks;
+    lo = clo + per * blk;
+    hi = min(chi, lo + per);
+  };
+
+  // step 0: acc <- g
+  {
+    const float4* g4 = reinterpret_cast<const float4*>(a.g);
+    for (int c = 0; c < N; ++c) {
+      long long lo, hi;
+      slice(c, lo, hi);
+      for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) mine[i] = g4[i];
+    }
+    publish();  // base+1
+  }
+  // reduce-scatter: N-1 steps
+  for (int s = 0; s < N - 1 && ok; ++s) {
+    const int c = ((r - s - 1) % N + N) % N;
+    ok = wait_prev(base + 1 + s);
+    if (!ok) break;
+    long long lo, hi;
+    slice(c, lo, hi);
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float4 x = ld_global_v4_volatile(theirs + i);
+      float4 y = mine[i];
+      y.x += x.x; y.y += x.y; y.z += x.z; y.w += x.w;
+      mine[i] = y;
+    }
+    if (s < N - 2) publish();
+  }
+  // owned chunk: average + optimizer; the payload that circulates from here on is the new params
+  OptScal sc{a.kind, a.lr, a.mu, a.b1, a.b2, a.eps, 1.0f / (float)N, 0.0f};
+  if (a.kind == 2 && a.adam_pows) sc.adam_step = a.lr * sqrtf(1.0f - a.adam_pows[1]) / (1.0f - a.adam_pows[0]);
+  __nv_bfloat16* pb = reinterpret_cast<__nv_bfloat16*>(a.p_bf16);
+  if (ok) {
+    const int c = (r + 1) % N;
+    long long lo, hi;
+    slice(c, lo, hi);
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float4 g = mine[i];
+      float4 p = *(reinterpret_cast<float4*>(a.p) + i);
+      float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
+      if (a.kind >= 1) m = *(reinterpret_cast<float4*>(a.m) + i);
+      if (a.kind == 2) v = *(reinterpret_cast<float4*>(a.v) + i);
+      p.x = opt_apply(sc, p.x, g.x, m.x, v.x);
+      p.y = opt_apply(sc, p.y, g.y, m.y, v.y);
+      p.z = opt_apply(sc, p.z, g.z, m.z, v.z);
+      p.w = opt_apply(sc, p.w, g.w, m.w, v.w);
+      if (a.kind >= 1) *(reinterpret_cast<float4*>(a.m) + i) = m;
+      if (a.kind == 2) *(reinterpret_cast<float4*>(a.v) + i) = v;
+      *(reinterpret_cast<float4*>(a.p) + i) = p;
+      if (pb) *(reinterpret_cast<uint2*>(pb) + i) = pack_bf16x4(p);
+      mine[i] = p;
+    }
+    publish();  // base+N  (N-2 publishes in the loop + the copy + this one)
+  }
+  // all-gather of the updated parameters: N-1 steps
+  for (int s = 0; s < N - 1 && ok; ++s) {
+    const int c = ((r - s) % N + N) % N;
+    ok = wait_prev(base + N + s);
+    if (!ok) break;
+    long long lo, hi;
+    slice(c, lo, hi);
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float4 p = ld_global_v4_volatile(theirs + i);
+      mine[i] = p;
+      *(reinterpret_cast<float4*>(a.p) + i) = p;
+      if (pb) *(reinterpret_cast<uint2*>(pb) + i) = pack_bf16x4(p);
+    }
+    if (s < N - 2) publish();
+  }
+  // Tell prev that its window is no longer read, and wait for the same from next, so that the next
+  // call may overwrite the windows.
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(back_flag_at_prev, base + 2u * N);
+    const bool fin = wait_flag_ge(back_flag_mine, base + 2u * N, ok ? a.timeout_ns : 1000000ull);
+    if ((!ok || !fin) && a.status) atomicCAS(a.status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
+    a.epoch[blk] = base + 2u * N;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Ping-pong latency probe
+// ------------------------------------------------------------------------------------------------
+__global__ void pingpong_kernel(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds,
+                                unsigned int base, unsigned long long* rtt, int* status) {
+  for (int i = 0; i < rounds; ++i) {
+    const uint32_t e = base + 1 + i;
+    if (role == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      st_release_sys(peer_flag, e);
+      if (!wait_flag_ge(my_flag, e, 1000000000ull)) {
+        if (status) atomicCAS(status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
+        return;
+      }
+      if (rtt) rtt[i] = globaltimer_ns() - t0;
+    } else {
+      if (!wait_flag_ge(my_flag, e, 1000000000ull)) {
+        if (status) atomicCAS(status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
+        return;
+      }
+      st_release_sys(peer_flag, e);
+    }
+  }
+}
+
+static int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s launch failed: %lld", what, (long long)e, 0);
+    return -7;
+  }
+  return 0;
+}
+
+static int validate_sync(const OnoSync* s) {
+  if (!s || s->nranks < 1 || s->nranks > ONO_MAX_RANKS || s->nblocks < 1 || s->n <= 0) {
+    set_error("bad sync args%s", "", 0, 0);
+    return -1;
+  }
+  if (s->algo == 1 && !s->g_mc) { set_error("NVLS needs multicast addresses%s", "", 0, 0); return -1; }
+  return 0;
+}
+
+}  // namespace ono
+
+using namespace ono;
+
+extern "C" int ono_sync_step(const OnoSync* s, ono_stream_t st) {
+  if (int rc = validate_sync(s)) return rc;
+  if (s->rank < 0 || s->rank >= s->nranks) { set_error("bad rank%s", "", 0, 0); return -1; }
+  sync_kernel<<<s->nblocks, 512, 0, (cudaStream_t)st>>>(*s);
+  return check_launch("sync_step");
+}
+
+extern "C" int ono_sync_step_emulated(const OnoSync* s, ono_stream_t st) {
+  if (int rc = validate_sync(s)) return rc;
+  if (s->algo != 0) { set_error("emulation supports algo 0 only%s", "", 0, 0); return -1; }
+  // All rank-blocks wait on one another, so they must be co-resident: cooperative launch, which
+  // fails cleanly if the grid does not fit.
+  OnoSync copy = *s;
+  void* args[] = {&copy};
+  dim3 grid(s->nblocks, s->nranks);
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)sync_kernel_emulated, grid, dim3(512), args, 0, (cudaStream_t)st);
+  if (e != cudaSuccess) {
+    set_error("cooperative launch failed: %s", cudaGetErrorString(e), 0, 0);
+    return -7;
+  }
+  return 0;
+}
+
+extern "C" int ono_ps_async_step(const OnoPsAsync* s, ono_stream_t st) {
+  if (!s || s->nranks < 1 || s->nranks > ONO_MAX_RANKS || s->nblocks < 1 || !s->g) {
+    set_error("bad ps_async args%s", "", 0, 0);
+    return -1;
+  }
+  ps_async_kernel<<<s->nblocks, 512, 0, (cudaStream_t)st>>>(*s);
+  return check_launch("ps_async_step");
+}
+
+extern "C" int ono_ring_allreduce(const OnoRing* r, ono_stream_t st) {
+  if (!r || r->nranks < 1 || r->nranks > ONO_MAX_RANKS || r->nblocks < 1 || r->n <= 0) {
+    set_error("bad ring args%s", "", 0, 0);
+    return -1;
+  }
+  ring_kernel<<<r->nblocks, 512, 0, (cudaStream_t)st>>>(*r);
+  return check_launch("ring_allreduce");
+}
+
+extern "C" int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base,
+                            unsigned long long* rtt, int* status, ono_stream_t st) {
+  pingpong_kernel<<<1, 1, 0, (cudaStream_t)st>>>(role, my_flag, peer_flag, rounds, base, rtt, status);
+  return check_launch("pingpong");
+}
+
+// Size of each ABI structure, so that a binding can check its own layout at load time.
+extern "C" int ono_sizeof(int which) {
+  switch (which) {
+    case 0: return (int)sizeof(OnoGemm);
+    case 1: return (int)sizeof(OnoLoss);
+    case 2: return (int)sizeof(OnoOptim);
+    case 3: return (int)sizeof(OnoRows);
+    case 4: return (int)sizeof(OnoSync);
+    case 5: return (int)sizeof(OnoPsAsync);
+    case 6: return (int)sizeof(OnoRing);
+    default: return -1;
+  }
+}

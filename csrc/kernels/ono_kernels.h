@@ -64,6 +64,165 @@ int ono_gemm(const OnoGemm* g, ono_stream_t stream);
 const char* ono_last_error(void);
 int ono_num_sms(void);
 
+// ---------------------------------------------------------------------------------------------
+// Loss (+ fused softmax) : reference arch/loss/{mse,cross_entropy}.rs and arch/layers/softmax.rs.
+// n = B*C normalises both the loss and the gradient (the reference's convention).
+//   kind 0 (MSE):  L = sum (p-y)^2 / n          g = 2 (p-y) / n
+//   kind 1 (CE):   L = -sum y ln max(p,eps) / n g = -(y / max(p,eps)) / n
+//   softmax = 1:   p = softmax(a) and d = p * (g - sum_k p_k g_k)   (softmax.rs:44-64)
+//   softmax = 0:   p = a and d = g * act'(aux)                     (last layer's activation)
+// ---------------------------------------------------------------------------------------------
+typedef struct OnoLoss {
+  const float* a;        // [B, ld]
+  const float* y;        // [B, ldy]
+  const float* aux;      // [B, ld] value act' is evaluated on (null -> a)
+  int B, C, ld, ldy;
+  int kind, softmax;
+  int dact; float dact_param; int relu_quirk;
+  float eps;
+  float* probs;          // optional [B, ld]
+  float* d_f32;          // optional [B, ld_d]
+  float* dT_f32;         // optional [C, ld_dT]
+  void* d_bf16;          // optional [B, ld_d]
+  void* dT_bf16;         // optional [C, ld_dT]
+  int ld_d, ld_dT;
+  double* loss_sum;      // += L (atomic)
+  int* correct;          // optional, += #rows whose argmax(p) == argmax(y)
+} OnoLoss;
+int ono_loss(const OnoLoss* l, ono_stream_t stream);
+
+// out[n] = beta*out[n] + sum_m d[m][n]   (bias gradient, dense.rs:58). dtype: 0 f32, 1 bf16.
+int ono_colsum(const void* d, int dtype, int M, int N, int ld, float* out, float beta, ono_stream_t stream);
+
+// Optimizers on a flat f32 shard (optimization/{gradient_descent,gradient_descent_with_momentum,adam}.rs).
+typedef struct OnoOptim {
+  float* p; const float* g; float* m; float* v;
+  long long n;
+  int kind;              // 0 SGD, 1 momentum, 2 Adam
+  float lr, mu, b1, b2, eps;
+  float grad_scale;      // g is multiplied by this first (1/N averaging)
+  const float* adam_pows;// device float[2] = {b1^t, b2^t} after this step's tick
+  void* p_bf16;          // optional bf16 shadow of p
+  int zero_grad;         // 1: g is zeroed after use (g must be writable)
+} OnoOptim;
+int ono_optim(const OnoOptim* o, ono_stream_t stream);
+int ono_adam_tick(float* pows, float b1, float b2, ono_stream_t stream);  // pows *= {b1, b2}
+// Round cadence (sequential.rs:129-141): p -= lr*g ; r += g ; optional bf16 shadow of p.
+int ono_local_sgd(float* p, const float* g, float* r, long long n, float lr, void* p_bf16, ono_stream_t stream);
+// sum of squares of x accumulated into *out (double); used for the gradient-norm switch metric.
+int ono_sumsq(const float* x, long long n, double* out, ono_stream_t stream);
+
+// Counter-based initialisers (Philox4x32-10 keyed by seed, counter = global element index) so that
+// any shard owner can generate exactly its slice. kind 0: U[lo,hi) ; 1: U[lo,hi] ; 2: N(a,b).
+int ono_init(float* out, long long n, unsigned long long index_offset, unsigned long long seed,
+             int kind, float a, float b, ono_stream_t stream);
+
+// Row gather / cast / transpose: for r in [0,R): src row = idx ? idx[r] : r.
+// Writes any of dst_f32 [R,ld_dst], dstT_f32 [W,ld_dstT], dst_bf16, dstT_bf16.
+typedef struct OnoRows {
+  const float* src; int ld_src;
+  const int* idx;        // optional
+  int R, W;
+  float* dst_f32; float* dstT_f32; void* dst_bf16; void* dstT_bf16;
+  int ld_dst, ld_dstT;
+} OnoRows;
+int ono_rows(const OnoRows* r, ono_stream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Fused gradient synchronisation over NVLink peer memory ("symmetric windows": the same buffer
+// allocated on every rank, every rank holding a mapped pointer to every peer's copy).
+//
+// One kernel = reduce-scatter of the workers' gradients into the owner of each parameter range
+// + averaging + the owner's optimizer step + all-gather of the fresh parameters to every rank
+// that consumes them. It expresses the reference's three exchanges:
+//   * ring all-reduce + local optimizer (worker/src/middlewares/worker_ring.rs:82-204,
+//     worker/src/workers/all_reduce.rs:114-133): every rank owns 1/N of the vector ("two-shot"),
+//     or every rank owns all of it and writes only to itself ("one-shot", small vectors);
+//   * parameter-server push + BlockingStore/BarrierSync update + pull
+//     (parameter_server/src/storage/blocking/shard.rs:56-92, synchronization/barrier.rs:41-50,
+//     comms/src/clusters/parameter_server.rs:50-81): only server ranks own ranges;
+//   * the switch between the two is a change of the ownership table only.
+// algo 0 = P2P loads/stores, algo 1 = NVLS (multimem.ld_reduce / multimem.st through NVSwitch).
+// Cross-rank waits are bounded; a timeout sets *status and the kernel returns.
+// ---------------------------------------------------------------------------------------------
+#define ONO_MAX_RANKS 8
+#define ONO_MAX_RANGES 16
+typedef struct OnoRange { long long begin, end; } OnoRange;   // element indices, begin % 4 == 0
+
+typedef struct OnoSyncLocal {
+  float* p_master;        // f32 master copy of the parameters this rank owns (indexed globally)
+  float* m; float* v;     // optimizer state of the owned ranges, indexed (global index - state_off)
+  long long state_off;
+  const float* adam_pows; // {b1^t, b2^t}
+  unsigned int* epoch;    // [nblocks] barrier epochs of this rank (device, zero-initialised)
+  double* sumsq;          // optional: += sum of squares of the averaged gradient over owned ranges
+  int* status;            // optional error word
+  int n_ranges;
+  OnoRange ranges[ONO_MAX_RANGES];
+} OnoSyncLocal;
+
+typedef struct OnoSync {
+  int nranks, rank, algo, nblocks;
+  long long n;                               // vector length (elements)
+  const float* g[ONO_MAX_RANKS];             // every rank's gradient window
+  float* p_out_f32[ONO_MAX_RANKS];           // every rank's f32 parameter window (null = not wanted)
+  void* p_out_bf16[ONO_MAX_RANKS];           // every rank's bf16 parameter window (null = not wanted)
+  unsigned int* flags[ONO_MAX_RANKS];        // every rank's signal pad [nblocks][ONO_MAX_RANKS]
+  const float* g_mc; float* p_mc_f32; void* p_mc_bf16;   // multicast addresses (algo 1)
+  unsigned int worker_mask;                  // ranks whose gradients are summed
+  unsigned int member_mask;                  // ranks taking part in the barriers
+  const unsigned int* live_mask;             // optional device word overriding member_mask (shrink)
+  int n_workers;                             // divisor of the average (reference: nworkers)
+  int kind; float lr, mu, b1, b2, eps;       // optimizer (OnoOptim kinds)
+  int divide;                                // 1: scale by 1/n_workers (0 reproduces WildStore)
+  int zero_grad;                             // 1: owners zero the summed gradient ranges afterwards
+  unsigned long long timeout_ns;
+  OnoSyncLocal loc[ONO_MAX_RANKS];           // a real launch reads loc[rank] only
+} OnoSync;
+
+int ono_sync_step(const OnoSync* s, ono_stream_t stream);
+// All ranks of the struct as one cooperative launch on ONE GPU (grid.y = rank). For single-GPU tests
+// of the multi-rank logic; algo must be 0.
+int ono_sync_step_emulated(const OnoSync* s, ono_stream_t stream);
+
+// Asynchronous parameter server (synchronization/non_blocking.rs:20-31 with BlockingStore or
+// storage/wild/shard.rs:43-58): the calling worker applies its own gradient to the owners' masters
+// over NVLink (optionally under a per-range lock) and keeps the fresh values as its pulled params.
+typedef struct OnoPsAsync {
+  int nranks, rank, nblocks;
+  const float* g;                            // this worker's gradient (local)
+  float* p_local_f32; void* p_local_bf16;    // this worker's parameter buffers (pull destination)
+  float* master[ONO_MAX_RANKS];              // owners' f32 masters (peer pointers), indexed globally
+  float* m[ONO_MAX_RANKS]; float* v[ONO_MAX_RANKS]; long long state_off[ONO_MAX_RANKS];
+  unsigned int* locks[ONO_MAX_RANKS];        // owners' lock words [ONO_MAX_RANGES] (null = wild)
+  int n_ranges[ONO_MAX_RANKS]; OnoRange ranges[ONO_MAX_RANKS][ONO_MAX_RANGES];
+  int n_workers; int divide;
+  int kind; float lr, mu, b1, b2, eps; const float* adam_pows;
+  int* status; unsigned long long timeout_ns;
+} OnoPsAsync;
+int ono_ps_async_step(const OnoPsAsync* s, ono_stream_t stream);
+
+// Ring all-reduce (reduce-scatter + all-gather, N-1 steps each, chunked like
+// worker/src/middlewares/mod.rs:15-59) with the average and SGD/momentum/Adam fused into the last
+// hop. `acc` is a symmetric scratch window of n floats per rank.
+typedef struct OnoRing {
+  int nranks, rank, nblocks;
+  long long n;
+  const float* g;                            // local gradient
+  float* acc[ONO_MAX_RANKS];                 // every rank's accumulation window
+  unsigned int* flags[ONO_MAX_RANKS];        // every rank's step flags [nblocks]
+  unsigned int* epoch;                       // [nblocks] local
+  float* p; float* m; float* v; const float* adam_pows; void* p_bf16;
+  int kind; float lr, mu, b1, b2, eps;
+  int* status; unsigned long long timeout_ns;
+} OnoRing;
+int ono_ring_allreduce(const OnoRing* r, ono_stream_t stream);
+
+// Flag ping-pong between two GPUs (node/src/stat_service.rs:107-152 rebuilt as a device probe).
+// role 0 pings, role 1 answers; rtt_ns[rounds] is written by role 0.
+int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base_epoch,
+                 unsigned long long* rtt_ns, int* status, ono_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,269 @@
+"""GPU training engine: explicit forward/backward over flat f32 parameters in HBM.
+
+The engine is the B200 counterpart of the reference's ``Sequential`` + ``ParamManager``
+(machine_learning/src/arch/sequential.rs:43-148, machine_learning/src/param_manager.rs:61-198):
+
+* parameters and gradients are two flat f32 vectors in the reference's external layout
+  (per layer ``W[in,out]`` row-major then ``b[out]``; conv ``K[F][C][k][k]`` then ``b[F]``), so that
+  collectives, optimizers and the safetensors export all work on the same buffer;
+* layers are views (offset tables) into those vectors;
+* every GEMM runs on the tcgen05 kernel; operands the tensor cores cannot address directly from the
+  flat vector (wrong major-ness for tf32, unaligned rows, bf16 tiles) are "compute copies" that
+  ``refresh()`` regenerates after each parameter update;
+* there is no autograd: each layer contributes explicit forward, dgrad and wgrad launches, and a
+  whole mini-batch step is a fixed kernel sequence that can be captured in a CUDA graph.
+
+Tile dtype ``tf32`` keeps every tensor in f32 and uses K-major operands only (transposed copies are
+written by the producing epilogue); ``bf16`` keeps bf16 activations/deltas and uses MN-major
+operands, so no transposed copies exist.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops import elementwise as ew
+from ..ops.gemm import gemm
+
+
+def _up(n: int, m: int = 16) -> int:
+    return (n + m - 1) // m * m
+
+
+@dataclass
+class LayerPlan:
+    kind: str                       # dense | conv | pool
+    in_features: int
+    out_features: int
+    act: str | None = None
+    act_param: float = 0.0
+    w_off: int = 0                  # offset of W in the flat vector
+    b_off: int = 0                  # offset of b
+    n_params: int = 0
+    extra: dict = field(default_factory=dict)
+
+
+def layer_param_count(spec: dict) -> int:
+    if spec["kind"] == "dense":
+        return (spec["in"] + 1) * spec["out"]
+    if spec["kind"] == "conv":
+        f, c, k = spec["kernel_dim"]
+        return f * c * k * k + f
+    return 0
+
+
+class GpuEngine:
+    """Forward/backward of a dense network for one fixed maximum batch size on one GPU."""
+
+    def __init__(self, layers: list[dict], *, batch_size: int, tile_dtype: str, loss: str,
+                 params: torch.Tensor, grads: torch.Tensor, params_bf16: torch.Tensor | None = None,
+                 leaky_relu_exact: bool = True, device=None):
+        if tile_dtype not in ("tf32", "bf16"):
+            raise ValueError("tile_dtype must be 'tf32' or 'bf16'")
+        self.dev = device or params.device
+        if self.dev.type != "cuda":
+            raise RuntimeError("GpuEngine needs a CUDA device; CPU runs use the C++ oracle engine")
+        self.bf16 = tile_dtype == "bf16"
+        self.B = batch_size
+        self.ldB = _up(batch_size)
+        self.loss = loss
+        self.relu_quirk = not leaky_relu_exact
+        self.params, self.grads, self.params_bf16 = params, grads, params_bf16
+        self.plans: list[LayerPlan] = []
+        off = 0
+        for sp in layers:
+            if sp["kind"] != "dense":
+                raise NotImplementedError("GpuEngine handles dense layers; see ConvEngine for conv/pool")
+            act = sp.get("act")
+            pl = LayerPlan("dense", sp["in"], sp["out"], act[0] if act else None, act[1] if act else 0.0)
+            pl.w_off, pl.b_off = off, off + sp["in"] * sp["out"]
+            pl.n_params = (sp["in"] + 1) * sp["out"]
+            off += pl.n_params
+            self.plans.append(pl)
+        self.n_params = off
+        if params.numel() < off or grads.numel() < off:
+            raise ValueError("flat parameter/gradient buffers are too small")
+        for i, pl in enumerate(self.plans[:-1]):
+            if pl.act == "softmax":
+                raise NotImplementedError("softmax is supported as the last activation only on the GPU engine")
+        self.softmax_last = self.plans[-1].act == "softmax"
+        self._alloc()
+
+    # ------------------------------------------------------------------------------------------
+    def _alloc(self) -> None:
+        dev, B, ldB = self.dev, self.B, self.ldB
+        cd = torch.bfloat16 if self.bf16 else torch.float32
+        f32 = torch.float32
+        z = lambda r, c, dt: torch.zeros(r, c, device=dev, dtype=dt)
+        L = self.plans
+        feats = [L[0].in_features] + [p.out_features for p in L]
+        self.lds = [_up(f) for f in feats]
+        # activations a[0] = input batch, a[l+1] = output of layer l
+        self.a = [z(B, self.lds[i], cd) for i in range(len(feats) - 1)]
+        self.logits = z(B, self.lds[-1], f32)
+        self.d = [None] + [z(B, self.lds[i], cd) for i in range(1, len(feats))]
+        self.zpre = [None] * len(feats)
+        for l, pl in enumerate(L):
+            if pl.act == "gelu":
+                self.zpre[l + 1] = z(B, self.lds[l + 1], cd)
+        if not self.bf16:
+            self.at = [z(feats[i], ldB, f32) for i in range(len(feats) - 1)]
+            self.dt = [None] + [z(feats[i], ldB, f32) for i in range(1, len(feats))]
+        self.ybuf = z(B, _up(feats[-1]), f32)
+        self.loss_sum = torch.zeros(1, device=dev, dtype=torch.float64)
+        self.correct = torch.zeros(1, device=dev, dtype=torch.int32)
+        self.status = torch.zeros(1, device=dev, dtype=torch.int32)
+        # weight operands
+        self.w_k, self.w_t, self.w_copy_needed, self.gw_tmp = [], [], [], []
+        for pl in L:
+            i, o = pl.in_features, pl.out_features
+            esz_mult = 8 if self.bf16 else 4
+            flat = self.params_bf16 if self.bf16 else self.params
+            direct = flat is not None and o % esz_mult == 0 and pl.w_off % esz_mult == 0 and \
+                (flat.data_ptr() + pl.w_off * flat.element_size()) % 16 == 0
+            if direct:
+                self.w_k.append(flat[pl.w_off:pl.w_off + i * o].view(i, o))
+                self.w_copy_needed.append(False)
+            else:
+                self.w_k.append(z(i, _up(o), cd)[:, :o])
+                self.w_copy_needed.append(True)
+            self.w_t.append(None if self.bf16 else z(o, _up(i), f32)[:, :i])
+            g_direct = o % 4 == 0 and pl.w_off % 4 == 0 and (self.grads.data_ptr() + 4 * pl.w_off) % 16 == 0
+            self.gw_tmp.append(None if g_direct else z(i, _up(o), f32)[:, :o])
+
+    def w_view(self, l: int) -> torch.Tensor:
+        pl = self.plans[l]
+        return self.params[pl.w_off:pl.w_off + pl.in_features * pl.out_features].view(pl.in_features, pl.out_features)
+
+    def b_view(self, l: int) -> torch.Tensor:
+        pl = self.plans[l]
+        return self.params[pl.b_off:pl.b_off + pl.out_features]
+
+    def gw_view(self, l: int) -> torch.Tensor:
+        pl = self.plans[l]
+        return self.grads[pl.w_off:pl.w_off + pl.in_features * pl.out_features].view(pl.in_features, pl.out_features)
+
+    def gb_view(self, l: int) -> torch.Tensor:
+        pl = self.plans[l]
+        return self.grads[pl.b_off:pl.b_off + pl.out_features]
+
+    # ------------------------------------------------------------------------------------------
+    def refresh(self, stream=None) -> int:
+        """Regenerate the compute copies of the weights from the f32 master. Returns #launches."""
+        n = 0
+        for l in range(len(self.plans)):
+            w = self.w_view(l)
+            if self.bf16:
+                if self.w_copy_needed[l]:
+                    ew.rows(w, dst_bf16=self.w_k[l], stream=stream)
+                    n += 1
+            else:
+                if self.w_copy_needed[l]:
+                    ew.rows(w, dst=self.w_k[l], dst_t=self.w_t[l], stream=stream)
+                else:
+                    ew.rows(w, dst_t=self.w_t[l], stream=stream)
+                n += 1
+        return n
+
+    def load_batch(self, x: torch.Tensor, y: torch.Tensor, nrows: int, idx: torch.Tensor | None = None,
+                   stream=None) -> int:
+        """Stage ``x[idx]`` (f32, [rows, in]) as the first GEMM's A operand and ``y[idx]`` as the labels."""
+        if self.bf16:
+            ew.rows(x, idx=idx, n_rows=nrows, dst_bf16=self.a[0], stream=stream)
+        else:
+            ew.rows(x, idx=idx, n_rows=nrows, dst=self.a[0], dst_t=self.at[0], stream=stream)
+        ew.rows(y, idx=idx, n_rows=nrows, dst=self.ybuf, stream=stream)
+        return 2
+
+    def forward(self, nrows: int, stream=None) -> int:
+        L, n = self.plans, 0
+        for l, pl in enumerate(L):
+            last = l == len(L) - 1
+            a_in = self.a[l][:nrows, :pl.in_features]
+            act = None if (last and self.softmax_last) else pl.act
+            kw = dict(bias=self.b_view(l), act=act, act_param=pl.act_param, status=self.status, stream=stream)
+            if last:
+                kw["out"] = self.logits[:nrows, :pl.out_features]
+            elif self.bf16:
+                kw["out_bf16"] = self.a[l + 1][:nrows, :pl.out_features]
+                if self.zpre[l + 1] is not None:
+                    kw["pre"] = self.zpre[l + 1][:nrows, :pl.out_features]
+            else:
+                kw["out"] = self.a[l + 1][:nrows, :pl.out_features]
+                kw["out_t"] = self.at[l + 1][:, :nrows]
+                if self.zpre[l + 1] is not None:
+                    kw["pre"] = self.zpre[l + 1][:nrows, :pl.out_features]
+            if self.bf16:
+                gemm(a_in, self.w_k[l], b_mn_major=True, **kw)
+            else:
+                gemm(a_in, self.w_t[l], **kw)
+            n += 1
+        return n
+
+    def loss_backward(self, nrows: int, stream=None) -> int:
+        y = self.ybuf
+        pl = self.plans[-1]
+        C = pl.out_features
+        lg = self.logits[:nrows, :C]
+        kw = dict(kind=self.loss, softmax=self.softmax_last, loss_sum=self.loss_sum, correct=self.correct,
+                  stream=stream)
+        if not self.softmax_last and pl.act is not None:
+            kw.update(dact=pl.act, dact_param=pl.act_param, relu_quirk=self.relu_quirk)
+        if self.bf16:
+            kw["d_bf16"] = self.d[-1][:nrows, :C]
+        else:
+            kw["d"] = self.d[-1][:nrows, :C]
+            kw["d_t"] = self.dt[-1][:, :nrows]
+        ew.loss_backward(lg, y[:nrows, :C], **kw)
+        return 1
+
+    def backward(self, nrows: int, accumulate: bool = False, stream=None) -> int:
+        """dgrad + wgrad + bias-grad for every layer; gradients land in the flat gradient vector."""
+        L, n = self.plans, 0
+        beta = 1.0 if accumulate else 0.0
+        for l in range(len(L) - 1, -1, -1):
+            pl = L[l]
+            i, o = pl.in_features, pl.out_features
+            d_out = self.d[l + 1][:nrows, :o]
+            # wgrad: dW[in,out] = A_{l}^T d
+            tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
+            wbeta = beta if self.gw_tmp[l] is None else 0.0
+            if self.bf16:
+                gemm(self.a[l][:nrows, :i], d_out, a_mn_major=True, b_mn_major=True, out=tgt, beta=wbeta,
+                     status=self.status, stream=stream)
+            else:
+                gemm(self.at[l][:, :nrows], self.dt[l + 1][:, :nrows], out=tgt, beta=wbeta, status=self.status,
+                     stream=stream)
+            n += 1
+            if self.gw_tmp[l] is not None:
+                if accumulate:
+                    self.gw_view(l).add_(tgt)
+                else:
+                    ew.rows(tgt, dst=self.gw_view(l), stream=stream)
+                n += 1
+            ew.colsum(d_out, self.gb_view(l), beta=beta, stream=stream)
+            n += 1
+            if l == 0:
+                break
+            # dgrad through the previous layer's activation: d_{l} = (d_{l+1} W^T) * act'(a_l)
+            prev = L[l - 1]
+            stored = self.zpre[l] if prev.act == "gelu" else self.a[l]
+            kw = dict(status=self.status, stream=stream)
+            if prev.act is not None:
+                kw.update(aux=stored[:nrows, :i], dact=prev.act, dact_param=prev.act_param,
+                          relu_quirk=self.relu_quirk)
+            if self.bf16:
+                gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
+            else:
+                gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], out_t=self.dt[l][:, :nrows], **kw)
+            n += 1
+        return n
+
+    def step(self, x: torch.Tensor, y: torch.Tensor, nrows: int, idx=None, accumulate=False, stream=None) -> int:
+        """load -> forward -> loss -> backward. Returns the number of kernels launched."""
+        n = self.load_batch(x, y, nrows, idx, stream)
+        n += self.forward(nrows, stream)
+        n += self.loss_backward(nrows, stream)
+        n += self.backward(nrows, accumulate, stream)
+        return n

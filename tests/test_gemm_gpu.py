@@ -82,11 +82,20 @@ def test_gemm_epilogue(dtype):
         assert (out - ref).abs().max().item() < tol
         assert (ob.float() - ref).abs().max().item() < tol + 2e-2 * ref.abs().max().item()
         assert (otb.float().t() - ref).abs().max().item() < tol + 2e-2 * ref.abs().max().item()
-        # backward: v = (a @ b^T) * act'(stored)
+        # backward: v = (a @ b^T) * act'(stored), with the derivative evaluated on the stored tensor
+        # exactly as the kernel does (the reference differentiates through the stored activation).
         stored = (pre if act == "gelu" else out).clone()
-        zz = z.clone().requires_grad_(True)
-        fn(zz).backward(torch.ones_like(zz))
-        dref = (a.float() @ b.float().t()) * zz.grad
+        if act == "relu":
+            deriv = (stored > 0).float()
+        elif act == "sigmoid":
+            deriv = stored * (1 - stored / param)
+        elif act == "tanh":
+            deriv = param - stored * stored / param
+        else:
+            zz = stored.clone().requires_grad_(True)
+            fn(zz).backward(torch.ones_like(zz))
+            deriv = zz.grad
+        dref = (a.float() @ b.float().t()) * deriv
         base = torch.ones(M, N, device="cuda")
         dout = base.clone()
         gemm(a, b, out=dout, aux=stored, dact=act, dact_param=param, beta=2.0)
