@@ -1,0 +1,135 @@
+// model.json / training.json: the two documents that drive a run, in the reference's serde encoding
+// (orchestrator/src/configs/model.rs:9-126, orchestrator/src/configs/training.rs:14-135,
+// docs/config-schema.md). Unit enum variants are bare strings, struct variants single-key objects.
+// Unknown fields are ignored, which is what lets the additive "b200" block ride in training.json.
+#pragma once
+#include <array>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "json.hpp"
+
+namespace ono {
+
+struct InvalidConfig : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+// ---- model ------------------------------------------------------------------------------------
+struct ParamGenConfig {
+  enum Kind { Const, Uniform, UniformInclusive, XavierUniform, LecunUniform, Normal, Kaiming, Xavier, Lecun } kind = Kaiming;
+  float a = 0.f, b = 0.f;  // value | low,high | mean,std_dev
+  Json to_json() const;
+  static ParamGenConfig from_json(const Json& j);
+};
+
+struct ActFnConfig {
+  enum Kind { Sigmoid, Softmax, Tanh, ReLU, Gelu } kind = ReLU;
+  float param = 0.f;  // amp | slope
+  Json to_json() const;
+  static ActFnConfig from_json(const Json& j);
+  const char* name() const;
+};
+
+struct LayerConfig {
+  enum Kind { Dense, Conv, MaxPooling } kind = Dense;
+  size_t output_size = 0;                 // dense
+  std::array<size_t, 3> input_dim{};      // conv / pool: (c, h, w)
+  std::array<size_t, 3> kernel_dim{};     // conv: (filters, in_channels, k)
+  size_t filter_size = 0;                 // pool
+  size_t stride = 1, padding = 0;
+  ParamGenConfig init;
+  std::optional<ActFnConfig> act_fn;
+  Json to_json() const;
+  static LayerConfig from_json(const Json& j);
+  size_t out_size() const;                        // flattened output size (model.rs:64-105)
+  std::optional<size_t> expected_input_size() const;
+  size_t param_count(size_t input_size) const;    // weights + biases
+};
+
+struct ModelConfig {
+  std::vector<LayerConfig> layers;
+  Json to_json() const;
+  static ModelConfig from_json(const Json& j);
+  size_t param_count(size_t x_size) const;
+};
+
+// ---- training ---------------------------------------------------------------------------------
+struct OptimizerConfig {
+  enum Kind { GradientDescent, Momentum, Adam } kind = GradientDescent;
+  double lr = 0.01, mu = 0.0, b1 = 0.9, b2 = 0.999, eps = 1e-8;
+  Json to_json() const;
+  static OptimizerConfig from_json(const Json& j);
+};
+
+struct DatasetConfig {
+  bool is_inline = true;
+  std::string samples_path, labels_path;
+  std::vector<float> samples, labels;
+  size_t x_size = 0, y_size = 0;
+  // Inline data may travel outside the document (large arrays stay binary); then `rows` says how
+  // many rows the detached arrays hold. Additive key, ignored by the reference's parser.
+  size_t rows_hint = 0;
+  Json to_json() const;
+  static DatasetConfig from_json(const Json& j);
+};
+
+struct AlgorithmConfig {
+  enum Kind { ParameterServer, AllReduce, StrategySwitch } kind = AllReduce;
+  size_t nservers = 0;
+  enum Sync { Barrier, NonBlocking } synchronizer = Barrier;
+  enum Store { Blocking, Wild } store = Blocking;
+  Json to_json() const;
+  static AlgorithmConfig from_json(const Json& j);
+};
+
+struct SerializerConfig {
+  bool sparse = false;
+  double r = 0.0;
+  Json to_json() const;
+  static SerializerConfig from_json(const Json& j);
+};
+
+// Additive block understood by this runtime only; every field optional.
+struct B200Config {
+  std::string sync_every = "round";       // "round" (reference cadence) | "step"
+  std::string tile_dtype = "tf32";        // "tf32" | "bf16"
+  std::string wire_dtype = "f32";         // "f32" | "f16" | "bf16"
+  std::string allreduce = "auto";         // "auto" | "ring" | "oneshot" | "twoshot" | "nvls"
+  std::string sharding = "layer";         // "layer" (reference LPT) | "even"
+  std::string switch_metric = "loss";     // "loss" | "grad_norm"
+  size_t switch_window = 6;
+  double switch_threshold = 0.01;
+  bool leaky_relu_exact = true;
+  size_t global_batch = 0;                // 0 = batch_size is per worker (reference)
+  bool switch_resets_progress = false;
+  bool colocate = false;                  // server ranks also train (B200 extension)
+  std::string data = "host";              // "host": per-step H2D from pinned memory | "device"
+  bool present = false;
+  Json to_json() const;
+  static B200Config from_json(const Json& j);
+};
+
+struct TrainingConfig {
+  std::vector<std::string> addrs;
+  AlgorithmConfig algorithm;
+  SerializerConfig serializer;
+  DatasetConfig dataset;
+  OptimizerConfig optimizer;
+  enum Loss { Mse, CrossEntropy } loss_fn = Mse;
+  size_t batch_size = 1, max_epochs = 1, offline_epochs = 0;
+  std::optional<unsigned long long> seed;
+  std::optional<double> early_stopping_tolerance;
+  B200Config b200;
+  Json to_json(bool with_data = true) const;
+  static TrainingConfig from_json(const Json& j);
+};
+
+// Semantic validation (orchestrator/src/configs/validator.rs:28-203). Throws InvalidConfig.
+// n_samples_override: used when the dataset is local and its size was read by the caller.
+void validate_configs(const ModelConfig& model, const TrainingConfig& training);
+size_t dataset_rows(const DatasetConfig& d);
+
+}  // namespace ono
