@@ -1,0 +1,203 @@
+#!/usr/bin/env python
+"""Headline benchmark: samples/sec of the flagship training step on N B200s of one node.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched once per GPU by torchrun)
+    python bench.py --impl reference ...                      (the reference itself, if installable)
+
+Flagship = the deep dense MLP named by the baseline configs: 8 layers of width 8192 (GELU) + a
+1000-class head, input N(0,1) of width 8192, f32 master weights with bf16 tensor-core tiles, SGD with
+momentum 0.9, batch 512 per GPU (weak scaling), parameter server with the flat parameter vector split
+evenly over min(4, N) server ranks that also train (every GPU is a worker). Random-init weights and
+synthetic data of that shape. Other configs: ``--config mlp|wide|cnn`` (see CONFIGS).
+
+Two measurements, both through the public API (``orchestra.orchestrate(...).wait()``):
+  value  device-timed K steps with the dataset resident in HBM (inputs gathered on the device)
+  e2e    the same run with the dataset in pinned host memory: every step's inputs cross PCIe inside
+         the timed region and the step's loss is read back to the host
+Timing: CUDA events on the training stream, after W warm-up steps, with synchronize + barrier on both
+sides, max over ranks. Every step reads inputs (8 MB+ activations) and 2.7 GB of weights/gradients,
+far above the 126 MB L2, so no explicit L2 flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: (x_size, hidden layers [(width, act)], classes, tile, optimizer, per-gpu batch, strategy)
+    "deep": dict(x=8192, hidden=[(8192, "gelu")] * 8, classes=1000, tile="bf16", opt=("momentum", 0.01, 0.9),
+                 batch=512, strategy="ps4", init="kaiming", data="normal",
+                 model="deep-mlp-8x8192-gelu-1000 (545M params)"),
+    "wide": dict(x=784, hidden=[(4096, "relu")] * 3, classes=10, tile="tf32", opt=("adam", 1e-3), batch=1024,
+                 strategy="ar", init="kaiming", data="uniform", model="wide-mlp-784-4096x3-10"),
+    "mlp": dict(x=784, hidden=[(128, "relu")], classes=10, tile="tf32", opt=("sgd", 0.01), batch=32, strategy="ar",
+                init="xavier_uniform", data="uniform", model="mlp-784-128-10"),
+}
+
+
+def reference_arm() -> None:
+    why = ("the reference is a Rust workspace whose Python module builds with maturin + cargo; neither a Rust "
+           "toolchain nor vendored crates exist offline (pip install: \"No module named 'maturin'\")")
+    if os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "orchestra")):
+        why = "baseline/_ref holds no built extension module (no Rust toolchain offline)"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
+def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: int = 0):
+    import numpy as np
+
+    import orchestra
+    from orchestra import Sequential
+    from orchestra.activations import GELU, ReLU, Softmax
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import Kaiming, XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import Adam, GradientDescent, GradientDescentWithMomentum
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync
+
+    init = Kaiming() if cfg["init"] == "kaiming" else XavierUniform()
+    act = {"gelu": GELU, "relu": lambda: ReLU(0.0)}
+    layers = [Dense(w, init, act[a]()) for w, a in cfg["hidden"]] + [Dense(cfg["classes"], init, Softmax())]
+    model = Sequential(layers)
+    B = cfg["batch"]
+    steps_per_epoch = 8
+    rows = n_gpus * B * steps_per_epoch
+    rng = np.random.default_rng(seed)
+    if cfg["data"] == "normal":
+        xs = rng.standard_normal((rows, cfg["x"]), dtype=np.float32)
+    else:
+        xs = rng.random((rows, cfg["x"]), dtype=np.float32)
+    ys = np.zeros((rows, cfg["classes"]), dtype=np.float32)
+    ys[np.arange(rows), rng.integers(0, cfg["classes"], rows)] = 1.0
+    ds = InlineDataset(xs, ys, cfg["x"], cfg["classes"])
+    o = cfg["opt"]
+    opt = {"sgd": lambda: GradientDescent(o[1]), "momentum": lambda: GradientDescentWithMomentum(o[1], o[2]),
+           "adam": lambda: Adam(o[1])}[o[0]]()
+    epochs = -(-steps_total // steps_per_epoch)
+    addrs = [f"gpu:{i}" for i in range(n_gpus)]
+    b200 = {"sync_every": "step", "tile_dtype": cfg["tile"], "data": data_mode, "sharding": "even", "colocate": True}
+    if cfg["strategy"] == "ps4":
+        training = orchestra.parameter_server(addrs, min(4, n_gpus), ds, opt, CrossEntropy(), BarrierSync(),
+                                              BlockingStore(), max_epochs=epochs, batch_size=B, seed=seed, b200=b200)
+        par = f"ps(servers={min(4, n_gpus)},colocated)+dp{n_gpus}"
+    else:
+        training = orchestra.all_reduce(addrs, ds, opt, CrossEntropy(), max_epochs=epochs, batch_size=B, seed=seed,
+                                        b200=b200)
+        par = f"dp{n_gpus}"
+    return model, training, par
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc, self.lines = None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        time.sleep(0.1)
+        sm, mx, reasons = [], [], set()
+        for ln in list(self.lines):
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9 or f[0] != "0":
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 2:] if sm else []
+        return {"sm_mhz": busy[len(busy) // 2] if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", default="deep", choices=sorted(CONFIGS))
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm()
+        return
+    import torch
+    import torch.distributed as dist
+
+    from orchestra import orchestrate
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    cfg = CONFIGS[args.config]
+    W, K = max(3, args.warmup), args.steps
+    os.environ["ONO_BENCH_WARMUP"], os.environ["ONO_BENCH_STEPS"] = str(W), str(K)
+    results = {}
+    clocks = None
+    for mode in ("device", "host"):
+        model, training, par = build_run(cfg, world, W + K, mode)
+        sampler = ClockSampler() if (rank == 0 and mode == "device") else None
+        if sampler:
+            sampler.start()
+        trained = orchestrate(model, training).wait(quiet=True)
+        if sampler:
+            clocks = sampler.stop()
+        results[mode] = trained.metrics()
+        del trained
+        torch.cuda.empty_cache()
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        m, e = results["device"], results["host"]
+        gb = cfg["batch"] * world
+        value = gb * K / (m["bench_ms"] / 1e3)
+        e2e = gb * K / e["bench_wall_s"]
+        out = {
+            "metric": "samples/sec (device-timed, max over ranks)", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": m["bench_ms"] / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
+            "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
+                       "optimizer": cfg["opt"][0], "l2": "per-step working set (weights+grads > 2 GB) exceeds L2",
+                       "sync": m["sync_mode"]},
+            "clocks": clocks,
+            "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["bench_wall_s"] * 1e3 / K,
+                    "device_ms_per_step": e["bench_ms"] / K},
+            "gpu_launches": int(m["launches_per_step"]) * K,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

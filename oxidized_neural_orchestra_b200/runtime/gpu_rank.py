@@ -1,0 +1,153 @@
+"""One GPU rank of a run: worker, parameter server, or both, decided by the plan it is handed.
+
+Counterpart of the reference's role runtimes (worker/src/workers/{all_reduce,parameter_server}.rs,
+parameter_server/src/service/pserver.rs, node/src/router.rs:166-341) rebuilt around HBM-resident
+flat buffers in a symmetric NVLink window and fused kernels:
+
+    per mini-batch   H2D of the batch (pinned host memory, copy stream) -> CUDA graph of
+                     {gather/cast, forward GEMMs, fused softmax-loss, dgrad/wgrad GEMMs, bias grads,
+                      [round cadence: local SGD + residual accumulate]}
+    per sync point   one fused kernel: reduce-scatter of gradients into the owners + average +
+                     optimizer + all-gather of fresh parameters (ownership table = strategy)
+
+Ranks run SPMD: every rank derives the same plan and applies the same policy to the same gathered
+losses, so stop / early-stop / switch decisions need no messaging beyond one small all-gather per round.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import threading
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from orchestra import _orchestra as core
+
+from ..models.engine import GpuEngine
+from ..ops import _lib
+from ..ops import elementwise as ew
+from ..parallel import sync as S
+from ..parallel.symmetric import SymmetricWindow, WindowLayout
+
+ACT_NAME = {"sigmoid": "sigmoid", "tanh": "tanh", "relu": "relu", "re_l_u": "relu"}
+
+
+def engine_layers_from_plan(plan: dict) -> list[dict]:
+    """LayerSpec documents -> the engine's layer descriptions."""
+    out = []
+    for l in plan["layers"]:
+        (kind, body), = l["spec"].items()
+        act = body.get("act_fn")
+        if act is None:
+            a = None
+        elif isinstance(act, str):
+            a = (act, 0.0)
+        else:
+            (an, ab), = act.items()
+            a = (ACT_NAME[an], float(ab.get("amp", ab.get("slope", 0.0))))
+        if kind == "dense":
+            out.append({"kind": "dense", "in": body["dim"][0], "out": body["dim"][1], "act": a})
+        elif kind == "conv":
+            out.append({"kind": "conv", "input_dim": body["input_dim"], "kernel_dim": body["kernel_dim"],
+                        "stride": body["stride"], "padding": body["padding"], "act": a})
+        else:
+            out.append({"kind": "pool", "input_dim": body["input_dim"], "filter_size": body["filter_size"],
+                        "stride": body["stride"], "padding": body["padding"], "act": a})
+    return out
+
+
+def optimizer_cfg(spec: dict) -> S.OptimizerCfg:
+    (name, b), = spec.items()
+    lr = b.get("learning_rate", b.get("lr"))
+    if name == "gradient_descent":
+        return S.OptimizerCfg("sgd", lr)
+    if name == "gradient_descent_with_momentum":
+        return S.OptimizerCfg("momentum", lr, mu=b.get("momentum", b.get("mu", 0.0)))
+    return S.OptimizerCfg("adam", lr, b1=b.get("beta1", b.get("b1", 0.9)), b2=b.get("beta2", b.get("b2", 0.999)),
+                          eps=b.get("epsilon", b.get("eps", 1e-8)))
+
+
+def snap_ranges(ranges_per_rank: list[list[tuple[int, int]]], n_pad: int) -> list[list[tuple[int, int]]]:
+    """Move every interior boundary down to a multiple of 4 elements (the kernels work on float4), the
+    same rule on both sides of a boundary so the ranges still partition ``[0, n_pad)``."""
+    out = []
+    n_true_end = max((e for rs in ranges_per_rank for _, e in rs), default=0)
+    for rs in ranges_per_rank:
+        cur = []
+        for b, e in rs:
+            b2 = b // 4 * 4
+            e2 = n_pad if e == n_true_end else e // 4 * 4
+            if e2 > b2:
+                cur.append((b2, e2))
+        out.append(cur)
+    return out
+
+
+class BatchFeeder:
+    """Stages mini-batches from pinned host memory to the device on a copy stream, one step ahead.
+
+    The dataset partition stays in host memory (as on the reference's workers); every step's inputs
+    cross PCIe inside the timed region. A background thread gathers the next batch's rows into a
+    pinned staging buffer while the GPU works on the current one.
+    """
+
+    def __init__(self, xs: np.ndarray, ys: np.ndarray, x_size: int, y_size: int, batch: int, device, seed: int,
+                 device_resident: bool = False):
+        self.rows = xs.size // x_size
+        self.x_size, self.y_size, self.batch = x_size, y_size, batch
+        self.device = device
+        self.seed = seed
+        self.host_x = torch.from_numpy(np.ascontiguousarray(xs.reshape(self.rows, x_size)))
+        self.host_y = torch.from_numpy(np.ascontiguousarray(ys.reshape(self.rows, y_size)))
+        self.device_resident = device_resident
+        if device_resident:
+            self.dev_all_x = self.host_x.to(device)
+            self.dev_all_y = self.host_y.to(device)
+        self.nslots = 2
+        self.pin_x = [torch.empty(batch, x_size).pin_memory() for _ in range(self.nslots)]
+        self.pin_y = [torch.empty(batch, y_size).pin_memory() for _ in range(self.nslots)]
+        self.dev_x = [torch.zeros(batch, x_size, device=device) for _ in range(self.nslots)]
+        self.dev_y = [torch.zeros(batch, y_size, device=device) for _ in range(self.nslots)]
+        self.copy_stream = torch.cuda.Stream(device=device)
+        self.ready = [torch.cuda.Event() for _ in range(self.nslots)]
+        self.consumed = [torch.cuda.Event() for _ in range(self.nslots)]
+        self.h2d_bytes_per_step = batch * (x_size + y_size) * 4
+        self._perm = None
+        self._epoch = -1
+
+    def steps_per_epoch(self) -> int:
+        return (self.rows + self.batch - 1) // self.batch
+
+    def _indices(self, epoch: int, step: int) -> torch.Tensor:
+        if epoch != self._epoch:
+            g = torch.Generator()
+            g.manual_seed((self.seed * 1000003 + epoch) & 0x7FFFFFFFFFFFFFFF)
+            self._perm = torch.randperm(self.rows, generator=g)
+            self._epoch = epoch
+        lo = step * self.batch
+        return self._perm[lo:min(self.rows, lo + self.batch)]
+
+    def stage(self, slot: int, epoch: int, step: int) -> int:
+        """Gather the batch on the host and start its H2D copy. Returns the number of rows."""
+        idx = self._indices(epoch, step)
+        n = idx.numel()
+        if self.device_resident:
+            with torch.cuda.stream(self.copy_stream):
+                self.copy_stream.wait_event(self.consumed[slot])
+                di = idx.to(self.device, non_blocking=True)
+                torch.index_select(self.dev_all_x, 0, di, out=self.dev_x[slot][:n])
+                torch.index_select(self.dev_all_y, 0, di, out=self.dev_y[slot][:n])
+                self.ready[slot].record(self.copy_stream)
+            return n
+        self.consumed[slot].synchronize()  # the pinned buffer's previous copy has been issued and read
+        torch.index_select(self.host_x, 0, idx, out=self.pin_x[slot][:n])
+        torch.index_select(self.host_y, 0, idx, out=self.pin_y[slot][:n])
+        with torch.cuda.stream(self.copy_stream):
+            self.copy_stream.wait_event(self.consumed[slot])
+            self.dev_x[slot][:n].copy_(self.pin_x[slot][:n], non_blocking=True)
+            self.dev_y[slot][:n].copy_(self.pin_y[slot][:n], non_blocking=True)
+            self.ready[slot].record(self.copy_stream)
+        return n

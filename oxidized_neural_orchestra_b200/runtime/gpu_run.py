@@ -1,0 +1,174 @@
+"""Entry point of a GPU rank's training run: ``run(rank_state)`` drives the loops of gpu_loop.py
+to completion and returns the final parameters (rank 0) and the device-timed step records."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import gpu_loop as L
+
+
+def _drain_loss(r, slot: int, pending: list) -> float:
+    if not pending[slot]:
+        return 0.0
+    r.loss_evt[slot].synchronize()
+    pending[slot] = False
+    return float(r.loss_pin[slot].item())
+
+
+def _norm_check(r, hist: list) -> int:
+    """Feed the per-step global gradient norms gathered since the last check to the switch tracker."""
+    if not hist:
+        return 0
+    v = torch.stack(hist).reshape(-1)
+    if r.world > 1:
+        dist.all_reduce(v, group=r.group)
+    decision = 0
+    for x in v.cpu().numpy():
+        if r.policy.on_metric(math.sqrt(max(float(x), 0.0))) == 2:
+            decision = 2
+    hist.clear()
+    return decision
+
+
+def _bench_hook(r, it: int) -> None:
+    """Optional timed window [warmup, warmup + steps) bracketed by synchronize + barrier on both sides
+    (set through ONO_BENCH_WARMUP / ONO_BENCH_STEPS; used by the benchmark harness)."""
+    if r.bench is None:
+        return
+    w, k = r.bench
+    if it == w or it == w + k:
+        torch.cuda.synchronize(r.dev)
+        if r.world > 1:
+            dist.barrier(group=r.group)
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(r.stream)
+        r.bench_events.append(ev)
+        r.bench_wall.append(__import__("time").perf_counter())
+
+
+def run(r) -> dict:
+    import os
+
+    w, k = os.environ.get("ONO_BENCH_WARMUP"), os.environ.get("ONO_BENCH_STEPS")
+    r.bench = (int(w), int(k)) if w is not None and k is not None else None
+    r.bench_events, r.bench_wall = [], []
+    r.extra_rows = {}
+    r.stop_reason = "max_epochs"
+    epoch, it = 0, 0
+    pending = [False, False]
+    norm_hist: list = []
+    check_every = int(r.b200.get("switch_check_every", 10))
+    while epoch < r.max_epochs:
+        decision = 0
+        epoch_losses: list[float] = []
+        if r.cadence == "step":
+            steps = L._steps_per_epoch(r)
+            total, cnt = 0.0, 0
+            staged = [0, 0]
+            if r.engine is not None:
+                staged[it % 2] = r.feeder.stage(it % 2, epoch, 0)
+            for s in range(steps):
+                slot = it % 2
+                _bench_hook(r, it)
+                if r.engine is not None:
+                    total += _drain_loss(r, slot, pending)
+                    L.run_batch(r, slot, staged[slot])
+                    pending[slot] = True
+                    cnt += 1
+                    if s + 1 < steps:
+                        staged[slot ^ 1] = r.feeder.stage(slot ^ 1, epoch, s + 1)
+                else:
+                    L.server_step(r)
+                it += 1
+                if r.grad_norm_switch and not r.switched:
+                    with torch.cuda.stream(r.stream):
+                        norm_hist.append(r.sumsq.clone())
+                        r.sumsq.zero_()
+                    if len(norm_hist) >= check_every and _norm_check(r, norm_hist) == 2:
+                        decision = 2
+                        break
+            if r.engine is not None:
+                total += _drain_loss(r, 0, pending) + _drain_loss(r, 1, pending)
+                epoch_losses.append(total / max(1, cnt))
+            if decision != 2:
+                epoch += 1
+        else:
+            nep = min(r.max_epochs - epoch, r.offline + 1)
+            for e in range(nep):
+                if r.engine is None:
+                    continue
+                steps = r.feeder.steps_per_epoch()
+                total, cnt = 0.0, 0
+                staged = [0, 0]
+                staged[it % 2] = r.feeder.stage(it % 2, epoch + e, 0)
+                for s in range(steps):
+                    slot = it % 2
+                    total += _drain_loss(r, slot, pending)
+                    L.run_batch(r, slot, staged[slot])
+                    pending[slot] = True
+                    cnt += 1
+                    if s + 1 < steps:
+                        staged[slot ^ 1] = r.feeder.stage(slot ^ 1, epoch + e, s + 1)
+                    it += 1
+                total += _drain_loss(r, 0, pending) + _drain_loss(r, 1, pending)
+                epoch_losses.append(total / max(1, cnt))
+            # one exchange per round: residual -> owners -> fresh parameters everywhere
+            with torch.cuda.stream(r.stream):
+                r._launch_sync(r.G, r.stream)
+                if r.engine is not None:
+                    if r.sync_mode != "async":
+                        r.W.copy_(r.C)
+                    r.G.zero_()
+                    r.engine.refresh(stream=r.stream)
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(r.stream)
+            r.round_events = getattr(r, "round_events", []) + [ev]
+            epoch += nep
+        if decision != 2:
+            decision = L.report_and_decide(r, epoch_losses)
+        L.check_status(r)
+        if decision == 1:
+            break
+        if decision == 2 and r.algorithm == "strategy_switch" and not r.switched:
+            L.do_switch(r)
+            pending = [False, False]
+    _bench_hook(r, it)
+    torch.cuda.synchronize(r.dev)
+    L.check_status(r)
+    # final parameters: the owners' ranges are authoritative (session.rs:293-359); all-reduce replicas
+    # are identical and rank 0's copy is taken (session.rs:371-412)
+    if r.sync_mode == "async" or (r.algorithm != "all_reduce" and r.world > 1):
+        tmp = torch.zeros_like(r.C)
+        for b, e in r.own[r.rank]:
+            tmp[b:e] = r.C[b:e]
+        if r.world > 1:
+            dist.all_reduce(tmp, group=r.group)
+        final = tmp
+    else:
+        final = r.C
+    params = final[:r.n].cpu().numpy() if r.rank == 0 else None
+    ms = []
+    evs = r.step_events
+    for a, b in zip(evs[:-1], evs[1:]):
+        ms.append(a.elapsed_time(b))
+    metrics = {
+        "step_ms": ms, "steps": len(evs), "step_wall": r.step_wall, "launches_per_step": r.launches_per_step,
+        "h2d_bytes_per_step": r.feeder.h2d_bytes_per_step if r.feeder is not None else 0,
+        "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
+        "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
+    }
+    if len(r.bench_events) == 2:
+        metrics["bench_ms"] = r.bench_events[0].elapsed_time(r.bench_events[1])
+        metrics["bench_wall_s"] = r.bench_wall[1] - r.bench_wall[0]
+        if r.world > 1:  # the slowest rank defines the time
+            t = torch.tensor([metrics["bench_ms"], metrics["bench_wall_s"]], dtype=torch.float64, device=r.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=r.group)
+            metrics["bench_ms"], metrics["bench_wall_s"] = float(t[0]), float(t[1])
+    r.result = {"params": params, "metrics": metrics}
+    # every process closes its own event stream (the other events come from rank 0 only)
+    r.emit({"kind": "complete", "worker": 0, "losses": [], "text": r.stop_reason})
+    return {"params": params, "metrics": metrics}

@@ -1,0 +1,282 @@
+"""The SPMD training loop of one GPU rank (see gpu_rank.py for the pieces it is made of)."""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import math
+import threading
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from orchestra import _orchestra as core
+
+from ..models.engine import GpuEngine
+from ..ops import _lib
+from ..ops import elementwise as ew
+from ..parallel import sync as S
+from ..parallel.symmetric import SymmetricWindow, WindowLayout
+from .gpu_rank import BatchFeeder, engine_layers_from_plan, optimizer_cfg, snap_ranges
+
+
+def _up(n, m=16):
+    return (n + m - 1) // m * m
+
+
+class GpuRank:
+    def __init__(self, plan: dict, rank: int, world: int, device: torch.device, xs: np.ndarray, ys: np.ndarray,
+                 emit, stop_event: threading.Event, group=None, warmup_steps: int = 0):
+        self.plan, self.rank, self.world, self.dev, self.group = plan, rank, world, device, group
+        self.emit, self.stop_event = emit, stop_event
+        b = plan["b200"]
+        self.b200 = b
+        self.cadence = b.get("sync_every", "round")
+        self.tile = b.get("tile_dtype", "tf32")
+        self.algorithm = plan["algorithm"]
+        self.n = plan["n_params"]
+        self.n_pad = _up(self.n, 16)
+        self.seed = plan["seed"] if plan.get("seed") is not None else int(time.time())
+        self.x_size = plan["layers"][0]["input_size"]
+        self.y_size = plan["layers"][-1]["output_size"]
+        self.worker_ranks = [w["rank"] for w in plan["workers"]]
+        self.widx = self.worker_ranks.index(rank) if rank in self.worker_ranks else None
+        self.server_ranks = [s["rank"] for s in plan["servers"]]
+        self.warmup_steps = warmup_steps
+        self.launches_per_step = 0
+        self.step_events: list[torch.cuda.Event] = []
+        self.step_wall: list[float] = []
+        self.switched = False
+        self.stream = torch.cuda.Stream(device=device)
+        wspec = plan["workers"][self.widx if self.widx is not None else 0]["spec"]
+        self.trainer = wspec["trainer"]
+        self.max_epochs = self.trainer["max_epochs"]
+        self.offline = self.trainer["offline_epochs"]
+        self.loss_kind = self.trainer["loss_fn"]
+        self.local_lr = optimizer_cfg(self.trainer["optimizer"]).lr
+        if self.algorithm == "parameter_server":
+            self.opt = optimizer_cfg(plan["servers"][0]["spec"]["optimizer"])
+            sp = plan["servers"][0]["spec"]
+            self.async_ps = sp["synchronizer"] == "non_blocking" or sp["store"] == "wild"
+            self.wild = sp["store"] == "wild"
+        else:
+            self.opt = optimizer_cfg(self.trainer["optimizer"])
+            self.async_ps = self.wild = False
+        self._alloc_window()
+        self._init_params()
+        self._build_engine(xs, ys)
+        self._policy()
+        self._set_ownership_initial()
+
+    # ------------------------------------------------------------------------------------------
+    def _alloc_window(self):
+        lay = WindowLayout()
+        lay.add("params", self.n_pad, torch.float32)
+        lay.add("grads", self.n_pad, torch.float32)
+        if self.tile == "bf16":
+            lay.add("params_bf16", self.n_pad, torch.bfloat16)
+        needs_async = self.async_ps
+        if self.algorithm == "strategy_switch":
+            for a in self.plan["switch"]["post_actions"]:
+                if a["action"] == "upgrade":
+                    needs_async = a["spec"]["synchronizer"] == "non_blocking" or a["spec"]["store"] == "wild"
+        if needs_async:
+            lay.add("m", self.n_pad, torch.float32)
+            lay.add("v", self.n_pad, torch.float32)
+            lay.add("locks", _lib.MAX_RANGES * 512, torch.int32)
+        self.layout = lay
+        self.win = SymmetricWindow(lay.size, self.dev, self.group)
+        self.C = lay.tensor(self.win, "params")
+        self.G = lay.tensor(self.win, "grads")
+        self.shadow = lay.tensor(self.win, "params_bf16") if self.tile == "bf16" else None
+        if needs_async:
+            self.m_win, self.v_win = lay.tensor(self.win, "m"), lay.tensor(self.win, "v")
+        z = lambda n, dt=torch.float32: torch.zeros(n, dtype=dt, device=self.dev)
+        self.m_loc, self.v_loc = z(self.n_pad), z(self.n_pad)
+        self.adam_pows = torch.ones(2, device=self.dev)
+        self.epoch_words = torch.zeros(1024, dtype=torch.int32, device=self.dev)
+        self.sync_status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.dev)
+
+    def _init_params(self):
+        """Every rank generates the whole vector from the per-layer generators: the same Philox
+        counters give the same values everywhere (replicas identical by construction)."""
+        with torch.cuda.stream(self.stream):
+            for l in self.plan["layers"]:
+                pg = l["param_gen"]
+                if pg is None:
+                    continue
+                dst = self.C[l["offset"]:l["offset"] + l["n_params"]]
+                (kind, body), = pg.items()
+                if kind == "const":
+                    dst.fill_(body["value"])
+                elif kind == "inline":
+                    dst.copy_(torch.tensor(body["params"], dtype=torch.float32))
+                else:
+                    (dn, db), = body["distribution"].items()
+                    fi, fo = db.get("fan_in", 1), db.get("fan_out", 0)
+                    if dn == "uniform":
+                        k, a, bb = "uniform", db["low"], db["high"]
+                    elif dn == "uniform_inclusive":
+                        k, a, bb = "uniform_inclusive", db["low"], db["high"]
+                    elif dn == "normal":
+                        k, a, bb = "normal", db["mean"], db["std_dev"]
+                    elif dn == "xavier_uniform":
+                        r = math.sqrt(6.0 / (fi + fo)); k, a, bb = "uniform_inclusive", -r, r
+                    elif dn == "lecun_uniform":
+                        r = math.sqrt(3.0 / fi); k, a, bb = "uniform_inclusive", -r, r
+                    elif dn == "kaiming":
+                        k, a, bb = "normal", 0.0, math.sqrt(2.0 / fi)
+                    elif dn == "xavier":
+                        k, a, bb = "normal", 0.0, math.sqrt(2.0 / (fi + fo))
+                    else:
+                        k, a, bb = "normal", 0.0, math.sqrt(1.0 / fi)
+                    ew.philox_init(dst, seed=self.seed, index_offset=body.get("index_offset", l["offset"]), kind=k,
+                                   a=a, b=bb, stream=self.stream)
+            if self.shadow is not None:
+                self.shadow.copy_(self.C)
+        self.stream.synchronize()
+
+    def _build_engine(self, xs, ys):
+        self.engine = None
+        self.feeder = None
+        if self.widx is None:
+            return
+        layers = engine_layers_from_plan(self.plan)
+        B = self.trainer["batch_size"]
+        if self.cadence == "step":
+            self.W, self.g = self.C, self.G
+        else:
+            self.W = self.C.clone()
+            self.g = torch.zeros_like(self.C)
+        self.engine = GpuEngine(layers, batch_size=B, tile_dtype=self.tile, loss=self.loss_kind, params=self.W,
+                                grads=self.g, params_bf16=self.shadow,
+                                leaky_relu_exact=self.b200.get("leaky_relu_exact", True))
+        self.feeder = BatchFeeder(xs, ys, self.x_size, self.y_size, B, self.dev, self.seed,
+                                  device_resident=self.b200.get("data", "host") == "device")
+        self.loss_pin = [torch.zeros(1, dtype=torch.float64).pin_memory() for _ in range(2)]
+        self.loss_evt = [torch.cuda.Event() for _ in range(2)]
+        self.graphs: dict = {}
+        self.warm: set = set()
+        with torch.cuda.stream(self.stream):
+            self.engine.refresh(stream=self.stream)
+        self.stream.synchronize()
+
+    def _policy(self):
+        p = core.SessionPolicy(len(self.worker_ranks))
+        es = self.plan.get("early_stopping")
+        if es:
+            p.enable_early_stopping(es["window"], es["tolerance"])
+        sw = self.plan.get("switch")
+        if sw:
+            p.enable_switch(sw["window"], sw["threshold"])
+            p.set_switch_on_metric(sw.get("metric", "loss") == "grad_norm")
+        self.policy = p
+        self.grad_norm_switch = bool(sw) and sw.get("metric", "loss") == "grad_norm"
+
+    # ------------------------------------------------------------------------------------------
+    # ownership table = strategy
+    # ------------------------------------------------------------------------------------------
+    def _set_ownership_initial(self):
+        W = self.world
+        if self.algorithm == "parameter_server":
+            owners = {s["rank"]: [tuple(r) for r in s["ranges"]] for s in self.plan["servers"]}
+            self._set_ownership([owners.get(r, []) for r in range(W)], self.worker_ranks, self.opt,
+                                "async" if self.async_ps else "fused", self.wild)
+            return
+        mode = self.b200.get("allreduce", "auto")
+        if mode == "auto":
+            mode = "oneshot" if (self.n_pad * 4 <= 256 * 1024 and W > 1) else "twoshot"
+        if mode == "oneshot":
+            ranges = [[(0, self.n_pad)] for _ in range(W)]
+        else:
+            ranges = S.even_ranges(self.n_pad, list(range(W)), W)
+        kind = {"oneshot": "oneshot", "twoshot": "fused", "nvls": "fused", "ring": "ring", "nccl": "nccl"}[mode]
+        self.use_nvls = mode == "nvls"
+        self._set_ownership(ranges, self.worker_ranks, self.opt, kind, False)
+
+    def _set_ownership(self, ranges, workers, opt, mode, wild):
+        W = self.world
+        self.own = snap_ranges(ranges, self.n_pad)
+        self.sync_workers = list(workers)
+        self.sync_mode = mode
+        self.sync_opt = opt
+        n4 = self.n_pad // 4
+        self.nblocks = int(min(128, max(1, -(-n4 // (512 * 4)))))
+        wmask = sum(1 << r for r in workers)
+        allmask = (1 << W) - 1
+        lay, win = self.layout, self.win
+        dest = set(workers) | {0}
+        if mode in ("fused", "oneshot"):
+            s = _lib.OnoSync()
+            oneshot = mode == "oneshot"
+            pf = [p if (r in dest and not oneshot) or r == self.rank else None
+                  for r, p in enumerate(win.peer_ptrs(lay.offset("params")))]
+            if self.tile == "bf16":
+                pb = [p if (r in dest and not oneshot) or r == self.rank else None
+                      for r, p in enumerate(win.peer_ptrs(lay.offset("params_bf16")))]
+            else:
+                pb = [None] * W
+            nvls = getattr(self, "use_nvls", False) and win.mc_ptr != 0 and W > 1
+            S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=1 if nvls else 0,
+                        g_ptrs=win.peer_ptrs(lay.offset("grads")), p_f32_ptrs=pf, p_bf16_ptrs=pb,
+                        flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
+                        opt=opt, divide=not wild, timeout_ns=10_000_000_000,
+                        g_mc=win.mc(lay.offset("grads")) or None, p_mc_f32=win.mc(lay.offset("params")) or None)
+            S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
+                         v=self.v_loc.data_ptr(), state_off=0, adam_pows=self.adam_pows.data_ptr(),
+                         epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
+                         sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
+                         status=self.sync_status.data_ptr())
+            self.sync_struct = s
+        elif mode == "async":
+            a = _lib.OnoPsAsync()
+            a.nranks, a.rank, a.nblocks = W, self.rank, self.nblocks
+            for r in range(W):
+                a.master[r] = win.peer_ptrs(lay.offset("params"))[r]
+                a.m[r] = win.peer_ptrs(lay.offset("m"))[r]
+                a.v[r] = win.peer_ptrs(lay.offset("v"))[r]
+                a.state_off[r] = 0
+                a.locks[r] = None if wild else win.peer_ptrs(lay.offset("locks"))[r]
+                a.n_ranges[r] = len(self.own[r])
+                for i, (b, e) in enumerate(self.own[r]):
+                    a.ranges[r][i].begin, a.ranges[r][i].end = b, e
+            a.n_workers, a.divide = len(workers), int(not wild)
+            a.kind = S.OPT_KIND[opt.kind]
+            a.lr, a.mu, a.b1, a.b2, a.eps = opt.lr, opt.mu, opt.b1, opt.b2, opt.eps
+            a.adam_pows = self.adam_pows.data_ptr()
+            a.status = self.sync_status.data_ptr()
+            a.timeout_ns = 10_000_000_000
+            self.async_struct = a
+        elif mode == "ring":
+            if "acc" not in lay.regions:
+                raise RuntimeError("ring all-reduce needs the accumulation window (set b200.allreduce before start)")
+
+    def _launch_sync(self, g_tensor: torch.Tensor, stream) -> int:
+        """One synchronisation of `g_tensor` (the window's gradient region) into the parameters."""
+        n = 0
+        if self.sync_opt.kind == "adam":
+            ew.adam_tick(self.adam_pows, self.sync_opt.b1, self.sync_opt.b2, stream=stream)
+            n += 1
+        if self.sync_mode in ("fused", "oneshot"):
+            S.launch_sync(self.sync_struct, stream=stream)
+            n += 1
+        elif self.sync_mode == "async":
+            if self.widx is not None and self.rank in self.sync_workers:
+                a = self.async_struct
+                a.g = g_tensor.data_ptr()
+                a.p_local_f32 = self.W.data_ptr()
+                a.p_local_bf16 = self.shadow.data_ptr() if self.shadow is not None else None
+                _lib.check(_lib.load().ono_ps_async_step(C.byref(a), _lib.stream_ptr(stream)), "ono_ps_async_step")
+                n += 1
+        elif self.sync_mode == "nccl":
+            with torch.cuda.stream(stream):
+                if self.world > 1:
+                    dist.all_reduce(g_tensor, group=self.group)
+            ew.optim_step(self.C, g_tensor, kind=self.sync_opt.kind, lr=self.sync_opt.lr, mu=self.sync_opt.mu,
+                          b1=self.sync_opt.b1, b2=self.sync_opt.b2, eps=self.sync_opt.eps, m=self.m_loc,
+                          v=self.v_loc, adam_pows=self.adam_pows, grad_scale=1.0 / len(self.sync_workers),
+                          p_bf16=self.shadow, stream=stream)
+            n += 2
+        return n

@@ -1,0 +1,71 @@
+"""End-to-end runs on one GPU through the public API, checked against the CPU oracle run of the same
+configuration (same Philox initial parameters; one batch per epoch so the batch order cannot differ)."""
+import numpy as np
+import pytest
+
+import orchestra
+from orchestra import Sequential, orchestrate
+from orchestra.activations import GELU, ReLU, Sigmoid, Softmax
+from orchestra.arch import Dense
+from orchestra.datasets import InlineDataset
+from orchestra.initialization import XavierUniform
+from orchestra.loss_fns import CrossEntropy, Mse
+from orchestra.optimizers import Adam, GradientDescent, GradientDescentWithMomentum
+from orchestra.store import BlockingStore
+from orchestra.sync import BarrierSync
+
+pytestmark = pytest.mark.gpu
+
+
+def _data(n=64, x=784, y=10, seed=0):
+    rng = np.random.default_rng(seed)
+    xs = rng.random((n, x), dtype=np.float32)
+    ys = np.eye(y, dtype=np.float32)[rng.integers(0, y, n)]
+    return xs, ys
+
+
+def _mlp():
+    return Sequential([Dense(128, XavierUniform(), ReLU(0.0)), Dense(10, XavierUniform(), Softmax())])
+
+
+@pytest.mark.parametrize("cadence", ["round", "step"])
+@pytest.mark.parametrize("opt", [GradientDescent(0.5), Adam(0.01), GradientDescentWithMomentum(0.2, 0.9)])
+def test_single_gpu_all_reduce_tracks_the_cpu_oracle(cadence, opt):
+    xs, ys = _data()
+    hist = {}
+    for dev in ("cpu", "gpu"):
+        tr = orchestra.all_reduce([f"{dev}:0"], InlineDataset(xs, ys, 784, 10), opt, CrossEntropy(), max_epochs=12,
+                                  batch_size=64, seed=5, b200={"sync_every": cadence})
+        m = orchestrate(_mlp(), tr).wait(quiet=True)
+        hist[dev] = (np.array(m.loss_history()), m.weights_array())
+    (lc, wc), (lg, wg) = hist["cpu"], hist["gpu"]
+    assert lc.shape == lg.shape == (12,)
+    assert lg[-1] < lg[0]
+    assert np.allclose(lc, lg, rtol=2e-2, atol=1e-5)
+    assert np.abs(wc - wg).max() < 2e-2 * max(1.0, np.abs(wc).max())
+
+
+def test_single_gpu_parameter_server_bf16_gelu_and_metrics():
+    xs, ys = _data(n=256, x=256, y=16)
+    model = Sequential([Dense(512, XavierUniform(), GELU()), Dense(256, XavierUniform(), Sigmoid()),
+                        Dense(16, XavierUniform(), Softmax())])
+    tr = orchestra.parameter_server(["gpu:0"], 1, InlineDataset(xs, ys, 256, 16), GradientDescentWithMomentum(0.1, 0.9),
+                                    CrossEntropy(), BarrierSync(), BlockingStore(), max_epochs=6, batch_size=64, seed=1,
+                                    b200={"sync_every": "step", "tile_dtype": "bf16", "colocate": True, "sharding": "even"})
+    m = orchestrate(model, tr).wait(quiet=True)
+    h = m.loss_history()
+    assert len(h) == 6 and h[-1] < h[0]
+    met = m.metrics()
+    assert met["steps"] == 24 and met["launches_per_step"] > 5
+    assert met["h2d_bytes_per_step"] == 64 * (256 + 16) * 4 and met["d2h_bytes_per_step"] == 8
+
+
+def test_single_gpu_mse_regression_and_ragged_batches():
+    rng = np.random.default_rng(3)
+    xs = rng.random((50, 8), dtype=np.float32)
+    ys = (xs @ rng.random((8, 2), dtype=np.float32)).astype(np.float32)
+    model = Sequential([Dense(32, XavierUniform(), Sigmoid()), Dense(2, XavierUniform())])
+    tr = orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 8, 2), Adam(0.02), Mse(), max_epochs=40, batch_size=16,
+                              seed=2)
+    h = orchestrate(model, tr).wait(quiet=True).loss_history()
+    assert len(h) == 40 and h[-1] < 0.5 * h[0]
