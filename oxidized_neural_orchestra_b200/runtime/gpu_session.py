@@ -82,14 +82,14 @@ def partition_for(plan: dict, rank: int, xs: np.ndarray, ys: np.ndarray, x_size:
 def start_gpu_session(model_cfg: dict, training_cfg: dict, dataset, kind: str):
     from .session import load_dataset_arrays
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("gpu:/host:port addresses need CUDA devices; use cpu:<i> addresses for CPU ranks")
     addrs = training_cfg["addrs"]
     plan = json.loads(core.adapt_configs(json.dumps(model_cfg), json.dumps(training_cfg)))
     if kind == "tcp":
         from .node import start_remote_session
 
         return start_remote_session(plan, model_cfg, training_cfg, dataset)
+    if not torch.cuda.is_available():
+        raise RuntimeError("gpu:<i> addresses need CUDA devices; use cpu:<i> addresses for CPU ranks")
     if dist.is_initialized():
         world, rank = dist.get_world_size(), dist.get_rank()
         if world != len(addrs):

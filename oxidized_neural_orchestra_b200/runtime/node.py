@@ -1,0 +1,274 @@
+"""The role-agnostic node process and the orchestrator's view of it.
+
+Like the reference's ``node`` binary (node/src/main.rs:27-54, node/src/router.rs:79-220) a node
+listens on ``HOST:PORT``, waits for an orchestrator, and only learns what it is (worker, parameter
+server, both) from the spec it is handed. One session at a time; after ``disconnect`` it goes back to
+listening.
+
+    PORT=40000 python -m oxidized_neural_orchestra_b200.runtime.node [--device gpu --gpu 0 | --device cpu]
+
+Session protocol on the control channel (wire.py): ``connect/accept`` handshake, ``create_node{spec}``
+followed by the node's dataset partition (``share_dataset_size`` / data chunks / ``eof`` twice), then
+the node streams ``event`` messages (rank 0 relays every worker's losses), honours ``stop_after_epoch``,
+finishes with ``done`` and serves ``request_params`` until ``disconnect``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import queue
+import sys
+import threading
+import uuid
+
+import numpy as np
+
+from . import wire
+
+
+def run_rank(job: dict, xs: np.ndarray, ys: np.ndarray, emit, stop_event, device_kind: str, gpu: int | None = None) -> dict:
+    """Join the process group described by ``job`` and run this node's rank to completion."""
+    import torch
+    import torch.distributed as dist
+
+    from orchestra import _orchestra as core
+
+    rank, world = job["rank"], job["world"]
+    plan = json.loads(core.adapt_configs(json.dumps(job["model"]), json.dumps(job["training"]), json.dumps(job.get("stats") or {}) if job.get("stats") else ""))
+    own_group = False
+    if world > 1 and not dist.is_initialized():
+        os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = job["master_addr"], str(job["master_port"])
+        if device_kind == "gpu":
+            torch.cuda.set_device(gpu or 0)
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", gpu or 0))
+        else:
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+        own_group = True
+    try:
+        if device_kind == "gpu":
+            from .gpu_run import run
+            from .gpu_worker import GpuRank
+
+            dev = torch.device("cuda", gpu or 0)
+            torch.cuda.set_device(dev)
+            return run(GpuRank(plan, rank, world, dev, xs, ys, emit, stop_event))
+        from .cpu_rank import CpuRank
+
+        return CpuRank(plan, rank, world, xs, ys, emit, stop_event).run()
+    finally:
+        if own_group:
+            dist.destroy_process_group()
+
+
+def serve(host: str, port: int, device_kind: str, gpu: int | None, once: bool = False, ready: threading.Event | None = None) -> None:
+    """Accept loop of a node (router.rs:79-113)."""
+    node_id = str(uuid.uuid4())
+    lsock = wire.listen(host, port)
+    if ready is not None:
+        ready.set()
+    while True:
+        conn, _ = lsock.accept()
+        ch = wire.Channel(conn)
+        try:
+            ch.accept_as("Node", node_id)
+            _session(ch, device_kind, gpu)
+        except (ConnectionError, OSError) as e:
+            print(f"[ono-node {host}:{port}] session ended: {e}", file=sys.stderr)
+        finally:
+            ch.close()
+        if once:
+            lsock.close()
+            return
+
+
+def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
+    while True:
+        kind, msg = ch.recv(timeout=None)
+        if kind != "control":
+            continue
+        if msg == "disconnect":
+            return
+        if isinstance(msg, dict) and "stats_request" in msg:
+            # NVSwitch is uniform; report no measurements and let the planner treat pairs as equidistant
+            ch.send_command({"stats_response": {"stats": []}})
+            continue
+        if msg == "ping":
+            ch.send_command("pong")
+            continue
+        if isinstance(msg, dict) and "create_node" in msg:
+            job = msg["create_node"]["spec"]
+            xs, ys = ch.recv_dataset()
+            stop_event = threading.Event()
+            send_lock = threading.Lock()
+            result: dict = {}
+
+            def emit(ev):
+                if job["rank"] == 0 or ev["kind"] in ("complete", "error"):
+                    with send_lock:
+                        ch.send_command({"event": ev})
+
+            def body():
+                try:
+                    result.update(run_rank(job, xs, ys, emit, stop_event, device_kind, gpu))
+                except BaseException as e:
+                    emit({"kind": "error", "worker": 0, "losses": [], "text": f"{type(e).__name__}: {e}"})
+                    emit({"kind": "complete", "worker": 0, "losses": [], "text": "error"})
+                with send_lock:
+                    ch.send_command("done")
+
+            t = threading.Thread(target=body, daemon=True)
+            t.start()
+            # serve the orchestrator while training runs and afterwards (all_reduce.rs:137-152)
+            while True:
+                kind, m = ch.recv(timeout=None)
+                if kind != "control":
+                    continue
+                if m == "stop_after_epoch":
+                    stop_event.set()
+                elif m == "request_params":
+                    t.join()
+                    p = result.get("params")
+                    with send_lock:
+                        ch.send_floats(wire.KIND_PARAMS, p if p is not None else np.zeros(0, dtype=np.float32))
+                        ch.send_command({"event": {"kind": "metrics", "worker": 0, "losses": [],
+                                                   "text": json.dumps(_jsonable(result.get("metrics", {})))}})
+                elif m == "disconnect":
+                    stop_event.set()
+                    t.join()
+                    return
+
+
+def _jsonable(d: dict) -> dict:
+    out = {}
+    for k, v in d.items():
+        if isinstance(v, (np.floating, np.integer)):
+            v = v.item()
+        out[k] = v
+    return out
+
+
+class RemoteHandle:
+    """Orchestrator side of a run on listening nodes (orchestrator/src/sessions/session.rs:57-167)."""
+
+    def __init__(self, plan: dict, model_cfg: dict, training_cfg: dict, xs: np.ndarray, ys: np.ndarray, x_size: int, y_size: int):
+        addrs = training_cfg["addrs"]
+        self.n_workers = len(plan["workers"])
+        self._q: queue.Queue = queue.Queue()
+        self._chs: list[wire.Channel] = []
+        self._done_nodes = 0
+        self._params = None
+        self._metrics: dict = {}
+        self._closed = False
+        master_port = wire.free_port()
+        master_addr = addrs[0].rsplit(":", 1)[0]
+        part = {w["rank"]: w["partition"] for w in plan["workers"]}
+        my_id = str(uuid.uuid4())
+        for rank, addr in enumerate(addrs):
+            host, port = addr.rsplit(":", 1)
+            ch = wire.connect(host, int(port))
+            ch.connect_as("Orchestrator", my_id)
+            if ch.peer_entity != "Node":
+                raise ConnectionError(f"{addr} answered as {ch.peer_entity}, expected a node")
+            self._chs.append(ch)
+        for rank, ch in enumerate(self._chs):
+            job = {"model": model_cfg, "training": training_cfg, "rank": rank, "world": len(addrs),
+                   "master_addr": "127.0.0.1" if master_addr in ("localhost", "127.0.0.1") else master_addr,
+                   "master_port": master_port}
+            ch.send_command({"create_node": {"spec": job}})
+            b, e = part.get(rank, (0, 0))
+            ch.send_dataset(xs[b * x_size:e * x_size], ys[b * y_size:e * y_size])
+        self._threads = [threading.Thread(target=self._reader, args=(r, ch), daemon=True) for r, ch in enumerate(self._chs)]
+        for t in self._threads:
+            t.start()
+
+    def _reader(self, rank: int, ch: wire.Channel):
+        try:
+            while True:
+                kind, msg = ch.recv(timeout=None)
+                if kind == "params":
+                    if rank == 0:
+                        self._params = np.array(msg, dtype=np.float32)
+                    continue
+                if msg == "done":
+                    self._q.put(("done", rank, None))
+                    if rank != 0:
+                        return
+                    continue
+                if isinstance(msg, dict) and "event" in msg:
+                    ev = msg["event"]
+                    if ev["kind"] == "metrics":
+                        self._metrics = json.loads(ev["text"])
+                        self._q.put(("metrics", rank, None))
+                        return
+                    self._q.put(("event", rank, ev))
+        except (ConnectionError, OSError) as e:
+            self._q.put(("event", rank, {"kind": "error", "worker": rank, "losses": [], "text": f"node {rank} lost: {e}"}))
+            self._q.put(("done", rank, None))
+
+    def stop(self):
+        for ch in self._chs:
+            try:
+                ch.send_command("stop_after_epoch")
+            except OSError:
+                pass
+
+    def events(self):
+        done, complete_ev = 0, None
+        while done < len(self._chs):
+            what, rank, ev = self._q.get()
+            if what == "done":
+                done += 1
+            elif what == "event":
+                if ev["kind"] == "complete":
+                    if rank == 0:
+                        complete_ev = ev
+                    continue
+                yield ev
+        yield complete_ev or {"kind": "complete", "worker": 0, "losses": [], "text": "error"}
+
+    def result(self):
+        if not self._closed:
+            self._chs[0].send_command("request_params")
+            while True:
+                what, rank, ev = self._q.get()
+                if what == "metrics":
+                    break
+            for ch in self._chs:
+                try:
+                    ch.send_command("disconnect")
+                except OSError:
+                    pass
+                ch.close()
+            self._closed = True
+        return (self._params if self._params is not None else np.zeros(0, dtype=np.float32)), self._metrics
+
+
+def start_remote_session(plan, model_cfg, training_cfg, dataset):
+    from .session import load_dataset_arrays
+
+    xs, ys = load_dataset_arrays(dataset)
+    return RemoteHandle(plan, model_cfg, training_cfg, xs, ys, dataset.x_size, dataset.y_size)
+
+
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description="role-agnostic training node (awaits a spec from an orchestrator)")
+    ap.add_argument("--host", default=os.environ.get("HOST", "127.0.0.1"))
+    ap.add_argument("--port", type=int, default=int(os.environ["PORT"]) if "PORT" in os.environ else None)
+    ap.add_argument("--device", choices=("cpu", "gpu"), default=None)
+    ap.add_argument("--gpu", type=int, default=None)
+    ap.add_argument("--once", action="store_true", help="serve one session, then exit")
+    a = ap.parse_args(argv)
+    if a.port is None:
+        ap.error("a port is required (--port or the PORT environment variable)")
+    kind = a.device
+    if kind is None:
+        import torch
+
+        kind = "gpu" if torch.cuda.is_available() else "cpu"
+    print(f"[ono-node] listening on {a.host}:{a.port} ({kind})", file=sys.stderr)
+    serve(a.host, a.port, kind, a.gpu, once=a.once)
+
+
+if __name__ == "__main__":
+    main()
