@@ -15,7 +15,7 @@ import time
 from . import wire
 
 
-def spawn_nodes(n: int, device: str, gpus: list[int] | None = None) -> tuple[list[subprocess.Popen], list[str]]:
+def spawn_nodes(n: int, device: str, gpus: list[int] | None = None, once: bool = True) -> tuple[list[subprocess.Popen], list[str]]:
     procs, addrs = [], []
     root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     env = dict(os.environ)
@@ -23,7 +23,7 @@ def spawn_nodes(n: int, device: str, gpus: list[int] | None = None) -> tuple[lis
     for i in range(n):
         port = wire.free_port()
         cmd = [sys.executable, "-m", "oxidized_neural_orchestra_b200.runtime.node", "--host", "127.0.0.1", "--port",
-               str(port), "--device", device, "--once"]
+               str(port), "--device", device] + (["--once"] if once else [])
         if device == "gpu":
             cmd += ["--gpu", str(gpus[i] if gpus else i)]
         procs.append(subprocess.Popen(cmd, env=env))

@@ -72,6 +72,10 @@ def serve(host: str, port: int, device_kind: str, gpu: int | None, once: bool = 
         ch = wire.Channel(conn)
         try:
             ch.accept_as("Node", node_id)
+        except (ConnectionError, OSError, ValueError):
+            ch.close()  # a port probe or a stranger: not a session
+            continue
+        try:
             _session(ch, device_kind, gpu)
         except (ConnectionError, OSError) as e:
             print(f"[ono-node {host}:{port}] session ended: {e}", file=sys.stderr)
@@ -160,6 +164,7 @@ class RemoteHandle:
         self._params = None
         self._metrics: dict = {}
         self._closed = False
+        self._events_finished = False
         master_port = wire.free_port()
         master_addr = addrs[0].rsplit(":", 1)[0]
         part = {w["rank"]: w["partition"] for w in plan["workers"]}
@@ -214,6 +219,8 @@ class RemoteHandle:
                 pass
 
     def events(self):
+        if self._events_finished:
+            return
         done, complete_ev = 0, None
         while done < len(self._chs):
             what, rank, ev = self._q.get()
@@ -225,6 +232,7 @@ class RemoteHandle:
                         complete_ev = ev
                     continue
                 yield ev
+        self._events_finished = True
         yield complete_ev or {"kind": "complete", "worker": 0, "losses": [], "text": "error"}
 
     def result(self):
