@@ -80,57 +80,68 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
 
   double sq = 0.0;
   if (ok) {
-    const long long stride = (long long)a.nblocks * blockDim.x;
+    // Two float4 per thread and iteration, all loads issued before the first use, so that enough
+    // bytes are in flight per SM to cover HBM / NVLink latency.
+    constexpr int U = 2;
+    const long long stride = (long long)a.nblocks * blockDim.x * U;
     for (int ri = 0; ri < L.n_ranges; ++ri) {
       const long long b4 = L.ranges[ri].begin >> 2;
       const long long e4 = (L.ranges[ri].end + 3) >> 2;
-      for (long long i4 = b4 + (long long)blk * blockDim.x + threadIdx.x; i4 < e4; i4 += stride) {
-        float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (a.algo == 1) {
-          g = multimem_ld_reduce_add_v4(reinterpret_cast<const float4*>(a.g_mc) + i4);
-        } else {
-          float4 part[ONO_MAX_RANKS];
+      for (long long base = b4 + (long long)blk * blockDim.x * U + threadIdx.x; base < e4; base += stride) {
+        float4 g[U], p[U], m[U], v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i4 = base + (long long)u * blockDim.x;
+          g[u] = p[u] = m[u] = v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i4 >= e4) continue;
+          if (a.algo == 1) {
+            g[u] = multimem_ld_reduce_add_v4(reinterpret_cast<const float4*>(a.g_mc) + i4);
+          } else {
+#pragma unroll
+            for (int q = 0; q < ONO_MAX_RANKS; ++q)  // fixed rank order: run-to-run deterministic
+              if (q < a.nranks && ((workers >> q) & 1u)) {
+                const float4 x = ld_global_v4_volatile(reinterpret_cast<const float4*>(a.g[q]) + i4);
+                g[u].x += x.x; g[u].y += x.y; g[u].z += x.z; g[u].w += x.w;
+              }
+          }
+          const long long si = (i4 << 2) - L.state_off;
+          p[u] = *(reinterpret_cast<const float4*>(L.p_master) + i4);
+          if (a.kind >= 1) m[u] = *reinterpret_cast<const float4*>(L.m + si);
+          if (a.kind == 2) v[u] = *reinterpret_cast<const float4*>(L.v + si);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i4 = base + (long long)u * blockDim.x;
+          if (i4 >= e4) continue;
+          const long long si = (i4 << 2) - L.state_off;
+          float4 pp = p[u];
+          pp.x = opt_apply(s, pp.x, g[u].x, m[u].x, v[u].x);
+          pp.y = opt_apply(s, pp.y, g[u].y, m[u].y, v[u].y);
+          pp.z = opt_apply(s, pp.z, g[u].z, m[u].z, v[u].z);
+          pp.w = opt_apply(s, pp.w, g[u].w, m[u].w, v[u].w);
+          if (L.sumsq) {
+            const float gx = g[u].x * s.gs, gy = g[u].y * s.gs, gz = g[u].z * s.gs, gw = g[u].w * s.gs;
+            sq += (double)(gx * gx + gy * gy) + (double)(gz * gz + gw * gw);
+          }
+          if (a.kind >= 1) *reinterpret_cast<float4*>(L.m + si) = m[u];
+          if (a.kind == 2) *reinterpret_cast<float4*>(L.v + si) = v[u];
+          *(reinterpret_cast<float4*>(L.p_master) + i4) = pp;
+          if (a.algo == 1) {
+            if (a.p_mc_f32) multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, pp);
+          } else {
+#pragma unroll
+            for (int q = 0; q < ONO_MAX_RANKS; ++q)
+              if (q < a.nranks && a.p_out_f32[q] && a.p_out_f32[q] != L.p_master)
+                *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = pp;
+          }
+          const uint2 pb = pack_bf16x4(pp);
 #pragma unroll
           for (int q = 0; q < ONO_MAX_RANKS; ++q)
-            if (q < a.nranks && ((workers >> q) & 1u))
-              part[q] = ld_global_v4_volatile(reinterpret_cast<const float4*>(a.g[q]) + i4);
-#pragma unroll
-          for (int q = 0; q < ONO_MAX_RANKS; ++q)  // fixed rank order: run-to-run deterministic
-            if (q < a.nranks && ((workers >> q) & 1u)) {
-              g.x += part[q].x; g.y += part[q].y; g.z += part[q].z; g.w += part[q].w;
-            }
+            if (q < a.nranks && a.p_out_bf16[q])
+              *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
+          if (a.zero_grad && ((workers >> rank) & 1u))
+            *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        const long long si = (i4 << 2) - L.state_off;
-        float4 p = *(reinterpret_cast<const float4*>(L.p_master) + i4);
-        float4 m = make_float4(0.f, 0.f, 0.f, 0.f), v = m;
-        if (a.kind >= 1) m = *reinterpret_cast<const float4*>(L.m + si);
-        if (a.kind == 2) v = *reinterpret_cast<const float4*>(L.v + si);
-        p.x = opt_apply(s, p.x, g.x, m.x, v.x);
-        p.y = opt_apply(s, p.y, g.y, m.y, v.y);
-        p.z = opt_apply(s, p.z, g.z, m.z, v.z);
-        p.w = opt_apply(s, p.w, g.w, m.w, v.w);
-        if (L.sumsq) {
-          const float gx = g.x * s.gs, gy = g.y * s.gs, gz = g.z * s.gs, gw = g.w * s.gs;
-          sq += (double)(gx * gx + gy * gy) + (double)(gz * gz + gw * gw);
-        }
-        if (a.kind >= 1) *reinterpret_cast<float4*>(L.m + si) = m;
-        if (a.kind == 2) *reinterpret_cast<float4*>(L.v + si) = v;
-        *(reinterpret_cast<float4*>(L.p_master) + i4) = p;
-        if (a.algo == 1) {
-          if (a.p_mc_f32) multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, p);
-        } else {
-#pragma unroll
-          for (int q = 0; q < ONO_MAX_RANKS; ++q)
-            if (q < a.nranks && a.p_out_f32[q] && a.p_out_f32[q] != L.p_master)
-              *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = p;
-        }
-        const uint2 pb = pack_bf16x4(p);
-#pragma unroll
-        for (int q = 0; q < ONO_MAX_RANKS; ++q)
-          if (q < a.nranks && a.p_out_bf16[q])
-            *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
-        if (a.zero_grad && ((workers >> rank) & 1u))
-          *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
   }
@@ -145,8 +156,8 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
   if (threadIdx.x == 0) L.epoch[blk] = e0 + 2;
 }
 
-__global__ void __launch_bounds__(512) sync_kernel(const OnoSync a) { sync_body(a, a.rank, blockIdx.x); }
-__global__ void __launch_bounds__(512) sync_kernel_emulated(const OnoSync a) { sync_body(a, blockIdx.y, blockIdx.x); }
+__global__ void __launch_bounds__(512, 2) sync_kernel(const OnoSync a) { sync_body(a, a.rank, blockIdx.x); }
+__global__ void __launch_bounds__(512, 2) sync_kernel_emulated(const OnoSync a) { sync_body(a, blockIdx.y, blockIdx.x); }
 
 // ------------------------------------------------------------------------------------------------
 // Asynchronous parameter server: worker-driven remote read-modify-write of the owners' shards.

@@ -203,7 +203,9 @@ class GpuRank:
         self.sync_mode = mode
         self.sync_opt = opt
         n4 = self.n_pad // 4
-        self.nblocks = int(min(128, max(1, -(-n4 // (512 * 4)))))
+        # two resident 512-thread blocks per SM at most: blocks of different ranks wait on one another,
+        # so the whole grid must be co-resident (the same count on every rank)
+        self.nblocks = int(min(2 * _lib.load().ono_num_sms(), max(1, -(-n4 // (512 * 2)))))
         wmask = sum(1 << r for r in workers)
         allmask = (1 << W) - 1
         lay, win = self.layout, self.win

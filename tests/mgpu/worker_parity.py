@@ -1,0 +1,82 @@
+"""SPMD body of the multi-GPU parity test: run under torchrun, one process per GPU.
+
+Every rank trains the same small MLP through the public API on `gpu:<i>` addresses with each strategy
+and fused-kernel variant, and rank 0 compares the result with the in-process CPU oracle run of the same
+configuration (one batch per worker and epoch, so batch order cannot differ)."""
+import json
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+import orchestra  # noqa: E402
+from orchestra import Sequential, orchestrate  # noqa: E402
+from orchestra.activations import ReLU, Softmax, Tanh  # noqa: E402
+from orchestra.arch import Dense  # noqa: E402
+from orchestra.datasets import InlineDataset  # noqa: E402
+from orchestra.initialization import XavierUniform  # noqa: E402
+from orchestra.loss_fns import CrossEntropy  # noqa: E402
+from orchestra.optimizers import Adam, GradientDescent, GradientDescentWithMomentum  # noqa: E402
+from orchestra.store import BlockingStore, WildStore  # noqa: E402
+from orchestra.sync import BarrierSync, NonBlockingSync  # noqa: E402
+
+
+def main():
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world = dist.get_rank(), dist.get_world_size()
+    rng = np.random.default_rng(0)
+    rows = 48 * world
+    xs = rng.random((rows, 200), dtype=np.float32)
+    ys = np.eye(10, dtype=np.float32)[rng.integers(0, 10, rows)]
+    model = Sequential([Dense(300, XavierUniform(), Tanh()), Dense(120, XavierUniform(), ReLU(0.0)),
+                        Dense(10, XavierUniform(), Softmax())])
+    ds = lambda: InlineDataset(xs, ys, 200, 10)
+    gpu = [f"gpu:{i}" for i in range(world)]
+    cpu = [f"cpu:{i}" for i in range(world)]
+    cases = []
+    for cadence in ("step", "round"):
+        for ar in ("twoshot", "oneshot", "nvls", "nccl"):
+            cases.append((f"ar-{ar}-{cadence}", lambda a, c=cadence, m=ar: orchestra.all_reduce(
+                a, ds(), Adam(0.01), CrossEntropy(), 6, 48, seed=4, b200={"sync_every": c, "allreduce": m})))
+        cases.append((f"ps-colocated-even-{cadence}", lambda a, c=cadence: orchestra.parameter_server(
+            a, max(1, world // 2), ds(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), BarrierSync(),
+            BlockingStore(), 6, 48, seed=4, b200={"sync_every": c, "colocate": True, "sharding": "even"})))
+    if world >= 2:
+        cases.append(("ps-pure-servers-layer-round", lambda a: orchestra.parameter_server(
+            a, 1, ds(), GradientDescent(0.2), CrossEntropy(), BarrierSync(), BlockingStore(), 6, 48, seed=4)))
+        cases.append(("ps-async-wild-round", lambda a: orchestra.parameter_server(
+            a, 1, ds(), GradientDescent(0.05), CrossEntropy(), NonBlockingSync(), WildStore(), 6, 48, seed=4)))
+        cases.append(("switch-round", lambda a: orchestra.strategy_switch(
+            a, 1, ds(), Adam(0.01), CrossEntropy(), BarrierSync(), BlockingStore(), 8, 48, seed=4,
+            b200={"switch_window": 2, "switch_threshold": 10.0})))
+    report = {}
+    ok = True
+    for name, make in cases:
+        got = orchestrate(model, make(gpu)).wait(quiet=True)
+        met = got.metrics()
+        if rank == 0:
+            ref = orchestrate(model, make(cpu)).wait(quiet=True)
+            lg, lr = np.array(got.loss_history()), np.array(ref.loss_history())
+            same_len = lg.shape == lr.shape
+            dl = float(np.abs(lg - lr).max() / max(1e-9, np.abs(lr).max())) if same_len else float("inf")
+            dw = float(np.abs(got.weights_array() - ref.weights_array()).max())
+            # asynchronous pushes land in a different order on GPUs than in the oracle's rank order
+            tol_w = 0.2 if "async" in name else 5e-2
+            good = same_len and dl < 0.1 and dw < tol_w and lg[-1] < lg[0]
+            report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "nvls": met.get("nvls"), "mode": met.get("sync_mode"),
+                            "switched": met.get("switched")}
+            ok = ok and good
+        dist.barrier()
+    if rank == 0:
+        print("MGPU_REPORT " + json.dumps(report))
+        print("MGPU_OK" if ok else "MGPU_FAIL")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
