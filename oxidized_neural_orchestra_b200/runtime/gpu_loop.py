@@ -83,9 +83,13 @@ def exchange(r, values: list[float]) -> np.ndarray:
     v = torch.tensor(values, dtype=torch.float64, device=r.dev)
     if r.world == 1:
         return v.cpu().numpy().reshape(1, -1)
-    out = torch.empty(r.world * len(values), dtype=torch.float64, device=r.dev)
-    dist.all_gather_into_tensor(out, v, group=r.group)
-    return out.cpu().numpy().reshape(r.world, -1)
+    # Issued on the training stream: the collective must not start before this rank's fused kernels
+    # have retired, or the two would wait on each other for SM space across ranks.
+    with torch.cuda.stream(r.stream):
+        out = torch.empty(r.world * len(values), dtype=torch.float64, device=r.dev)
+        dist.all_gather_into_tensor(out, v.to(r.dev), group=r.group)
+        host = out.cpu()
+    return host.numpy().reshape(r.world, -1)
 
 
 def check_status(r) -> None:
@@ -132,6 +136,7 @@ def do_switch(r) -> None:
     """All-reduce -> parameter server in place: the promoted ranks adopt the ranges they will own
     (every replica already holds the full vector), optimizer state restarts, and their data is
     re-scattered to the remaining workers (node/src/router.rs:305-341, worker/src/builder.rs:165-200)."""
+    torch.cuda.synchronize(r.dev)
     acts = r.plan["switch"]["post_actions"]
     promoted = [a["rank"] for a in acts if a["action"] == "upgrade"]
     remaining = [a["rank"] for a in acts if a["action"] == "switch"]

@@ -23,11 +23,13 @@ def _norm_check(r, hist: list) -> int:
     """Feed the per-step global gradient norms gathered since the last check to the switch tracker."""
     if not hist:
         return 0
-    v = torch.stack(hist).reshape(-1)
-    if r.world > 1:
-        dist.all_reduce(v, group=r.group)
+    with torch.cuda.stream(r.stream):  # ordered after this rank's fused kernels (see gpu_loop.exchange)
+        v = torch.stack(hist).reshape(-1)
+        if r.world > 1:
+            dist.all_reduce(v, group=r.group)
+        host = v.cpu().numpy()
     decision = 0
-    for x in v.cpu().numpy():
+    for x in host:
         if r.policy.on_metric(math.sqrt(max(float(x), 0.0))) == 2:
             decision = 2
     hist.clear()

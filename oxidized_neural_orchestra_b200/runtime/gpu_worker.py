@@ -182,6 +182,7 @@ class GpuRank:
         W = self.world
         if self.algorithm == "parameter_server":
             owners = {s["rank"]: [tuple(r) for r in s["ranges"]] for s in self.plan["servers"]}
+            self.use_nvls = self.b200.get("allreduce") == "nvls"
             self._set_ownership([owners.get(r, []) for r in range(W)], self.worker_ranks, self.opt,
                                 "async" if self.async_ps else "fused", self.wild)
             return
