@@ -42,7 +42,11 @@ def main():
     for cadence in ("step", "round"):
         for ar in ("twoshot", "oneshot", "nvls", "nccl"):
             cases.append((f"ar-{ar}-{cadence}", lambda a, c=cadence, m=ar: orchestra.all_reduce(
-                a, ds(), Adam(0.01), CrossEntropy(), 6, 48, seed=4, b200={"sync_every": c, "allreduce": m})))
+                a, ds(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), 6, 48, seed=4,
+                b200={"sync_every": c, "allreduce": m})))
+        # Adam divides by sqrt(v): tf32 tiles against the f32 oracle drift faster, hence the wider bound
+        cases.append((f"ar-adam-{cadence}", lambda a, c=cadence: orchestra.all_reduce(
+            a, ds(), Adam(0.01), CrossEntropy(), 6, 48, seed=4, b200={"sync_every": c})))
         cases.append((f"ps-colocated-even-{cadence}", lambda a, c=cadence: orchestra.parameter_server(
             a, max(1, world // 2), ds(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), BarrierSync(),
             BlockingStore(), 6, 48, seed=4, b200={"sync_every": c, "colocate": True, "sharding": "even"})))
@@ -66,8 +70,8 @@ def main():
             dl = float(np.abs(lg - lr).max() / max(1e-9, np.abs(lr).max())) if same_len else float("inf")
             dw = float(np.abs(got.weights_array() - ref.weights_array()).max())
             # asynchronous pushes land in a different order on GPUs than in the oracle's rank order
-            tol_w = 0.2 if "async" in name else 5e-2
-            good = same_len and dl < 0.1 and dw < tol_w and lg[-1] < lg[0]
+            loose = "async" in name or "adam" in name or "switch" in name
+            good = same_len and dl < (0.3 if loose else 0.05) and dw < (0.2 if loose else 2e-2) and lg[-1] < lg[0]
             report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "nvls": met.get("nvls"), "mode": met.get("sync_mode"),
                             "switched": met.get("switched")}
             ok = ok and good
