@@ -461,3 +461,94 @@ extern "C" int ono_sizeof(int which) {
     default: return -1;
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free single-GPU form of the fused step (see ono_noalloc.h).
+// ------------------------------------------------------------------------------------------------
+#include "ono_noalloc.h"
+
+namespace ono {
+// Flag pad [ONO_NOALLOC_MAX_BLOCKS][ONO_MAX_RANKS] followed by the epoch words [ONO_NOALLOC_MAX_BLOCKS].
+// Zero at load time; afterwards the stamps only grow.
+static __device__ __align__(256) unsigned int g_noalloc_scratch[ONO_NOALLOC_SCRATCH_BYTES / 4];
+
+// Device address of the scratch array, looked up once per device. In host code the array's name is
+// only a handle for the runtime, never an address a kernel may be given.
+static unsigned int* noalloc_scratch_ptr() {
+  constexpr int kMaxDevices = 64;
+  static unsigned int* cache[kMaxDevices] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("no current CUDA device%s", "", 0, 0);
+    return nullptr;
+  }
+  if (!cache[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("cudaGetSymbolAddress failed: %s", cudaGetErrorString(e), 0, 0);
+      return nullptr;
+    }
+    cache[dev] = static_cast<unsigned int*>(ptr);
+  }
+  return cache[dev];
+}
+}  // namespace ono
+
+extern "C" int ono_sync_step_noalloc(const OnoNoAllocStep* s, ono_stream_t st) {
+  if (!s || !s->p || !s->g || s->n <= 0) { set_error("bad no-alloc step args%s", "", 0, 0); return -1; }
+  if (s->kind < 0 || s->kind > 2) { set_error("unknown optimizer kind%s", "", 0, 0); return -1; }
+  if (s->kind >= 1 && !s->m) { set_error("optimizer state m missing%s", "", 0, 0); return -1; }
+  if (s->kind == 2 && (!s->v || !s->adam_pows)) { set_error("adam state missing%s", "", 0, 0); return -1; }
+  if (((uintptr_t)s->p | (uintptr_t)s->g | (uintptr_t)s->m | (uintptr_t)s->v) & 15) {
+    set_error("buffers must be 16-byte aligned%s", "", 0, 0);
+    return -1;
+  }
+  if (s->nblocks > ONO_NOALLOC_MAX_BLOCKS) {
+    set_error("nblocks %s%lld exceeds the built-in scratch (max %lld blocks)", "", (long long)s->nblocks,
+              (long long)ONO_NOALLOC_MAX_BLOCKS);
+    return -2;
+  }
+  unsigned int* scratch = noalloc_scratch_ptr();
+  if (!scratch) return -3;
+  int nblocks = s->nblocks;
+  if (nblocks <= 0) {
+    const long long n4 = (s->n + 3) >> 2;
+    long long want = (n4 + 1023) / 1024;
+    const long long cap = 2LL * ono_num_sms();
+    if (want > cap) want = cap;
+    if (want > ONO_NOALLOC_MAX_BLOCKS) want = ONO_NOALLOC_MAX_BLOCKS;
+    nblocks = want < 1 ? 1 : (int)want;
+  }
+  OnoSync a;
+  memset(&a, 0, sizeof(a));
+  a.nranks = 1;
+  a.rank = 0;
+  a.algo = 0;
+  a.nblocks = nblocks;
+  a.n = s->n;
+  a.g[0] = s->g;
+  a.p_out_f32[0] = s->p;
+  a.p_out_bf16[0] = s->p_bf16;
+  a.flags[0] = scratch;
+  a.worker_mask = a.member_mask = 1u;
+  a.n_workers = s->n_workers < 1 ? 1 : s->n_workers;
+  a.kind = s->kind;
+  a.lr = s->lr; a.mu = s->mu; a.b1 = s->b1; a.b2 = s->b2; a.eps = s->eps;
+  a.divide = a.n_workers > 1 ? 1 : 0;
+  a.timeout_ns = 2000000000ull;
+  OnoSyncLocal& L = a.loc[0];
+  L.p_master = s->p;
+  L.m = s->m;
+  L.v = s->v;
+  L.state_off = 0;
+  L.adam_pows = s->adam_pows;
+  L.epoch = scratch + (size_t)ONO_NOALLOC_MAX_BLOCKS * ONO_MAX_RANKS;
+  L.sumsq = s->sumsq;
+  L.status = s->status;
+  L.n_ranges = 1;
+  L.ranges[0].begin = 0;
+  L.ranges[0].end = s->n;
+  sync_kernel<<<nblocks, 512, 0, (cudaStream_t)st>>>(a);
+  return check_launch("sync_step_noalloc");
+}
