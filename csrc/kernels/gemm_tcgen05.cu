@@ -45,6 +45,7 @@ struct GemmDev {
   OnoEpilogue epi;
   int* status;
   unsigned long long timeout_ns;
+  int tma_out;  // 0: thread stores only; 1: out_f32 leaves through a TMA store; 2: out_bf16 does
 };
 
 template <int BN>
@@ -60,7 +61,7 @@ __device__ __forceinline__ void fail(const GemmDev& p, volatile int* abort_flag,
 
 // Processes 32 consecutive columns [n0, n0+32) of row m held in v[].
 __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[32], int m, int n0,
-                                               int M, int N) {
+                                               int M, int N, int tma_out) {
   const bool row_ok = m < M;
   const int ncols = min(32, N - n0);
   const bool full = ncols == 32;
@@ -144,7 +145,7 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
       }
     }
   }
-  if (row_ok && e.out_f32) {
+  if (row_ok && e.out_f32 && tma_out != 1) {
     float* o = e.out_f32 + row_off;
     if (full) {
 #pragma unroll
@@ -164,7 +165,7 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
       }
     }
   }
-  if (row_ok && e.out_bf16) {
+  if (row_ok && e.out_bf16 && tma_out != 2) {
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(e.out_bf16) + row_off;
     if (full) {
 #pragma unroll
@@ -202,7 +203,7 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
 template <int ESIZE, int BN>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmDev p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmDev p) {
   constexpr int BM = 128;
   constexpr int BK = 128 / ESIZE;      // one 128-byte swizzle row of K per stage
   constexpr int UMMA_K = 32 / ESIZE;   // 8 for tf32, 16 for bf16
@@ -213,6 +214,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  // two 16 KB output staging tiles (128 rows x 128 B) behind the operand ring, for TMA stores
+  uint8_t* cstage = smem + (size_t)STAGES * STAGE_BYTES;
 
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
@@ -242,6 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (p.tma_out) tma_prefetch_desc(&tmC);
   }
   if (warp == 5) {
     tmem_alloc(&tmem_base_smem, TMEM_COLS);
@@ -344,18 +348,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue warps 0..3 (TMEM lanes 32*warp .. 32*warp+31) ----------------
     int t = 0;
     bool ok = true;
+    uint32_t cchunk = 0;  // staged chunks so far: alternates the two staging tiles across tiles too
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
       const int m0 = (tile % num_m) * BM;
       const int n0 = (tile / num_m) * BN;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
-      if (!mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget)) {
-        if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
+      const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget);
+      // The four epilogue warps must agree before they meet at named barriers below.
+      uint32_t all_got;
+      asm volatile(
+          "{\n\t.reg .pred pin, pout;\n\tsetp.ne.u32 pin, %1, 0;\n\t"
+          "bar.red.and.pred pout, 1, 128, pin;\n\tselp.u32 %0, 1, 0, pout;\n\t}"
+          : "=r"(all_got)
+          : "r"((uint32_t)got)
+          : "memory");
+      if (!all_got) {
+        if (lane == 0 && !got) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
         ok = false;
         break;
       }
       tc_fence_after();
-      const int m = m0 + warp * 32 + lane;
+      const int row = warp * 32 + lane;
+      const int m = m0 + row;
       const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -367,11 +382,48 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        epilogue_chunk(p.epi, v, m, nc, p.M, p.N);
+        epilogue_chunk(p.epi, v, m, nc, p.M, p.N, p.tma_out);
+        if (p.tma_out) {
+          // registers -> swizzled staging tile -> one TMA store per 128 x 32 chunk; the TMA unit
+          // clips rows >= M and columns >= N
+          uint8_t* stage = cstage + (size_t)(cchunk & 1u) * 16384u;
+          if (threadIdx.x == 0) tma_store_wait_read<1>();  // the store that last read this tile is done
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (p.tma_out == 1) {
+            uint8_t* rp = stage + row * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(rp + ((j ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            uint8_t* rp = stage + row * 64;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+              uint4 pk;
+              pk.x = *reinterpret_cast<uint32_t*>(&t0);
+              pk.y = *reinterpret_cast<uint32_t*>(&t1);
+              pk.z = *reinterpret_cast<uint32_t*>(&t2);
+              pk.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(rp + ((j ^ ((row >> 1) & 3)) << 4)) = pk;
+            }
+          }
+          fence_proxy_async_smem();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 0) {
+            tma_store_2d(&tmC, stage, nc, m0);
+            tma_store_commit();
+          }
+          ++cchunk;
+        }
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty_bar[buf]);
     }
+    if (p.tma_out && threadIdx.x == 0) tma_store_wait_all<0>();  // global writes done before exit
   }
 
   tc_fence_before();
@@ -428,6 +480,23 @@ int encode_map_2d(CUtensorMap* map, const void* base, int esize, long long rows,
   return 0;
 }
 
+// Output tile map for the TMA-store epilogue: box = {32 columns, 128 rows}; the 128-byte (f32) or
+// 64-byte (bf16) rows use the matching swizzle so that the staging writes are bank-conflict free.
+static int encode_out_map(CUtensorMap* map, const void* base, int esize, long long rows, long long cols, long long ld) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled unavailable%s", ""); return -2; }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld * esize)};
+  cuuint32_t box[2] = {32u, 128u};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  esize == 4 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (output) failed (%s%lld)", "", (long long)r); return -4; }
+  return 0;
+}
+
 // Fills the device-side operand description and encodes the operand's tensor map.
 static int make_operand(OperandDev* od, CUtensorMap* map, const void* ptr, int esize, int major,
                         int MN, int K, int ld, int tile_mn) {
@@ -467,10 +536,10 @@ static int num_sms() {
 }
 
 template <int ESIZE, int BN>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDev& p, int max_ctas,
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmDev& p, int max_ctas,
                   cudaStream_t stream) {
   constexpr int STAGES = TileCfg<BN>::STAGES;
-  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN * 128) + 1024;
+  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN * 128) + 2 * 16384 + 1024;
   static bool attr_set = false;
   auto kern = gemm_tcgen05_kernel<ESIZE, BN>;
   if (!attr_set) {
@@ -481,7 +550,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmDev& p
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
   int grid = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > tiles) grid = tiles;
-  kern<<<grid, 192, smem, stream>>>(ta, tb, p);
+  kern<<<grid, 192, smem, stream>>>(ta, tb, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gemm launch: %s", cudaGetErrorString(e)); return -7; }
   return 0;
@@ -532,16 +601,26 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   if (rc) return rc;
   rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, bn);
   if (rc) return rc;
+  // One row-major output may leave through TMA stores (coalesced, off the LSU path): the f32 output
+  // when it is not accumulated into, else the bf16 output.
+  CUtensorMap tc;
+  memset(&tc, 0, sizeof(tc));
+  p.tma_out = 0;
+  if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0) {
+    if (encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out) == 0) p.tma_out = 1;
+  } else if (e.out_bf16 && ((uintptr_t)e.out_bf16 & 15) == 0) {
+    if (encode_out_map(&tc, e.out_bf16, 2, g->M, g->N, e.ld_out) == 0) p.tma_out = 2;
+  }
   const uint32_t fmt = g->dtype == ONO_TF32 ? 2u : 1u;  // TF32 / BF16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
             ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
   if (esize == 4) {
-    if (bn == 32) return launch<4, 32>(ta, tb, p, g->max_ctas, stream);
-    if (bn == 128) return launch<4, 128>(ta, tb, p, g->max_ctas, stream);
-    return launch<4, 256>(ta, tb, p, g->max_ctas, stream);
+    if (bn == 32) return launch<4, 32>(ta, tb, tc, p, g->max_ctas, stream);
+    if (bn == 128) return launch<4, 128>(ta, tb, tc, p, g->max_ctas, stream);
+    return launch<4, 256>(ta, tb, tc, p, g->max_ctas, stream);
   }
-  if (bn == 32) return launch<2, 32>(ta, tb, p, g->max_ctas, stream);
-  if (bn == 128) return launch<2, 128>(ta, tb, p, g->max_ctas, stream);
-  return launch<2, 256>(ta, tb, p, g->max_ctas, stream);
+  if (bn == 32) return launch<2, 32>(ta, tb, tc, p, g->max_ctas, stream);
+  if (bn == 128) return launch<2, 128>(ta, tb, tc, p, g->max_ctas, stream);
+  return launch<2, 256>(ta, tb, tc, p, g->max_ctas, stream);
 }
