@@ -135,10 +135,14 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
                 *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = pp;
           }
           const uint2 pb = pack_bf16x4(pp);
+          if (a.algo == 1 && a.p_mc_bf16) {
+            multimem_st_bf16x4(reinterpret_cast<uint2*>(a.p_mc_bf16) + i4, pb);
+          } else {
 #pragma unroll
-          for (int q = 0; q < ONO_MAX_RANKS; ++q)
-            if (q < a.nranks && a.p_out_bf16[q])
-              *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
+            for (int q = 0; q < ONO_MAX_RANKS; ++q)
+              if (q < a.nranks && a.p_out_bf16[q])
+                *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
+          }
           if (a.zero_grad && ((workers >> rank) & 1u))
             *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
         }

@@ -73,6 +73,11 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (j < ncols) v[j] += __ldg(e.bias + n0 + j);
+  } else if (e.bias_bf16) {
+    const __nv_bfloat16* bb = reinterpret_cast<const __nv_bfloat16*>(e.bias_bf16) + n0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (j < ncols) v[j] += __bfloat162float(bb[j]);
   }
   const size_t row_off = (size_t)m * e.ld_out + n0;
   if (row_ok && e.pre_f32) {

@@ -29,6 +29,7 @@ typedef struct OnoEpilogue {
   float* pre_f32;            // [M, ld_out] pre-activation, optional
   void* pre_bf16;            // [M, ld_out] pre-activation, optional
   const float* bias;         // [N], optional
+  const void* bias_bf16;     // [N] bias in bf16, optional (used when bias is null)
   const float* aux_f32;      // [M, ld_aux], optional (stored activation or pre-activation)
   const void* aux_bf16;      // same in bf16, optional
   int ld_out, ld_outT, ld_aux;
@@ -168,7 +169,7 @@ typedef struct OnoSync {
   float* p_out_f32[ONO_MAX_RANKS];           // every rank's f32 parameter window (null = not wanted)
   void* p_out_bf16[ONO_MAX_RANKS];           // every rank's bf16 parameter window (null = not wanted)
   unsigned int* flags[ONO_MAX_RANKS];        // every rank's signal pad [nblocks][ONO_MAX_RANKS]
-  const float* g_mc; float* p_mc_f32; void* p_mc_bf16;   // multicast addresses (algo 1)
+  const float* g_mc; float* p_mc_f32; void* p_mc_bf16;   // multicast addresses (algo 1); null = per-peer stores
   unsigned int worker_mask;                  // ranks whose gradients are summed
   unsigned int member_mask;                  // ranks taking part in the barriers
   const unsigned int* live_mask;             // optional device word overriding member_mask (shrink)

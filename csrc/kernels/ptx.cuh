@@ -269,4 +269,9 @@ __device__ __forceinline__ void multimem_st_v4(float4* mc_ptr, float4 v) {
                : "memory");
 }
 
+// NVLS: four bf16 values (two packed 32-bit words) delivered to every GPU of the multicast group.
+__device__ __forceinline__ void multimem_st_bf16x4(void* mc_ptr, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1,%2};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y) : "memory");
+}
+
 }  // namespace ono

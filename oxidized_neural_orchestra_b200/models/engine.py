@@ -58,7 +58,8 @@ class GpuEngine:
 
     def __init__(self, layers: list[dict], *, batch_size: int, tile_dtype: str, loss: str,
                  params: torch.Tensor, grads: torch.Tensor, params_bf16: torch.Tensor | None = None,
-                 leaky_relu_exact: bool = True, device=None):
+                 leaky_relu_exact: bool = True, device=None, bias_from_shadow: bool = False):
+        self.bias_from_shadow = bias_from_shadow
         if tile_dtype not in ("tf32", "bf16"):
             raise ValueError("tile_dtype must be 'tf32' or 'bf16'")
         self.dev = device or params.device
@@ -136,8 +137,17 @@ class GpuEngine:
         pl = self.plans[l]
         return self.params[pl.w_off:pl.w_off + pl.in_features * pl.out_features].view(pl.in_features, pl.out_features)
 
+    @property
+    def needs_f32_params(self) -> bool:
+        """False when every operand the engine reads comes from the bf16 shadow (weights used in place
+        and biases read as bf16): then only the owner of a range needs its f32 master."""
+        return not (self.bf16 and self.bias_from_shadow and self.params_bf16 is not None
+                    and not any(self.w_copy_needed))
+
     def b_view(self, l: int) -> torch.Tensor:
         pl = self.plans[l]
+        if not self.needs_f32_params:
+            return self.params_bf16[pl.b_off:pl.b_off + pl.out_features]
         return self.params[pl.b_off:pl.b_off + pl.out_features]
 
     def gw_view(self, l: int) -> torch.Tensor:

@@ -81,7 +81,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
             e.pre_f32 = pre.data_ptr()
         else:
             e.pre_bf16 = pre.data_ptr()
-    e.bias = _ptr(bias)
+    if bias is not None and bias.dtype == torch.bfloat16:
+        e.bias_bf16 = bias.data_ptr()
+    else:
+        e.bias = _ptr(bias)
     if aux is not None:
         if aux.dtype == torch.float32:
             e.aux_f32 = aux.data_ptr()

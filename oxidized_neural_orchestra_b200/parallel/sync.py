@@ -61,14 +61,15 @@ def fill_sync(s: "_lib.OnoSync", *, nranks: int, rank: int, n: int, nblocks: int
               g_ptrs: list[int], p_f32_ptrs: list[int | None], p_bf16_ptrs: list[int | None],
               flag_ptrs: list[int], worker_mask: int, member_mask: int, n_workers: int,
               opt: OptimizerCfg, divide: bool = True, timeout_ns: int = 2_000_000_000,
-              g_mc: int | None = None, p_mc_f32: int | None = None, live_mask: int | None = None) -> None:
+              g_mc: int | None = None, p_mc_f32: int | None = None, p_mc_bf16: int | None = None,
+              live_mask: int | None = None) -> None:
     s.nranks, s.rank, s.algo, s.nblocks, s.n = nranks, rank, algo, nblocks, n
     for r in range(nranks):
         s.g[r] = g_ptrs[r]
         s.p_out_f32[r] = p_f32_ptrs[r]
         s.p_out_bf16[r] = p_bf16_ptrs[r]
         s.flags[r] = flag_ptrs[r]
-    s.g_mc, s.p_mc_f32 = g_mc, p_mc_f32
+    s.g_mc, s.p_mc_f32, s.p_mc_bf16 = g_mc, p_mc_f32, p_mc_bf16
     s.worker_mask, s.member_mask, s.live_mask = worker_mask, member_mask, live_mask
     s.n_workers = n_workers
     s.kind = OPT_KIND[opt.kind]

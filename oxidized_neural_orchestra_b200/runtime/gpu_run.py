@@ -143,7 +143,9 @@ def run(r) -> dict:
     L.check_status(r)
     # final parameters: the owners' ranges are authoritative (session.rs:293-359); all-reduce replicas
     # are identical and rank 0's copy is taken (session.rs:371-412)
-    if r.sync_mode == "async" or (r.algorithm != "all_reduce" and r.world > 1):
+    # (with bf16 tiles only the owner of a range holds its up-to-date f32 master, so the owners'
+    # ranges are collected whenever ownership is partitioned; one-shot replicates ownership)
+    if r.world > 1 and r.sync_mode != "oneshot":
         tmp = torch.zeros_like(r.C)
         for b, e in r.own[r.rank]:
             tmp[b:e] = r.C[b:e]

@@ -152,7 +152,8 @@ class GpuRank:
             self.g = torch.zeros_like(self.C)
         self.engine = GpuEngine(layers, batch_size=B, tile_dtype=self.tile, loss=self.loss_kind, params=self.W,
                                 grads=self.g, params_bf16=self.shadow,
-                                leaky_relu_exact=self.b200.get("leaky_relu_exact", True))
+                                leaky_relu_exact=self.b200.get("leaky_relu_exact", True),
+                                bias_from_shadow=self.cadence == "step")
         self.feeder = BatchFeeder(xs, ys, self.x_size, self.y_size, B, self.dev, self.seed,
                                   device_resident=self.b200.get("data", "host") == "device")
         self.loss_pin = [torch.zeros(1, dtype=torch.float64).pin_memory() for _ in range(2)]
@@ -182,13 +183,16 @@ class GpuRank:
         W = self.world
         if self.algorithm == "parameter_server":
             owners = {s["rank"]: [tuple(r) for r in s["ranges"]] for s in self.plan["servers"]}
-            self.use_nvls = self.b200.get("allreduce") == "nvls"
+            self.use_nvls = self.b200.get("allreduce", "auto") in ("nvls", "auto")
             self._set_ownership([owners.get(r, []) for r in range(W)], self.worker_ranks, self.opt,
                                 "async" if self.async_ps else "fused", self.wild)
             return
         mode = self.b200.get("allreduce", "auto")
         if mode == "auto":
-            mode = "oneshot" if (self.n_pad * 4 <= 256 * 1024 and W > 1) else "twoshot"
+            if self.n_pad * 4 <= 256 * 1024 and W > 1:
+                mode = "oneshot"
+            else:  # in-switch reduction whenever the fabric offers a multicast address
+                mode = "nvls" if (self.win.mc_ptr and W > 1) else "twoshot"
         if mode == "oneshot":
             ranges = [[(0, self.n_pad)] for _ in range(W)]
         else:
@@ -211,10 +215,19 @@ class GpuRank:
         allmask = (1 << W) - 1
         lay, win = self.layout, self.win
         dest = set(workers) | {0}
+        # f32 parameters travel to other ranks only if somebody reads them there: with bf16 tiles in
+        # step cadence every consumer reads the bf16 shadow, and the owner keeps the only f32 master
+        engines_need_f32 = self.cadence != "step" or self.tile != "bf16" or (
+            self.engine is not None and self.engine.needs_f32_params)
+        if W > 1 and self.tile == "bf16" and self.cadence == "step":
+            flag = torch.tensor([1.0 if engines_need_f32 else 0.0], device=self.dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
+            engines_need_f32 = bool(flag.item() > 0)
+        self.f32_everywhere = engines_need_f32
         if mode in ("fused", "oneshot"):
             s = _lib.OnoSync()
             oneshot = mode == "oneshot"
-            pf = [p if (r in dest and not oneshot) or r == self.rank else None
+            pf = [p if (r in dest and not oneshot and engines_need_f32) or r == self.rank else None
                   for r, p in enumerate(win.peer_ptrs(lay.offset("params")))]
             if self.tile == "bf16":
                 pb = [p if (r in dest and not oneshot) or r == self.rank else None
@@ -226,7 +239,9 @@ class GpuRank:
                         g_ptrs=win.peer_ptrs(lay.offset("grads")), p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
-                        g_mc=win.mc(lay.offset("grads")) or None, p_mc_f32=win.mc(lay.offset("params")) or None)
+                        g_mc=win.mc(lay.offset("grads")) or None,
+                        p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
+                        p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
                          v=self.v_loc.data_ptr(), state_off=0, adam_pows=self.adam_pows.data_ptr(),
                          epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
