@@ -228,14 +228,31 @@ class GpuEngine:
         ew.loss_backward(lg, y[:nrows, :C], **kw)
         return 1
 
-    def backward(self, nrows: int, accumulate: bool = False, stream=None) -> int:
-        """dgrad + wgrad + bias-grad for every layer; gradients land in the flat gradient vector."""
+    def backward(self, nrows: int, accumulate: bool = False, stream=None, after_layer=None) -> int:
+        """dgrad + wgrad + bias-grad for every layer; gradients land in the flat gradient vector.
+
+        Per layer the input gradient is computed first, so that nothing reads the layer's weights once
+        its own gradient is complete: ``after_layer(l)`` may then start synchronising (and overwriting)
+        that layer's parameters while the layers below are still running."""
         L, n = self.plans, 0
         beta = 1.0 if accumulate else 0.0
         for l in range(len(L) - 1, -1, -1):
             pl = L[l]
             i, o = pl.in_features, pl.out_features
             d_out = self.d[l + 1][:nrows, :o]
+            if l > 0:
+                # dgrad through the previous layer's activation: d_{l} = (d_{l+1} W^T) * act'(a_l)
+                prev = L[l - 1]
+                stored = self.zpre[l] if prev.act == "gelu" else self.a[l]
+                kw = dict(status=self.status, stream=stream)
+                if prev.act is not None:
+                    kw.update(aux=stored[:nrows, :i], dact=prev.act, dact_param=prev.act_param,
+                              relu_quirk=self.relu_quirk)
+                if self.bf16:
+                    gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
+                else:
+                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], out_t=self.dt[l][:, :nrows], **kw)
+                n += 1
             # wgrad: dW[in,out] = A_{l}^T d
             tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
             wbeta = beta if self.gw_tmp[l] is None else 0.0
@@ -254,26 +271,15 @@ class GpuEngine:
                 n += 1
             ew.colsum(d_out, self.gb_view(l), beta=beta, stream=stream)
             n += 1
-            if l == 0:
-                break
-            # dgrad through the previous layer's activation: d_{l} = (d_{l+1} W^T) * act'(a_l)
-            prev = L[l - 1]
-            stored = self.zpre[l] if prev.act == "gelu" else self.a[l]
-            kw = dict(status=self.status, stream=stream)
-            if prev.act is not None:
-                kw.update(aux=stored[:nrows, :i], dact=prev.act, dact_param=prev.act_param,
-                          relu_quirk=self.relu_quirk)
-            if self.bf16:
-                gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
-            else:
-                gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], out_t=self.dt[l][:, :nrows], **kw)
-            n += 1
+            if after_layer is not None:
+                n += after_layer(l) or 0
         return n
 
-    def step(self, x: torch.Tensor, y: torch.Tensor, nrows: int, idx=None, accumulate=False, stream=None) -> int:
+    def step(self, x: torch.Tensor, y: torch.Tensor, nrows: int, idx=None, accumulate=False, stream=None,
+             after_layer=None) -> int:
         """load -> forward -> loss -> backward. Returns the number of kernels launched."""
         n = self.load_batch(x, y, nrows, idx, stream)
         n += self.forward(nrows, stream)
         n += self.loss_backward(nrows, stream)
-        n += self.backward(nrows, accumulate, stream)
+        n += self.backward(nrows, accumulate, stream, after_layer)
         return n

@@ -30,6 +30,28 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
     f, e = r.feeder, r.engine
     e.loss_sum.zero_()
     n = 1
+    if with_sync and r.buckets:
+        # bucketed: each layer's gradients are synchronised on the communication stream as soon as
+        # they exist, while backward continues below that layer
+        if r.sync_opt.kind == "adam":
+            ew.adam_tick(r.adam_pows, r.sync_opt.b1, r.sync_opt.b2, stream=st)
+            n += 1
+        comm = r.comm_stream
+
+        def after_layer(l):
+            k = 0
+            for bk in r.bucket_after.get(l, ()):
+                ev = torch.cuda.Event()
+                ev.record(st)
+                comm.wait_event(ev)
+                S.launch_sync(bk, stream=comm)
+                k += 1
+            return k
+
+        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st, after_layer=after_layer)
+        st.wait_stream(comm)
+        n += e.refresh(stream=st)
+        return n
     n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
     if r.cadence == "round":
         # sequential.rs:129-141: stateless SGD on the working copy, residual += grad
@@ -71,7 +93,13 @@ def run_batch(r, slot: int, nrows: int) -> None:
 def server_step(r) -> None:
     """A pure server rank takes part in the synchronisation only."""
     with torch.cuda.stream(r.stream):
-        r._launch_sync(r.G, r.stream)
+        if r.buckets:  # the same launches, in the same order, as the workers issue
+            if r.sync_opt.kind == "adam":
+                ew.adam_tick(r.adam_pows, r.sync_opt.b1, r.sync_opt.b2, stream=r.stream)
+            for _, bk in r.buckets:
+                S.launch_sync(bk, stream=r.stream)
+        else:
+            r._launch_sync(r.G, r.stream)
         ev = torch.cuda.Event(enable_timing=True)
         ev.record(r.stream)
     r.step_events.append(ev)

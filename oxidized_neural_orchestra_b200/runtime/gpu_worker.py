@@ -49,6 +49,7 @@ class GpuRank:
         self.step_wall: list[float] = []
         self.switched = False
         self.stream = torch.cuda.Stream(device=device)
+        self.comm_stream = torch.cuda.Stream(device=device)
         wspec = plan["workers"][self.widx if self.widx is not None else 0]["spec"]
         self.trainer = wspec["trainer"]
         self.max_epochs = self.trainer["max_epochs"]
@@ -204,6 +205,7 @@ class GpuRank:
     def _set_ownership(self, ranges, workers, opt, mode, wild):
         W = self.world
         self.own = snap_ranges(ranges, self.n_pad)
+        self.buckets, self.bucket_after = [], {}
         self.sync_workers = list(workers)
         self.sync_mode = mode
         self.sync_opt = opt
@@ -248,6 +250,7 @@ class GpuRank:
                          sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
                          status=self.sync_status.data_ptr())
             self.sync_struct = s
+            self._build_buckets()
         elif mode == "async":
             a = _lib.OnoPsAsync()
             a.nranks, a.rank, a.nblocks = W, self.rank, self.nblocks
@@ -270,6 +273,55 @@ class GpuRank:
         elif mode == "ring":
             if "acc" not in lay.regions:
                 raise RuntimeError("ring all-reduce needs the accumulation window (set b200.allreduce before start)")
+
+    def _build_buckets(self) -> None:
+        """Split the fused synchronisation into per-layer buckets, in backward order, so that a bucket
+        can run on the communication stream as soon as its layers' gradients exist while the layers
+        below are still in backward (the reference exchanges only after the whole round:
+        worker/src/workers/all_reduce.rs:114-133).
+
+        A float4 group that straddles two layers goes with the lower layer, whose gradient is the last
+        of the two to be produced."""
+        import os
+
+        self.buckets = []           # [(launch_after_layer, OnoSync)] in launch order
+        self.bucket_after: dict[int, list] = {}
+        # On one GPU the exchange is a pure HBM pass that only competes with the (equally HBM-bound)
+        # weight-gradient GEMMs: measured slower when overlapped, so buckets are a multi-GPU default.
+        default = "1" if self.world > 1 else "0"
+        if (self.sync_mode != "fused" or self.cadence != "step" or os.environ.get("ONO_OVERLAP", default) == "0"):
+            return
+        up4 = lambda x: (x + 3) // 4 * 4
+        layers = [l for l in self.plan["layers"] if l["n_params"] > 0]
+        min_elems = 4 << 20
+        sms = _lib.load().ono_num_sms()
+        pending_end = self.n_pad
+        cur_end = None
+        for idx in range(len(layers) - 1, -1, -1):
+            l = layers[idx]
+            begin = 0 if idx == 0 else up4(l["offset"])
+            if cur_end is None:
+                cur_end = pending_end
+            if cur_end - begin >= min_elems or idx == 0:
+                if cur_end > begin:
+                    s = _lib.OnoSync.from_buffer_copy(self.sync_struct)
+                    mine = []
+                    for b, e in self.own[self.rank]:
+                        lo, hi = max(b, begin), min(e, cur_end)
+                        if hi > lo:
+                            mine.append((lo, hi))
+                    loc = s.loc[self.rank]
+                    loc.n_ranges = len(mine)
+                    for i, (b, e) in enumerate(mine):
+                        loc.ranges[i].begin, loc.ranges[i].end = b, e
+                    # one block per SM at most: these kernels share the SMs with the running GEMMs
+                    owners = max(1, sum(1 for r in self.own if r))
+                    s.nblocks = int(min(sms, max(1, -(-((cur_end - begin) // 4 // owners) // (512 * 2)))))
+                    entry = (l["index"], s)
+                    self.buckets.append(entry)
+                    self.bucket_after.setdefault(l["index"], []).append(s)
+                pending_end = begin
+                cur_end = None
 
     def _launch_sync(self, g_tensor: torch.Tensor, stream) -> int:
         """One synchronisation of `g_tensor` (the window's gradient region) into the parameters."""
