@@ -45,6 +45,7 @@ struct GemmDev {
   OnoEpilogue epi;
   int* status;
   unsigned long long timeout_ns;
+  int split_k;  // > 1: K is split over that many work items per tile, partials added with atomics
   int tma_out;  // 0: thread stores only; 1: out_f32 leaves through a TMA store; 2: out_bf16 does
 };
 
@@ -266,6 +267,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int total_tiles = num_m * num_n;
   const int KB = (p.K + BK - 1) / BK;
   const uint64_t budget = p.timeout_ns;
+  // split-K: a work item is (tile, split); split s reduces k-blocks [s*KB_PER, min(KB, (s+1)*KB_PER))
+  // and adds its partial product to the output with atomics (the host guarantees no split is empty).
+  const int SPLITS = p.split_k > 1 ? p.split_k : 1;
+  const int KB_PER = (KB + SPLITS - 1) / SPLITS;
+  const int total_work = total_tiles * SPLITS;
 
   if (warp == 4) {
     if (lane == 0) {
@@ -273,10 +279,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+        const int tile = work / SPLITS, split = work % SPLITS;
         const int m0 = (tile % num_m) * BM;
         const int n0 = (tile / num_m) * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        const int kb0 = split * KB_PER, kb1 = min(KB, kb0 + KB_PER);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abortp, budget)) {
             fail(p, abortp, ONO_ERR_TIMEOUT_EMPTY);
             ok = false;
@@ -312,7 +320,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t phase = 0;
       int t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x, ++t) {
+        const int split = work % SPLITS;
+        const int kb0 = split * KB_PER, kb1 = min(KB, kb0 + KB_PER);
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         if (!mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1u, abortp, budget)) {
@@ -322,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, budget)) {
             fail(p, abortp, ONO_ERR_TIMEOUT_FULL);
             ok = false;
@@ -337,8 +347,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 make_smem_desc_sw128(a_addr + k * p.a.kstep_bytes, p.a.lbo_bytes, p.a.sbo_bytes);
             const uint64_t bdesc =
                 make_smem_desc_sw128(b_addr + k * p.b.kstep_bytes, p.b.lbo_bytes, p.b.sbo_bytes);
-            if (ESIZE == 4) umma_tf32(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
-            else umma_f16(d_tmem, adesc, bdesc, p.idesc, (kb | k) != 0);
+            if (ESIZE == 4) umma_tf32(d_tmem, adesc, bdesc, p.idesc, (kb != kb0) || (k != 0));
+            else umma_f16(d_tmem, adesc, bdesc, p.idesc, (kb != kb0) || (k != 0));
           }
           umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -354,7 +364,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int t = 0;
     bool ok = true;
     uint32_t cchunk = 0;  // staged chunks so far: alternates the two staging tiles across tiles too
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+    for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x, ++t) {
+      const int tile = work / SPLITS;
       const int m0 = (tile % num_m) * BM;
       const int n0 = (tile / num_m) * BN;
       const int buf = t & 1;
@@ -387,6 +398,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (SPLITS > 1) {
+          // partial product of one K range: accumulate into the (pre-zeroed) f32 output
+          if (m < p.M && p.epi.out_f32) {
+            float* o = p.epi.out_f32 + (size_t)m * p.epi.ld_out + nc;
+            const int ncols = min(32, p.N - nc);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) atomicAdd(o + j, v[j] * p.epi.alpha);
+          }
+          continue;
+        }
         epilogue_chunk(p.epi, v, m, nc, p.M, p.N, p.tma_out);
         if (p.tma_out) {
           // registers -> swizzled staging tile -> one TMA store per 128 x 32 chunk; the TMA unit
@@ -552,7 +574,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return -6; }
     attr_set = true;
   }
-  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * (p.split_k > 1 ? p.split_k : 1);
   int grid = max_ctas > 0 ? max_ctas : num_sms();
   if (grid > tiles) grid = tiles;
   kern<<<grid, 192, smem, stream>>>(ta, tb, tc, p);
@@ -606,12 +628,34 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   if (rc) return rc;
   rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, bn);
   if (rc) return rc;
+  // split-K (g->split_k > 1, or 0 = automatic for tall-K problems with few output tiles): only the
+  // plain accumulate-into-f32 epilogue is supported, and the caller zeroes the output first.
+  {
+    const int BKe = 128 / esize;
+    const int KBh = (g->K + BKe - 1) / BKe;
+    const long long tiles0 = (long long)((g->M + 127) / 128) * ((g->N + bn - 1) / bn);
+    int sk = g->split_k;
+    if (sk > KBh) sk = KBh;
+    if (sk > 1) {
+      const int per = (KBh + sk - 1) / sk;
+      sk = (KBh + per - 1) / per;  // no empty split
+      if (!e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || e.bias || e.bias_bf16 ||
+          e.act != ACT_NONE || e.dact != ACT_NONE || e.beta != 0.0f) {
+        set_error("split-K supports a plain f32 output only%s", "");
+        return -1;
+      }
+    }
+    p.split_k = sk > 1 ? sk : 1;
+    (void)tiles0;
+  }
   // One row-major output may leave through TMA stores (coalesced, off the LSU path): the f32 output
   // when it is not accumulated into, else the bf16 output.
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_out = 0;
-  if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0) {
+  if (p.split_k > 1) {
+    // atomics path, no TMA store
+  } else if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0) {
     if (encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out) == 0) p.tma_out = 1;
   } else if (e.out_bf16 && ((uintptr_t)e.out_bf16 & 15) == 0) {
     if (encode_out_map(&tc, e.out_bf16, 2, g->M, g->N, e.ld_out) == 0) p.tma_out = 2;

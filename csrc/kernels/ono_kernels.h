@@ -56,6 +56,8 @@ typedef struct OnoGemm {
   int a_major, b_major;
   int bn;          // tile N: 0 = auto, else 32 / 128 / 256
   int max_ctas;    // 0 = one per SM
+  int split_k;     // > 1: split K over that many CTAs per tile; out_f32 must be zero on entry and is
+                   //      accumulated with atomics (plain f32 output only). 0 / 1 = off
   OnoEpilogue epi;
   int* status;     // device int, set non-zero on an in-kernel timeout; may be null
 } OnoGemm;
@@ -128,6 +130,24 @@ typedef struct OnoRows {
   int ld_dst, ld_dstT;
 } OnoRows;
 int ono_rows(const OnoRows* r, ono_stream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Convolution / pooling helpers around the GEMM (conv.cu). Image activations are pixel-major
+// matrices [B*H*W, ld]; dtype 0 = f32, 1 = bf16. K is the square kernel (conv) or filter (pool) size.
+// ---------------------------------------------------------------------------------------------
+typedef struct OnoConvGeom { int B, C, H, W, K, S, P, OH, OW; } OnoConvGeom;
+int ono_im2col(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* cols, int ld_cols, void* colsT,
+               int ld_colsT, ono_stream_t stream);
+int ono_col2im(const OnoConvGeom* g, int dtype, const void* dcols, int ld_dcols, const void* aux, int ld_aux, int dact,
+               float dact_param, int relu_quirk, void* dx, int ld_dx, void* dxT, int ld_dxT, ono_stream_t stream);
+int ono_pool_fwd(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* y, int ldy, void* yT, int ld_yT, int* arg,
+                 int act, float act_param, ono_stream_t stream);
+int ono_pool_bwd(const OnoConvGeom* g, int dtype, const void* d, int ldd, const void* y, int ldy, const int* arg, int act,
+                 float act_param, int relu_quirk, float* dx, int ld_dx, ono_stream_t stream);
+int ono_nchw_flat(int dtype, int B, int C, int HW, int to_flat, void* img, int ld_img, void* flat, int ld_flat, void* outT,
+                  int ld_outT, const void* aux, int ld_aux, int dact, float dact_param, int relu_quirk, ono_stream_t stream);
+int ono_finish_delta(int dtype, long long rows, int C, const float* src, int ld_src, const void* aux, int ld_aux, int dact,
+                     float dact_param, int relu_quirk, void* dst, int ld_dst, void* dstT, int ld_dstT, ono_stream_t stream);
 
 // ---------------------------------------------------------------------------------------------
 // Fused gradient synchronisation over NVLink peer memory ("symmetric windows": the same buffer

@@ -184,7 +184,11 @@ class GpuRank:
         W = self.world
         if self.algorithm == "parameter_server":
             owners = {s["rank"]: [tuple(r) for r in s["ranges"]] for s in self.plan["servers"]}
-            self.use_nvls = self.b200.get("allreduce", "auto") in ("nvls", "auto")
+            # Few owners for many workers: each owner would pull (N-1) shards over its own links, while
+            # the switch-side reduction delivers one reduced shard. Worth it when owners < N - 1.
+            pref = self.b200.get("allreduce", "auto")
+            n_owners = len(owners)
+            self.use_nvls = pref == "nvls" or (pref == "auto" and n_owners < W - 1)
             self._set_ownership([owners.get(r, []) for r in range(W)], self.worker_ranks, self.opt,
                                 "async" if self.async_ps else "fused", self.wild)
             return
@@ -192,8 +196,10 @@ class GpuRank:
         if mode == "auto":
             if self.n_pad * 4 <= 256 * 1024 and W > 1:
                 mode = "oneshot"
-            else:  # in-switch reduction whenever the fabric offers a multicast address
-                mode = "nvls" if (self.win.mc_ptr and W > 1) else "twoshot"
+            else:
+                # With every rank an owner, peer loads move (N-1)/N of the vector per GPU and direction,
+                # the in-switch reduction a full vector outbound: plain P2P is the better two-shot.
+                mode = "twoshot"
         if mode == "oneshot":
             ranges = [[(0, self.n_pad)] for _ in range(W)]
         else:
@@ -286,10 +292,9 @@ class GpuRank:
 
         self.buckets = []           # [(launch_after_layer, OnoSync)] in launch order
         self.bucket_after: dict[int, list] = {}
-        # On one GPU the exchange is a pure HBM pass that only competes with the (equally HBM-bound)
-        # weight-gradient GEMMs: measured slower when overlapped, so buckets are a multi-GPU default.
-        default = "1" if self.world > 1 else "0"
-        if (self.sync_mode != "fused" or self.cadence != "step" or os.environ.get("ONO_OVERLAP", default) == "0"):
+        # Measured on 1 and 2 B200s: the bucket kernels (one block per SM, sharing the SMs with the
+        # GEMMs) lose more bandwidth than the overlap wins, so buckets are opt-in (ONO_OVERLAP=1).
+        if (self.sync_mode != "fused" or self.cadence != "step" or os.environ.get("ONO_OVERLAP", "0") == "0"):
             return
         up4 = lambda x: (x + 3) // 4 * 4
         layers = [l for l in self.plan["layers"] if l["n_params"] > 0]
