@@ -1,0 +1,234 @@
+"""Convolution / pooling layers ahead of the dense stack on the GPU.
+
+The reference runs ``Conv2d`` as per-sample im2col + GEMM and ``MaxPooling`` as a scalar window scan
+(machine_learning/src/arch/layers/conv/conv2d.rs:61-190, arch/layers/max_pooling.rs:47-157). Here a
+convolution is one batched tcgen05 GEMM ``cols[B*oh*ow, C*k*k] @ K[F, C*k*k]^T`` with bias and activation
+in its epilogue, the weight gradient a split-K GEMM over all output pixels of the batch, the input
+gradient a GEMM followed by a gather-form col2im; the kernel tensor ``K[F][C][k][k]`` is used in place
+from the flat parameter vector. Image activations are pixel-major ``[B*H*W, ld]``; the flattened
+NCHW order dense layers expect is restored by one conversion kernel at the conv -> dense boundary.
+
+Supported model shape: ``(conv | max_pooling)* dense+`` - every model of the reference.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import conv as cv
+from ..ops import elementwise as ew
+from ..ops.gemm import gemm
+from .engine import GpuEngine, _up
+
+
+class ConvNetEngine:
+    """``ConvFront`` + the dense ``GpuEngine``, with the interface the rank runtime uses."""
+
+    def __init__(self, layers: list[dict], *, batch_size: int, tile_dtype: str, loss: str, params: torch.Tensor,
+                 grads: torch.Tensor, params_bf16: torch.Tensor | None = None, leaky_relu_exact: bool = True,
+                 bias_from_shadow: bool = False):
+        nfront = 0
+        while nfront < len(layers) and layers[nfront]["kind"] != "dense":
+            nfront += 1
+        if nfront == len(layers):
+            raise NotImplementedError("a model needs at least one dense layer after its conv/pool layers on the GPU")
+        if any(l["kind"] != "dense" for l in layers[nfront:]):
+            raise NotImplementedError("conv/pool layers after a dense layer are not supported on the GPU engine")
+        self.bf16 = tile_dtype == "bf16"
+        self.dev = params.device
+        self.B = batch_size
+        self.relu_quirk = not leaky_relu_exact
+        self.params, self.grads, self.params_bf16 = params, grads, params_bf16
+        self.T = torch.bfloat16 if self.bf16 else torch.float32
+        off = 0
+        self.front = []
+        for sp in layers[:nfront]:
+            c, h, w = sp["input_dim"]
+            d = dict(sp)
+            if sp["kind"] == "conv":
+                f, _, k = sp["kernel_dim"]
+                d.update(C=c, H=h, W=w, F=f, K=k, off=off, n=f * c * k * k + f)
+                off += d["n"]
+            else:
+                d.update(C=c, H=h, W=w, F=c, K=sp["filter_size"], off=off, n=0)
+            d["S"], d["P"] = sp["stride"], sp["padding"]
+            d["OH"] = (h + 2 * d["P"] - d["K"]) // d["S"] + 1
+            d["OW"] = (w + 2 * d["P"] - d["K"]) // d["S"] + 1
+            self.front.append(d)
+        self.front_params = off
+        last = self.front[-1]
+        dense_layers = layers[nfront:]
+        assert dense_layers[0]["in"] == last["F"] * last["OH"] * last["OW"]
+        self.dense = GpuEngine(dense_layers, batch_size=batch_size, tile_dtype=tile_dtype, loss=loss,
+                               params=params[off:], grads=grads[off:],
+                               params_bf16=None if params_bf16 is None else params_bf16[off:],
+                               leaky_relu_exact=leaky_relu_exact, bias_from_shadow=False, input_grad=True)
+        self.loss_sum, self.correct, self.status = self.dense.loss_sum, self.dense.correct, self.dense.status
+        self._alloc()
+
+    # the f32 master is read for the (small) kernel tensors and biases of the front
+    needs_f32_params = True
+
+    def _alloc(self):
+        B, T, dev = self.B, self.T, self.dev
+        z = lambda r, c, dt=T: torch.zeros(r, c, device=dev, dtype=dt)
+        for j, d in enumerate(self.front):
+            Min, Mout = B * d["H"] * d["W"], B * d["OH"] * d["OW"]
+            d["y"] = z(Mout, _up(d["F"]))
+            d["dy"] = z(Mout, _up(d["F"]))
+            if d["kind"] == "conv":
+                ckk = d["C"] * d["K"] * d["K"]
+                d["ckk"] = ckk
+                d["cols"] = z(Mout, _up(ckk))
+                d["dcols"] = z(Mout, _up(ckk)) if j > 0 else None
+                d["gk_tmp"] = z(d["F"], _up(ckk), torch.float32)
+                if not self.bf16:
+                    d["colsT"] = z(ckk, _up(Mout))
+                    d["dyT"] = z(d["F"], _up(Mout))
+                    d["kt"] = z(ckk, _up(d["F"]))                     # K^T for dgrad
+                mult = 8 if self.bf16 else 4
+                flat = self.params_bf16 if self.bf16 else self.params
+                direct = flat is not None and ckk % mult == 0 and d["off"] % mult == 0 and \
+                    (flat.data_ptr() + d["off"] * flat.element_size()) % 16 == 0
+                d["k_direct"] = direct
+                d["kop"] = flat[d["off"]:d["off"] + d["F"] * ckk].view(d["F"], ckk) if direct else z(d["F"], _up(ckk))[:, :ckk]
+            else:
+                d["arg"] = torch.zeros(Mout, d["C"], device=dev, dtype=torch.int32)
+                d["dx32"] = z(Min, _up(d["C"]), torch.float32)
+        c0 = self.front[0]
+        self.x0 = z(B * c0["H"] * c0["W"], _up(c0["C"]))      # pixel-major input batch
+        self.xflat = z(B, _up(c0["C"] * c0["H"] * c0["W"]))   # the batch as rows, in the tile dtype
+
+    def _k_view(self, d):
+        return self.params[d["off"]:d["off"] + d["F"] * d["ckk"]].view(d["F"], d["ckk"])
+
+    def _kb_view(self, d):
+        return self.params[d["off"] + d["F"] * d["ckk"]:d["off"] + d["n"]]
+
+    def refresh(self, stream=None) -> int:
+        n = 0
+        for d in self.front:
+            if d["kind"] != "conv":
+                continue
+            k = self._k_view(d)
+            if self.bf16:
+                if not d["k_direct"]:
+                    ew.rows(k, dst_bf16=d["kop"], stream=stream)
+                    n += 1
+            else:
+                if d["k_direct"]:
+                    ew.rows(k, dst_t=d["kt"][:, :d["F"]], stream=stream)
+                else:
+                    ew.rows(k, dst=d["kop"], dst_t=d["kt"][:, :d["F"]], stream=stream)
+                n += 1
+        return n + self.dense.refresh(stream)
+
+    def _act(self, d):
+        a = d.get("act")
+        return (a[0], a[1]) if a else (None, 0.0)
+
+    def forward_front(self, x: torch.Tensor, nrows: int, stream=None) -> int:
+        n = 0
+        c0 = self.front[0]
+        xin = c0["C"] * c0["H"] * c0["W"]
+        if self.bf16:
+            ew.rows(x, n_rows=nrows, dst_bf16=self.xflat, stream=stream)
+        else:
+            ew.rows(x, n_rows=nrows, dst=self.xflat, stream=stream)
+        n += 1
+        hw = c0["H"] * c0["W"]
+        cv.nchw_flat(nrows, c0["C"], hw, False, self.x0, self.xflat[:, :xin], stream=stream)
+        n += 1
+        cur = self.x0
+        for d in self.front:
+            Mout = nrows * d["OH"] * d["OW"]
+            g = cv.geom(nrows, d["C"], d["H"], d["W"], d["K"], d["S"], d["P"])
+            act, ap = self._act(d)
+            if d["kind"] == "conv":
+                cv.im2col(g, cur, d["cols"], None if self.bf16 else d["colsT"], stream=stream)
+                kw = dict(bias=self._kb_view(d), act=act, act_param=ap, status=self.status, stream=stream)
+                if self.bf16:
+                    kw["out_bf16"] = d["y"][:Mout, :d["F"]]
+                else:
+                    kw["out"] = d["y"][:Mout, :d["F"]]
+                gemm(d["cols"][:Mout, :d["ckk"]], d["kop"], **kw)
+                n += 2
+            else:
+                cv.pool_fwd(g, cur, d["y"], d["arg"], act=act, act_param=ap, stream=stream)
+                n += 1
+            cur = d["y"]
+        last = self.front[-1]
+        de = self.dense
+        cv.nchw_flat(nrows, last["F"], last["OH"] * last["OW"], True, last["y"], de.a[0],
+                     out_t=None if self.bf16 else de.at[0], stream=stream)
+        return n + 1
+
+    def backward_front(self, nrows: int, accumulate: bool, stream=None) -> int:
+        n = 0
+        de = self.dense
+        last = self.front[-1]
+        act, ap = self._act(last) if last["kind"] == "conv" else (None, 0.0)
+        want_t = (not self.bf16) and last["kind"] == "conv"
+        cv.nchw_flat(nrows, last["F"], last["OH"] * last["OW"], False, last["dy"], de.d[0],
+                     out_t=last["dyT"] if want_t else None, aux=last["y"], dact=act, dact_param=ap,
+                     relu_quirk=self.relu_quirk, stream=stream)
+        n += 1
+        for j in range(len(self.front) - 1, -1, -1):
+            d = self.front[j]
+            prev = self.front[j - 1] if j > 0 else None
+            Mout, Min = nrows * d["OH"] * d["OW"], nrows * d["H"] * d["W"]
+            g = cv.geom(nrows, d["C"], d["H"], d["W"], d["K"], d["S"], d["P"])
+            pact, pap = (self._act(prev) if (prev is not None and prev["kind"] == "conv") else (None, 0.0))
+            prev_t = prev is not None and prev["kind"] == "conv" and not self.bf16
+            if d["kind"] == "conv":
+                F, ckk = d["F"], d["ckk"]
+                dy = d["dy"][:Mout, :F]
+                if prev is not None:
+                    if self.bf16:
+                        gemm(dy, d["kop"], b_mn_major=True, out_bf16=d["dcols"][:Mout, :ckk], status=self.status, stream=stream)
+                    else:
+                        gemm(dy, d["kt"][:, :F], out=d["dcols"][:Mout, :ckk], status=self.status, stream=stream)
+                    cv.col2im(g, d["dcols"], prev["dy"], prev["dyT"] if prev_t else None, aux=prev["y"], dact=pact,
+                              dact_param=pap, relu_quirk=self.relu_quirk, stream=stream)
+                    n += 2
+                # weight gradient: K = every output pixel of the batch, tiny output -> split-K
+                tmp = d["gk_tmp"]
+                tmp.zero_()
+                kb = -(-Mout // (64 if self.bf16 else 32))
+                split = max(1, min(kb, 128))
+                if self.bf16:
+                    gemm(dy, d["cols"][:Mout, :ckk], a_mn_major=True, b_mn_major=True, out=tmp[:, :ckk], split_k=split,
+                         status=self.status, stream=stream)
+                else:
+                    gemm(d["dyT"][:, :Mout], d["colsT"][:, :Mout], out=tmp[:, :ckk], split_k=split, status=self.status,
+                         stream=stream)
+                gk = self.grads[d["off"]:d["off"] + F * ckk].view(F, ckk)
+                if accumulate:
+                    gk.add_(tmp[:, :ckk])
+                else:
+                    ew.rows(tmp[:, :ckk], dst=gk, stream=stream)
+                ew.colsum(dy, self.grads[d["off"] + F * ckk:d["off"] + d["n"]], beta=1.0 if accumulate else 0.0, stream=stream)
+                n += 4
+            else:
+                if prev is None:
+                    continue
+                act, ap = self._act(d)
+                d["dx32"].zero_()
+                cv.pool_bwd(g, d["dy"], d["y"], d["arg"], d["dx32"], act=act, act_param=ap, relu_quirk=self.relu_quirk,
+                            stream=stream)
+                cv.finish_delta(Min, d["C"], d["dx32"], prev["dy"], prev["dyT"] if prev_t else None, aux=prev["y"],
+                                dact=pact, dact_param=pap, relu_quirk=self.relu_quirk, stream=stream)
+                n += 3
+        return n
+
+    def step(self, x, y, nrows, idx=None, accumulate=False, stream=None, after_layer=None) -> int:
+        if idx is not None:
+            raise NotImplementedError("index gather is done by the batch feeder for conv models")
+        de = self.dense
+        n = self.forward_front(x, nrows, stream)
+        ew.rows(y, n_rows=nrows, dst=de.ybuf, stream=stream)
+        n += 1
+        n += de.forward(nrows, stream)
+        n += de.loss_backward(nrows, stream)
+        n += de.backward(nrows, accumulate, stream)
+        n += self.backward_front(nrows, accumulate, stream)
+        return n

@@ -58,8 +58,10 @@ class GpuEngine:
 
     def __init__(self, layers: list[dict], *, batch_size: int, tile_dtype: str, loss: str,
                  params: torch.Tensor, grads: torch.Tensor, params_bf16: torch.Tensor | None = None,
-                 leaky_relu_exact: bool = True, device=None, bias_from_shadow: bool = False):
+                 leaky_relu_exact: bool = True, device=None, bias_from_shadow: bool = False,
+                 input_grad: bool = False):
         self.bias_from_shadow = bias_from_shadow
+        self.input_grad = input_grad  # also produce d[0], the gradient w.r.t. the input batch
         if tile_dtype not in ("tf32", "bf16"):
             raise ValueError("tile_dtype must be 'tf32' or 'bf16'")
         self.dev = device or params.device
@@ -103,7 +105,7 @@ class GpuEngine:
         # activations a[0] = input batch, a[l+1] = output of layer l
         self.a = [z(B, self.lds[i], cd) for i in range(len(feats) - 1)]
         self.logits = z(B, self.lds[-1], f32)
-        self.d = [None] + [z(B, self.lds[i], cd) for i in range(1, len(feats))]
+        self.d = [z(B, self.lds[0], cd) if self.input_grad else None] + [z(B, self.lds[i], cd) for i in range(1, len(feats))]
         self.zpre = [None] * len(feats)
         for l, pl in enumerate(L):
             if pl.act == "gelu":
@@ -240,9 +242,11 @@ class GpuEngine:
             pl = L[l]
             i, o = pl.in_features, pl.out_features
             d_out = self.d[l + 1][:nrows, :o]
-            if l > 0:
-                # dgrad through the previous layer's activation: d_{l} = (d_{l+1} W^T) * act'(a_l)
-                prev = L[l - 1]
+            if l > 0 or self.input_grad:
+                # dgrad through the previous layer's activation: d_{l} = (d_{l+1} W^T) * act'(a_l);
+                # for l = 0 this is the raw gradient w.r.t. the input batch (whoever produced the
+                # batch applies its own activation derivative)
+                prev = L[l - 1] if l > 0 else LayerPlan("input", 0, i)
                 stored = self.zpre[l] if prev.act == "gelu" else self.a[l]
                 kw = dict(status=self.status, stream=stream)
                 if prev.act is not None:
@@ -251,7 +255,8 @@ class GpuEngine:
                 if self.bf16:
                     gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
                 else:
-                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], out_t=self.dt[l][:, :nrows], **kw)
+                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
+                         out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
                 n += 1
             # wgrad: dW[in,out] = A_{l}^T d
             tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)

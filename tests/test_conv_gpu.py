@@ -1,0 +1,109 @@
+"""Convolution / pooling on the GPU engine against PyTorch autograd (NCHW, fp32) and the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+LAYERS = [
+    dict(kind="conv", input_dim=[1, 12, 12], kernel_dim=[8, 1, 3], stride=1, padding=1, act=("relu", 0.0)),
+    dict(kind="pool", input_dim=[8, 12, 12], filter_size=2, stride=2, padding=0, act=None),
+    dict(kind="conv", input_dim=[8, 6, 6], kernel_dim=[16, 8, 3], stride=2, padding=1, act=("tanh", 1.0)),
+    dict(kind="dense", **{"in": 16 * 3 * 3, "out": 32}, act=("sigmoid", 1.0)),
+    dict(kind="dense", **{"in": 32, "out": 10}, act=("softmax", 0.0)),
+]
+
+
+def _torch_ref(params, x, y):
+    off = 0
+    ps = []
+
+    def take(shape):
+        nonlocal off
+        n = int(np.prod(shape))
+        t = params[off:off + n].view(*shape).clone().requires_grad_(True)
+        off += n
+        ps.append(t)
+        return t
+
+    B = x.shape[0]
+    a = x.view(B, 1, 12, 12)
+    k1, b1 = take((8, 1, 3, 3)), take((8,))
+    a = torch.relu(F.conv2d(a, k1, b1, stride=1, padding=1))
+    a = F.max_pool2d(a, 2, 2)
+    k2, b2 = take((16, 8, 3, 3)), take((16,))
+    a = torch.tanh(F.conv2d(a, k2, b2, stride=2, padding=1))
+    a = a.reshape(B, -1)                      # NCHW flatten, the reference's order
+    w3, b3 = take((144, 32)), take((32,))
+    a = torch.sigmoid(a @ w3 + b3)
+    w4, b4 = take((32, 10)), take((10,))
+    p = torch.softmax(a @ w4 + b4, 1)
+    L = -(y * torch.log(p.clamp_min(1.1920929e-07))).sum() / p.numel()
+    L.backward()
+    return L.item(), torch.cat([t.grad.reshape(-1) for t in ps])
+
+
+@pytest.mark.parametrize("tile", ["tf32", "bf16"])
+def test_conv_engine_grads_match_autograd(tile):
+    from oxidized_neural_orchestra_b200.models.conv_engine import ConvNetEngine
+
+    torch.manual_seed(0)
+    n = 8 * 9 + 8 + 16 * 72 + 16 + 145 * 32 + 33 * 10
+    npad = (n + 15) // 16 * 16
+    params = torch.zeros(npad, device="cuda")
+    params[:n] = torch.randn(n, device="cuda") * 0.2
+    grads = torch.zeros(npad, device="cuda")
+    pb = params.to(torch.bfloat16) if tile == "bf16" else None
+    B = 24
+    eng = ConvNetEngine(LAYERS, batch_size=B, tile_dtype=tile, loss="cross_entropy", params=params, grads=grads,
+                        params_bf16=pb)
+    eng.refresh()
+    x = torch.rand(B, 144, device="cuda") + 0.05   # positive inputs: zero padding never wins the max
+    y = F.one_hot(torch.randint(0, 10, (B,), device="cuda"), 10).float()
+    eng.step(x, y, B)
+    torch.cuda.synchronize()
+    assert eng.status.item() == 0
+    pref = pb.float() if tile == "bf16" else params
+    xr = x.to(torch.bfloat16).float() if tile == "bf16" else x
+    ref_loss, ref_g = _torch_ref(pref[:n], xr, y)
+    tol = 6e-2 if tile == "bf16" else 2e-2
+    assert abs(eng.loss_sum.item() - ref_loss) <= tol * abs(ref_loss)
+    err = (grads[:n] - ref_g).abs().max().item()
+    assert err <= tol * ref_g.abs().max().item(), (err, ref_g.abs().max().item())
+    # ragged batch + accumulation into the same gradient buffer
+    if tile == "tf32":
+        grads.zero_()
+        eng.step(x[:10].contiguous(), y[:10].contiguous(), 10)
+        eng.step(x[10:].contiguous(), y[10:].contiguous(), 14, accumulate=True)
+        torch.cuda.synchronize()
+        _, g1 = _torch_ref(params[:n], x[:10], y[:10])
+        _, g2 = _torch_ref(params[:n], x[10:], y[10:])
+        assert (grads[:n] - (g1 + g2)).abs().max().item() <= tol * (g1 + g2).abs().max().item()
+
+
+def test_cnn_through_the_api_tracks_the_oracle():
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import ReLU, Softmax
+    from orchestra.arch import Conv2d, Dense, MaxPooling
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import Kaiming
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescentWithMomentum
+
+    rng = np.random.default_rng(0)
+    xs = rng.random((32, 64), dtype=np.float32) + 0.05
+    ys = np.eye(4, dtype=np.float32)[rng.integers(0, 4, 32)]
+    model = Sequential([Conv2d((1, 8, 8), (6, 1, 3), 1, 1, Kaiming(), ReLU(0.0)), MaxPooling((6, 8, 8), 2, 2, 0),
+                        Conv2d((6, 4, 4), (8, 6, 3), 1, 0, Kaiming(), ReLU(0.0)), Dense(4, Kaiming(), Softmax())])
+    out = {}
+    for dev in ("cpu", "gpu"):
+        tr = orchestra.all_reduce([f"{dev}:0"], InlineDataset(xs, ys, 64, 4), GradientDescentWithMomentum(0.2, 0.9),
+                                  CrossEntropy(), max_epochs=10, batch_size=32, seed=3)
+        m = orchestrate(model, tr).wait(quiet=True)
+        out[dev] = (np.array(m.loss_history()), m.weights_array())
+    (lc, wc), (lg, wg) = out["cpu"], out["gpu"]
+    assert lg[-1] < lg[0]
+    assert np.allclose(lc, lg, rtol=5e-2, atol=1e-5)
+    assert np.abs(wc - wg).max() < 5e-2 * max(1.0, np.abs(wc).max())
