@@ -40,7 +40,12 @@ CONFIGS = {
                  strategy="ar", init="kaiming", data="uniform", model="wide-mlp-784-4096x3-10"),
     "mlp": dict(x=784, hidden=[(128, "relu")], classes=10, tile="tf32", opt=("sgd", 0.01), batch=32, strategy="ar",
                 init="xavier_uniform", data="uniform", model="mlp-784-128-10"),
+    # conv entries: (filters, kernel, stride, padding), all ReLU; global batch 2048 over 6 workers = 342 per worker
+    "cnn": dict(x=784, conv_input=(1, 28, 28), conv=[(32, 3, 1, 1), (64, 3, 2, 1), (64, 3, 2, 1)], hidden=[(128, "relu")],
+                classes=10, tile="tf32", opt=("adam", 1e-3), batch=342, strategy="ps2", init="kaiming", data="uniform",
+                model="cnn-3conv-2dense-28x28"),
 }
+SWITCH = {"metric": "grad_norm", "window": 50, "threshold": 1e-2}
 
 
 def reference_arm() -> None:
@@ -67,7 +72,14 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
 
     init = Kaiming() if cfg["init"] == "kaiming" else XavierUniform()
     act = {"gelu": GELU, "relu": lambda: ReLU(0.0)}
-    layers = [Dense(w, init, act[a]()) for w, a in cfg["hidden"]] + [Dense(cfg["classes"], init, Softmax())]
+    layers = []
+    if cfg.get("conv"):
+        from orchestra.arch import Conv2d
+        c, h, w_ = cfg["conv_input"]
+        for f, k, s, p in cfg["conv"]:
+            layers.append(Conv2d((c, h, w_), (f, c, k), s, p, init, ReLU(0.0)))
+            c, h, w_ = f, (h + 2 * p - k) // s + 1, (w_ + 2 * p - k) // s + 1
+    layers += [Dense(w, init, act[a]()) for w, a in cfg["hidden"]] + [Dense(cfg["classes"], init, Softmax())]
     model = Sequential(layers)
     B = cfg["batch"]
     steps_per_epoch = 8
@@ -86,10 +98,15 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
     epochs = -(-steps_total // steps_per_epoch)
     addrs = [f"gpu:{i}" for i in range(n_gpus)]
     b200 = {"sync_every": "step", "tile_dtype": cfg["tile"], "data": data_mode, "sharding": "even", "colocate": True}
-    if cfg["strategy"] == "ps4":
-        training = orchestra.parameter_server(addrs, min(4, n_gpus), ds, opt, CrossEntropy(), BarrierSync(),
-                                              BlockingStore(), max_epochs=epochs, batch_size=B, seed=seed, b200=b200)
-        par = f"ps(servers={min(4, n_gpus)},colocated)+dp{n_gpus}"
+    strat = cfg["strategy"]
+    if strat.startswith("ps") or strat.startswith("ss"):
+        ns = min(int(strat[2:] or 2), n_gpus)
+        if strat.startswith("ss"):
+            b200.update(switch_metric=SWITCH["metric"], switch_window=SWITCH["window"], switch_threshold=SWITCH["threshold"])
+        fn = orchestra.parameter_server if strat.startswith("ps") else orchestra.strategy_switch
+        training = fn(addrs, ns, ds, opt, CrossEntropy(), BarrierSync(), BlockingStore(), max_epochs=epochs, batch_size=B,
+                      seed=seed, b200=b200)
+        par = f"{strat[:2]}(servers={ns},colocated)+dp{n_gpus}"
     else:
         training = orchestra.all_reduce(addrs, ds, opt, CrossEntropy(), max_epochs=epochs, batch_size=B, seed=seed,
                                         b200=b200)
@@ -142,6 +159,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--config", default="deep", choices=sorted(CONFIGS))
+    ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -158,8 +176,18 @@ def main() -> None:
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.strategy:
+        cfg["strategy"] = args.strategy
     W, K = max(3, args.warmup), args.steps
+    if args.impl == "nccl":
+        sys.path.insert(0, os.path.join(ROOT, "baseline"))
+        import torch_nccl
+        st = cfg["strategy"]
+        torch_nccl.main(cfg, args.config, st[:2], int(st[2:] or 2) if st != "ar" else 1, K, W, SWITCH, ClockSampler)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     os.environ["ONO_BENCH_WARMUP"], os.environ["ONO_BENCH_STEPS"] = str(W), str(K)
     results = {}
     clocks = None

@@ -107,6 +107,9 @@ struct B200Config {
   bool switch_resets_progress = false;
   bool colocate = false;                  // server ranks also train (B200 extension)
   std::string data = "host";              // "host": per-step H2D from pinned memory | "device"
+  double comm_timeout_s = 300.0;          // a collective or device wait that exceeds this ends the run with an error
+  std::string trace_path;                 // chrome-trace JSON of the run's phases (empty = off)
+  std::string metrics_path;               // JSONL, one record per round / step window (empty = off)
   bool present = false;
   Json to_json() const;
   static B200Config from_json(const Json& j);

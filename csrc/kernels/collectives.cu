@@ -155,7 +155,8 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
     if ((threadIdx.x & 31) == 0 && sq != 0.0) atomicAdd(L.sumsq, sq);
   }
   // Nobody leaves before every member has stopped reading gradients and writing parameters.
-  const bool ok2 = rank_barrier(a.flags, a.nranks, rank, blk, members, e0 + 2, budget);
+  // After a failed entry barrier the exit barrier only gets a token budget: the peer is already known absent.
+  const bool ok2 = rank_barrier(a.flags, a.nranks, rank, blk, members, e0 + 2, ok ? budget : 1000000ull);
   if (!ok2 && ok && threadIdx.x == 0 && L.status) atomicCAS(L.status, 0, ONO_ERR_TIMEOUT_BARRIER);
   if (threadIdx.x == 0) L.epoch[blk] = e0 + 2;
 }

@@ -221,6 +221,8 @@ class Session:
                 stop_reason = ev.get("text") or stop_reason
         prog._flush(final=True)
         if error is not None and stop_reason == "error":
+            if hasattr(self._h, "close"):
+                self._h.close()
             raise RuntimeError(f"training failed: {error}")
         params, metrics = self._h.result()
         self._result = TrainedModel(params, self._model_cfg, self._training.dataset.x_size, prog.history, stop_reason,

@@ -38,12 +38,17 @@ def run_rank(job: dict, xs: np.ndarray, ys: np.ndarray, emit, stop_event, device
     plan = json.loads(core.adapt_configs(json.dumps(job["model"]), json.dumps(job["training"]), json.dumps(job.get("stats") or {}) if job.get("stats") else ""))
     own_group = False
     if world > 1 and not dist.is_initialized():
+        import datetime
+
         os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = job["master_addr"], str(job["master_port"])
+        # a collective whose peer died ends with an error after this long instead of waiting forever
+        limit = datetime.timedelta(seconds=float(plan["b200"].get("comm_timeout_s", 300.0)))
         if device_kind == "gpu":
             torch.cuda.set_device(gpu or 0)
-            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", gpu or 0))
+            dist.init_process_group("nccl", rank=rank, world_size=world, timeout=limit,
+                                    device_id=torch.device("cuda", gpu or 0))
         else:
-            dist.init_process_group("gloo", rank=rank, world_size=world)
+            dist.init_process_group("gloo", rank=rank, world_size=world, timeout=limit)
         own_group = True
     try:
         if device_kind == "gpu":
@@ -130,6 +135,10 @@ def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
                     continue
                 if m == "stop_after_epoch":
                     stop_event.set()
+                elif m == "abort":
+                    # another node was lost: stop at the next boundary; a collective that is already waiting
+                    # for the dead peer ends by its own time limit and reports through body()
+                    stop_event.set()
                 elif m == "request_params":
                     t.join()
                     p = result.get("params")
@@ -165,6 +174,7 @@ class RemoteHandle:
         self._metrics: dict = {}
         self._closed = False
         self._events_finished = False
+        self._failed = False
         master_port = wire.free_port()
         master_addr = addrs[0].rsplit(":", 1)[0]
         part = {w["rank"]: w["partition"] for w in plan["workers"]}
@@ -210,6 +220,28 @@ class RemoteHandle:
         except (ConnectionError, OSError) as e:
             self._q.put(("event", rank, {"kind": "error", "worker": rank, "losses": [], "text": f"node {rank} lost: {e}"}))
             self._q.put(("done", rank, None))
+            self._abort(rank)
+
+    def _abort(self, lost_rank: int):
+        """Tell the surviving nodes that a member is gone (the reference ends the whole session on a worker
+        io error: orchestrator/src/sessions/event_listener.rs:128-132)."""
+        self._failed = True
+        for r, ch in enumerate(self._chs):
+            if r != lost_rank:
+                try:
+                    ch.send_command("abort")
+                except OSError:
+                    pass
+
+    def close(self):
+        """Drop every control connection (nodes go back to listening)."""
+        for ch in self._chs:
+            try:
+                ch.send_command("disconnect")
+            except OSError:
+                pass
+            ch.close()
+        self._closed = True
 
     def stop(self):
         for ch in self._chs:
@@ -233,6 +265,8 @@ class RemoteHandle:
                     continue
                 yield ev
         self._events_finished = True
+        if self._failed:
+            complete_ev = {"kind": "complete", "worker": 0, "losses": [], "text": "error"}
         yield complete_ev or {"kind": "complete", "worker": 0, "losses": [], "text": "error"}
 
     def result(self):
