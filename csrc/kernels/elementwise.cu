@@ -5,6 +5,8 @@
 // optimization/{gradient_descent,gradient_descent_with_momentum,adam}.rs, param_manager.rs:168-197.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+
+#include <algorithm>
 #include <stdint.h>
 
 #include "../core/philox.h"
@@ -124,25 +126,64 @@ __global__ void loss_kernel(const OnoLoss l) {
 // ------------------------------------------------------------------------------------------------
 // Column sums (bias gradient). Block = 32 columns x 8 row-lanes.
 // ------------------------------------------------------------------------------------------------
+// Rows are split into `nchunks` slabs (grid.y) so that a tall, narrow matrix (the bias gradient of a
+// convolution: hundreds of thousands of rows, 32 columns) still fills the GPU. Every slab writes its
+// partial column sums to a scratch array; the last slab to finish for a column block (counted with an
+// atomic) adds the partials in slab order, so the result does not depend on the arrival order.
+// The scratch is shared by all calls of a process: calls must not overlap on the device (they are
+// issued on one stream by the engines).
+constexpr int CS_MAX_PART = 1 << 21;    // floats
+constexpr int CS_MAX_COLBLOCKS = 1024;
+__device__ float g_cs_part[CS_MAX_PART];
+__device__ unsigned int g_cs_count[CS_MAX_COLBLOCKS];
+
 template <typename T>
-__global__ void colsum_kernel(const T* d, int M, int N, int ld, float* out, float beta) {
+__device__ __forceinline__ float cs_load(const T* p) {
+  if constexpr (sizeof(T) == 4) return *p;
+  else return __bfloat162float(*p);
+}
+
+template <typename T>
+__global__ void colsum_kernel(const T* d, int M, int N, int ld, float* out, float beta, int rows_per, int nchunks) {
   __shared__ float s[8][33];
+  __shared__ int s_last;
   const int col = blockIdx.x * 32 + threadIdx.x;
-  float acc = 0.0f;
+  const int m0 = blockIdx.y * rows_per, m1 = min(M, m0 + rows_per);
+  float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
   if (col < N) {
-    for (int m = threadIdx.y; m < M; m += 8) {
-      if constexpr (sizeof(T) == 4) acc += d[(size_t)m * ld + col];
-      else acc += __bfloat162float(d[(size_t)m * ld + col]);
+    int m = m0 + threadIdx.y;
+    for (; m + 24 < m1; m += 32) {   // four independent loads in flight per thread
+      a0 += cs_load(d + (size_t)m * ld + col);
+      a1 += cs_load(d + (size_t)(m + 8) * ld + col);
+      a2 += cs_load(d + (size_t)(m + 16) * ld + col);
+      a3 += cs_load(d + (size_t)(m + 24) * ld + col);
     }
+    for (; m < m1; m += 8) a0 += cs_load(d + (size_t)m * ld + col);
   }
-  s[threadIdx.y][threadIdx.x] = acc;
+  s[threadIdx.y][threadIdx.x] = (a0 + a1) + (a2 + a3);
   __syncthreads();
-  if (threadIdx.y == 0 && col < N) {
-    float t = 0.0f;
+  float t = 0.0f;
+  if (threadIdx.y == 0) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) t += s[i][threadIdx.x];
-    out[col] = beta != 0.0f ? beta * out[col] + t : t;
   }
+  if (nchunks == 1) {
+    if (threadIdx.y == 0 && col < N) out[col] = beta != 0.0f ? beta * out[col] + t : t;
+    return;
+  }
+  if (threadIdx.y == 0) g_cs_part[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 32 + threadIdx.x] = t;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0 && threadIdx.y == 0) s_last = atomicAdd(&g_cs_count[blockIdx.x], 1u) == (unsigned)nchunks - 1u;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.y == 0 && col < N) {
+    float sum = 0.0f;
+    for (int c = 0; c < nchunks; ++c) sum += __ldcg(&g_cs_part[((size_t)c * gridDim.x + blockIdx.x) * 32 + threadIdx.x]);
+    out[col] = beta != 0.0f ? beta * out[col] + sum : sum;
+  }
+  if (threadIdx.x == 0 && threadIdx.y == 0) g_cs_count[blockIdx.x] = 0u;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -311,9 +352,16 @@ extern "C" int ono_loss(const OnoLoss* l, ono_stream_t st) {
 
 extern "C" int ono_colsum(const void* d, int dtype, int M, int N, int ld, float* out, float beta, ono_stream_t st) {
   if (!d || !out || M <= 0 || N <= 0) { set_error("bad colsum args%s", "", 0, 0); return -1; }
-  dim3 block(32, 8), grid((N + 31) / 32);
-  if (dtype == 0) colsum_kernel<float><<<grid, block, 0, (cudaStream_t)st>>>((const float*)d, M, N, ld, out, beta);
-  else colsum_kernel<__nv_bfloat16><<<grid, block, 0, (cudaStream_t)st>>>((const __nv_bfloat16*)d, M, N, ld, out, beta);
+  const int gx = (N + 31) / 32;
+  int nchunks = 1;
+  if (gx <= CS_MAX_COLBLOCKS) {
+    nchunks = std::max(1, std::min({(M + 127) / 128, (4 * 148 + gx - 1) / gx, CS_MAX_PART / (gx * 32)}));
+  }
+  const int rows_per = (((M + nchunks - 1) / nchunks) + 7) / 8 * 8;
+  nchunks = (M + rows_per - 1) / rows_per;
+  dim3 block(32, 8), grid(gx, nchunks);
+  if (dtype == 0) colsum_kernel<float><<<grid, block, 0, (cudaStream_t)st>>>((const float*)d, M, N, ld, out, beta, rows_per, nchunks);
+  else colsum_kernel<__nv_bfloat16><<<grid, block, 0, (cudaStream_t)st>>>((const __nv_bfloat16*)d, M, N, ld, out, beta, rows_per, nchunks);
   return launch_ok("colsum");
 }
 

@@ -8,6 +8,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
+from ..utils.trace import MetricsSink, Tracer
 from . import gpu_loop as L
 
 
@@ -52,6 +53,32 @@ def _bench_hook(r, it: int) -> None:
         r.bench_wall.append(__import__("time").perf_counter())
 
 
+def _record_epoch(r, tracer, sink, ev_first: int, epoch_first: int, epoch_now: int, losses: list, t_epoch: float) -> None:
+    """One metrics record and the device spans of the steps recorded since ``ev_first``."""
+    import time
+
+    evs = r.step_events[ev_first:]
+    dev_ms, worst = 0.0, 0.0
+    if len(evs) >= 2:
+        evs[-1].synchronize()
+        for a, b in zip(evs[:-1], evs[1:]):
+            d = a.elapsed_time(b)
+            dev_ms += d
+            worst = max(worst, d)
+            tracer.device_span("step", a, b, epoch=epoch_first)
+    wall = time.perf_counter() - t_epoch
+    tracer.events.append({"name": "epoch", "ph": "X", "pid": r.rank, "tid": 0, "ts": (t_epoch - tracer.t0) * 1e6,
+                          "dur": wall * 1e6, "args": {"epoch": epoch_first, "losses": losses}}) if tracer.on else None
+    steps = max(0, len(evs) - 1)
+    rows = steps * int(getattr(r.engine, "B", 0) or 0)
+    sink.write(epoch=epoch_now, epochs_in_record=max(1, epoch_now - epoch_first), loss=(losses[-1] if losses else None),
+               steps=steps, device_ms=dev_ms, max_step_ms=worst, wall_s=wall,
+               samples_per_sec=(rows / (dev_ms / 1e3) if dev_ms > 0 else None),
+               epochs_per_sec=(max(1, epoch_now - epoch_first) / wall if wall > 0 else None),
+               strategy=("parameter_server" if r.switched else r.algorithm), sync_mode=r.sync_mode,
+               h2d_bytes_per_step=(r.feeder.h2d_bytes_per_step if r.feeder is not None else 0))
+
+
 def run(r) -> dict:
     import os
 
@@ -64,9 +91,13 @@ def run(r) -> dict:
     pending = [False, False]
     norm_hist: list = []
     check_every = int(r.b200.get("switch_check_every", 10))
+    tracer = r.tracer = Tracer(r.b200.get("trace_path") or None, r.rank)
+    sink = MetricsSink(r.b200.get("metrics_path") or None, r.rank)
+    tracer.device_anchor(r.stream)
     while epoch < r.max_epochs:
         decision = 0
         epoch_losses: list[float] = []
+        ev_first, epoch_first, t_epoch = len(r.step_events), epoch, __import__("time").perf_counter()
         if r.cadence == "step":
             steps = L._steps_per_epoch(r)
             total, cnt = 0.0, 0
@@ -130,13 +161,17 @@ def run(r) -> dict:
                 ev.record(r.stream)
             r.round_events = getattr(r, "round_events", []) + [ev]
             epoch += nep
+        if tracer.on or sink.on:
+            _record_epoch(r, tracer, sink, ev_first, epoch_first, epoch, epoch_losses, t_epoch)
         if decision != 2:
-            decision = L.report_and_decide(r, epoch_losses)
+            with tracer.span("report_and_decide", epoch=epoch):
+                decision = L.report_and_decide(r, epoch_losses)
         L.check_status(r)
         if decision == 1:
             break
         if decision == 2 and r.algorithm == "strategy_switch" and not r.switched:
-            L.do_switch(r)
+            with tracer.span("strategy_switch", epoch=epoch):
+                L.do_switch(r)
             pending = [False, False]
     _bench_hook(r, it)
     torch.cuda.synchronize(r.dev)
@@ -172,6 +207,7 @@ def run(r) -> dict:
             t = torch.tensor([metrics["bench_ms"], metrics["bench_wall_s"]], dtype=torch.float64, device=r.dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=r.group)
             metrics["bench_ms"], metrics["bench_wall_s"] = float(t[0]), float(t[1])
+    tracer.write()
     r.result = {"params": params, "metrics": metrics}
     # every process closes its own event stream (the other events come from rank 0 only)
     r.emit({"kind": "complete", "worker": 0, "losses": [], "text": r.stop_reason})

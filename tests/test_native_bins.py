@@ -1,0 +1,150 @@
+"""The native executables: ``ono-orchestrator`` (headless run from model.json + training.json) and
+``ono-node`` (role-agnostic listener; node/src/main.rs:27-54, router.rs:79-220, stat_service.rs:69-152)."""
+import json
+import os
+import shutil
+import socket
+import subprocess
+import time
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.skipif(shutil.which("g++") is None, reason="needs a C++ compiler")
+
+
+@pytest.fixture(scope="module")
+def bins():
+    from oxidized_neural_orchestra_b200 import build
+
+    built = {p.name: str(p) for p in build.build_bins()}
+    assert {"ono-node", "ono-orchestrator"} <= set(built)
+    return built
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _configs(tmp_path, addrs, algorithm="all_reduce", epochs=6):
+    rng = np.random.default_rng(0)
+    xs = rng.random((40, 6)).astype(np.float32)
+    ys = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 40)]
+    model = {"layers": [{"dense": {"output_size": 5, "init": "xavier_uniform", "act_fn": {"tanh": {"amp": 1.0}}}},
+                        {"dense": {"output_size": 3, "init": "xavier_uniform", "act_fn": "softmax"}}]}
+    tr = {"addrs": addrs, "algorithm": algorithm,
+          "dataset": {"src": {"inline": {"samples": xs.reshape(-1).tolist(), "labels": ys.reshape(-1).tolist()}}, "x_size": 6, "y_size": 3},
+          "optimizer": {"adam": {"lr": 0.05, "b1": 0.9, "b2": 0.999, "eps": 1e-8}}, "loss_fn": "cross_entropy",
+          "batch_size": 5, "max_epochs": epochs, "offline_epochs": 0, "seed": 3}
+    mp, tp = tmp_path / "model.json", tmp_path / f"training_{len(addrs)}_{addrs[0].split(':')[0]}.json"
+    mp.write_text(json.dumps(model))
+    tp.write_text(json.dumps(tr))
+    return str(mp), str(tp), model, tr, xs, ys
+
+
+def _run_orchestrator(bins, mp, tp, *extra, timeout=300):
+    r = subprocess.run([bins["ono-orchestrator"], mp, tp, "--quiet", *extra], capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stderr[-2000:]
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def _python_reference(model, tr, xs, ys):
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import Adam
+
+    m = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+    cfg = orchestra.all_reduce([f"cpu:{i}" for i in range(len(tr["addrs"]))], InlineDataset(xs, ys, 6, 3), Adam(0.05),
+                               CrossEntropy(), tr["max_epochs"], 5, seed=3)
+    return orchestrate(m, cfg).wait(quiet=True)
+
+
+def test_orchestrator_trains_in_process_and_writes_the_reference_checkpoint_layout(bins, tmp_path):
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, ["cpu:0", "cpu:1", "cpu:2"])
+    out = tmp_path / "m.safetensors"
+    res = _run_orchestrator(bins, mp, tp, "--save", str(out))
+    ref = _python_reference(model, tr, xs, ys)
+    assert res["stop_reason"] == "max_epochs" and res["n_params"] == 53
+    assert np.allclose(res["loss_history"], ref.loss_history(), rtol=1e-6)
+    from orchestra import _orchestra as core
+
+    tensors = {t[0]: (t[1], np.asarray(t[2])) for t in core.load_safetensors(str(out))}
+    order = ["layer_0.weight", "layer_0.bias", "layer_1.weight", "layer_1.bias"]
+    assert sorted(tensors) == sorted(order)
+    assert list(tensors["layer_0.weight"][0]) == [6, 5] and list(tensors["layer_1.bias"][0]) == [3]
+    flat = np.concatenate([tensors[k][1].reshape(-1) for k in order])
+    assert np.allclose(flat, ref.weights_array(), atol=1e-6)
+
+
+def test_orchestrator_rejects_an_invalid_config(bins, tmp_path):
+    mp, tp, *_ = _configs(tmp_path, ["cpu:0"])
+    bad = json.loads(open(tp).read())
+    bad["batch_size"] = 10_000
+    open(tp, "w").write(json.dumps(bad))
+    r = subprocess.run([bins["ono-orchestrator"], mp, tp], capture_output=True, text=True, timeout=60)
+    assert r.returncode == 1 and "batch_size" in r.stderr
+
+
+@pytest.fixture()
+def cxx_nodes(bins):
+    ports = [_free_port() for _ in range(3)]
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""), ONO_LOG="warn")
+    procs = [subprocess.Popen([bins["ono-node"], "--port", str(p), "--device", "cpu"], env=env) for p in ports]
+    for p in ports:                      # wait until each listens (a refused probe is not a session)
+        for _ in range(100):
+            try:
+                socket.create_connection(("127.0.0.1", p), timeout=0.2).close()
+                break
+            except OSError:
+                time.sleep(0.05)
+    yield [f"127.0.0.1:{p}" for p in ports]
+    for p in procs:
+        p.kill()
+    for p in procs:
+        p.wait(timeout=30)
+
+
+def test_nodes_serve_a_single_rank_natively_and_many_ranks_through_rank_processes(bins, cxx_nodes, tmp_path):
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, cxx_nodes[:1])
+    one = _run_orchestrator(bins, mp, tp)
+    assert one["stop_reason"] == "max_epochs" and one["loss_history"][-1] < one["loss_history"][0]
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, cxx_nodes)
+    three = _run_orchestrator(bins, mp, tp)
+    ref = _python_reference(model, tr, xs, ys)
+    assert np.allclose(three["loss_history"], ref.loss_history(), rtol=1e-6)
+    # the nodes went back to listening: a second session on the same processes
+    again = _run_orchestrator(bins, mp, tp)
+    assert np.allclose(again["loss_history"], three["loss_history"], rtol=1e-9)
+
+
+def test_node_latency_probe_answers_with_min_max_mean_per_peer(cxx_nodes):
+    from oxidized_neural_orchestra_b200.runtime import wire
+
+    chs = []
+    for a in cxx_nodes[:2]:
+        host, port = a.rsplit(":", 1)
+        ch = wire.connect(host, int(port))
+        ch.connect_as("Orchestrator")
+        assert ch.peer_entity == "Node"
+        chs.append(ch)
+    # node 0 only accepts, node 1 pings node 0 (orchestrator/src/configs/stat_requester.rs:52-72)
+    chs[0].send_command({"stats_request": {"ping": {"addrs": [], "rounds": 5, "incoming": 1}}})
+    chs[1].send_command({"stats_request": {"ping": {"addrs": [cxx_nodes[0]], "rounds": 5, "incoming": 0}}})
+    _, r1 = chs[1].recv(timeout=30)
+    _, r0 = chs[0].recv(timeout=30)
+    rtts = r1["stats_response"]["stats"]["ping"]["rtts"]
+    assert list(rtts) == [cxx_nodes[0]]
+    st = rtts[cxx_nodes[0]]
+    assert 0 < st["min"] <= st["mean"] <= st["max"] < 1e9
+    assert r0["stats_response"]["stats"]["ping"]["rtts"] == {}
+    for ch in chs:
+        ch.send_command("disconnect")
+        ch.close()
