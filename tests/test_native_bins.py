@@ -148,3 +148,20 @@ def test_node_latency_probe_answers_with_min_max_mean_per_peer(cxx_nodes):
     for ch in chs:
         ch.send_command("disconnect")
         ch.close()
+
+
+def test_orchestui_renders_the_dashboard_and_autosaves_into_the_model_repository(bins, tmp_path):
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, ["cpu:0", "cpu:1", "cpu:2"],
+                                         algorithm={"parameter_server": {"nservers": 1, "synchronizer": "barrier", "store": "blocking"}})
+    r = subprocess.run([bins["orchestui"], "--render-once", mp, tp, "--size", "120x34"], capture_output=True, text=True,
+                       timeout=120, cwd=tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    frame = r.stdout
+    for panel in ("average loss", "workers", "log", "parameters", "topology"):
+        assert panel in frame
+    assert "finished: max_epochs" in frame and "parameter server" in frame and "progress 6/6" in frame
+    saved = list((tmp_path / "safetensors").glob("*_*.safetensors"))     # <adjective>_<term>.safetensors
+    assert len(saved) == 1
+    from orchestra import _orchestra as core
+
+    assert sum(np.asarray(t[2]).size for t in core.load_safetensors(str(saved[0]))) == 53
