@@ -93,3 +93,55 @@ def start_spawned_session(plan, model_cfg, training_cfg, dataset, device: str = 
             p.kill()
         raise
     return SpawnedHandle(inner, procs)
+
+
+def main(argv=None) -> None:
+    """``python -m oxidized_neural_orchestra_b200.runtime.launch --nodes N [--base-port P] [--device cpu|gpu] [--native]``:
+    bring up N listening nodes on this machine and keep them running until interrupted (the local stand-in for
+    the reference's ``make cluster-up``: docker/gen_compose.py:44-151 starts node-i on port 40000+i)."""
+    import argparse
+    import signal
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--nodes", type=int, default=3)
+    ap.add_argument("--base-port", type=int, default=40000)
+    ap.add_argument("--device", choices=("cpu", "gpu"), default=None)
+    ap.add_argument("--native", action="store_true", help="start the C++ ono-node executable instead of the Python node")
+    a = ap.parse_args(argv)
+    device = a.device
+    if device is None:
+        import torch
+
+        device = "gpu" if torch.cuda.is_available() else "cpu"
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    env = dict(os.environ)
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    procs = []
+    for i in range(a.nodes):
+        port = a.base_port + i
+        if a.native:
+            cmd = [os.path.join(root, "bin", "ono-node"), "--port", str(port)] + (["--gpu", str(i)] if device == "gpu" else ["--device", "cpu"])
+        else:
+            cmd = [sys.executable, "-m", "oxidized_neural_orchestra_b200.runtime.node", "--host", "127.0.0.1", "--port", str(port),
+                   "--device", device] + (["--gpu", str(i)] if device == "gpu" else [])
+        procs.append(subprocess.Popen(cmd, env=env))
+        print(f"node-{i}: 127.0.0.1:{port} ({device})", file=sys.stderr)
+    signal.signal(signal.SIGTERM, lambda *_: sys.exit(0))
+    try:
+        for p in procs:
+            p.wait()
+    except (KeyboardInterrupt, SystemExit):
+        pass
+    finally:
+        for p in procs:      # exactly the children started above
+            if p.poll() is None:
+                p.terminate()
+        for p in procs:
+            try:
+                p.wait(timeout=10)
+            except subprocess.TimeoutExpired:
+                p.kill()
+
+
+if __name__ == "__main__":
+    main()
