@@ -54,15 +54,15 @@ def cmd_gemm(a):
     B = torch.randn(a.n, a.k, device="cuda", dtype=dt)
     out = torch.zeros(a.m, a.n, device="cuda")
     for _ in range(3):
-        gemm(A, B, out=out, bn=a.bn)
-    ms = _time(lambda: gemm(A, B, out=out, bn=a.bn), a.iters)
+        gemm(A, B, out=out, bn=a.bn, pair=a.pair)
+    ms = _time(lambda: gemm(A, B, out=out, bn=a.bn, pair=a.pair), a.iters)
     torch.backends.cuda.matmul.allow_tf32 = True
     Bt = B.t()
     for _ in range(3):
         torch.matmul(A, Bt)
     ref = _time(lambda: torch.matmul(A, Bt), a.iters)
     fl = 2.0 * a.m * a.n * a.k
-    print(json.dumps({"kernel": "gemm_tcgen05", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "ms": ms,
+    print(json.dumps({"kernel": "gemm_tcgen05", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "pair": a.pair, "ms": ms,
                       "tflops": fl / ms / 1e9, "cublas_ms": ref, "cublas_tflops": fl / ref / 1e9}))
 
 
@@ -187,7 +187,7 @@ def main():
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=4096); g.add_argument("--dtype", default="bf16")
-    g.add_argument("--bn", type=int, default=0); g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--bn", type=int, default=0); g.add_argument("--pair", type=int, default=0); g.add_argument("--iters", type=int, default=20)
     s = sub.add_parser("sync")
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)

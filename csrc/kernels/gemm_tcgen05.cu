@@ -19,6 +19,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 
 #include "act.cuh"
@@ -206,17 +207,26 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
   }
 }
 
-template <int ESIZE, int BN>
+// PAIR = true: two CTAs of a cluster work on one 256 x BN tile (tcgen05 cta_group::2). Each CTA stages its own
+// 128 rows of A and its own BN/2 rows of B, so every byte of B crosses L2 -> SM once per pair instead of
+// once per CTA; the leader CTA (cluster rank 0) issues the MMAs for both, each CTA drains its own TMEM.
+template <int ESIZE, int BN, bool PAIR>
 __global__ void __launch_bounds__(192, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmDev p) {
-  constexpr int BM = 128;
+  constexpr int BM = 128;              // rows per CTA
+  constexpr int TILE_M = PAIR ? 256 : 128;
   constexpr int BK = 128 / ESIZE;      // one 128-byte swizzle row of K per stage
   constexpr int UMMA_K = 32 / ESIZE;   // 8 for tf32, 16 for bf16
   constexpr int KSTEPS = BK / UMMA_K;  // 4
-  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = TileCfg<BN>::STAGES;
+  constexpr int BN_CTA = PAIR ? BN / 2 : BN;   // rows of B staged by one CTA
+  constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_CTA * 128, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
   constexpr uint32_t TMEM_COLS = TileCfg<BN>::TMEM_COLS;
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const bool leader = crank == 0u;
+  const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;      // CTA or CTA pair
+  const int units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -242,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 128);
+      mbar_init(&tmem_empty_bar[b], PAIR ? 256 : 128);   // the leader's barrier counts both CTAs' epilogue threads
     }
     mbar_init(&drain_bar, 1);
     abort_flag = 0;
@@ -254,15 +264,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (p.tma_out) tma_prefetch_desc(&tmC);
   }
   if (warp == 5) {
-    tmem_alloc(&tmem_base_smem, TMEM_COLS);
-    tmem_relinquish();
+    if (PAIR) { tmem_alloc_pair(&tmem_base_smem, TMEM_COLS); tmem_relinquish_pair(); }
+    else { tmem_alloc(&tmem_base_smem, TMEM_COLS); tmem_relinquish(); }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything is signalled across CTAs
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
 
-  const int num_m = (p.M + BM - 1) / BM;
+  const int num_m = (p.M + TILE_M - 1) / TILE_M;
   const int num_n = (p.N + BN - 1) / BN;
   const int total_tiles = num_m * num_n;
   const int KB = (p.K + BK - 1) / BK;
@@ -279,10 +290,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x) {
+      for (int work = unit; work < total_work && ok; work += units) {
         const int tile = work / SPLITS, split = work % SPLITS;
-        const int m0 = (tile % num_m) * BM;
-        const int n0 = (tile / num_m) * BN;
+        const int m0 = (tile % num_m) * TILE_M + (int)crank * BM;
+        const int n0 = (tile / num_m) * BN + (int)crank * (PAIR ? BN_CTA : 0);
         const int kb0 = split * KB_PER, kb1 = min(KB, kb0 + KB_PER);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abortp, budget)) {
@@ -290,19 +301,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             ok = false;
             break;
           }
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          // pair: both CTAs' copies complete on the leader's barrier, which expects the bytes of both
+          if (!PAIR) mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          else if (leader) mbar_expect_tx(&full_bar[stage], 2u * STAGE_BYTES);
+          const uint32_t full_remote = PAIR ? mapa_shared(smem_u32(&full_bar[stage]), 0u) : 0u;
           uint8_t* sa = smem + (size_t)stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           const int k0 = kb * BK;
           for (int i = 0; i < p.a.n_box; ++i) {
             const int mn = m0 + i * p.a.box_mn;
-            tma_load_2d(sa + i * p.a.box_stride_bytes, &tmA, &full_bar[stage],
-                        p.a.mn_major ? mn : k0, p.a.mn_major ? k0 : mn);
+            if (PAIR) tma_load_2d_pair(sa + i * p.a.box_stride_bytes, &tmA, full_remote,
+                                       p.a.mn_major ? mn : k0, p.a.mn_major ? k0 : mn);
+            else tma_load_2d(sa + i * p.a.box_stride_bytes, &tmA, &full_bar[stage],
+                             p.a.mn_major ? mn : k0, p.a.mn_major ? k0 : mn);
           }
           for (int i = 0; i < p.b.n_box; ++i) {
             const int mn = n0 + i * p.b.box_mn;
-            tma_load_2d(sb + i * p.b.box_stride_bytes, &tmB, &full_bar[stage],
-                        p.b.mn_major ? mn : k0, p.b.mn_major ? k0 : mn);
+            if (PAIR) tma_load_2d_pair(sb + i * p.b.box_stride_bytes, &tmB, full_remote,
+                                       p.b.mn_major ? mn : k0, p.b.mn_major ? k0 : mn);
+            else tma_load_2d(sb + i * p.b.box_stride_bytes, &tmB, &full_bar[stage],
+                             p.b.mn_major ? mn : k0, p.b.mn_major ? k0 : mn);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -314,13 +332,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 5) {
-    if (lane == 0) {
-      // ---------------- MMA issuer ----------------
+    if (lane == 0 && leader) {
+      // ---------------- MMA issuer (the pair's leader issues for both CTAs) ----------------
       int stage = 0;
       uint32_t phase = 0;
       int t = 0;
       bool ok = true;
-      for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x, ++t) {
+      for (int work = unit; work < total_work && ok; work += units, ++t) {
         const int split = work % SPLITS;
         const int kb0 = split * KB_PER, kb1 = min(KB, kb0 + KB_PER);
         const int buf = t & 1;
@@ -347,16 +365,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 make_smem_desc_sw128(a_addr + k * p.a.kstep_bytes, p.a.lbo_bytes, p.a.sbo_bytes);
             const uint64_t bdesc =
                 make_smem_desc_sw128(b_addr + k * p.b.kstep_bytes, p.b.lbo_bytes, p.b.sbo_bytes);
-            if (ESIZE == 4) umma_tf32(d_tmem, adesc, bdesc, p.idesc, (kb != kb0) || (k != 0));
-            else umma_f16(d_tmem, adesc, bdesc, p.idesc, (kb != kb0) || (k != 0));
+            const uint32_t acc = (kb != kb0) || (k != 0);
+            if (PAIR) {
+              if (ESIZE == 4) umma_tf32_pair(d_tmem, adesc, bdesc, p.idesc, acc);
+              else umma_f16_pair(d_tmem, adesc, bdesc, p.idesc, acc);
+            } else {
+              if (ESIZE == 4) umma_tf32(d_tmem, adesc, bdesc, p.idesc, acc);
+              else umma_f16(d_tmem, adesc, bdesc, p.idesc, acc);
+            }
           }
-          umma_commit(&empty_bar[stage]);  // the stage is free once these MMAs have read it
+          // the stage is free (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) umma_commit_pair_mc(&empty_bar[stage], 3);
+          else umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit(&tmem_full_bar[buf]);
+        if (ok) {
+          if (PAIR) umma_commit_pair_mc(&tmem_full_bar[buf], 3);
+          else umma_commit(&tmem_full_bar[buf]);
+        }
       }
       // Make sure no MMA is still running before TMEM is released.
-      umma_commit(&drain_bar);
+      if (PAIR) umma_commit_pair(&drain_bar);
+      else umma_commit(&drain_bar);
       mbar_wait_bounded(&drain_bar, 0, abortp, ok ? budget : 1000000ull);
     }
   } else {
@@ -364,9 +394,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int t = 0;
     bool ok = true;
     uint32_t cchunk = 0;  // staged chunks so far: alternates the two staging tiles across tiles too
-    for (int work = blockIdx.x; work < total_work && ok; work += gridDim.x, ++t) {
+    const uint32_t tmem_empty_remote[2] = {PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[0]), 0u) : 0u,
+                                           PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[1]), 0u) : 0u};
+    for (int work = unit; work < total_work && ok; work += units, ++t) {
       const int tile = work / SPLITS;
-      const int m0 = (tile % num_m) * BM;
+      const int m0 = (tile % num_m) * TILE_M + (int)crank * BM;
       const int n0 = (tile / num_m) * BN;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
@@ -448,16 +480,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty_bar[buf]);
+      if (PAIR) mbar_arrive_cluster(tmem_empty_remote[buf]);
+      else mbar_arrive(&tmem_empty_bar[buf]);
     }
     if (p.tma_out && threadIdx.x == 0) tma_store_wait_all<0>();  // global writes done before exit
   }
 
   tc_fence_before();
   __syncthreads();
+  // pair: neither CTA retires its shared memory, barriers or TMEM while the other may still touch them
+  if (PAIR) cluster_sync_all();
   if (warp == 5) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (PAIR) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -562,22 +598,58 @@ static int num_sms() {
   return g_num_sms;
 }
 
-template <int ESIZE, int BN>
+template <int ESIZE, int BN, bool PAIR>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmDev& p, int max_ctas,
                   cudaStream_t stream) {
-  constexpr int STAGES = TileCfg<BN>::STAGES;
-  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN * 128) + 2 * 16384 + 1024;
+  constexpr int BN_CTA = PAIR ? BN / 2 : BN;
+  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
+  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN_CTA * 128) + 2 * 16384 + 1024;
   static bool attr_set = false;
-  auto kern = gemm_tcgen05_kernel<ESIZE, BN>;
+  static int max_pairs = 0;
+  auto kern = gemm_tcgen05_kernel<ESIZE, BN, PAIR>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return -6; }
+    if (PAIR) {
+      // how many 2-CTA clusters the device can hold at once (an SM count that is odd inside a GPC loses one)
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3(2 * num_sms());
+      q.blockDim = dim3(192);
+      q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      q.attrs = at;
+      q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) { cudaGetLastError(); n = num_sms() / 2; }
+      max_pairs = n;
+    }
     attr_set = true;
   }
-  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN) * (p.split_k > 1 ? p.split_k : 1);
-  int grid = max_ctas > 0 ? max_ctas : num_sms();
-  if (grid > tiles) grid = tiles;
-  kern<<<grid, 192, smem, stream>>>(ta, tb, tc, p);
+  const int tile_m = PAIR ? 256 : 128;
+  const int tiles = ((p.M + tile_m - 1) / tile_m) * ((p.N + BN - 1) / BN) * (p.split_k > 1 ? p.split_k : 1);
+  if (!PAIR) {
+    int grid = max_ctas > 0 ? max_ctas : num_sms();
+    if (grid > tiles) grid = tiles;
+    kern<<<grid, 192, smem, stream>>>(ta, tb, tc, p);
+  } else {
+    int pairs = max_ctas > 0 ? std::max(1, max_ctas / 2) : max_pairs;
+    if (pairs > max_pairs) pairs = max_pairs;
+    if (pairs > tiles) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+    if (le != cudaSuccess) { set_error("gemm pair launch: %s", cudaGetErrorString(le)); return -7; }
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("gemm launch: %s", cudaGetErrorString(e)); return -7; }
   return 0;
@@ -626,7 +698,9 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   CUtensorMap ta, tb;
   int rc = make_operand(&p.a, &ta, g->A, esize, g->a_major, g->M, g->K, g->lda, 128);
   if (rc) return rc;
-  rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, bn);
+  // CTA pairs: on request only for now (M must span more than one 128-row block to be worth a pair)
+  const bool pair = g->pair > 0 && bn >= 128 && g->M > 128;
+  rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, pair ? bn / 2 : bn);
   if (rc) return rc;
   // split-K (g->split_k > 1, or 0 = automatic for tall-K problems with few output tiles): only the
   // plain accumulate-into-f32 epilogue is supported, and the caller zeroes the output first.
@@ -662,14 +736,20 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   }
   const uint32_t fmt = g->dtype == ONO_TF32 ? 2u : 1u;  // TF32 / BF16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
-            ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+            ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
 
-  if (esize == 4) {
-    if (bn == 32) return launch<4, 32>(ta, tb, tc, p, g->max_ctas, stream);
-    if (bn == 128) return launch<4, 128>(ta, tb, tc, p, g->max_ctas, stream);
-    return launch<4, 256>(ta, tb, tc, p, g->max_ctas, stream);
+  if (pair) {
+    if (esize == 4) return bn == 128 ? launch<4, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
+                                     : launch<4, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
+    return bn == 128 ? launch<2, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
+                     : launch<2, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
   }
-  if (bn == 32) return launch<2, 32>(ta, tb, tc, p, g->max_ctas, stream);
-  if (bn == 128) return launch<2, 128>(ta, tb, tc, p, g->max_ctas, stream);
-  return launch<2, 256>(ta, tb, tc, p, g->max_ctas, stream);
+  if (esize == 4) {
+    if (bn == 32) return launch<4, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
+    if (bn == 128) return launch<4, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
+    return launch<4, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
+  }
+  if (bn == 32) return launch<2, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
+  if (bn == 128) return launch<2, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
+  return launch<2, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
 }

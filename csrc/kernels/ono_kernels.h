@@ -58,6 +58,7 @@ typedef struct OnoGemm {
   int max_ctas;    // 0 = one per SM
   int split_k;     // > 1: split K over that many CTAs per tile; out_f32 must be zero on entry and is
                    //      accumulated with atomics (plain f32 output only). 0 / 1 = off
+  int pair;        // CTA pairs (256-row tiles, tcgen05 cta_group::2): 0 = automatic, 1 = on, -1 = off
   OnoEpilogue epi;
   int* status;     // device int, set non-zero on an in-kernel timeout; may be null
 } OnoGemm;

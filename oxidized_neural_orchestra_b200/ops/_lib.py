@@ -27,7 +27,7 @@ class OnoGemm(C.Structure):
     _fields_ = [
         ("A", C.c_void_p), ("B", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
         ("lda", C.c_int), ("ldb", C.c_int), ("dtype", C.c_int), ("a_major", C.c_int),
-        ("b_major", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int), ("split_k", C.c_int), ("epi", OnoEpilogue),
+        ("b_major", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int), ("split_k", C.c_int), ("pair", C.c_int), ("epi", OnoEpilogue),
         ("status", C.c_void_p),
     ]
 

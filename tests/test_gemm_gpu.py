@@ -100,3 +100,46 @@ def test_gemm_epilogue(dtype):
         dout = base.clone()
         gemm(a, b, out=dout, aux=stored, dact=act, dact_param=param, beta=2.0)
         assert (dout - (dref + 2.0)).abs().max().item() < 5e-2 * max(1.0, dref.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape,bn", [((256, 256, 128), 256), ((512, 1024, 512), 256), ((300, 200, 136), 128),
+                                      ((1024, 4096, 784), 256), ((129, 257, 72), 128), ((2048, 512, 4096), 0)])
+def test_gemm_cta_pairs_k_major(dtype, shape, bn):
+    """256-row tiles on CTA pairs (cta_group::2) give the same numbers as the fp32 reference."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(3)
+    ld = lambda n: (n + 15) // 16 * 16
+    a = torch.randn(M, ld(K), device="cuda", dtype=dtype)[:, :K]
+    b = torch.randn(N, ld(K), device="cuda", dtype=dtype)[:, :K]
+    bias = torch.randn(N, device="cuda")
+    out = torch.zeros(M, ld(N), device="cuda")[:, :N]
+    ob = torch.zeros(M, ld(N), device="cuda", dtype=torch.bfloat16)[:, :N]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, b, out=out, out_bf16=ob, bias=bias, bn=bn, pair=1, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(a, b, False, False) + bias.double()
+    scale = ref.abs().max().item()
+    assert (out.double() - ref).abs().max().item() <= _tol(dtype, K) * scale
+    assert (ob.double() - ref).abs().max().item() <= 1e-2 * scale
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+def test_gemm_cta_pairs_mn_major_and_split_k(a_mn, b_mn):
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = 512, 768, 1024
+    torch.manual_seed(4)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    ref = _ref(a, b, a_mn, b_mn)
+    for split in (0, 4):
+        out = torch.zeros(M, N, device="cuda")
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, split_k=split, pair=1, status=status)
+        torch.cuda.synchronize()
+        assert status.item() == 0
+        assert (out.double() - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
