@@ -5,9 +5,10 @@
 //   warp 4 (one elected lane)  TMA producer: cp.async.bulk.tensor tiles -> 128B-swizzled smem ring
 //   warp 5 (one elected lane)  MMA issuer:   tcgen05.mma (kind::tf32 | kind::f16/bf16), f32
 //                                            accumulators in TMEM, double buffered (2 x BN columns)
-//   warps 0-3                  epilogue:     tcgen05.ld TMEM -> registers, bias / activation /
-//                                            activation-derivative / accumulate, stores (row-major
-//                                            and transposed, f32 and bf16)
+//   warps 0-3 and 6-9          epilogue:     two groups taking alternate 32-column chunks: tcgen05.ld
+//                                            TMEM -> registers, bias / activation / activation-
+//                                            derivative / accumulate, stores (row-major through a
+//                                            swizzled staging tile + TMA store, transposed, f32, bf16)
 //
 // Operands may be K-major or (bf16 only) MN-major; the difference is confined to the TMA box
 // pattern and three descriptor fields computed on the host (see make_operand()).
@@ -211,7 +212,7 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
 // 128 rows of A and its own BN/2 rows of B, so every byte of B crosses L2 -> SM once per pair instead of
 // once per CTA; the leader CTA (cluster rank 0) issues the MMAs for both, each CTA drains its own TMEM.
 template <int ESIZE, int BN, bool PAIR>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmDev p) {
   constexpr int BM = 128;              // rows per CTA
@@ -230,7 +231,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  // two 16 KB output staging tiles (128 rows x 128 B) behind the operand ring, for TMA stores
+  // eight 4 KB output staging tiles (one per epilogue warp: 32 rows x 128 B) behind the operand ring, for TMA stores
   uint8_t* cstage = smem + (size_t)STAGES * STAGE_BYTES;
 
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -252,7 +253,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], PAIR ? 256 : 128);   // the leader's barrier counts both CTAs' epilogue threads
+      mbar_init(&tmem_empty_bar[b], PAIR ? 512 : 256);   // 8 epilogue warps; a pair's leader counts both CTAs'
     }
     mbar_init(&drain_bar, 1);
     abort_flag = 0;
@@ -393,7 +394,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue warps 0..3 (TMEM lanes 32*warp .. 32*warp+31) ----------------
     int t = 0;
     bool ok = true;
-    uint32_t cchunk = 0;  // staged chunks so far: alternates the two staging tiles across tiles too
+    // Two groups of four warps (warps 0-3 and 6-9) take alternate 32-column chunks of the accumulator, each
+    // group. Every warp owns a 4 KB staging tile (its 32 rows x 32 columns) and its own TMA-store queue, so eight
+    // stores are in flight per CTA and no warp waits for another.
+    const int grp = warp >= 6 ? 1 : 0;
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
+    uint8_t* const wstage = cstage + (size_t)(grp * 4 + quad) * 4096u;
     const uint32_t tmem_empty_remote[2] = {PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[0]), 0u) : 0u,
                                            PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[1]), 0u) : 0u};
     for (int work = unit; work < total_work && ok; work += units, ++t) {
@@ -403,25 +409,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
       const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget);
-      // The four epilogue warps must agree before they meet at named barriers below.
-      uint32_t all_got;
-      asm volatile(
-          "{\n\t.reg .pred pin, pout;\n\tsetp.ne.u32 pin, %1, 0;\n\t"
-          "bar.red.and.pred pout, 1, 128, pin;\n\tselp.u32 %0, 1, 0, pout;\n\t}"
-          : "=r"(all_got)
-          : "r"((uint32_t)got)
-          : "memory");
-      if (!all_got) {
-        if (lane == 0 && !got) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row = warp * 32 + lane;
+      const int row = quad * 32 + lane;
       const int m = m0 + row;
-      const uint32_t t_row = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(buf * BN);
+      const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = grp; c < BN / 32; c += 2) {
         const int nc = n0 + c * 32;
         if (nc >= p.N) break;  // uniform across the CTA
         uint32_t r[32];
@@ -443,19 +441,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         epilogue_chunk(p.epi, v, m, nc, p.M, p.N, p.tma_out);
         if (p.tma_out) {
-          // registers -> swizzled staging tile -> one TMA store per 128 x 32 chunk; the TMA unit
+          // registers -> swizzled staging tile -> one TMA store per warp and 32 x 32 chunk; the TMA unit
           // clips rows >= M and columns >= N
-          uint8_t* stage = cstage + (size_t)(cchunk & 1u) * 16384u;
-          if (threadIdx.x == 0) tma_store_wait_read<1>();  // the store that last read this tile is done
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the tile
+          __syncwarp();
           if (p.tma_out == 1) {
-            uint8_t* rp = stage + row * 128;
+            uint8_t* rp = wstage + lane * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               *reinterpret_cast<float4*>(rp + ((j ^ (row & 7)) << 4)) =
                   make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
           } else {
-            uint8_t* rp = stage + row * 64;
+            uint8_t* rp = wstage + lane * 64;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
@@ -471,19 +468,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
           fence_proxy_async_smem();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 0) {
-            tma_store_2d(&tmC, stage, nc, m0);
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, wstage, nc, m0 + quad * 32);
             tma_store_commit();
           }
-          ++cchunk;
         }
       }
       tc_fence_before();
       if (PAIR) mbar_arrive_cluster(tmem_empty_remote[buf]);
       else mbar_arrive(&tmem_empty_bar[buf]);
     }
-    if (p.tma_out && threadIdx.x == 0) tma_store_wait_all<0>();  // global writes done before exit
+    if (p.tma_out && lane == 0) tma_store_wait_all<0>();  // global writes done before exit
   }
 
   tc_fence_before();
@@ -543,14 +539,14 @@ int encode_map_2d(CUtensorMap* map, const void* base, int esize, long long rows,
   return 0;
 }
 
-// Output tile map for the TMA-store epilogue: box = {32 columns, 128 rows}; the 128-byte (f32) or
+// Output tile map for the TMA-store epilogue: box = {32 columns, 32 rows}; the 128-byte (f32) or
 // 64-byte (bf16) rows use the matching swizzle so that the staging writes are bank-conflict free.
 static int encode_out_map(CUtensorMap* map, const void* base, int esize, long long rows, long long cols, long long ld) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { set_error("cuTensorMapEncodeTiled unavailable%s", ""); return -2; }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)(ld * esize)};
-  cuuint32_t box[2] = {32u, 128u};
+  cuuint32_t box[2] = {32u, 32u};   // one epilogue warp's rows
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -614,7 +610,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
       // how many 2-CTA clusters the device can hold at once (an SM count that is odd inside a GPC loses one)
       cudaLaunchConfig_t q = {};
       q.gridDim = dim3(2 * num_sms());
-      q.blockDim = dim3(192);
+      q.blockDim = dim3(320);
       q.dynamicSmemBytes = smem;
       cudaLaunchAttribute at[1];
       at[0].id = cudaLaunchAttributeClusterDimension;
@@ -632,14 +628,14 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   if (!PAIR) {
     int grid = max_ctas > 0 ? max_ctas : num_sms();
     if (grid > tiles) grid = tiles;
-    kern<<<grid, 192, smem, stream>>>(ta, tb, tc, p);
+    kern<<<grid, 320, smem, stream>>>(ta, tb, tc, p);
   } else {
     int pairs = max_ctas > 0 ? std::max(1, max_ctas / 2) : max_pairs;
     if (pairs > max_pairs) pairs = max_pairs;
     if (pairs > tiles) pairs = tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
-    cfg.blockDim = dim3(192);
+    cfg.blockDim = dim3(320);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute at[1];
