@@ -4,13 +4,16 @@
 //
 // Activations of image layers are 2-D matrices [B*H*W, ldc] (one row per pixel, channels contiguous),
 // which is exactly what the GEMM epilogue writes for Y = cols * K^T; the column order of `cols` is
-// (c, ky, kx), i.e. the reference's kernel layout K[F][C][k][k] is used as the GEMM operand in place.
+// (ky, kx, c) (channels fastest: coalesced gathers), so the reference's kernel layout K[F][C][k][k] is permuted
+// into that order when parameters are refreshed.
 // Semantics kept from the reference: zero padding, output size floor((H+2p-k)/s)+1 (trailing rows and
 // columns the strided window never reaches are dropped), zero padding competes in the max, and a
 // pooling gradient whose arg-max lies in the padding is dropped.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <algorithm>
 
 #include "act.cuh"
 #include "ono_kernels.h"
@@ -27,51 +30,271 @@ __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { retu
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-// cols[r, q] = x[(b, oy*s+ky-p, ox*s+kx-p), c]  with r = (b, oy, ox), q = (c, ky, kx); optional colsT.
+// Column order of `cols` is q = (ky, kx, c): channels fastest, so that both the gather below and the GEMM
+// operand rows are contiguous runs of the pixel-major input. The kernel tensor K[F][C][k][k] is permuted to
+// that order once per parameter refresh (kperm_kernel), and the weight gradient is permuted back.
+//
+// cols[r, q] = x[(b, oy*s+ky-p, ox*s+kx-p), c]  with r = (b, oy, ox); optional transposed copy colsT[q, r].
+// One block handles a 32 x 32 tile of (r, q): reads and the row-major write are coalesced along q, the
+// transposed write goes through shared memory and is coalesced along r.
 template <typename T>
 __global__ void im2col_kernel(const OnoConvGeom g, const T* x, int ldx, T* cols, int ld_cols, T* colsT, int ld_colsT) {
+  __shared__ float tile[32][33];
+  __shared__ int s_iy0[32], s_ix0[32], s_img[32];   // per tile row: window origin and image index (divisions once per row)
   const int ckk = g.C * g.K * g.K;
-  const long long total = (long long)g.B * g.OH * g.OW * ckk;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int q = (int)(i % ckk);
-    const long long r = i / ckk;
-    const int kx = q % g.K, ky = (q / g.K) % g.K, c = q / (g.K * g.K);
-    const int ox = (int)(r % g.OW), oy = (int)((r / g.OW) % g.OH), b = (int)(r / ((long long)g.OW * g.OH));
-    const int iy = oy * g.S + ky - g.P, ix = ox * g.S + kx - g.P;
-    T v = from_f32<T>(0.f);
-    if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) v = x[((long long)(b * g.H + iy) * g.W + ix) * ldx + c];
-    cols[r * ld_cols + q] = v;
-    if (colsT) colsT[(long long)q * ld_colsT + r] = v;
+  const long long rows = (long long)g.B * g.OH * g.OW;
+  const int qtiles = (ckk + 31) / 32;
+  const long long ntiles = ((rows + 31) / 32) * qtiles;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long r0 = (t / qtiles) * 32;
+    const int q0 = (int)(t % qtiles) * 32;
+    const int q = q0 + threadIdx.x;
+    const int c = q % g.C, kx = (q / g.C) % g.K, ky = q / (g.C * g.K);
+    if (threadIdx.y == 0) {
+      const long long r = r0 + threadIdx.x;
+      const int ox = (int)(r % g.OW), oy = (int)((r / g.OW) % g.OH);
+      s_iy0[threadIdx.x] = oy * g.S - g.P;
+      s_ix0[threadIdx.x] = ox * g.S - g.P;
+      s_img[threadIdx.x] = (int)(r / ((long long)g.OW * g.OH));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int rr = threadIdx.y + 8 * j;
+      const long long r = r0 + rr;
+      float v = 0.f;
+      if (r < rows && q < ckk) {
+        const int iy = s_iy0[rr] + ky, ix = s_ix0[rr] + kx;
+        if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W)
+          v = to_f32(x[((long long)(s_img[rr] * g.H + iy) * g.W + ix) * ldx + c]);
+        cols[r * ld_cols + q] = from_f32<T>(v);
+      }
+      tile[rr][threadIdx.x] = v;
+    }
+    if (colsT) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int qq = threadIdx.y + 8 * j;
+        const long long r = r0 + threadIdx.x;
+        if (r < rows && q0 + qq < ckk) colsT[(long long)(q0 + qq) * ld_colsT + r] = from_f32<T>(tile[threadIdx.x][qq]);
+      }
+      __syncthreads();
+    } else {
+      __syncthreads();   // s_* are rewritten by the next tile
+    }
   }
 }
 
-// dx[(b,iy,ix), c] = act'(aux) * sum_{ky,kx} dcols[(b,oy,ox), (c,ky,kx)] over the windows covering it.
+// dx[(b,iy,ix), c] = act'(aux) * sum_{ky,kx} dcols[(b,oy,ox), (ky,kx,c)] over the windows covering the pixel
+// (gather form: no atomics). One block handles 32 pixels x 32 channels; the optional transposed copy
+// dxT[c, pix] goes through shared memory.
 template <typename T>
 __global__ void col2im_kernel(const OnoConvGeom g, const T* dcols, int ld_dcols, const T* aux, int ld_aux, int dact,
                               float dact_param, int relu_quirk, T* dx, int ld_dx, T* dxT, int ld_dxT) {
-  const long long total = (long long)g.B * g.H * g.W * g.C;
+  __shared__ float tile[32][33];
+  __shared__ int s_iy[32], s_ix[32], s_img[32];
+  const long long npix = (long long)g.B * g.H * g.W;
+  const int ctiles = (g.C + 31) / 32;
+  const long long ntiles = ((npix + 31) / 32) * ctiles;
+  const int shift = g.S == 1 ? 0 : g.S == 2 ? 1 : g.S == 4 ? 2 : -1;   // power-of-two strides avoid the divisions
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long p0 = (t / ctiles) * 32;
+    const int c0 = (int)(t % ctiles) * 32;
+    const int c = c0 + threadIdx.x;
+    if (threadIdx.y == 0) {
+      const long long pix = p0 + threadIdx.x;
+      s_ix[threadIdx.x] = (int)(pix % g.W) + g.P;
+      s_iy[threadIdx.x] = (int)((pix / g.W) % g.H) + g.P;
+      s_img[threadIdx.x] = (int)(pix / ((long long)g.W * g.H));
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int pp = threadIdx.y + 8 * j;
+      const long long pix = p0 + pp;
+      float acc = 0.f;
+      if (pix < npix && c < g.C) {
+        const int ixp = s_ix[pp], iyp = s_iy[pp];
+        const long long img_row = (long long)s_img[pp] * g.OH;
+        for (int ky = 0; ky < g.K; ++ky) {
+          const int ty = iyp - ky;
+          if (ty < 0) break;
+          int oy;
+          if (shift >= 0) { if (ty & (g.S - 1)) continue; oy = ty >> shift; }
+          else { if (ty % g.S) continue; oy = ty / g.S; }
+          if (oy >= g.OH) continue;
+          const T* rowp = dcols + (img_row + oy) * g.OW * (long long)ld_dcols + (ky * g.K) * g.C + c;
+          for (int kx = 0; kx < g.K; ++kx) {
+            const int tx = ixp - kx;
+            if (tx < 0) break;
+            int ox;
+            if (shift >= 0) { if (tx & (g.S - 1)) continue; ox = tx >> shift; }
+            else { if (tx % g.S) continue; ox = tx / g.S; }
+            if (ox >= g.OW) continue;
+            acc += to_f32(rowp[(long long)ox * ld_dcols + kx * g.C]);
+          }
+        }
+        if (dact != ACT_NONE) acc = act_bwd(dact, dact_param, relu_quirk, to_f32(aux[pix * ld_aux + c]), acc);
+        dx[pix * ld_dx + c] = from_f32<T>(acc);
+      }
+      tile[pp][threadIdx.x] = acc;
+    }
+    if (dxT) {
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int cc = threadIdx.y + 8 * j;
+        const long long pix = p0 + threadIdx.x;
+        if (pix < npix && c0 + cc < g.C) dxT[(long long)(c0 + cc) * ld_dxT + pix] = from_f32<T>(tile[threadIdx.x][cc]);
+      }
+      __syncthreads();
+    } else {
+      __syncthreads();
+    }
+  }
+}
+
+// Kernel tensor between the parameter layout K[F][C][k][k] (f32, contiguous) and the operand layout
+// [F][(ky,kx,c)] used by the GEMMs. dir 0: parameters -> operand (dst, dtype T, leading dimension ld_dst) and
+// optionally its transpose dstT[(ky,kx,c)][F]; dir 1: f32 operand-ordered gradient (src, ld_src) -> parameter
+// order, dst = beta * dst + src.
+template <typename T>
+__global__ void kperm_kernel(int F, int C, int K, int dir, const float* src, int ld_src, void* dst_, int ld_dst, T* dstT,
+                             int ld_dstT, float beta) {
+  const int ckk = C * K * K;
+  const long long total = (long long)F * ckk;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int c = (int)(i % g.C);
-    const long long pix = i / g.C;
-    const int ix = (int)(pix % g.W), iy = (int)((pix / g.W) % g.H), b = (int)(pix / ((long long)g.W * g.H));
-    float acc = 0.f;
-    for (int ky = 0; ky < g.K; ++ky) {
-      const int ty = iy + g.P - ky;
-      if (ty < 0 || ty % g.S) continue;
-      const int oy = ty / g.S;
-      if (oy >= g.OH) continue;
-      for (int kx = 0; kx < g.K; ++kx) {
-        const int tx = ix + g.P - kx;
-        if (tx < 0 || tx % g.S) continue;
-        const int ox = tx / g.S;
-        if (ox >= g.OW) continue;
-        acc += to_f32(dcols[((long long)(b * g.OH + oy) * g.OW + ox) * ld_dcols + (c * g.K + ky) * g.K + kx]);
+    const int f = (int)(i / ckk), q = (int)(i % ckk);                   // q in operand order (ky, kx, c)
+    const int c = q % C, kx = (q / C) % K, ky = q / (C * K);
+    const long long pidx = ((long long)(f * C + c) * K + ky) * K + kx;    // parameter order
+    if (dir == 0) {
+      const float v = src[pidx];
+      reinterpret_cast<T*>(dst_)[(long long)f * ld_dst + q] = from_f32<T>(v);
+      if (dstT) dstT[(long long)q * ld_dstT + f] = from_f32<T>(v);
+    } else {
+      float* d = reinterpret_cast<float*>(dst_);
+      const float v = src[(long long)f * ld_src + q];
+      d[pidx] = beta != 0.f ? beta * d[pidx] + v : v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Single-input-channel convolution (the first layer of every image model of the reference), computed
+// directly on CUDA cores: with C = 1 the GEMM would have K = k*k <= 25, far too short for the tensor
+// cores, and im2col would write k*k times the input. Thread x = filter, thread y strides over output
+// pixels; the k*k taps of a pixel are broadcast loads, the filter's weights live in registers.
+// ------------------------------------------------------------------------------------------------
+constexpr int C1_MAXKK = 25;  // up to 5 x 5 kernels
+
+template <typename T>
+__global__ void conv1_fwd_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const float* kparams, const float* bias,
+                                 int act, float act_param, T* y, int ldy) {
+  const int kk = g.K * g.K;
+  const int f = blockIdx.y * 32 + threadIdx.x;
+  float w[C1_MAXKK];
+#pragma unroll
+  for (int i = 0; i < C1_MAXKK; ++i) w[i] = (i < kk && f < F) ? kparams[(long long)f * kk + i] : 0.f;
+  const float bv = (bias && f < F) ? bias[f] : 0.f;
+  // A warp takes 32 consecutive output pixels: lane l works out the window origin of pixel r0 + l once (the
+  // divisions), then the warp walks the 32 pixels with the coordinates broadcast by shuffles.
+  const int rows = g.B * g.OH * g.OW;
+  const int ohw = g.OH * g.OW;
+  for (int r0 = (blockIdx.x * blockDim.y + threadIdx.y) * 32; r0 < rows; r0 += gridDim.x * blockDim.y * 32) {
+    const int rl = min(r0 + (int)threadIdx.x, rows - 1);
+    const int img_l = rl / ohw, rem = rl - img_l * ohw;
+    const int oy_l = rem / g.OW, ox_l = rem - oy_l * g.OW;
+    const int my_iy0 = oy_l * g.S - g.P, my_ix0 = ox_l * g.S - g.P, my_base = img_l * g.H;
+    const int np = min(32, rows - r0);
+    for (int pp = 0; pp < np; ++pp) {
+      const int iy0 = __shfl_sync(0xffffffffu, my_iy0, pp), ix0 = __shfl_sync(0xffffffffu, my_ix0, pp);
+      const int base = __shfl_sync(0xffffffffu, my_base, pp);
+      float acc = bv;
+#pragma unroll
+      for (int i = 0; i < C1_MAXKK; ++i) {
+        if (i >= kk) break;
+        const int ky = i / g.K, kx = i - ky * g.K;
+        const int iy = iy0 + ky, ix = ix0 + kx;
+        if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) acc += w[i] * to_f32(x[(long long)((base + iy) * g.W + ix) * ldx]);
+      }
+      if (f < F) y[(long long)(r0 + pp) * ldy + f] = from_f32<T>(act_fwd(act, act_param, acc));
+    }
+  }
+}
+
+// dK[f][ky][kx] = sum over output pixels dy[r][f] * x[tap], db[f] = sum dy[r][f]. Every block writes one row of
+// partial sums to a scratch array; the last block to finish (atomic ticket) adds the rows in block order, so the
+// result does not depend on scheduling. Calls must not overlap on the device (one training stream).
+constexpr int C1_MAXBLOCKS = 592;
+constexpr int C1_MAXF = 128;
+__device__ float g_c1_part[C1_MAXBLOCKS * C1_MAXF * (C1_MAXKK + 1)];
+__device__ unsigned int g_c1_ticket;
+
+template <typename T>
+__global__ void conv1_wgrad_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const T* dy, int ld_dy, float* gk,
+                                   float* gb, float beta) {
+  __shared__ float red[8][32][C1_MAXKK + 2];
+  __shared__ int s_last;
+  const int kk = g.K * g.K;
+  const int nfb = (F + 31) / 32;
+  float acc[C1_MAXKK + 1];
+  const int rows = g.B * g.OH * g.OW;
+  const int ohw = g.OH * g.OW;
+  for (int fb = 0; fb < nfb; ++fb) {
+    const int f = fb * 32 + threadIdx.x;
+#pragma unroll
+    for (int i = 0; i <= C1_MAXKK; ++i) acc[i] = 0.f;
+    for (int r0 = (blockIdx.x * blockDim.y + threadIdx.y) * 32; r0 < rows; r0 += gridDim.x * blockDim.y * 32) {
+      const int rl = min(r0 + (int)threadIdx.x, rows - 1);
+      const int img_l = rl / ohw, rem = rl - img_l * ohw;
+      const int oy_l = rem / g.OW, ox_l = rem - oy_l * g.OW;
+      const int my_iy0 = oy_l * g.S - g.P, my_ix0 = ox_l * g.S - g.P, my_base = img_l * g.H;
+      const int np = min(32, rows - r0);
+      for (int pp = 0; pp < np; ++pp) {
+        const int iy0 = __shfl_sync(0xffffffffu, my_iy0, pp), ix0 = __shfl_sync(0xffffffffu, my_ix0, pp);
+        const int base = __shfl_sync(0xffffffffu, my_base, pp);
+        const float d = f < F ? to_f32(dy[(long long)(r0 + pp) * ld_dy + f]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < C1_MAXKK; ++i) {
+          if (i >= kk) break;
+          const int ky = i / g.K, kx = i - ky * g.K;
+          const int iy = iy0 + ky, ix = ix0 + kx;
+          if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) acc[i] += d * to_f32(x[(long long)((base + iy) * g.W + ix) * ldx]);
+        }
+        acc[C1_MAXKK] += d;
       }
     }
-    if (dact != ACT_NONE) acc = act_bwd(dact, dact_param, relu_quirk, to_f32(aux[pix * ld_aux + c]), acc);
-    dx[pix * ld_dx + c] = from_f32<T>(acc);
-    if (dxT) dxT[(long long)c * ld_dxT + pix] = from_f32<T>(acc);
+#pragma unroll
+    for (int i = 0; i <= C1_MAXKK; ++i) red[threadIdx.y][threadIdx.x][i] = acc[i];
+    __syncthreads();
+    if (threadIdx.y == 0 && f < F) {
+      float* out = g_c1_part + ((size_t)blockIdx.x * C1_MAXF + f) * (C1_MAXKK + 1);
+      for (int i = 0; i <= C1_MAXKK; ++i) {
+        if (i >= kk && i != C1_MAXKK) continue;
+        float t = 0.f;
+#pragma unroll
+        for (int yy = 0; yy < 8; ++yy) t += red[yy][threadIdx.x][i];
+        out[i] = t;
+      }
+    }
+    __syncthreads();
   }
+  __threadfence();
+  if (threadIdx.x == 0 && threadIdx.y == 0) s_last = atomicAdd(&g_c1_ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const int per = kk + 1;
+  for (int idx = threadIdx.y * 32 + threadIdx.x; idx < F * per; idx += 256) {
+    const int f = idx / per, i = idx % per;
+    const int slot = i < kk ? i : C1_MAXKK;
+    float t = 0.f;
+    for (unsigned b = 0; b < gridDim.x; ++b) t += __ldcg(&g_c1_part[((size_t)b * C1_MAXF + f) * (C1_MAXKK + 1) + slot]);
+    float* dst = i < kk ? gk + (long long)f * kk + i : gb + f;
+    *dst = beta != 0.f ? beta * (*dst) + t : t;
+  }
+  if (threadIdx.x == 0 && threadIdx.y == 0) g_c1_ticket = 0u;
 }
 
 // y[(b,oy,ox), c] = max over the window of the zero-padded input; arg[...] = input pixel (iy*W+ix) of the
@@ -181,19 +404,58 @@ typedef __nv_bfloat16 bf16;
 extern "C" int ono_im2col(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* cols, int ld_cols, void* colsT,
                           int ld_colsT, ono_stream_t st) {
   const long long n = (long long)g->B * g->OH * g->OW * g->C * g->K * g->K;
+  const dim3 blk(32, 8);
+  const int grid = grid_of(n / 4);
   ONO_DISPATCH(dtype,
-               (im2col_kernel<float><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(*g, (const float*)x, ldx, (float*)cols, ld_cols, (float*)colsT, ld_colsT)),
-               (im2col_kernel<bf16><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(*g, (const bf16*)x, ldx, (bf16*)cols, ld_cols, (bf16*)colsT, ld_colsT)))
+               (im2col_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const float*)x, ldx, (float*)cols, ld_cols, (float*)colsT, ld_colsT)),
+               (im2col_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const bf16*)x, ldx, (bf16*)cols, ld_cols, (bf16*)colsT, ld_colsT)))
   return done("im2col");
 }
 
 extern "C" int ono_col2im(const OnoConvGeom* g, int dtype, const void* dcols, int ld_dcols, const void* aux, int ld_aux,
                           int dact, float dact_param, int relu_quirk, void* dx, int ld_dx, void* dxT, int ld_dxT, ono_stream_t st) {
-  const long long n = (long long)g->B * g->H * g->W * g->C;
+  const long long n = (long long)g->B * g->H * g->W * ((g->C + 31) / 32 * 32);
+  const dim3 blk(32, 8);
+  const int grid = grid_of(n / 4);
   ONO_DISPATCH(dtype,
-               (col2im_kernel<float><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(*g, (const float*)dcols, ld_dcols, (const float*)aux, ld_aux, dact, dact_param, relu_quirk, (float*)dx, ld_dx, (float*)dxT, ld_dxT)),
-               (col2im_kernel<bf16><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(*g, (const bf16*)dcols, ld_dcols, (const bf16*)aux, ld_aux, dact, dact_param, relu_quirk, (bf16*)dx, ld_dx, (bf16*)dxT, ld_dxT)))
+               (col2im_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const float*)dcols, ld_dcols, (const float*)aux, ld_aux, dact, dact_param, relu_quirk, (float*)dx, ld_dx, (float*)dxT, ld_dxT)),
+               (col2im_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const bf16*)dcols, ld_dcols, (const bf16*)aux, ld_aux, dact, dact_param, relu_quirk, (bf16*)dx, ld_dx, (bf16*)dxT, ld_dxT)))
   return done("col2im");
+}
+
+extern "C" int ono_conv1_fwd(const OnoConvGeom* g, int F, int dtype, const void* x, int ldx, const float* kparams, const float* bias,
+                             int act, float act_param, void* y, int ldy, ono_stream_t st) {
+  if (!g || g->C != 1 || g->K * g->K > C1_MAXKK || F <= 0) { set_error("conv1_fwd: needs one input channel and k <= 5%s", "", 0, 0); return -1; }
+  const long long rows = (long long)g->B * g->OH * g->OW;
+  if (rows >= (1ll << 31)) { set_error("conv1_fwd: too many output pixels%s", "", 0, 0); return -1; }
+  const dim3 blk(32, 8), grid((unsigned)std::min<long long>((rows + 255) / 256, 148 * 8), (F + 31) / 32);
+  ONO_DISPATCH(dtype,
+               (conv1_fwd_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
+               (conv1_fwd_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))
+  return done("conv1_fwd");
+}
+
+extern "C" int ono_conv1_wgrad(const OnoConvGeom* g, int F, int dtype, const void* x, int ldx, const void* dy, int ld_dy, float* gk,
+                               float* gb, float beta, ono_stream_t st) {
+  if (!g || g->C != 1 || g->K * g->K > C1_MAXKK || F <= 0 || F > C1_MAXF) { set_error("conv1_wgrad: needs one input channel, k <= 5, F <= 128%s", "", 0, 0); return -1; }
+  const long long rows = (long long)g->B * g->OH * g->OW;
+  const dim3 blk(32, 8);
+  if (rows >= (1ll << 31)) { set_error("conv1_wgrad: too many output pixels%s", "", 0, 0); return -1; }
+  const int grid = (int)std::min<long long>((rows + 255) / 256, C1_MAXBLOCKS);
+  ONO_DISPATCH(dtype,
+               (conv1_wgrad_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy, gk, gb, beta)),
+               (conv1_wgrad_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy, gk, gb, beta)))
+  return done("conv1_wgrad");
+}
+
+extern "C" int ono_conv_kperm(int F, int C, int K, int dir, int dtype, const float* src, int ld_src, void* dst, int ld_dst,
+                              void* dstT, int ld_dstT, float beta, ono_stream_t st) {
+  if (F <= 0 || C <= 0 || K <= 0 || !src || !dst) { set_error("bad kperm args%s", "", 0, 0); return -1; }
+  const long long n = (long long)F * C * K * K;
+  ONO_DISPATCH(dtype,
+               (kperm_kernel<float><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(F, C, K, dir, src, ld_src, dst, ld_dst, (float*)dstT, ld_dstT, beta)),
+               (kperm_kernel<bf16><<<grid_of(n), 256, 0, (cudaStream_t)st>>>(F, C, K, dir, src, ld_src, dst, ld_dst, (bf16*)dstT, ld_dstT, beta)))
+  return done("conv_kperm");
 }
 
 extern "C" int ono_pool_fwd(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* y, int ldy, void* yT, int ld_yT,

@@ -141,6 +141,16 @@ int ono_im2col(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* co
                int ld_colsT, ono_stream_t stream);
 int ono_col2im(const OnoConvGeom* g, int dtype, const void* dcols, int ld_dcols, const void* aux, int ld_aux, int dact,
                float dact_param, int relu_quirk, void* dx, int ld_dx, void* dxT, int ld_dxT, ono_stream_t stream);
+// Direct convolution for a single input channel (k <= 5, at most 128 filters for the gradient): forward with bias + activation, and the weight + bias gradient
+// (deterministic two-stage reduction; gk = beta*gk + dK in parameter order [F][k][k], gb likewise).
+int ono_conv1_fwd(const OnoConvGeom* g, int F, int dtype, const void* x, int ldx, const float* kparams, const float* bias, int act,
+                  float act_param, void* y, int ldy, ono_stream_t st);
+int ono_conv1_wgrad(const OnoConvGeom* g, int F, int dtype, const void* x, int ldx, const void* dy, int ld_dy, float* gk, float* gb,
+                    float beta, ono_stream_t st);
+// Kernel tensor K[F][C][k][k] (f32) <-> GEMM operand order [F][(ky,kx,c)]: dir 0 parameters -> operand (dtype of dst and
+// dstT: 0 f32, 1 bf16; dstT optional, [(ky,kx,c)][F]); dir 1 operand-ordered f32 gradient -> parameter order, dst = beta*dst + src.
+int ono_conv_kperm(int F, int C, int K, int dir, int dtype, const float* src, int ld_src, void* dst, int ld_dst, void* dstT,
+                   int ld_dstT, float beta, ono_stream_t st);
 int ono_pool_fwd(const OnoConvGeom* g, int dtype, const void* x, int ldx, void* y, int ldy, void* yT, int ld_yT, int* arg,
                  int act, float act_param, ono_stream_t stream);
 int ono_pool_bwd(const OnoConvGeom* g, int dtype, const void* d, int ldd, const void* y, int ldy, const int* arg, int act,

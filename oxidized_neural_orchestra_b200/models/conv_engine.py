@@ -4,8 +4,9 @@ The reference runs ``Conv2d`` as per-sample im2col + GEMM and ``MaxPooling`` as 
 (machine_learning/src/arch/layers/conv/conv2d.rs:61-190, arch/layers/max_pooling.rs:47-157). Here a
 convolution is one batched tcgen05 GEMM ``cols[B*oh*ow, C*k*k] @ K[F, C*k*k]^T`` with bias and activation
 in its epilogue, the weight gradient a split-K GEMM over all output pixels of the batch, the input
-gradient a GEMM followed by a gather-form col2im; the kernel tensor ``K[F][C][k][k]`` is used in place
-from the flat parameter vector. Image activations are pixel-major ``[B*H*W, ld]``; the flattened
+gradient a GEMM followed by a gather-form col2im. Columns are ordered (ky, kx, c) - channels fastest - so
+that the gathers read and write contiguous runs; the kernel tensor ``K[F][C][k][k]`` is permuted into that
+order at every parameter refresh and the weight gradient is permuted back into the flat gradient vector. Image activations are pixel-major ``[B*H*W, ld]``; the flattened
 NCHW order dense layers expect is restored by one conversion kernel at the conv -> dense boundary.
 
 Supported model shape: ``(conv | max_pooling)* dense+`` - every model of the reference.
@@ -78,6 +79,10 @@ class ConvNetEngine:
             if d["kind"] == "conv":
                 ckk = d["C"] * d["K"] * d["K"]
                 d["ckk"] = ckk
+                # first layer with one input channel: direct CUDA-core kernels (K = k*k is too short for the tensor cores)
+                d["direct"] = j == 0 and d["C"] == 1 and d["K"] <= 5 and d["F"] <= 128
+                if d["direct"]:
+                    continue
                 d["cols"] = z(Mout, _up(ckk))
                 d["dcols"] = z(Mout, _up(ckk)) if j > 0 else None
                 d["gk_tmp"] = z(d["F"], _up(ckk), torch.float32)
@@ -85,12 +90,8 @@ class ConvNetEngine:
                     d["colsT"] = z(ckk, _up(Mout))
                     d["dyT"] = z(d["F"], _up(Mout))
                     d["kt"] = z(ckk, _up(d["F"]))                     # K^T for dgrad
-                mult = 8 if self.bf16 else 4
-                flat = self.params_bf16 if self.bf16 else self.params
-                direct = flat is not None and ckk % mult == 0 and d["off"] % mult == 0 and \
-                    (flat.data_ptr() + d["off"] * flat.element_size()) % 16 == 0
-                d["k_direct"] = direct
-                d["kop"] = flat[d["off"]:d["off"] + d["F"] * ckk].view(d["F"], ckk) if direct else z(d["F"], _up(ckk))[:, :ckk]
+                # the kernel tensor as a GEMM operand: rows in (ky, kx, c) order, rebuilt at every refresh
+                d["kop"] = z(d["F"], _up(ckk))[:, :ckk]
             else:
                 d["arg"] = torch.zeros(Mout, d["C"], device=dev, dtype=torch.int32)
                 d["dx32"] = z(Min, _up(d["C"]), torch.float32)
@@ -107,19 +108,11 @@ class ConvNetEngine:
     def refresh(self, stream=None) -> int:
         n = 0
         for d in self.front:
-            if d["kind"] != "conv":
+            if d["kind"] != "conv" or d.get("direct"):
                 continue
-            k = self._k_view(d)
-            if self.bf16:
-                if not d["k_direct"]:
-                    ew.rows(k, dst_bf16=d["kop"], stream=stream)
-                    n += 1
-            else:
-                if d["k_direct"]:
-                    ew.rows(k, dst_t=d["kt"][:, :d["F"]], stream=stream)
-                else:
-                    ew.rows(k, dst=d["kop"], dst_t=d["kt"][:, :d["F"]], stream=stream)
-                n += 1
+            cv.kernel_to_operand(d["F"], d["C"], d["K"], self._k_view(d), d["kop"],
+                                 None if self.bf16 else d["kt"][:, :d["F"]], stream=stream)
+            n += 1
         return n + self.dense.refresh(stream)
 
     def _act(self, d):
@@ -143,7 +136,10 @@ class ConvNetEngine:
             Mout = nrows * d["OH"] * d["OW"]
             g = cv.geom(nrows, d["C"], d["H"], d["W"], d["K"], d["S"], d["P"])
             act, ap = self._act(d)
-            if d["kind"] == "conv":
+            if d["kind"] == "conv" and d.get("direct"):
+                cv.conv1_fwd(g, d["F"], cur, self._k_view(d), self._kb_view(d), d["y"], act=act, act_param=ap, stream=stream)
+                n += 1
+            elif d["kind"] == "conv":
                 cv.im2col(g, cur, d["cols"], None if self.bf16 else d["colsT"], stream=stream)
                 kw = dict(bias=self._kb_view(d), act=act, act_param=ap, status=self.status, stream=stream)
                 if self.bf16:
@@ -167,7 +163,7 @@ class ConvNetEngine:
         de = self.dense
         last = self.front[-1]
         act, ap = self._act(last) if last["kind"] == "conv" else (None, 0.0)
-        want_t = (not self.bf16) and last["kind"] == "conv"
+        want_t = (not self.bf16) and last["kind"] == "conv" and not last.get("direct")
         cv.nchw_flat(nrows, last["F"], last["OH"] * last["OW"], False, last["dy"], de.d[0],
                      out_t=last["dyT"] if want_t else None, aux=last["y"], dact=act, dact_param=ap,
                      relu_quirk=self.relu_quirk, stream=stream)
@@ -178,8 +174,13 @@ class ConvNetEngine:
             Mout, Min = nrows * d["OH"] * d["OW"], nrows * d["H"] * d["W"]
             g = cv.geom(nrows, d["C"], d["H"], d["W"], d["K"], d["S"], d["P"])
             pact, pap = (self._act(prev) if (prev is not None and prev["kind"] == "conv") else (None, 0.0))
-            prev_t = prev is not None and prev["kind"] == "conv" and not self.bf16
-            if d["kind"] == "conv":
+            prev_t = prev is not None and prev["kind"] == "conv" and not self.bf16 and not prev.get("direct")
+            if d["kind"] == "conv" and d.get("direct"):
+                F, ckk = d["F"], d["ckk"]
+                cv.conv1_wgrad(g, F, self.x0, d["dy"], self.grads[d["off"]:d["off"] + F * ckk],
+                               self.grads[d["off"] + F * ckk:d["off"] + d["n"]], beta=1.0 if accumulate else 0.0, stream=stream)
+                n += 1
+            elif d["kind"] == "conv":
                 F, ckk = d["F"], d["ckk"]
                 dy = d["dy"][:Mout, :F]
                 if prev is not None:
@@ -201,11 +202,8 @@ class ConvNetEngine:
                 else:
                     gemm(d["dyT"][:, :Mout], d["colsT"][:, :Mout], out=tmp[:, :ckk], split_k=split, status=self.status,
                          stream=stream)
-                gk = self.grads[d["off"]:d["off"] + F * ckk].view(F, ckk)
-                if accumulate:
-                    gk.add_(tmp[:, :ckk])
-                else:
-                    ew.rows(tmp[:, :ckk], dst=gk, stream=stream)
+                gk = self.grads[d["off"]:d["off"] + F * ckk]
+                cv.operand_grad_to_kernel(F, d["C"], d["K"], tmp[:, :ckk], gk, beta=1.0 if accumulate else 0.0, stream=stream)
                 ew.colsum(dy, self.grads[d["off"] + F * ckk:d["off"] + d["n"]], beta=1.0 if accumulate else 0.0, stream=stream)
                 n += 4
             else:

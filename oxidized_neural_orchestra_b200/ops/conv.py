@@ -33,6 +33,11 @@ def _fn():
         lib.ono_pool_bwd.argtypes = [G, ci, vp, ci, vp, ci, vp, ci, cf, ci, vp, ci, vp]
         lib.ono_nchw_flat.argtypes = [ci, ci, ci, ci, ci, vp, ci, vp, ci, vp, ci, vp, ci, ci, cf, ci, vp]
         lib.ono_finish_delta.argtypes = [ci, ll, ci, vp, ci, vp, ci, ci, cf, ci, vp, ci, vp, ci, vp]
+        lib.ono_conv1_fwd.argtypes = [G, ci, ci, vp, ci, vp, vp, ci, cf, vp, ci, vp]
+        lib.ono_conv1_wgrad.argtypes = [G, ci, ci, vp, ci, vp, ci, vp, vp, cf, vp]
+        lib.ono_conv1_fwd.restype = lib.ono_conv1_wgrad.restype = ci
+        lib.ono_conv_kperm.argtypes = [ci, ci, ci, ci, ci, vp, ci, vp, ci, vp, ci, cf, vp]
+        lib.ono_conv_kperm.restype = ci
         for f in (lib.ono_im2col, lib.ono_col2im, lib.ono_pool_fwd, lib.ono_pool_bwd, lib.ono_nchw_flat, lib.ono_finish_delta):
             f.restype = ci
         _declared = True
@@ -97,3 +102,31 @@ def finish_delta(rows, C_, src_f32, dst, dst_t=None, aux=None, dact=None, dact_p
     _lib.check(lib.ono_finish_delta(_dt(dst), rows, C_, src_f32.data_ptr(), src_f32.stride(0), _p(aux), _ld(aux), ACT[dact],
                                     dact_param, int(relu_quirk), dst.data_ptr(), dst.stride(0), _p(dst_t), _ld(dst_t),
                                     _lib.stream_ptr(stream)), "ono_finish_delta")
+
+
+def kernel_to_operand(F, C_, K, params_f32, dst, dst_t=None, stream=None):
+    """K[F][C][k][k] (flat f32 parameters) -> GEMM operand rows in (ky, kx, c) order, plus its transpose."""
+    lib = _fn()
+    _lib.check(lib.ono_conv_kperm(F, C_, K, 0, _dt(dst), params_f32.data_ptr(), 0, dst.data_ptr(), dst.stride(0), _p(dst_t),
+                                  _ld(dst_t), 0.0, _lib.stream_ptr(stream)), "ono_conv_kperm")
+
+
+def operand_grad_to_kernel(F, C_, K, src_f32, grads_f32, beta=0.0, stream=None):
+    """f32 weight gradient in operand order [F][(ky, kx, c)] -> parameter order K[F][C][k][k], dst = beta*dst + src."""
+    lib = _fn()
+    _lib.check(lib.ono_conv_kperm(F, C_, K, 1, 0, src_f32.data_ptr(), src_f32.stride(0), grads_f32.data_ptr(), 0, None, 0,
+                                  float(beta), _lib.stream_ptr(stream)), "ono_conv_kperm")
+
+
+def conv1_fwd(g, F, x, kparams_f32, bias_f32, y, act=None, act_param=0.0, stream=None):
+    """Direct forward of a convolution with one input channel: y = act(conv(x, K) + b), K given in parameter order."""
+    lib = _fn()
+    _lib.check(lib.ono_conv1_fwd(C.byref(g), F, _dt(x), x.data_ptr(), x.stride(0), kparams_f32.data_ptr(), _p(bias_f32), ACT[act],
+                                 act_param, y.data_ptr(), y.stride(0), _lib.stream_ptr(stream)), "ono_conv1_fwd")
+
+
+def conv1_wgrad(g, F, x, dy, gk_f32, gb_f32, beta=0.0, stream=None):
+    """Weight and bias gradient of a one-input-channel convolution, written in parameter order (g = beta*g + d)."""
+    lib = _fn()
+    _lib.check(lib.ono_conv1_wgrad(C.byref(g), F, _dt(x), x.data_ptr(), x.stride(0), dy.data_ptr(), dy.stride(0), gk_f32.data_ptr(),
+                                   gb_f32.data_ptr(), float(beta), _lib.stream_ptr(stream)), "ono_conv1_wgrad")

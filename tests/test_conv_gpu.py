@@ -107,3 +107,31 @@ def test_cnn_through_the_api_tracks_the_oracle():
     assert lg[-1] < lg[0]
     assert np.allclose(lc, lg, rtol=5e-2, atol=1e-5)
     assert np.abs(wc - wg).max() < 5e-2 * max(1.0, np.abs(wc).max())
+
+
+def test_single_channel_first_layer_uses_direct_kernels_and_tracks_the_oracle():
+    """LeNet-style front: 5x5 convolution on one input channel (direct CUDA-core kernels), pooling, dense."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Conv2d, Dense, MaxPooling
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import Xavier
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+
+    rng = np.random.default_rng(1)
+    xs = rng.random((48, 144), dtype=np.float32)
+    ys = np.eye(5, dtype=np.float32)[rng.integers(0, 5, 48)]
+    model = Sequential([Conv2d((1, 12, 12), (6, 1, 5), 1, 2, Xavier(), Tanh()), MaxPooling((6, 12, 12), 2, 2, 0),
+                        Dense(5, Xavier(), Softmax())])
+    out = {}
+    for dev in ("cpu", "gpu"):
+        tr = orchestra.all_reduce([f"{dev}:0"], InlineDataset(xs, ys, 144, 5), GradientDescent(0.5), CrossEntropy(),
+                                  max_epochs=8, batch_size=16, seed=5)
+        m = orchestrate(model, tr).wait(quiet=True)
+        out[dev] = (np.array(m.loss_history()), m.weights_array())
+    (lc, wc), (lg, wg) = out["cpu"], out["gpu"]
+    assert lg[-1] < lg[0]
+    assert np.allclose(lc, lg, rtol=5e-2, atol=1e-5)
+    assert np.abs(wc - wg).max() < 5e-2 * max(1.0, np.abs(wc).max())
