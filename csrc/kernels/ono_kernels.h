@@ -255,6 +255,20 @@ int ono_ring_allreduce(const OnoRing* r, ono_stream_t stream);
 int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base_epoch,
                  unsigned long long* rtt_ns, int* status, ono_stream_t stream);
 
+// ---------------------------------------------------------------------------------------------
+// Gradient compression (comms/src/handles/compressor.rs, comms/src/sparse/protocol.rs), see compress.cu.
+// ---------------------------------------------------------------------------------------------
+// threshold = k-th smallest |x| of a seeded sample of <= 16384 elements, k = floor(sample * (1 - r)), >= min positive f16
+int ono_sparse_threshold(const float* x, long long n, float r, unsigned long long seed, float* thr_out, ono_stream_t st);
+// wire[i] = f16(x[i]) if |x[i]| >= *thr else 0, sent entries zeroed in x; thr == NULL sends everything (f16 wire);
+// *sent (optional) is incremented by the number of entries sent
+int ono_sparse_mask(float* x, long long n, const float* thr, float* wire, unsigned long long* sent, ono_stream_t st);
+// (index, f16) pairs of the selected entries in ascending index order; scratch holds ceil(n/1024) unsigned ints
+int ono_sparse_compact(float* x, long long n, const float* thr, unsigned int* scratch, unsigned int* idx, void* val_f16,
+                       unsigned int capacity, unsigned int* count, int zero_sent, ono_stream_t st);
+int ono_sparse_lift(float* acc, long long n, const unsigned int* idx, const void* val_f16, const unsigned int* count,
+                    unsigned int capacity, ono_stream_t st);
+
 #ifdef __cplusplus
 }
 #endif

@@ -155,7 +155,8 @@ def run(r) -> dict:
                 if r.engine is not None:
                     if r.sync_mode != "async":
                         r.W.copy_(r.C)
-                    r.G.zero_()
+                    if not r.compress:      # with a compressed wire the unsent part stays as the residual
+                        r.G.zero_()
                     r.engine.refresh(stream=r.stream)
                 ev = torch.cuda.Event(enable_timing=True)
                 ev.record(r.stream)
@@ -200,6 +201,10 @@ def run(r) -> dict:
         "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
         "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
     }
+    if r.compress:
+        sent = int(r.wire_sent.item())
+        metrics["wire"] = ("f16+sparse" if r.sparse_r is not None else "f16")
+        metrics["wire_sent_fraction"] = sent / max(1, r.wire_rounds * r.n_pad) if r.widx is not None else None
     if len(r.bench_events) == 2:
         metrics["bench_ms"] = r.bench_events[0].elapsed_time(r.bench_events[1])
         metrics["bench_wall_s"] = r.bench_wall[1] - r.bench_wall[0]

@@ -75,6 +75,14 @@ class GpuRank:
         lay = WindowLayout()
         lay.add("params", self.n_pad, torch.float32)
         lay.add("grads", self.n_pad, torch.float32)
+        # Compressed gradient wire (reference cadence only): peers reduce the `wire` region, which holds the f16-rounded
+        # entries a rank sends this round; what it does not send stays in `grads` as its residual
+        # (comms/src/handles/compressor.rs:71-118, worker/src/middlewares/server_cluster.rs:85-104).
+        ser = self.plan.get("serializer", "base")
+        self.sparse_r = float(ser["sparse_capable"]["r"]) if isinstance(ser, dict) else None
+        self.compress = self.cadence == "round" and (self.b200.get("wire_dtype") == "f16" or self.sparse_r is not None)
+        if self.compress:
+            lay.add("wire", self.n_pad, torch.float32)
         if self.tile == "bf16":
             lay.add("params_bf16", self.n_pad, torch.bfloat16)
         needs_async = self.async_ps
@@ -90,6 +98,12 @@ class GpuRank:
         self.win = SymmetricWindow(lay.size, self.dev, self.group)
         self.C = lay.tensor(self.win, "params")
         self.G = lay.tensor(self.win, "grads")
+        self.grad_region = "wire" if self.compress else "grads"
+        if self.compress:
+            self.wire = lay.tensor(self.win, "wire")
+            self.wire_thr = torch.zeros(1, device=self.dev)
+            self.wire_sent = torch.zeros(1, dtype=torch.int64, device=self.dev)
+            self.wire_rounds = 0
         self.shadow = lay.tensor(self.win, "params_bf16") if self.tile == "bf16" else None
         if needs_async:
             self.m_win, self.v_win = lay.tensor(self.win, "m"), lay.tensor(self.win, "v")
@@ -248,10 +262,10 @@ class GpuRank:
                 pb = [None] * W
             nvls = getattr(self, "use_nvls", False) and win.mc_ptr != 0 and W > 1
             S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=1 if nvls else 0,
-                        g_ptrs=win.peer_ptrs(lay.offset("grads")), p_f32_ptrs=pf, p_bf16_ptrs=pb,
+                        g_ptrs=win.peer_ptrs(lay.offset(self.grad_region)), p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
-                        g_mc=win.mc(lay.offset("grads")) or None,
+                        g_mc=win.mc(lay.offset(self.grad_region)) or None,
                         p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
                         p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
@@ -335,6 +349,19 @@ class GpuRank:
     def _launch_sync(self, g_tensor: torch.Tensor, stream) -> int:
         """One synchronisation of `g_tensor` (the window's gradient region) into the parameters."""
         n = 0
+        if self.compress and g_tensor is self.G:
+            from ..ops import compress as cp
+
+            if self.widx is not None:
+                thr = None
+                if self.sparse_r is not None:
+                    thr = cp.sparse_threshold(self.G[:self.n], self.sparse_r, self.seed + self.wire_rounds, out=self.wire_thr,
+                                              stream=stream)
+                    n += 1
+                cp.wire_mask(self.G, self.wire, thr, self.wire_sent, stream=stream)
+                n += 1
+            self.wire_rounds += 1
+            g_tensor = self.wire
         if self.sync_opt.kind == "adam":
             ew.adam_tick(self.adam_pows, self.sync_opt.b1, self.sync_opt.b2, stream=stream)
             n += 1

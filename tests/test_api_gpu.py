@@ -70,3 +70,36 @@ def test_single_gpu_mse_regression_and_ragged_batches():
                               seed=2)
     h = orchestrate(model, tr).wait(quiet=True).loss_history()
     assert len(h) == 40 and h[-1] < 0.5 * h[0]
+
+
+def test_compressed_gradient_wire_on_the_gpu_trains_and_reports_what_it_sent():
+    """f16 wire and the sparse serializer in the reference's round cadence (compressor.rs:71-118)."""
+    import numpy as np
+
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+    from orchestra.serializer import SparseSerializer
+
+    rng = np.random.default_rng(0)
+    xs = rng.random((256, 32), dtype=np.float32)
+    ys = np.eye(4, dtype=np.float32)[(xs[:, :4].argmax(1))]
+    model = Sequential([Dense(64, XavierUniform(), Tanh()), Dense(4, XavierUniform(), Softmax())])
+
+    def run(**kw):
+        tr = orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 32, 4), GradientDescent(0.5), CrossEntropy(), 30, 64, seed=2, **kw)
+        return orchestrate(model, tr).wait(quiet=True)
+
+    plain = run()
+    f16 = run(b200={"wire_dtype": "f16"})
+    sparse = run(serializer=SparseSerializer(0.25))
+    assert f16.metrics()["wire"] == "f16" and f16.metrics()["wire_sent_fraction"] == pytest.approx(1.0, abs=0.02)
+    assert sparse.metrics()["wire"] == "f16+sparse" and 0.1 < sparse.metrics()["wire_sent_fraction"] < 0.45
+    lp, lf, ls = (np.array(m.loss_history()) for m in (plain, f16, sparse))
+    assert np.allclose(lp, lf, rtol=2e-2)                      # f16 rounding barely moves the trajectory
+    assert ls[-1] < ls[0] and ls[-1] < 1.5 * lp[-1] + 0.05     # dropped entries arrive later through the residual
