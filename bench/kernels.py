@@ -117,7 +117,7 @@ def cmd_sweep(a):
     flush = torch.empty(64 << 20, device=dev)
     sms = lib.ono_num_sms()
     rows = []
-    size = 1024
+    size = max(1024, a.min_bytes)
     while size <= a.max_bytes:
         n = size // 4
         G[:n].normal_(0, 1e-3)
@@ -193,6 +193,7 @@ def main():
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
     w = sub.add_parser("sweep")
     w.add_argument("--max-bytes", type=int, default=1 << 30)
+    w.add_argument("--min-bytes", type=int, default=1024)
     a = ap.parse_args()
     {"gemm": cmd_gemm, "sync": cmd_sync, "sweep": cmd_sweep}[a.cmd](a)
 

@@ -315,11 +315,12 @@ __device__ __forceinline__ float4 ld_global_nc_v4(const float4* p) {
                : "l"(p));
   return v;
 }
-// Peer data written by another GPU during this kernel must not be read through the non-coherent
-// path; this is the plain (coherent at L2 of the owner) vector load.
+// Peer data written by another GPU must not be read through the non-coherent path or a stale L1 line: a relaxed
+// system-scope load goes to the point of coherence, and unlike a volatile load it is not ordered against the
+// thread's other loads, so many of them stay in flight per thread.
 __device__ __forceinline__ float4 ld_global_v4_volatile(const float4* p) {
   float4 v;
-  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                : "l"(p)
                : "memory");

@@ -26,6 +26,11 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+# CTAs a GEMM may use when the caller gives no limit (0 = one per SM). The rank runtime lowers it while gradient
+# buckets are synchronised during backward, so that the communication kernels find free SMs.
+DEFAULT_MAX_CTAS = 0
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          out: torch.Tensor | None = None, out_t: torch.Tensor | None = None,
          out_bf16: torch.Tensor | None = None, out_t_bf16: torch.Tensor | None = None,
@@ -59,7 +64,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     g.lda, g.ldb = a.stride(0), b.stride(0)
     g.dtype = 0 if a.dtype == torch.float32 else 1
     g.a_major, g.b_major = int(a_mn_major), int(b_mn_major)
-    g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas, split_k, pair
+    g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas or DEFAULT_MAX_CTAS, split_k, pair
     e = g.epi
     ld_out = ld_out_t = 0
     for t in (out, out_bf16, pre):

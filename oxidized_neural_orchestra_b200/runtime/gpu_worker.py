@@ -310,10 +310,20 @@ class GpuRank:
 
         self.buckets = []           # [(launch_after_layer, OnoSync)] in launch order
         self.bucket_after: dict[int, list] = {}
-        # Measured on 1 and 2 B200s: the bucket kernels (one block per SM, sharing the SMs with the
-        # GEMMs) lose more bandwidth than the overlap wins, so buckets are opt-in (ONO_OVERLAP=1).
+        # Opt-in (ONO_OVERLAP=1): measured slower than the single fused launch at 1, 2, 4 and 8 B200s. Peer loads are
+        # issued per thread, and NVLink throughput grows with the number of SMs issuing them (about 4-5 GB/s per SM):
+        # 16 / 32 SMs left to the bucket kernels moved gradients at roughly 70 / 140 GB/s on 4 GPUs, against 650 GB/s
+        # when the fused kernel owns the whole GPU after backward.
+        from ..ops import gemm as gemm_mod
+
+        gemm_mod.DEFAULT_MAX_CTAS = 0
         if (self.sync_mode != "fused" or self.cadence != "step" or os.environ.get("ONO_OVERLAP", "0") == "0"):
             return
+        # The persistent GEMM (one CTA per SM, all of its shared memory and most registers) and a 512-thread
+        # synchronisation block do not fit on one SM together, so the SMs are split: `comm_sms` of them are left to the
+        # bucket kernels, the GEMMs run on the rest.
+        comm_sms = max(1, min(int(os.environ.get("ONO_OVERLAP_SMS", "24")), _lib.load().ono_num_sms() // 2))
+        gemm_mod.DEFAULT_MAX_CTAS = _lib.load().ono_num_sms() - comm_sms
         up4 = lambda x: (x + 3) // 4 * 4
         layers = [l for l in self.plan["layers"] if l["n_params"] > 0]
         min_elems = 4 << 20
@@ -339,7 +349,7 @@ class GpuRank:
                         loc.ranges[i].begin, loc.ranges[i].end = b, e
                     # one block per SM at most: these kernels share the SMs with the running GEMMs
                     owners = max(1, sum(1 for r in self.own if r))
-                    s.nblocks = int(min(sms, max(1, -(-((cur_end - begin) // 4 // owners) // (512 * 2)))))
+                    s.nblocks = int(min(comm_sms, max(1, -(-((cur_end - begin) // 4 // owners) // (512 * 2)))))
                     entry = (l["index"], s)
                     self.buckets.append(entry)
                     self.bucket_after.setdefault(l["index"], []).append(s)
