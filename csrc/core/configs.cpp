@@ -387,6 +387,8 @@ Json B200Config::to_json() const {
   o.set("colocate", colocate);
   o.set("data", data);
   o.set("comm_timeout_s", comm_timeout_s);
+  o.set("heartbeat_s", heartbeat_s);
+  o.set("heartbeat_timeout_s", heartbeat_timeout_s);
   o.set("trace_path", trace_path);
   o.set("metrics_path", metrics_path);
   return o;
@@ -418,6 +420,8 @@ B200Config B200Config::from_json(const Json& j) {
   if (const Json* v = j.find("switch_resets_progress")) c.switch_resets_progress = v->as_bool();
   if (const Json* v = j.find("colocate")) c.colocate = v->as_bool();
   if (const Json* v = j.find("comm_timeout_s")) c.comm_timeout_s = float_positive(v->as_double(), "b200.comm_timeout_s");
+  if (const Json* v = j.find("heartbeat_s")) c.heartbeat_s = float_non_negative(v->as_double(), "b200.heartbeat_s");
+  if (const Json* v = j.find("heartbeat_timeout_s")) c.heartbeat_timeout_s = float_non_negative(v->as_double(), "b200.heartbeat_timeout_s");
   if (const Json* v = j.find("trace_path")) c.trace_path = v->as_string();
   if (const Json* v = j.find("metrics_path")) c.metrics_path = v->as_string();
   return c;

@@ -262,6 +262,7 @@ class RemoteSession final : public Session {
         if (const Json* l = evj->find("losses"))
           for (auto& v : l->items()) ev.losses.push_back(v.is_null() ? std::nan("") : v.as_double());
         if (const Json* t = evj->find("text"); t && t->is_string()) ev.text = t->as_string();
+        if (ev.kind == "heartbeat") continue;   // liveness only
         if (ev.kind == "metrics") {
           { std::lock_guard<std::mutex> lk(mu_); metrics_ = Json::parse(ev.text); got_metrics_ = true; }
           cv_.notify_all();

@@ -20,6 +20,7 @@ import os
 import queue
 import sys
 import threading
+import time
 import uuid
 
 import numpy as np
@@ -128,6 +129,24 @@ def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
 
             t = threading.Thread(target=body, daemon=True)
             t.start()
+            # liveness: a counter the orchestrator watches; a node whose process is alive but whose rank is stuck
+            # keeps beating, so the beat also carries whether the training thread is still running
+            hb_every = float(job["training"].get("b200", {}).get("heartbeat_s", 2.0) or 0.0)
+            hb_stop = threading.Event()
+
+            def beat():
+                k = 0
+                while not hb_stop.wait(hb_every):
+                    k += 1
+                    try:
+                        with send_lock:
+                            ch.send_command({"event": {"kind": "heartbeat", "worker": job["rank"], "losses": [],
+                                                       "text": json.dumps({"beat": k, "training": t.is_alive()})}})
+                    except OSError:
+                        return
+
+            if hb_every > 0:
+                threading.Thread(target=beat, daemon=True).start()
             # serve the orchestrator while training runs and afterwards (all_reduce.rs:137-152)
             while True:
                 kind, m = ch.recv(timeout=None)
@@ -148,6 +167,7 @@ def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
                                                    "text": json.dumps(_jsonable(result.get("metrics", {})))}})
                 elif m == "disconnect":
                     stop_event.set()
+                    hb_stop.set()
                     t.join()
                     return
 
@@ -175,6 +195,10 @@ class RemoteHandle:
         self._closed = False
         self._events_finished = False
         self._failed = False
+        b200 = training_cfg.get("b200") or {}
+        self._hb_timeout = float(b200.get("heartbeat_timeout_s", 0.0) or 0.0)   # 0 = do not judge liveness by beats
+        self._last_seen = [time.monotonic()] * len(addrs)
+        self._node_done = [False] * len(addrs)
         master_port = wire.free_port()
         master_addr = addrs[0].rsplit(":", 1)[0]
         part = {w["rank"]: w["partition"] for w in plan["workers"]}
@@ -196,6 +220,23 @@ class RemoteHandle:
         self._threads = [threading.Thread(target=self._reader, args=(r, ch), daemon=True) for r, ch in enumerate(self._chs)]
         for t in self._threads:
             t.start()
+        if self._hb_timeout > 0:
+            threading.Thread(target=self._watchdog, daemon=True).start()
+
+    def _watchdog(self):
+        """Declare a node dead after `heartbeat_timeout_s` of silence (its process may hang without closing the
+        connection) and end the session the way a lost connection does."""
+        while not self._closed and not self._events_finished:
+            time.sleep(min(1.0, self._hb_timeout / 4))
+            now = time.monotonic()
+            for r, seen in enumerate(self._last_seen):
+                if not self._node_done[r] and not self._failed and now - seen > self._hb_timeout:
+                    self._node_done[r] = True
+                    self._q.put(("event", r, {"kind": "error", "worker": r, "losses": [],
+                                               "text": f"node {r} lost: silent for {now - seen:.1f} s"}))
+                    self._q.put(("done", r, None))
+                    self._abort(r)
+                    self._chs[r].close()
 
     def _reader(self, rank: int, ch: wire.Channel):
         try:
@@ -206,12 +247,16 @@ class RemoteHandle:
                         self._params = np.array(msg, dtype=np.float32)
                     continue
                 if msg == "done":
+                    self._node_done[rank] = True
                     self._q.put(("done", rank, None))
                     if rank != 0:
                         return
                     continue
+                self._last_seen[rank] = time.monotonic()
                 if isinstance(msg, dict) and "event" in msg:
                     ev = msg["event"]
+                    if ev["kind"] == "heartbeat":
+                        continue
                     if ev["kind"] == "metrics":
                         self._metrics = json.loads(ev["text"])
                         self._q.put(("metrics", rank, None))

@@ -77,6 +77,46 @@ def test_a_node_that_dies_mid_run_ends_the_session_with_an_error():
             p.wait(timeout=30)
 
 
+def test_a_node_that_stops_answering_is_dropped_after_the_heartbeat_timeout():
+    """The process stays alive and its connection open, it just stops running (SIGSTOP): only the missing
+    heartbeats tell the orchestrator."""
+    import signal
+
+    procs, addrs = spawn_nodes(2, "cpu", once=True)
+    try:
+        rng = np.random.default_rng(0)
+        xs = rng.random((60, 6), dtype=np.float32)
+        ys = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 60)]
+        model = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+        tr = orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), GradientDescent(0.01), CrossEntropy(), 1_000_000, 5,
+                                  seed=1, b200={"comm_timeout_s": 4.0, "heartbeat_s": 0.25, "heartbeat_timeout_s": 2.0})
+        s = orchestrate(model, tr)
+        box = {}
+
+        def waiter():
+            try:
+                box["model"] = s.wait(quiet=True)
+            except RuntimeError as e:
+                box["error"] = str(e)
+
+        t = threading.Thread(target=waiter, daemon=True)
+        t.start()
+        time.sleep(1.5)
+        procs[1].send_signal(signal.SIGSTOP)       # exactly the child started above
+        t.join(timeout=60)
+        assert not t.is_alive(), "the session hung behind a silent node"
+        assert "silent" in box.get("error", "") or "lost" in box.get("error", "") or "rror" in box.get("error", "")
+    finally:
+        for p in procs:
+            try:
+                p.send_signal(signal.SIGCONT)
+            except OSError:
+                pass
+            p.kill()
+        for p in procs:
+            p.wait(timeout=30)
+
+
 def test_control_channel_reports_a_silent_peer_instead_of_blocking():
     lsock = wire.listen("127.0.0.1", 0)
     port = lsock.getsockname()[1]
