@@ -1,0 +1,172 @@
+#!/usr/bin/env python
+"""Strategy benchmark suites over the public API, in the spirit of the reference's harness
+(benchmarks/run_issue_benchmarks.py:64-229, benchmarks/issue/{suites,runner,metrics,results}.py).
+
+    python bench/suites.py [--suite strategies|scalability|offline] [--model lenet5|nielsen|both]
+                           [--nodes gpu|cpu] [--rows 4096] [--epochs 4] [--repeats 1] [--out bench/results]
+
+Every run trains LeNet-5 or the Nielsen network on seeded MNIST-shaped synthetic data (class prototypes plus
+noise) through ``orchestrate(...).wait()`` and records, like the reference (benchmarks/issue/metrics.py:11-32):
+``train_seconds`` (wall clock of ``wait``), ``samples_per_sec = samples * epochs / train_seconds``,
+``epochs_per_sec``, ``final_loss``, ``accuracy`` on a held-out set (evaluated with a plain PyTorch restatement
+of the model loaded from the trained weights, as benchmarks/issue/models.py:138-154 does), ``loss_per_sec`` and
+``accuracy_per_sec``. Results go to ``<out>/history.jsonl`` (one record per repeat) and ``<out>/summary.md``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "examples"))
+
+
+def make_data(rows: int, seed: int):
+    rng = np.random.default_rng(seed)
+    proto = rng.random((10, 784), dtype=np.float32)
+    def draw(n):
+        labels = rng.integers(0, 10, n)
+        xs = np.clip(proto[labels] + 0.35 * rng.standard_normal((n, 784), dtype=np.float32), 0, 1).astype(np.float32)
+        return xs, labels
+    xtr, ltr = draw(rows)
+    xte, lte = draw(max(256, rows // 8))
+    return xtr, np.eye(10, dtype=np.float32)[ltr], xte, lte
+
+
+def torch_accuracy(model_name: str, weights: np.ndarray, xs: np.ndarray, labels: np.ndarray) -> float:
+    """Plain PyTorch restatement of the two models, fed with the flat parameter vector (layout: per layer W then b;
+    dense W is [in, out], conv W is [F, C, k, k])."""
+    import torch
+    import torch.nn.functional as F
+
+    w = torch.from_numpy(np.asarray(weights, dtype=np.float32))
+    off = 0
+
+    def take(*shape):
+        nonlocal off
+        n = int(np.prod(shape))
+        t = w[off:off + n].view(*shape)
+        off += n
+        return t
+
+    x = torch.from_numpy(xs).view(-1, 1, 28, 28)
+    # the reference pads pooling inputs with zeros that compete in the max; neither model pads its pools
+    if model_name == "nielsen":
+        k, b = take(20, 1, 5, 5), take(20)
+        a = F.max_pool2d(F.conv2d(x, k, b), 2, 2).flatten(1)
+        a = torch.sigmoid(a @ take(20 * 12 * 12, 100) + take(100))
+        z = a @ take(100, 10) + take(10)
+    else:
+        k, b = take(6, 1, 5, 5), take(6)
+        a = F.max_pool2d(torch.tanh(F.conv2d(x, k, b, padding=2)), 2, 2)
+        k, b = take(16, 6, 5, 5), take(16)
+        a = F.max_pool2d(torch.tanh(F.conv2d(a, k, b)), 2, 2).flatten(1)
+        a = torch.tanh(a @ take(400, 120) + take(120))
+        a = torch.tanh(a @ take(120, 84) + take(84))
+        z = a @ take(84, 10) + take(10)
+    assert off == w.numel(), (off, w.numel())
+    return float((z.argmax(1).numpy() == labels).mean())
+
+
+def suites(kind: str, n_nodes: int):
+    """(label, strategy, workers, servers, extra) tuples; the reference's suites use 3/5/7 workers and 2 servers
+    (benchmarks/issue/suites.py:148-178), capped here by the nodes available."""
+    cap = lambda w: max(1, min(w, n_nodes))
+    if kind == "strategies":
+        return [("all_reduce", "ar", cap(5), 0, {}), ("ps_blocking", "ps", cap(5), min(2, cap(5)), {}),
+                ("ps_non_blocking", "ps_async", cap(5), min(2, cap(5)), {}), ("strategy_switch", "ss", cap(5), min(2, cap(5)), {})]
+    if kind == "scalability":
+        return [(f"all_reduce_{w}w", "ar", w, 0, {}) for w in sorted({cap(1), cap(3), cap(5), cap(7)})] + \
+               [(f"ps_{w}w_2s", "ps", w, min(2, w), {}) for w in sorted({cap(3), cap(5)})]
+    if kind == "offline":
+        return [(f"all_reduce_offline{e}", "ar", cap(3), 0, {"offline_epochs": e}) for e in (0, 1, 4)]
+    raise SystemExit(f"unknown suite {kind}")
+
+
+def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, epochs, batch):
+    import orchestra
+    from mnist_models import lenet5, nielsen
+    from orchestra import orchestrate
+    from orchestra.datasets import InlineDataset
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync, NonBlockingSync
+
+    xtr, ytr, xte, lte = data
+    addrs = [f"{prefix}:{i}" for i in range(workers)]
+    ds = InlineDataset(xtr, ytr, 784, 10)
+    common = dict(max_epochs=epochs, batch_size=batch, seed=42, **extra)
+    b200 = {"colocate": True} if prefix == "gpu" else None
+    opt, loss = GradientDescent(0.5), CrossEntropy()   # the loss is normalised by batch x classes (cross_entropy.rs:35-47)
+    if strategy == "ar":
+        cfg = orchestra.all_reduce(addrs, ds, opt, loss, **common)
+    else:
+        sync = NonBlockingSync() if strategy == "ps_async" else BarrierSync()
+        fn = orchestra.strategy_switch if strategy == "ss" else orchestra.parameter_server
+        kw = dict(common, b200=b200) if b200 and servers >= workers else (dict(common, b200=b200) if b200 else common)
+        if prefix == "cpu" and servers >= workers:
+            return None                      # the reference needs at least one pure worker
+        cfg = fn(addrs, servers, ds, opt, loss, sync, BlockingStore(), **kw)
+    model = {"lenet5": lenet5, "nielsen": nielsen}[model_name]()
+    t0 = time.perf_counter()
+    trained = orchestrate(model, cfg).wait(quiet=True)
+    secs = time.perf_counter() - t0
+    hist = trained.loss_history()
+    acc = torch_accuracy(model_name, trained.weights_array(), xte, lte)
+    done = len(hist)
+    return {"suite_label": label, "model": model_name, "strategy": strategy, "workers": workers, "servers": servers,
+            "backend": prefix, "epochs": done, "samples": len(xtr), "train_seconds": secs,
+            "samples_per_sec": len(xtr) * done / secs, "epochs_per_sec": done / secs, "final_loss": hist[-1] if hist else None,
+            "accuracy": acc, "loss_per_sec": (hist[0] - hist[-1]) / secs if len(hist) > 1 else 0.0,
+            "accuracy_per_sec": acc / secs, "switched": bool(trained.metrics().get("switched", False)), **extra}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--suite", default="strategies")
+    ap.add_argument("--model", default="both", choices=("lenet5", "nielsen", "both"))
+    ap.add_argument("--nodes", default=None, choices=("gpu", "cpu"))
+    ap.add_argument("--rows", type=int, default=4096)
+    ap.add_argument("--epochs", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--repeats", type=int, default=1)
+    ap.add_argument("--out", default=os.path.join(ROOT, "bench", "results"))
+    a = ap.parse_args()
+    import torch
+
+    prefix = a.nodes or ("gpu" if torch.cuda.is_available() else "cpu")
+    n_nodes = torch.cuda.device_count() if prefix == "gpu" else 7
+    os.makedirs(a.out, exist_ok=True)
+    data = make_data(a.rows, 42)
+    records = []
+    with open(os.path.join(a.out, "history.jsonl"), "a") as hist:
+        for model_name in (("lenet5", "nielsen") if a.model == "both" else (a.model,)):
+            for label, strategy, workers, servers, extra in suites(a.suite, n_nodes):
+                for rep in range(a.repeats):
+                    rec = run_one(model_name, label, strategy, workers, servers, extra, prefix, data, a.epochs, a.batch)
+                    if rec is None:
+                        continue
+                    rec.update(suite=a.suite, repeat=rep, time=time.time())
+                    hist.write(json.dumps(rec) + "\n")
+                    hist.flush()
+                    records.append(rec)
+                    print(f"{model_name:8s} {label:22s} {rec['samples_per_sec']:12.0f} samples/s  loss {rec['final_loss']:.5f}  "
+                          f"acc {rec['accuracy']:.3f}", file=sys.stderr)
+    with open(os.path.join(a.out, "summary.md"), "w") as f:
+        f.write(f"# Suite `{a.suite}` on `{prefix}` nodes ({a.rows} samples, {a.epochs} epochs, batch {a.batch})\n\n")
+        f.write("| model | run | workers | servers | samples/s | epochs/s | final loss | accuracy | switched |\n|---|---|---|---|---|---|---|---|---|\n")
+        for r in records:
+            f.write(f"| {r['model']} | {r['suite_label']} | {r['workers']} | {r['servers']} | {r['samples_per_sec']:.0f} | "
+                    f"{r['epochs_per_sec']:.3f} | {r['final_loss']:.5f} | {r['accuracy']:.3f} | {r['switched']} |\n")
+    print(json.dumps({"suite": a.suite, "runs": len(records), "out": a.out}))
+
+
+if __name__ == "__main__":
+    main()

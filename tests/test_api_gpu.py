@@ -103,3 +103,23 @@ def test_compressed_gradient_wire_on_the_gpu_trains_and_reports_what_it_sent():
     lp, lf, ls = (np.array(m.loss_history()) for m in (plain, f16, sparse))
     assert np.allclose(lp, lf, rtol=2e-2)                      # f16 rounding barely moves the trajectory
     assert ls[-1] < ls[0] and ls[-1] < 1.5 * lp[-1] + 0.05     # dropped entries arrive later through the residual
+
+
+def test_trace_and_metrics_files_of_a_gpu_run(tmp_path):
+    import json
+
+    rng = np.random.default_rng(0)
+    xs = rng.random((128, 16), dtype=np.float32)
+    ys = np.eye(4, dtype=np.float32)[rng.integers(0, 4, 128)]
+    model = Sequential([Dense(32, XavierUniform(), ReLU(0.0)), Dense(4, XavierUniform(), Softmax())])
+    tp, mp = tmp_path / "trace.json", tmp_path / "metrics.jsonl"
+    tr = orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 16, 4), GradientDescent(0.1), CrossEntropy(), 3, 32, seed=1,
+                              b200={"sync_every": "step", "trace_path": str(tp), "metrics_path": str(mp)})
+    orchestrate(model, tr).wait(quiet=True)
+    doc = json.load(open(tp))
+    names = [e["name"] for e in doc["traceEvents"]]
+    assert names.count("epoch") == 3 and "step" in names and "report_and_decide" in names
+    steps = [e for e in doc["traceEvents"] if e["name"] == "step"]
+    assert all(e["tid"] == 1 and e["dur"] > 0 for e in steps)          # device spans from CUDA events
+    recs = [json.loads(l) for l in open(mp)]
+    assert len(recs) == 3 and all(r["steps"] >= 1 and r["device_ms"] > 0 and r["samples_per_sec"] > 0 for r in recs)
