@@ -93,6 +93,40 @@ def cmd_sync(a):
                       "bytes_per_elem": per}))
 
 
+def cmd_sync_emulated(a):
+    """All ranks of the two-shot reduce-scatter + optimizer + all-gather kernel as ONE cooperative launch on one GPU
+    (grid.y = rank, every rank with its own buffers): the cross-rank flag protocol and the peer loads and stores run
+    for real, only the wires are missing. Used to profile the multi-rank kernel where ncu may not wrap a multi-process run."""
+    from oxidized_neural_orchestra_b200.ops import _lib
+    from oxidized_neural_orchestra_b200.parallel import sync as S
+
+    R, n = a.emulate_ranks, a.elems
+    z = lambda dt=torch.float32: torch.zeros(n, device="cuda", dtype=dt)
+    g, p, m, v = [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)]
+    for t in g:
+        t.normal_(0, 1e-3)
+    nblocks = max(1, min(_lib.load().ono_num_sms() // R, n // 4 // 1024))
+    flags = [torch.zeros(nblocks * 8, device="cuda", dtype=torch.int32) for _ in range(R)]
+    epoch = [torch.zeros(nblocks, device="cuda", dtype=torch.int32) for _ in range(R)]
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    pows = torch.full((2,), 0.5, device="cuda")
+    s = _lib.OnoSync()
+    S.fill_sync(s, nranks=R, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=[t.data_ptr() for t in g],
+                p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[None] * R, flag_ptrs=[t.data_ptr() for t in flags],
+                worker_mask=(1 << R) - 1, member_mask=(1 << R) - 1, n_workers=R, opt=S.OptimizerCfg(kind=a.opt, lr=0.01, mu=0.9))
+    ranges = S.even_ranges(n, list(range(R)), R)
+    for r in range(R):
+        S.fill_local(s.loc[r], p_master=p[r].data_ptr(), m=m[r].data_ptr(), v=v[r].data_ptr(), state_off=0,
+                     adam_pows=pows.data_ptr(), epoch=epoch[r].data_ptr(), ranges=ranges[r], status=status.data_ptr())
+    for _ in range(3):
+        S.launch_sync(s, emulated=True)
+    ms = _time(lambda: S.launch_sync(s, emulated=True), a.iters)
+    assert status.item() == 0
+    per = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + 4 * R + 4 * R     # owner state + R gradient reads + R parameter writes
+    print(json.dumps({"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "ms": ms,
+                      "GBs_local_hbm": per * n / ms / 1e6, "blocks_per_rank": nblocks}))
+
+
 def cmd_sweep(a):
     from oxidized_neural_orchestra_b200.ops import _lib
     from oxidized_neural_orchestra_b200.parallel import sync as S
@@ -191,10 +225,13 @@ def main():
     s = sub.add_parser("sync")
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
+    s.add_argument("--emulate-ranks", type=int, default=0, help="run R ranks as one cooperative launch on this GPU")
     w = sub.add_parser("sweep")
     w.add_argument("--max-bytes", type=int, default=1 << 30)
     w.add_argument("--min-bytes", type=int, default=1024)
     a = ap.parse_args()
+    if a.cmd == "sync" and a.emulate_ranks > 1:
+        return cmd_sync_emulated(a)
     {"gemm": cmd_gemm, "sync": cmd_sync, "sweep": cmd_sweep}[a.cmd](a)
 
 
