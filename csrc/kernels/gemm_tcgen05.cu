@@ -10,7 +10,7 @@
 //                                            derivative / accumulate, stores (row-major through a
 //                                            swizzled staging tile + TMA store, transposed, f32, bf16)
 //
-// Operands may be K-major or (bf16 only) MN-major; the difference is confined to the TMA box
+// Operands may be K-major or MN-major (bf16 and tf32); the difference is confined to the TMA box
 // pattern and three descriptor fields computed on the host (see make_operand()).
 // All mbarrier waits are bounded; on a timeout the kernel records a code in *status, every role
 // leaves its loop, TMEM is freed and the kernel returns normally.
@@ -38,6 +38,7 @@ struct OperandDev {
   int box_mn;         // MN extent covered by one box
   uint32_t box_stride_bytes;
   uint32_t lbo_bytes, sbo_bytes, kstep_bytes;
+  uint32_t layout_type;  // shared-memory descriptor layout: 2 = 128B swizzle, 1 = 128B swizzle on 32B units
 };
 
 struct GemmDev {
@@ -363,9 +364,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int k = 0; k < KSTEPS; ++k) {
             const uint64_t adesc =
-                make_smem_desc_sw128(a_addr + k * p.a.kstep_bytes, p.a.lbo_bytes, p.a.sbo_bytes);
+                make_smem_desc_sw128(a_addr + k * p.a.kstep_bytes, p.a.lbo_bytes, p.a.sbo_bytes, p.a.layout_type);
             const uint64_t bdesc =
-                make_smem_desc_sw128(b_addr + k * p.b.kstep_bytes, p.b.lbo_bytes, p.b.sbo_bytes);
+                make_smem_desc_sw128(b_addr + k * p.b.kstep_bytes, p.b.lbo_bytes, p.b.sbo_bytes, p.b.layout_type);
             const uint32_t acc = (kb != kb0) || (k != 0);
             if (PAIR) {
               if (ESIZE == 4) umma_tf32_pair(d_tmem, adesc, bdesc, p.idesc, acc);
@@ -522,7 +523,7 @@ static EncodeTiledFn get_encode_fn() {
 // 2-D row-major global matrix [rows, cols] with leading dimension ld (elements); box = {box_cols
 // (innermost, 128 bytes), box_rows}; 128-byte swizzle.
 int encode_map_2d(CUtensorMap* map, const void* base, int esize, long long rows, long long cols,
-                  long long ld, int box_cols, int box_rows) {
+                  long long ld, int box_cols, int box_rows, bool swizzle_32b_units = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) { set_error("cuTensorMapEncodeTiled unavailable%s", ""); return -2; }
   if (((uintptr_t)base & 15) != 0) { set_error("TMA base not 16-byte aligned%s", ""); return -3; }
@@ -533,8 +534,8 @@ int encode_map_2d(CUtensorMap* map, const void* base, int esize, long long rows,
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = esize == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%s%lld)", "", (long long)r); return -4; }
   return 0;
 }
@@ -568,9 +569,24 @@ static int make_operand(OperandDev* od, CUtensorMap* map, const void* ptr, int e
     od->lbo_bytes = 16;      // unused for a single swizzle atom along K
     od->sbo_bytes = 1024;    // 8 rows x 128 bytes
     od->kstep_bytes = 32;    // one UMMA_K slice inside the 128-byte row
+    od->layout_type = 2;
     return encode_map_2d(map, ptr, esize, MN, K, ld, BK, tile_mn);
   }
-  if (esize != 2) { set_error("MN-major operands are supported for bf16 only%s", ""); return -5; }
+  if (esize == 4) {
+    // 32-bit MN-major operands: rows of 32 elements (128 bytes) of MN, swizzled on 32-byte units in atoms of 4 K-rows
+    // (the layout tcgen05 defines for tf32 operands whose MN dimension is contiguous); one MMA (UMMA_K = 8) reads two atoms.
+    const int chunk4 = 32;
+    od->mn_major = 1;
+    od->n_box = tile_mn / chunk4;
+    if (od->n_box < 1) { set_error("MN-major tile too narrow%s", ""); return -5; }
+    od->box_mn = chunk4;
+    od->box_stride_bytes = (uint32_t)BK * 128u;
+    od->lbo_bytes = od->box_stride_bytes;   // between 32-wide MN atoms
+    od->sbo_bytes = 512;                    // between groups of 4 K-rows
+    od->kstep_bytes = 8u * 128u;            // UMMA_K rows of K
+    od->layout_type = 1;
+    return encode_map_2d(map, ptr, esize, K, MN, ld, chunk4, BK, true);
+  }
   const int chunk = 128 / esize;  // 64 elements of MN per 128-byte row
   od->mn_major = 1;
   od->n_box = tile_mn / chunk;
@@ -580,6 +596,7 @@ static int make_operand(OperandDev* od, CUtensorMap* map, const void* ptr, int e
   od->lbo_bytes = od->box_stride_bytes;        // between 64-wide MN atoms
   od->sbo_bytes = 1024;                        // between groups of 8 K-rows
   od->kstep_bytes = (32 / esize) * 128u;       // UMMA_K rows of K
+  od->layout_type = 2;
   return encode_map_2d(map, ptr, esize, K, MN, ld, chunk, BK);
 }
 

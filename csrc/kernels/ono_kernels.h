@@ -43,9 +43,9 @@ typedef struct OnoEpilogue {
 
 // D[M,N] = A[M,K] * B[K,N] with f32 accumulation in TMEM.
 //   A: a_major == K_MAJOR  -> memory is [M, lda] with K contiguous
-//      a_major == MN_MAJOR -> memory is [K, lda] with M contiguous (bf16 only)
+//      a_major == MN_MAJOR -> memory is [K, lda] with M contiguous
 //   B: b_major == K_MAJOR  -> memory is [N, ldb] with K contiguous
-//      b_major == MN_MAJOR -> memory is [K, ldb] with N contiguous (bf16 only)
+//      b_major == MN_MAJOR -> memory is [K, ldb] with N contiguous
 // Leading dimensions are in elements and must make row strides a multiple of 16 bytes.
 typedef struct OnoGemm {
   const void* A;

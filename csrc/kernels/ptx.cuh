@@ -265,15 +265,15 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 //   leading offset bits [16,30)  (bytes >> 4)
 //   stride offset  bits [32,46)  (bytes >> 4)
 //   version        bits [46,48)  = 1
-//   layout type    bits [61,64)  = 2 (SWIZZLE_128B)
+//   layout type    bits [61,64)  = 2 (SWIZZLE_128B) or 1 (SWIZZLE_128B on 32-byte units: MN-major 32-bit operands)
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes) {
+                                                         uint32_t sbo_bytes, uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
+  d |= static_cast<uint64_t>(layout_type & 7u) << 61;   // 2: 128-byte swizzle; 1: 128-byte swizzle on 32-byte units
   return d;
 }
 

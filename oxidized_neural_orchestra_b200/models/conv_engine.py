@@ -155,7 +155,7 @@ class ConvNetEngine:
         last = self.front[-1]
         de = self.dense
         cv.nchw_flat(nrows, last["F"], last["OH"] * last["OW"], True, last["y"], de.a[0],
-                     out_t=None if self.bf16 else de.at[0], stream=stream)
+                     out_t=None if de.at is None else de.at[0], stream=stream)
         return n + 1
 
     def backward_front(self, nrows: int, accumulate: bool, stream=None) -> int:

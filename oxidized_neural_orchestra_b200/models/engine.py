@@ -110,7 +110,13 @@ class GpuEngine:
         for l, pl in enumerate(L):
             if pl.act == "gelu":
                 self.zpre[l + 1] = z(B, self.lds[l + 1], cd)
-        if not self.bf16:
+        # MN-major operands let every GEMM read activations, deltas and weights as they are stored. bf16 always does;
+        # for tf32 the MN-major tiles (32-element rows, twelve small TMA boxes per stage) measured slower than K-major
+        # tiles fed from transposed compute copies (wide MLP step 1.20 ms against 1.13 ms), so it is opt-in: ONO_TF32_MN=1
+        import os
+        self.mn = self.bf16 or os.environ.get("ONO_TF32_MN", "0") == "1"
+        self.at = self.dt = None
+        if not self.mn:
             self.at = [z(feats[i], ldB, f32) for i in range(len(feats) - 1)]
             self.dt = [None] + [z(feats[i], ldB, f32) for i in range(1, len(feats))]
         self.ybuf = z(B, _up(feats[-1]), f32)
@@ -131,7 +137,7 @@ class GpuEngine:
             else:
                 self.w_k.append(z(i, _up(o), cd)[:, :o])
                 self.w_copy_needed.append(True)
-            self.w_t.append(None if self.bf16 else z(o, _up(i), f32)[:, :i])
+            self.w_t.append(None if self.mn else z(o, _up(i), f32)[:, :i])
             g_direct = o % 4 == 0 and pl.w_off % 4 == 0 and (self.grads.data_ptr() + 4 * pl.w_off) % 16 == 0
             self.gw_tmp.append(None if g_direct else z(i, _up(o), f32)[:, :o])
 
@@ -170,6 +176,10 @@ class GpuEngine:
                 if self.w_copy_needed[l]:
                     ew.rows(w, dst_bf16=self.w_k[l], stream=stream)
                     n += 1
+            elif self.mn:
+                if self.w_copy_needed[l]:
+                    ew.rows(w, dst=self.w_k[l], stream=stream)
+                    n += 1
             else:
                 if self.w_copy_needed[l]:
                     ew.rows(w, dst=self.w_k[l], dst_t=self.w_t[l], stream=stream)
@@ -183,6 +193,8 @@ class GpuEngine:
         """Stage ``x[idx]`` (f32, [rows, in]) as the first GEMM's A operand and ``y[idx]`` as the labels."""
         if self.bf16:
             ew.rows(x, idx=idx, n_rows=nrows, dst_bf16=self.a[0], stream=stream)
+        elif self.mn:
+            ew.rows(x, idx=idx, n_rows=nrows, dst=self.a[0], stream=stream)
         else:
             ew.rows(x, idx=idx, n_rows=nrows, dst=self.a[0], dst_t=self.at[0], stream=stream)
         ew.rows(y, idx=idx, n_rows=nrows, dst=self.ybuf, stream=stream)
@@ -203,10 +215,11 @@ class GpuEngine:
                     kw["pre"] = self.zpre[l + 1][:nrows, :pl.out_features]
             else:
                 kw["out"] = self.a[l + 1][:nrows, :pl.out_features]
-                kw["out_t"] = self.at[l + 1][:, :nrows]
+                if not self.mn:
+                    kw["out_t"] = self.at[l + 1][:, :nrows]
                 if self.zpre[l + 1] is not None:
                     kw["pre"] = self.zpre[l + 1][:nrows, :pl.out_features]
-            if self.bf16:
+            if self.mn:
                 gemm(a_in, self.w_k[l], b_mn_major=True, **kw)
             else:
                 gemm(a_in, self.w_t[l], **kw)
@@ -226,7 +239,8 @@ class GpuEngine:
             kw["d_bf16"] = self.d[-1][:nrows, :C]
         else:
             kw["d"] = self.d[-1][:nrows, :C]
-            kw["d_t"] = self.dt[-1][:, :nrows]
+            if not self.mn:
+                kw["d_t"] = self.dt[-1][:, :nrows]
         ew.loss_backward(lg, y[:nrows, :C], **kw)
         return 1
 
@@ -254,6 +268,8 @@ class GpuEngine:
                               relu_quirk=self.relu_quirk)
                 if self.bf16:
                     gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
+                elif self.mn:
+                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], **kw)
                 else:
                     gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
                          out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
@@ -261,7 +277,7 @@ class GpuEngine:
             # wgrad: dW[in,out] = A_{l}^T d
             tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
             wbeta = beta if self.gw_tmp[l] is None else 0.0
-            if self.bf16:
+            if self.mn:
                 gemm(self.a[l][:nrows, :i], d_out, a_mn_major=True, b_mn_major=True, out=tgt, beta=wbeta,
                      status=self.status, stream=stream)
             else:

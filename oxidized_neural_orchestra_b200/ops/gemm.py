@@ -7,7 +7,7 @@ and transposed outputs in f32/bf16). Operands are described the way the hardware
 * ``a``: ``[M, K]`` (K contiguous, "K-major") or, with ``a_mn_major=True``, ``[K, M]``
 * ``b``: ``[N, K]`` (K contiguous)              or, with ``b_mn_major=True``, ``[K, N]``
 
-MN-major operands are bf16 only. f32 tensors run as tf32 tiles straight from the f32 storage.
+MN-major operands: bf16, and f32/tf32 (128-byte swizzle on 32-byte units). f32 tensors run as tf32 tiles straight from the f32 storage.
 This mirrors the three GEMMs of the reference's Dense layer
 (machine_learning/src/arch/layers/dense.rs:36-64): forward ``X·W``, ``d·Wᵀ`` and ``Xᵀ·d``.
 """

@@ -143,3 +143,22 @@ def test_gemm_cta_pairs_mn_major_and_split_k(a_mn, b_mn):
         torch.cuda.synchronize()
         assert status.item() == 0
         assert (out.double() - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("shape", [(128, 128, 64), (256, 320, 200), (512, 1024, 512), (1000, 4096, 1024)])
+def test_gemm_tf32_mn_major(a_mn, b_mn, shape):
+    """f32 storage with the M / N dimension contiguous (tf32 tiles, 128-byte swizzle on 32-byte units)."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(5)
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda")
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda")
+    out = torch.zeros(M, N, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, b, a_mn_major=a_mn, b_mn_major=b_mn, out=out, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = _ref(a, b, a_mn, b_mn)
+    assert (out.double() - ref).abs().max().item() <= 4e-3 * ref.abs().max().item()
