@@ -386,6 +386,8 @@ Json B200Config::to_json() const {
   o.set("switch_resets_progress", switch_resets_progress);
   o.set("colocate", colocate);
   o.set("data", data);
+  o.set("probe", probe);
+  o.set("grad_push", grad_push);
   o.set("comm_timeout_s", comm_timeout_s);
   o.set("heartbeat_s", heartbeat_s);
   o.set("heartbeat_timeout_s", heartbeat_timeout_s);
@@ -413,12 +415,14 @@ B200Config B200Config::from_json(const Json& j) {
   str("sharding", c.sharding, {"layer", "even"});
   str("switch_metric", c.switch_metric, {"loss", "grad_norm"});
   str("data", c.data, {"host", "device"});
+  str("grad_push", c.grad_push, {"auto", "on", "off"});
   if (const Json* v = j.find("switch_window")) { c.switch_window = nonzero(*v, "b200.switch_window"); if (c.switch_window < 2) throw InvalidConfig("b200.switch_window must be at least 2"); }
   if (const Json* v = j.find("switch_threshold")) c.switch_threshold = float_non_negative(v->as_double(), "b200.switch_threshold");
   if (const Json* v = j.find("leaky_relu_exact")) c.leaky_relu_exact = v->as_bool();
   if (const Json* v = j.find("global_batch")) c.global_batch = non_negative(*v, "b200.global_batch");
   if (const Json* v = j.find("switch_resets_progress")) c.switch_resets_progress = v->as_bool();
   if (const Json* v = j.find("colocate")) c.colocate = v->as_bool();
+  if (const Json* v = j.find("probe")) c.probe = v->as_bool();
   if (const Json* v = j.find("comm_timeout_s")) c.comm_timeout_s = float_positive(v->as_double(), "b200.comm_timeout_s");
   if (const Json* v = j.find("heartbeat_s")) c.heartbeat_s = float_non_negative(v->as_double(), "b200.heartbeat_s");
   if (const Json* v = j.find("heartbeat_timeout_s")) c.heartbeat_timeout_s = float_non_negative(v->as_double(), "b200.heartbeat_timeout_s");

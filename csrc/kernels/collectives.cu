@@ -126,7 +126,7 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
           if (a.kind >= 1) *reinterpret_cast<float4*>(L.m + si) = m[u];
           if (a.kind == 2) *reinterpret_cast<float4*>(L.v + si) = v[u];
           *(reinterpret_cast<float4*>(L.p_master) + i4) = pp;
-          if (a.algo == 1) {
+          if (a.algo != 0) {   // 1: in-switch reduction and multicast stores; 2: multicast stores only
             if (a.p_mc_f32) multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, pp);
           } else {
 #pragma unroll
@@ -135,7 +135,7 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
                 *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = pp;
           }
           const uint2 pb = pack_bf16x4(pp);
-          if (a.algo == 1 && a.p_mc_bf16) {
+          if (a.algo != 0 && a.p_mc_bf16) {
             multimem_st_bf16x4(reinterpret_cast<uint2*>(a.p_mc_bf16) + i4, pb);
           } else {
 #pragma unroll

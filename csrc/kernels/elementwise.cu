@@ -350,6 +350,20 @@ extern "C" int ono_loss(const OnoLoss* l, ono_stream_t st) {
   return launch_ok("loss");
 }
 
+namespace ono {
+__global__ void push_add_kernel(const float* src, float* dst, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    atomicAdd(dst + i, src[i]);   // result unused: compiled to a reduction that needs no reply
+}
+}  // namespace ono
+
+extern "C" int ono_push_add(const float* src, float* dst, long long n, ono_stream_t st) {
+  if (!src || !dst || n < 0) { set_error("bad push_add args%s", "", 0, 0); return -1; }
+  if (n == 0) return 0;
+  ono::push_add_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)st>>>(src, dst, n);
+  return launch_ok("push_add");
+}
+
 extern "C" int ono_colsum(const void* d, int dtype, int M, int N, int ld, float* out, float beta, ono_stream_t st) {
   if (!d || !out || M <= 0 || N <= 0) { set_error("bad colsum args%s", "", 0, 0); return -1; }
   const int gx = (N + 31) / 32;

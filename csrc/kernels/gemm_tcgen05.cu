@@ -49,7 +49,7 @@ struct GemmDev {
   int* status;
   unsigned long long timeout_ns;
   int split_k;  // > 1: K is split over that many work items per tile, partials added with atomics
-  int tma_out;  // 0: thread stores only; 1: out_f32 leaves through a TMA store; 2: out_bf16 does
+  int tma_out;  // 0: thread stores only; 1: out_f32 leaves through a TMA store; 2: out_bf16 does; 3: out_f32 += through TMA reduce-add
 };
 
 template <int BN>
@@ -154,7 +154,7 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
       }
     }
   }
-  if (row_ok && e.out_f32 && tma_out != 1) {
+  if (row_ok && e.out_f32 && tma_out != 1 && tma_out != 3) {
     float* o = e.out_f32 + row_off;
     if (full) {
 #pragma unroll
@@ -446,7 +446,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           // clips rows >= M and columns >= N
           if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the tile
           __syncwarp();
-          if (p.tma_out == 1) {
+          if (p.tma_out != 2) {
             uint8_t* rp = wstage + lane * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -471,7 +471,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmC, wstage, nc, m0 + quad * 32);
+            if (p.tma_out == 3) tma_reduce_add_2d(&tmC, wstage, nc, m0 + quad * 32);
+            else tma_store_2d(&tmC, wstage, nc, m0 + quad * 32);
             tma_store_commit();
           }
         }
@@ -740,7 +741,15 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_out = 0;
-  if (p.split_k > 1) {
+  if (e.reduce_out) {
+    if (p.split_k > 1 || !e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || ((uintptr_t)e.out_f32 & 15)) {
+      set_error("reduce_out supports a plain, 16-byte aligned f32 output only%s", "");
+      return -1;
+    }
+    rc = encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out);
+    if (rc) return rc;
+    p.tma_out = 3;
+  } else if (p.split_k > 1) {
     // atomics path, no TMA store
   } else if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0) {
     if (encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out) == 0) p.tma_out = 1;

@@ -252,6 +252,9 @@ class GpuEngine:
         that layer's parameters while the layers below are still running."""
         L, n = self.plans, 0
         beta = 1.0 if accumulate else 0.0
+        push = getattr(self, "push", None)
+        if push is not None and accumulate:
+            raise RuntimeError("gradient push cannot accumulate over several batches")
         for l in range(len(L) - 1, -1, -1):
             pl = L[l]
             i, o = pl.in_features, pl.out_features
@@ -274,6 +277,23 @@ class GpuEngine:
                     gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
                          out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
                 n += 1
+            if push is not None:
+                # weight gradient tiles are added straight into the accumulator of the rank that owns those rows (its
+                # window, over NVLink): the reduce-scatter happens inside the GEMM epilogue, tile by tile
+                for r0, r1, dst in push["w"][l]:
+                    if self.mn:
+                        gemm(self.a[l][:nrows, r0:r1], d_out, a_mn_major=True, b_mn_major=True, out=dst, reduce_out=True,
+                             status=self.status, stream=stream)
+                    else:
+                        gemm(self.at[l][r0:r1, :nrows], self.dt[l + 1][:, :nrows], out=dst, reduce_out=True,
+                             status=self.status, stream=stream)
+                    n += 1
+                ew.colsum(d_out, self.gb_view(l), beta=0.0, stream=stream)
+                ew.push_add(self.gb_view(l), push["b"][l], stream=stream)
+                n += 2
+                if after_layer is not None:
+                    n += after_layer(l) or 0
+                continue
             # wgrad: dW[in,out] = A_{l}^T d
             tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
             wbeta = beta if self.gw_tmp[l] is None else 0.0

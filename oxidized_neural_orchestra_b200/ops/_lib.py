@@ -19,7 +19,7 @@ class OnoEpilogue(C.Structure):
         ("bias", C.c_void_p), ("bias_bf16", C.c_void_p), ("aux_f32", C.c_void_p), ("aux_bf16", C.c_void_p),
         ("ld_out", C.c_int), ("ld_outT", C.c_int), ("ld_aux", C.c_int),
         ("act", C.c_int), ("act_param", C.c_float), ("dact", C.c_int), ("dact_param", C.c_float),
-        ("relu_quirk", C.c_int), ("alpha", C.c_float), ("beta", C.c_float),
+        ("relu_quirk", C.c_int), ("alpha", C.c_float), ("beta", C.c_float), ("reduce_out", C.c_int),
     ]
 
 

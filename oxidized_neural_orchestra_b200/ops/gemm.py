@@ -38,7 +38,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          act: str | None = None, act_param: float = 0.0,
          aux: torch.Tensor | None = None, dact: str | None = None, dact_param: float = 0.0,
          relu_quirk: bool = False, alpha: float = 1.0, beta: float = 0.0, bn: int = 0,
-         max_ctas: int = 0, split_k: int = 0, pair: int = 0, status: torch.Tensor | None = None, stream=None) -> None:
+         max_ctas: int = 0, split_k: int = 0, pair: int = 0, reduce_out: bool = False, status: torch.Tensor | None = None, stream=None) -> None:
     """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride."""
     if not a.is_cuda:
         raise RuntimeError("ono gemm needs CUDA tensors (there is no CPU fallback on this path)")
@@ -64,6 +64,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     g.lda, g.ldb = a.stride(0), b.stride(0)
     g.dtype = 0 if a.dtype == torch.float32 else 1
     g.a_major, g.b_major = int(a_mn_major), int(b_mn_major)
+    g.epi.reduce_out = int(reduce_out)
     g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas or DEFAULT_MAX_CTAS, split_k, pair
     e = g.epi
     ld_out = ld_out_t = 0

@@ -201,6 +201,7 @@ def run(r) -> dict:
         "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
         "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
     }
+    metrics["grad_push"] = bool(getattr(r, "push_active", False))
     if r.compress:
         sent = int(r.wire_sent.item())
         metrics["wire"] = ("f16+sparse" if r.sparse_r is not None else "f16")

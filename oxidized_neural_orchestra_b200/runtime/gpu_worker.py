@@ -4,6 +4,7 @@ from __future__ import annotations
 import ctypes as C
 import json
 import math
+import os
 import threading
 import time
 
@@ -83,6 +84,17 @@ class GpuRank:
         self.compress = self.cadence == "round" and (self.b200.get("wire_dtype") == "f16" or self.sparse_r is not None)
         if self.compress:
             lay.add("wire", self.n_pad, torch.float32)
+        # Gradient push (step cadence, dense models whose weight blocks are 16-byte aligned): the weight-gradient GEMMs
+        # add their output tiles into the accumulator of the rank that owns those rows, so the reduce-scatter rides on
+        # the GEMM epilogues instead of a separate pass over NVLink after backward.
+        gp = self.b200.get("grad_push", "auto")
+        lays = engine_layers_from_plan(self.plan)
+        aligned = all(l["kind"] == "dense" and l["out"] % 4 == 0 for l in lays) and \
+            all(pl["offset"] % 4 == 0 for pl in self.plan["layers"])
+        forced_single = os.environ.get("ONO_PUSH_SINGLE", "0") == "1"
+        self.push = self.cadence == "step" and gp == "on" and aligned and (self.world > 1 or forced_single)
+        if self.push:
+            lay.add("acc", self.n_pad, torch.float32)
         if self.tile == "bf16":
             lay.add("params_bf16", self.n_pad, torch.bfloat16)
         needs_async = self.async_ps
@@ -226,8 +238,62 @@ class GpuRank:
         self.use_nvls = mode == "nvls"
         self._set_ownership(ranges, self.worker_ranks, self.opt, kind, False)
 
+    def _snap_to_row_blocks(self, ranges):
+        """Move every interior ownership boundary down to a multiple of 128 rows of the weight matrix it falls into (or
+        to the start of that layer's bias block), so that a pushed GEMM tile never straddles two owners."""
+        marks = []                                     # (begin, end, row_len) of weight blocks, (begin, end, 0) of biases
+        for pl, l in zip(self.plan["layers"], engine_layers_from_plan(self.plan)):
+            w0 = pl["offset"]
+            marks.append((w0, w0 + l["in"] * l["out"], l["out"]))
+            marks.append((w0 + l["in"] * l["out"], w0 + l["in"] * l["out"] + l["out"], 0))
+
+        def snap(b):
+            if b >= self.n:
+                return self.n_pad
+            for lo, hi, row in marks:
+                if lo <= b < hi:
+                    return lo + ((b - lo) // (128 * row)) * 128 * row if row else lo
+            return b
+
+        return [[(snap(b) if b else 0, snap(e)) for b, e in rs if snap(e) > (snap(b) if b else 0)] for rs in ranges]
+
+    def _build_push(self):
+        """Per layer: the (row range, destination view) pieces of its weight gradient and the destination of its bias
+        gradient, each a view of the owner's accumulator region (a peer's window unless this rank owns it)."""
+        acc_off = self.layout.offset("acc") // 4
+        local = self.layout.tensor(self.win, "acc")
+
+        def view(owner, begin, rows, cols):
+            if owner == self.rank or self.win.handle is None:
+                return local[begin:begin + rows * cols].view(rows, cols)
+            return self.win.handle.get_buffer(owner, (rows, cols), torch.float32, acc_off + begin)
+
+        w, b = {}, {}
+        for li, pl in enumerate(self.engine.plans):
+            i, o = pl.in_features, pl.out_features
+            pieces = []
+            for owner, rs in enumerate(self.own):
+                for lo, hi in rs:
+                    a0, a1 = max(lo, pl.w_off), min(hi, pl.w_off + i * o)
+                    if a1 > a0:
+                        r0, r1 = (a0 - pl.w_off) // o, (a1 - pl.w_off) // o
+                        assert (a0 - pl.w_off) % o == 0 and (a1 - pl.w_off) % o == 0 and r0 % 8 == 0
+                        pieces.append((r0, r1, view(owner, a0, r1 - r0, o)))
+                    if lo <= pl.b_off < hi:
+                        b[li] = view(owner, pl.b_off, 1, o).view(-1)
+            w[li] = sorted(pieces, key=lambda t: t[0])
+        return {"w": w, "b": b}
+
     def _set_ownership(self, ranges, workers, opt, mode, wild):
         W = self.world
+        push = self.push and mode == "fused" and self.engine is not None and getattr(self.engine, "plans", None) is not None
+        if self.push and W > 1:       # every rank must take the same decision
+            flag = torch.tensor([1.0 if (push or self.engine is None) else 0.0], device=self.dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            push = push and bool(flag.item() > 0)
+        self.push_active = bool(self.push and mode == "fused" and (push or self.engine is None))
+        if self.push_active:
+            ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)
         self.buckets, self.bucket_after = [], {}
         self.sync_workers = list(workers)
@@ -261,11 +327,19 @@ class GpuRank:
             else:
                 pb = [None] * W
             nvls = getattr(self, "use_nvls", False) and win.mc_ptr != 0 and W > 1
-            S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=1 if nvls else 0,
-                        g_ptrs=win.peer_ptrs(lay.offset(self.grad_region)), p_f32_ptrs=pf, p_bf16_ptrs=pb,
+            algo = 1 if nvls else 0
+            g_region = self.grad_region
+            if self.push_active:
+                # gradients arrive already summed in this rank's accumulator: nothing to reduce over the wires, the
+                # kernel averages, applies the optimizer, zeroes the accumulator and distributes the parameters
+                # (through the switch's multicast when there is one)
+                g_region, wmask = "acc", 1 << self.rank
+                algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
+            S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=algo,
+                        g_ptrs=win.peer_ptrs(lay.offset(g_region)), p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
-                        g_mc=win.mc(lay.offset(self.grad_region)) or None,
+                        g_mc=(win.mc(lay.offset(g_region)) or None) if algo == 1 else None,
                         p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
                         p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
@@ -273,6 +347,12 @@ class GpuRank:
                          epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
                          sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
                          status=self.sync_status.data_ptr())
+            if self.push_active:
+                s.zero_grad = 1
+                if self.engine is not None:
+                    self.engine.push = self._build_push()
+            elif self.engine is not None and hasattr(self.engine, "push"):
+                self.engine.push = None
             self.sync_struct = s
             self._build_buckets()
         elif mode == "async":

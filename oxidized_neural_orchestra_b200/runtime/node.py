@@ -81,8 +81,12 @@ def serve(host: str, port: int, device_kind: str, gpu: int | None, once: bool = 
         except (ConnectionError, OSError, ValueError):
             ch.close()  # a port probe or a stranger: not a session
             continue
+        if ch.peer_entity == "Node":      # a peer measuring latency: answer its pings (stat_service.rs:107-152)
+            _answer_pings(ch)
+            ch.close()
+            continue
         try:
-            _session(ch, device_kind, gpu)
+            _session(ch, device_kind, gpu, lsock, node_id)
         except (ConnectionError, OSError) as e:
             print(f"[ono-node {host}:{port}] session ended: {e}", file=sys.stderr)
         finally:
@@ -92,7 +96,93 @@ def serve(host: str, port: int, device_kind: str, gpu: int | None, once: bool = 
             return
 
 
-def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
+def _answer_pings(ch: wire.Channel) -> None:
+    try:
+        while True:
+            kind, msg = ch.recv(timeout=30)
+            if kind == "control" and msg == "ping":
+                ch.send_command("pong")
+            else:
+                return
+    except (ConnectionError, OSError, TimeoutError):
+        return
+
+
+def _serve_ping_stats(lsock, node_id: str, req: dict) -> dict:
+    """All-pairs latency probe (node/src/stat_service.rs:69-152): connect to ``addrs`` and time ``rounds`` ping/pong
+    round trips with each, while answering the pings of ``incoming`` peers that connect to this node."""
+    rounds, incoming = int(req["rounds"]), int(req["incoming"])
+    threads = []
+
+    def responder():
+        try:
+            conn, _ = lsock.accept()
+        except OSError:
+            return
+        c = wire.Channel(conn)
+        try:
+            c.accept_as("Node", node_id)
+            _answer_pings(c)
+        except (ConnectionError, OSError, ValueError):
+            pass
+        c.close()
+
+    lsock.settimeout(30)
+    for _ in range(incoming):
+        t = threading.Thread(target=responder, daemon=True)
+        t.start()
+        threads.append(t)
+    rtts = {}
+    for addr in req["addrs"]:
+        host, port = addr.rsplit(":", 1)
+        try:
+            c = wire.connect(host, int(port), timeout=10)
+            c.connect_as("Node", node_id)
+            samples = []
+            for _ in range(rounds):
+                t0 = time.perf_counter_ns()
+                c.send_command("ping")
+                kind, msg = c.recv(timeout=10)
+                if msg != "pong":
+                    raise ConnectionError("expected pong")
+                samples.append(time.perf_counter_ns() - t0)
+            c.send_command("disconnect")
+            c.close()
+            rtts[addr] = {"min": float(min(samples)), "max": float(max(samples)), "mean": float(sum(samples) / len(samples))}
+        except (ConnectionError, OSError, TimeoutError) as e:
+            print(f"[ono-node] ping {addr}: {e}", file=sys.stderr)
+    for t in threads:
+        t.join()
+    lsock.settimeout(None)
+    return {"stats_response": {"stats": {"ping": {"rtts": rtts}}}}
+
+
+def obtain_stats(addrs: list[str], rounds: int = 10) -> dict:
+    """Orchestrator side of the probe (orchestrator/src/configs/stat_requester.rs:32-72): node i pings nodes 0..i-1 and
+    accepts the n-i-1 later ones. Returns ``{addr: {peer: max_rtt_ns}}`` (symmetric), the planner's input."""
+    chs = []
+    for a in addrs:
+        host, port = a.rsplit(":", 1)
+        ch = wire.connect(host, int(port))
+        ch.connect_as("Orchestrator")
+        chs.append(ch)
+    n = len(addrs)
+    for i, ch in enumerate(chs):
+        ch.send_command({"stats_request": {"ping": {"addrs": addrs[:i], "rounds": rounds, "incoming": n - i - 1}}})
+    stats: dict = {a: {} for a in addrs}
+    for i, ch in enumerate(chs):
+        _, msg = ch.recv(timeout=120)
+        body = msg.get("stats_response", {}).get("stats") if isinstance(msg, dict) else None
+        rtts = body.get("ping", {}).get("rtts", {}) if isinstance(body, dict) else {}
+        for peer, st in rtts.items():
+            stats[addrs[i]][peer] = int(st["max"])
+            stats[peer][addrs[i]] = int(st["max"])
+        ch.send_command("disconnect")
+        ch.close()
+    return stats
+
+
+def _session(ch: wire.Channel, device_kind: str, gpu: int | None, lsock=None, node_id: str = "") -> None:
     while True:
         kind, msg = ch.recv(timeout=None)
         if kind != "control":
@@ -100,8 +190,11 @@ def _session(ch: wire.Channel, device_kind: str, gpu: int | None) -> None:
         if msg == "disconnect":
             return
         if isinstance(msg, dict) and "stats_request" in msg:
-            # NVSwitch is uniform; report no measurements and let the planner treat pairs as equidistant
-            ch.send_command({"stats_response": {"stats": []}})
+            req = msg["stats_request"].get("ping") if isinstance(msg["stats_request"], dict) else None
+            if req is not None and lsock is not None:
+                ch.send_command(_serve_ping_stats(lsock, node_id, req))
+            else:
+                ch.send_command({"stats_response": {"stats": []}})
             continue
         if msg == "ping":
             ch.send_command("pong")
@@ -184,7 +277,8 @@ def _jsonable(d: dict) -> dict:
 class RemoteHandle:
     """Orchestrator side of a run on listening nodes (orchestrator/src/sessions/session.rs:57-167)."""
 
-    def __init__(self, plan: dict, model_cfg: dict, training_cfg: dict, xs: np.ndarray, ys: np.ndarray, x_size: int, y_size: int):
+    def __init__(self, plan: dict, model_cfg: dict, training_cfg: dict, xs: np.ndarray, ys: np.ndarray, x_size: int, y_size: int,
+                 stats: dict | None = None):
         addrs = training_cfg["addrs"]
         self.n_workers = len(plan["workers"])
         self._q: queue.Queue = queue.Queue()
@@ -211,7 +305,7 @@ class RemoteHandle:
                 raise ConnectionError(f"{addr} answered as {ch.peer_entity}, expected a node")
             self._chs.append(ch)
         for rank, ch in enumerate(self._chs):
-            job = {"model": model_cfg, "training": training_cfg, "rank": rank, "world": len(addrs),
+            job = {"model": model_cfg, "training": training_cfg, "rank": rank, "world": len(addrs), "stats": stats,
                    "master_addr": "127.0.0.1" if master_addr in ("localhost", "127.0.0.1") else master_addr,
                    "master_port": master_port}
             ch.send_command({"create_node": {"spec": job}})
@@ -335,7 +429,14 @@ def start_remote_session(plan, model_cfg, training_cfg, dataset):
     from .session import load_dataset_arrays
 
     xs, ys = load_dataset_arrays(dataset)
-    return RemoteHandle(plan, model_cfg, training_cfg, xs, ys, dataset.x_size, dataset.y_size)
+    stats = None
+    if (training_cfg.get("b200") or {}).get("probe"):
+        # measure the nodes' pairwise latency first and let the planner place servers / order the ring by it
+        from orchestra import _orchestra as core
+
+        stats = obtain_stats(training_cfg["addrs"])
+        plan = json.loads(core.adapt_configs(json.dumps(model_cfg), json.dumps(training_cfg), json.dumps(stats)))
+    return RemoteHandle(plan, model_cfg, training_cfg, xs, ys, dataset.x_size, dataset.y_size, stats)
 
 
 def main(argv=None) -> None:

@@ -67,13 +67,31 @@ def main():
         cases.append(("switch-round", lambda a: orchestra.strategy_switch(
             a, 1, ds(), Adam(0.002), CrossEntropy(), BarrierSync(), BlockingStore(), 8, 48, seed=4,
             b200={"switch_window": 2, "switch_threshold": 10.0})))
+    # gradient push: weight-gradient GEMMs add their tiles into the owner's window over NVLink (needs layer widths that
+    # are multiples of 4, hence its own model with 12 classes)
+    ys12 = np.eye(12, dtype=np.float32)[rng.integers(0, 12, rows)]
+    model12 = Sequential([Dense(384, XavierUniform(), Tanh()), Dense(128, XavierUniform(), ReLU(0.0)),
+                          Dense(12, XavierUniform(), Softmax())])
+    ds12 = lambda: InlineDataset(xs, ys12, 200, 12)
+    push_cases = []
+    for tile in ("tf32", "bf16"):
+        push_cases.append((f"push-ar-{tile}-step", lambda a, t=tile: orchestra.all_reduce(
+            a, ds12(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), 6, 48, seed=4,
+            b200={"sync_every": "step", "tile_dtype": t, "grad_push": "on"})))
+        push_cases.append((f"push-ps-{tile}-step", lambda a, t=tile: orchestra.parameter_server(
+            a, max(1, world // 2), ds12(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), BarrierSync(),
+            BlockingStore(), 6, 48, seed=4, b200={"sync_every": "step", "tile_dtype": t, "colocate": True,
+                                                   "sharding": "even", "grad_push": "on"})))
     report = {}
     ok = True
-    for name, make in cases:
-        got = orchestrate(model, make(gpu)).wait(quiet=True)
+    only = os.environ.get("ONO_PARITY_ONLY", "")
+    for name, make, mdl in [(n, m, model) for n, m in cases] + [(n, m, model12) for n, m in push_cases]:
+        if only and only not in name:
+            continue
+        got = orchestrate(mdl, make(gpu)).wait(quiet=True)
         met = got.metrics()
         if rank == 0:
-            ref = orchestrate(model, make(cpu)).wait(quiet=True)
+            ref = orchestrate(mdl, make(cpu)).wait(quiet=True)
             lg, lr = np.array(got.loss_history()), np.array(ref.loss_history())
             same_len = lg.shape == lr.shape
             dl = float(np.abs(lg - lr).max() / max(1e-9, np.abs(lr).max())) if same_len else float("inf")
@@ -82,9 +100,11 @@ def main():
             loose = any(k in name for k in ("async", "adam", "switch", "bf16"))
             # closeness to the oracle is the criterion; Adam's first steps move every weight by ~lr whatever the
             # gradient's size, so its loss need not fall within six steps
+            if name.startswith("push") and not met.get("grad_push"):
+                same_len = False          # the case must really have run with pushed gradients
             good = same_len and dl < (0.3 if loose else 0.05) and dw < (0.2 if loose else 2e-2) and (loose or lg[-1] < lg[0])
             report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "loss": [float(lg[0]), float(lg[-1])] if same_len else [], "nvls": met.get("nvls"), "mode": met.get("sync_mode"),
-                            "switched": met.get("switched")}
+                            "switched": met.get("switched"), "push": met.get("grad_push")}
             ok = ok and good
         dist.barrier()
     if rank == 0:

@@ -123,3 +123,25 @@ def test_trace_and_metrics_files_of_a_gpu_run(tmp_path):
     assert all(e["tid"] == 1 and e["dur"] > 0 for e in steps)          # device spans from CUDA events
     recs = [json.loads(l) for l in open(mp)]
     assert len(recs) == 3 and all(r["steps"] >= 1 and r["device_ms"] > 0 and r["samples_per_sec"] > 0 for r in recs)
+
+
+@pytest.mark.parametrize("tile", ["tf32", "bf16"])
+def test_gradient_push_through_the_gemm_epilogue_matches_the_plain_path(tile, monkeypatch):
+    """Weight-gradient tiles added into the owner's accumulator by TMA reductions (here the owner is this GPU)."""
+    monkeypatch.setenv("ONO_PUSH_SINGLE", "1")
+    xs, ys = _data(n=192, x=256, y=12)
+    model = Sequential([Dense(384, XavierUniform(), ReLU(0.0)), Dense(256, XavierUniform(), Sigmoid()),
+                        Dense(12, XavierUniform(), Softmax())])
+    out = {}
+    for push in ("off", "on"):
+        tr = orchestra.parameter_server(["gpu:0"], 1, InlineDataset(xs, ys, 256, 12), GradientDescentWithMomentum(0.2, 0.9),
+                                        CrossEntropy(), BarrierSync(), BlockingStore(), max_epochs=8, batch_size=64, seed=3,
+                                        b200={"sync_every": "step", "tile_dtype": tile, "colocate": True, "sharding": "even",
+                                              "grad_push": push})
+        m = orchestrate(model, tr).wait(quiet=True)
+        out[push] = (np.array(m.loss_history()), m.weights_array(), m.metrics())
+    assert out["on"][2]["grad_push"] is True and out["off"][2]["grad_push"] is False
+    assert out["on"][0][-1] < out["on"][0][0]
+    # same products, added by reductions instead of stores: equal up to the order of f32 additions
+    assert np.allclose(out["on"][0], out["off"][0], rtol=1e-4, atol=1e-6)
+    assert np.abs(out["on"][1] - out["off"][1]).max() < 1e-4

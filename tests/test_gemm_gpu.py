@@ -162,3 +162,27 @@ def test_gemm_tf32_mn_major(a_mn, b_mn, shape):
     assert status.item() == 0
     ref = _ref(a, b, a_mn, b_mn)
     assert (out.double() - ref).abs().max().item() <= 4e-3 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gemm_reduce_add_output_and_push_add(dtype):
+    """The output tile is added into the destination by TMA reductions (the form the weight gradient takes
+    when it is pushed into its owner's accumulator)."""
+    from oxidized_neural_orchestra_b200.ops.elementwise import push_add
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    torch.manual_seed(6)
+    M, N, K = 384, 520, 200
+    a = torch.randn(M, 208, device="cuda", dtype=dtype)[:, :K]
+    b = torch.randn(N, 208, device="cuda", dtype=dtype)[:, :K]
+    acc = torch.full((M, 528), 1.0, device="cuda")[:, :N]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        gemm(a, b, out=acc, reduce_out=True, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = 3.0 * _ref(a, b, False, False) + 1.0
+    assert (acc.double() - ref).abs().max().item() <= 3 * _tol(dtype, K) * ref.abs().max().item()
+    x, y = torch.arange(1000, device="cuda", dtype=torch.float32), torch.ones(1000, device="cuda")
+    push_add(x, y)
+    assert torch.equal(y, x + 1)

@@ -68,6 +68,22 @@ def test_nodes_strategy_switch_and_stop(nodes):
     assert m.stop_reason == "stopped" and len(m.loss_history()) < 100000
 
 
+def test_latency_probe_feeds_the_planner(nodes):
+    """All-pairs ping between the node processes, then a session planned from the measured round-trip times."""
+    from oxidized_neural_orchestra_b200.runtime.node import obtain_stats
+
+    stats = obtain_stats(nodes, rounds=4)
+    assert set(stats) == set(nodes)
+    for a in nodes:
+        assert set(stats[a]) == set(nodes) - {a} and all(0 < v < 10**9 for v in stats[a].values())
+        assert all(stats[a][b] == stats[b][a] for b in stats[a])
+    model, xs, ys = _setup()
+    tr = orchestra.parameter_server(nodes, 1, InlineDataset(xs, ys, 6, 3), GradientDescent(0.3), CrossEntropy(), BarrierSync(),
+                                    BlockingStore(), 4, 5, seed=3, b200={"probe": True})
+    m = orchestrate(model, tr).wait(quiet=True)
+    assert m.stop_reason == "max_epochs" and len(m.loss_history()) == 4
+
+
 def test_wire_framing_and_handshake_round_trip():
     import socket
     import struct
