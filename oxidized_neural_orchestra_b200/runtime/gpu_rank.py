@@ -86,6 +86,37 @@ def snap_ranges(ranges_per_rank: list[list[tuple[int, int]]], n_pad: int) -> lis
     return out
 
 
+def snap_to_row_blocks(ranges_per_rank, plan_layers, engine_layers, n, n_pad, rows=128):
+    """Move every interior ownership boundary down to a multiple of ``rows`` rows of the weight matrix it falls into
+    (or to the start of that layer's bias block), so that a weight-gradient tile pushed by a GEMM epilogue never
+    straddles two owners. The same rule applies to both sides of a boundary, so the ranges still partition the vector."""
+    marks = []                                     # (begin, end, row_len) of weight blocks, (begin, end, 0) of biases
+    for pl, l in zip(plan_layers, engine_layers):
+        if l["kind"] != "dense":
+            continue
+        w0 = pl["offset"]
+        marks.append((w0, w0 + l["in"] * l["out"], l["out"]))
+        marks.append((w0 + l["in"] * l["out"], w0 + l["in"] * l["out"] + l["out"], 0))
+
+    def snap(b):
+        if b >= n:
+            return n_pad
+        for lo, hi, row in marks:
+            if lo <= b < hi:
+                return lo + ((b - lo) // (rows * row)) * rows * row if row else lo
+        return b
+
+    out = []
+    for rs in ranges_per_rank:
+        cur = []
+        for b, e in rs:
+            b2, e2 = (snap(b) if b else 0), snap(e)
+            if e2 > b2:
+                cur.append((b2, e2))
+        out.append(cur)
+    return out
+
+
 class BatchFeeder:
     """Stages mini-batches from pinned host memory to the device on a copy stream, one step ahead.
 

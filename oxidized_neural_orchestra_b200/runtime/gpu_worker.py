@@ -19,7 +19,7 @@ from ..ops import _lib
 from ..ops import elementwise as ew
 from ..parallel import sync as S
 from ..parallel.symmetric import SymmetricWindow, WindowLayout
-from .gpu_rank import BatchFeeder, engine_layers_from_plan, optimizer_cfg, snap_ranges
+from .gpu_rank import BatchFeeder, engine_layers_from_plan, optimizer_cfg, snap_ranges, snap_to_row_blocks
 
 
 def _up(n, m=16):
@@ -239,23 +239,7 @@ class GpuRank:
         self._set_ownership(ranges, self.worker_ranks, self.opt, kind, False)
 
     def _snap_to_row_blocks(self, ranges):
-        """Move every interior ownership boundary down to a multiple of 128 rows of the weight matrix it falls into (or
-        to the start of that layer's bias block), so that a pushed GEMM tile never straddles two owners."""
-        marks = []                                     # (begin, end, row_len) of weight blocks, (begin, end, 0) of biases
-        for pl, l in zip(self.plan["layers"], engine_layers_from_plan(self.plan)):
-            w0 = pl["offset"]
-            marks.append((w0, w0 + l["in"] * l["out"], l["out"]))
-            marks.append((w0 + l["in"] * l["out"], w0 + l["in"] * l["out"] + l["out"], 0))
-
-        def snap(b):
-            if b >= self.n:
-                return self.n_pad
-            for lo, hi, row in marks:
-                if lo <= b < hi:
-                    return lo + ((b - lo) // (128 * row)) * 128 * row if row else lo
-            return b
-
-        return [[(snap(b) if b else 0, snap(e)) for b, e in rs if snap(e) > (snap(b) if b else 0)] for rs in ranges]
+        return snap_to_row_blocks(ranges, self.plan["layers"], engine_layers_from_plan(self.plan), self.n, self.n_pad)
 
     def _build_push(self):
         """Per layer: the (row range, destination view) pieces of its weight gradient and the destination of its bias

@@ -232,3 +232,31 @@ def test_csv_conversion_skips_header_and_caches(tmp_path):
     t.write_text("1\t2\n3\t4\n")
     assert core.read_f32_file(core.ensure_binary_dataset(str(t)), 1, 2).tolist() == [2.0, 3.0]
     assert core.ensure_binary_dataset(str(tmp_path / "x.bin")) == str(tmp_path / "x.bin")
+
+
+def test_ownership_boundaries_snap_to_row_blocks_for_pushed_gradients():
+    """Even flat shards moved to 128-row blocks of the weight matrices (biases never split), still a partition."""
+    from oxidized_neural_orchestra_b200.parallel.sync import even_ranges
+    from oxidized_neural_orchestra_b200.runtime.gpu_rank import snap_to_row_blocks
+
+    dims = [(512, 1024), (1024, 1024), (1024, 12)]
+    plan_layers, eng_layers, off = [], [], 0
+    for i, o in dims:
+        plan_layers.append({"offset": off})
+        eng_layers.append({"kind": "dense", "in": i, "out": o})
+        off += i * o + o
+    n, n_pad = off, (off + 15) // 16 * 16
+    for owners in (2, 3, 4):
+        ranges = even_ranges(n_pad, list(range(owners)), 4)
+        snapped = snap_to_row_blocks(ranges, plan_layers, eng_layers, n, n_pad)
+        flat = sorted(r for rs in snapped for r in rs)
+        assert flat[0][0] == 0 and flat[-1][1] == n_pad
+        assert all(a[1] == b[0] for a, b in zip(flat, flat[1:]))                 # contiguous, no overlap
+        starts = {pl["offset"]: (i, o) for pl, (i, o) in zip(plan_layers, dims)}
+        for b, _ in flat[1:]:
+            # every interior boundary is a layer start, a bias start, or a multiple of 128 rows inside a weight block
+            ok = False
+            for w0, (i, o) in starts.items():
+                if b == w0 or b == w0 + i * o or (w0 < b < w0 + i * o and (b - w0) % (128 * o) == 0):
+                    ok = True
+            assert ok, (owners, b)
