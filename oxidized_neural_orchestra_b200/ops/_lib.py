@@ -67,6 +67,7 @@ def _declare(lib) -> None:
         "ono_ps_async_step": [C.POINTER(OnoPsAsync), vp],
         "ono_ring_allreduce": [C.POINTER(OnoRing), vp],
         "ono_pingpong": [ci, vp, vp, ci, C.c_uint, vp, vp, vp],
+        "ono_push_add": [vp, vp, ll, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)

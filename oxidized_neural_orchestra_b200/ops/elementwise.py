@@ -68,11 +68,8 @@ def colsum(d: torch.Tensor, out: torch.Tensor, beta: float = 0.0, stream=None) -
 def push_add(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
     """``dst += src`` with reply-free reductions; ``dst`` may be a view of a peer GPU's window."""
     _need_cuda(src)
-    import ctypes as C
-
     lib = _lib.load()
-    _lib.check(lib.ono_push_add(C.c_void_p(src.data_ptr()), C.c_void_p(dst.data_ptr()), C.c_longlong(src.numel()),
-                                _lib.stream_ptr(stream)), "ono_push_add")
+    _lib.check(lib.ono_push_add(src.data_ptr(), dst.data_ptr(), src.numel(), _lib.stream_ptr(stream)), "ono_push_add")
 
 
 def optim_step(p: torch.Tensor, g: torch.Tensor, *, kind: str, lr: float, mu: float = 0.0, b1: float = 0.9,
