@@ -252,10 +252,10 @@ typedef struct OnoRing {
 } OnoRing;
 int ono_ring_allreduce(const OnoRing* r, ono_stream_t stream);
 
-// Flag ping-pong between two GPUs (node/src/stat_service.rs:107-152 rebuilt as a device probe).
-// role 0 pings, role 1 answers; rtt_ns[rounds] is written by role 0.
 // dst[i] += src[i] with reductions that need no reply (dst may be a peer GPU's memory).
 int ono_push_add(const float* src, float* dst, long long n, ono_stream_t stream);
+// Flag ping-pong between two GPUs (node/src/stat_service.rs:107-152 rebuilt as a device probe).
+// role 0 pings, role 1 answers; rtt_ns[rounds] is written by role 0.
 int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base_epoch,
                  unsigned long long* rtt_ns, int* status, ono_stream_t stream);
 

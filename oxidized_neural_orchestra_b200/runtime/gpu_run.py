@@ -181,7 +181,7 @@ def run(r) -> dict:
     # are identical and rank 0's copy is taken (session.rs:371-412)
     # (with bf16 tiles only the owner of a range holds its up-to-date f32 master, so the owners'
     # ranges are collected whenever ownership is partitioned; one-shot replicates ownership)
-    if r.world > 1 and r.sync_mode != "oneshot":
+    if r.world > 1 and r.sync_mode not in ("oneshot", "ring"):
         tmp = torch.zeros_like(r.C)
         for b, e in r.own[r.rank]:
             tmp[b:e] = r.C[b:e]

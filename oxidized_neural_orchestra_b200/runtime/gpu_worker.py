@@ -95,6 +95,11 @@ class GpuRank:
         self.push = self.cadence == "step" and gp == "on" and aligned and (self.world > 1 or forced_single)
         if self.push:
             lay.add("acc", self.n_pad, torch.float32)
+        # the ring all-reduce (the reference's algorithm, worker/src/middlewares/worker_ring.rs:112-204) circulates chunks
+        # through an accumulation window of its own
+        self.ring_wanted = self.b200.get("allreduce") == "ring" and self.algorithm != "parameter_server"
+        if self.ring_wanted:
+            lay.add("ring_acc", self.n_pad, torch.float32)
         if self.tile == "bf16":
             lay.add("params_bf16", self.n_pad, torch.bfloat16)
         needs_async = self.async_ps
@@ -230,7 +235,7 @@ class GpuRank:
                 # With every rank an owner, peer loads move (N-1)/N of the vector per GPU and direction,
                 # the in-switch reduction a full vector outbound: plain P2P is the better two-shot.
                 mode = "twoshot"
-        if mode == "oneshot":
+        if mode in ("oneshot", "ring"):      # every rank ends the exchange with the whole updated vector
             ranges = [[(0, self.n_pad)] for _ in range(W)]
         else:
             ranges = S.even_ranges(self.n_pad, list(range(W)), W)
@@ -359,8 +364,27 @@ class GpuRank:
             a.timeout_ns = 10_000_000_000
             self.async_struct = a
         elif mode == "ring":
-            if "acc" not in lay.regions:
-                raise RuntimeError("ring all-reduce needs the accumulation window (set b200.allreduce before start)")
+            if "ring_acc" not in lay.regions:
+                raise RuntimeError("ring all-reduce needs its accumulation window (set b200.allreduce before start)")
+            if set(workers) != set(range(W)):
+                raise RuntimeError("ring all-reduce needs every rank to be a worker")
+            r = _lib.OnoRing()
+            r.nranks, r.rank, r.n = W, self.rank, self.n_pad
+            r.nblocks = int(min(_lib.load().ono_num_sms(), max(1, self.n_pad // 4 // W // 512)))
+            for q in range(W):
+                r.acc[q] = win.peer_ptrs(lay.offset("ring_acc"))[q]
+                r.flags[q] = win.flag_ptrs[q] + 4096 * 4        # the second half of the flag pad
+            self.ring_epoch = getattr(self, "ring_epoch", None)
+            if self.ring_epoch is None:
+                self.ring_epoch = torch.zeros(1024, dtype=torch.int32, device=self.dev)
+            r.epoch = self.ring_epoch.data_ptr()
+            r.p, r.m, r.v = self.C.data_ptr(), self.m_loc.data_ptr(), self.v_loc.data_ptr()
+            r.adam_pows = self.adam_pows.data_ptr()
+            r.p_bf16 = self.shadow.data_ptr() if self.shadow is not None else None
+            r.kind = S.OPT_KIND[opt.kind]
+            r.lr, r.mu, r.b1, r.b2, r.eps = opt.lr, opt.mu, opt.b1, opt.b2, opt.eps
+            r.status, r.timeout_ns = self.sync_status.data_ptr(), 10_000_000_000
+            self.ring_struct = r
 
     def _build_buckets(self) -> None:
         """Split the fused synchronisation into per-layer buckets, in backward order, so that a bucket
@@ -450,6 +474,10 @@ class GpuRank:
                 a.p_local_bf16 = self.shadow.data_ptr() if self.shadow is not None else None
                 _lib.check(_lib.load().ono_ps_async_step(C.byref(a), _lib.stream_ptr(stream)), "ono_ps_async_step")
                 n += 1
+        elif self.sync_mode == "ring":
+            self.ring_struct.g = g_tensor.data_ptr()
+            _lib.check(_lib.load().ono_ring_allreduce(C.byref(self.ring_struct), _lib.stream_ptr(stream)), "ono_ring_allreduce")
+            n += 1
         elif self.sync_mode == "nccl":
             with torch.cuda.stream(stream):
                 if self.world > 1:

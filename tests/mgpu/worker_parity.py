@@ -40,7 +40,7 @@ def main():
     cpu = [f"cpu:{i}" for i in range(world)]
     cases = []
     for cadence in ("step", "round"):
-        for ar in ("twoshot", "oneshot", "nvls", "nccl"):
+        for ar in ("twoshot", "oneshot", "nvls", "ring", "nccl"):
             cases.append((f"ar-{ar}-{cadence}", lambda a, c=cadence, m=ar: orchestra.all_reduce(
                 a, ds(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), 6, 48, seed=4,
                 b200={"sync_every": c, "allreduce": m})))
