@@ -105,9 +105,11 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
               }
           }
           const long long si = (i4 << 2) - L.state_off;
-          p[u] = *(reinterpret_cast<const float4*>(L.p_master) + i4);
-          if (a.kind >= 1) m[u] = *reinterpret_cast<const float4*>(L.m + si);
-          if (a.kind == 2) v[u] = *reinterpret_cast<const float4*>(L.v + si);
+          // parameters and optimizer state are touched once per step: streaming (evict-first) accesses keep them from
+          // displacing the bf16 shadow and the activations the next forward reads
+          p[u] = __ldcs(reinterpret_cast<const float4*>(L.p_master) + i4);
+          if (a.kind >= 1) m[u] = __ldcs(reinterpret_cast<const float4*>(L.m + si));
+          if (a.kind == 2) v[u] = __ldcs(reinterpret_cast<const float4*>(L.v + si));
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -123,9 +125,9 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
             const float gx = g[u].x * s.gs, gy = g[u].y * s.gs, gz = g[u].z * s.gs, gw = g[u].w * s.gs;
             sq += (double)(gx * gx + gy * gy) + (double)(gz * gz + gw * gw);
           }
-          if (a.kind >= 1) *reinterpret_cast<float4*>(L.m + si) = m[u];
-          if (a.kind == 2) *reinterpret_cast<float4*>(L.v + si) = v[u];
-          *(reinterpret_cast<float4*>(L.p_master) + i4) = pp;
+          if (a.kind >= 1) __stcs(reinterpret_cast<float4*>(L.m + si), m[u]);
+          if (a.kind == 2) __stcs(reinterpret_cast<float4*>(L.v + si), v[u]);
+          __stcs(reinterpret_cast<float4*>(L.p_master) + i4, pp);
           if (a.algo != 0) {   // 1: in-switch reduction and multicast stores; 2: multicast stores only
             if (a.p_mc_f32) multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, pp);
           } else {
