@@ -100,6 +100,8 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
     b200 = {"sync_every": "step", "tile_dtype": cfg["tile"], "data": data_mode, "sharding": "even", "colocate": True}
     if cfg.get("grad_push"):
         b200["grad_push"] = cfg["grad_push"]
+    if cfg.get("grad_stage"):
+        b200["grad_stage"] = cfg["grad_stage"]
     strat = cfg["strategy"]
     if strat.startswith("ps") or strat.startswith("ss"):
         ns = min(int(strat[2:] or 2), n_gpus)
@@ -162,6 +164,7 @@ def main() -> None:
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--config", default="deep", choices=sorted(CONFIGS))
     ap.add_argument("--push", default=None, choices=("on", "off", "auto"), help="gradient push through the GEMM epilogues")
+    ap.add_argument("--stage", default=None, choices=("on", "off", "auto"), help="staged reduce-scatter during backward")
     ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -184,6 +187,8 @@ def main() -> None:
         cfg["strategy"] = args.strategy
     if args.push:
         cfg["grad_push"] = args.push
+    if args.stage:
+        cfg["grad_stage"] = args.stage
     W, K = max(3, args.warmup), args.steps
     if args.impl == "nccl":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -220,7 +225,7 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
             "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
                        "optimizer": cfg["opt"][0], "l2": "per-step working set (weights+grads > 2 GB) exceeds L2",
-                       "sync": m["sync_mode"], "grad_push": bool(m.get("grad_push", False))},
+                       "sync": m["sync_mode"], "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["bench_wall_s"] * 1e3 / K,

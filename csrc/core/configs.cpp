@@ -387,6 +387,7 @@ Json B200Config::to_json() const {
   o.set("colocate", colocate);
   o.set("data", data);
   o.set("probe", probe);
+  o.set("grad_stage", grad_stage);
   o.set("grad_push", grad_push);
   o.set("comm_timeout_s", comm_timeout_s);
   o.set("heartbeat_s", heartbeat_s);
@@ -416,6 +417,7 @@ B200Config B200Config::from_json(const Json& j) {
   str("switch_metric", c.switch_metric, {"loss", "grad_norm"});
   str("data", c.data, {"host", "device"});
   str("grad_push", c.grad_push, {"auto", "on", "off"});
+  str("grad_stage", c.grad_stage, {"auto", "on", "off"});
   if (const Json* v = j.find("switch_window")) { c.switch_window = nonzero(*v, "b200.switch_window"); if (c.switch_window < 2) throw InvalidConfig("b200.switch_window must be at least 2"); }
   if (const Json* v = j.find("switch_threshold")) c.switch_threshold = float_non_negative(v->as_double(), "b200.switch_threshold");
   if (const Json* v = j.find("leaky_relu_exact")) c.leaky_relu_exact = v->as_bool();

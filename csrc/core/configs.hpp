@@ -108,6 +108,7 @@ struct B200Config {
   bool colocate = false;                  // server ranks also train (B200 extension)
   std::string data = "host";              // "host": per-step H2D from pinned memory | "device"
   bool probe = false;                     // measure pairwise node latency before planning (host:port sessions)
+  std::string grad_stage = "auto";        // "auto" | "on" | "off": copy peers' finished gradient ranges into local staging during backward
   std::string grad_push = "auto";         // "auto" | "on" | "off": weight-gradient GEMMs add their tiles into the owner's accumulator
   double comm_timeout_s = 300.0;          // a collective or device wait that exceeds this ends the run with an error
   double heartbeat_s = 2.0;               // period of a node's liveness messages (0 = none)

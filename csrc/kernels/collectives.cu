@@ -440,6 +440,134 @@ extern "C" int ono_ps_async_step(const OnoPsAsync* s, ono_stream_t st) {
   return check_launch("ps_async_step");
 }
 
+// ------------------------------------------------------------------------------------------------
+// Staged reduce-scatter (see OnoStagePull). One thread per block drives a ring of shared-memory slots:
+// bulk load peer -> slot (completion on an mbarrier), bulk store slot -> local staging buffer.
+// ------------------------------------------------------------------------------------------------
+namespace ono {
+constexpr uint32_t PULL_CHUNK = 32768;   // bytes per bulk copy
+constexpr int PULL_SLOTS = 6;            // 192 KB of shared memory in flight per block
+
+__global__ void __launch_bounds__(32) stage_pull_kernel(const OnoStagePull a) {
+  extern __shared__ uint8_t pull_raw[];
+  uint8_t* slots = pull_raw + ((128u - (smem_u32(pull_raw) & 127u)) & 127u);
+  __shared__ __align__(8) uint64_t bar[PULL_SLOTS];
+  __shared__ int abort_flag;
+  if (threadIdx.x != 0) return;
+  for (int s = 0; s < PULL_SLOTS; ++s) mbar_init(&bar[s], 1);
+  abort_flag = 0;
+  mbar_fence_init();
+  const uint32_t want = *a.step;
+  // every source rank must have announced this bucket for this step before its window is read
+  for (int q = 0; q < a.nranks; ++q) {
+    if (!a.src[q] || q == a.rank) continue;
+    if (!wait_flag_ge(a.ready + q * ONO_STAGE_BUCKETS + a.bucket, want, a.timeout_ns)) {
+      if (a.status) atomicCAS(a.status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
+      return;
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");   // the copies below run in the async proxy, after the acquires above
+  // my work items: chunk g of the enumeration (source, range, offset) with g % nblocks == blockIdx.x
+  struct Item { const uint8_t* src; uint8_t* dst; uint32_t bytes; };
+  auto item = [&](long long want_idx, Item& out) -> bool {   // want_idx-th item of this block, in enumeration order
+    long long g = 0, mine = 0;
+    for (int q = 0; q < a.nranks; ++q) {
+      if (!a.src[q] || q == a.rank) continue;
+      for (int r = 0; r < a.n_ranges; ++r) {
+        const long long b0 = a.ranges[r].begin * 4ll, b1 = ((a.ranges[r].end + 3) / 4 * 4) * 4ll;
+        const long long nch = (b1 - b0 + PULL_CHUNK - 1) / PULL_CHUNK;
+        // chunks of this (q, r) that belong to this block: g + c with (g + c) % nblocks == blk
+        long long first = ((long long)blockIdx.x - g % a.nblocks + a.nblocks) % a.nblocks;
+        const long long cnt = first < nch ? (nch - first + a.nblocks - 1) / a.nblocks : 0;
+        if (want_idx < mine + cnt) {
+          const long long c = first + (want_idx - mine) * a.nblocks;
+          const long long off = b0 + c * PULL_CHUNK;
+          out.src = reinterpret_cast<const uint8_t*>(a.src[q]) + off;
+          out.dst = reinterpret_cast<uint8_t*>(a.dst[q]) + off;
+          out.bytes = (uint32_t)min((long long)PULL_CHUNK, b1 - off);
+          return true;
+        }
+        mine += cnt;
+        g += nch;
+      }
+    }
+    return false;
+  };
+  volatile int* abortp = &abort_flag;
+  Item it;
+  long long issued = 0;
+  for (; issued < PULL_SLOTS && item(issued, it); ++issued) {
+    mbar_expect_tx(&bar[issued], it.bytes);
+    bulk_load_1d(slots + (size_t)issued * PULL_CHUNK, it.src, it.bytes, &bar[issued]);
+  }
+  // A slot is refilled PULL_LAG items after its store was issued, so the wait for that store to have read the slot
+  // almost never blocks and PULL_SLOTS - PULL_LAG loads stay in flight.
+  constexpr int PULL_LAG = 2;
+  for (long long j = 0; item(j, it); ++j) {
+    const int s = (int)(j % PULL_SLOTS);
+    if (!mbar_wait_bounded(&bar[s], (uint32_t)((j / PULL_SLOTS) & 1), abortp, a.timeout_ns)) {
+      if (a.status) atomicCAS(a.status, 0, ONO_ERR_TIMEOUT_FULL);
+      break;
+    }
+    bulk_store_1d(it.dst, slots + (size_t)s * PULL_CHUNK, it.bytes);
+    tma_store_commit();
+    const long long jr = j - PULL_LAG;              // the store of item jr has had PULL_LAG items to drain
+    Item nx;
+    if (jr >= 0 && item(jr + PULL_SLOTS, nx)) {
+      tma_store_wait_read<PULL_LAG>();
+      const int sr = (int)(jr % PULL_SLOTS);
+      mbar_expect_tx(&bar[sr], nx.bytes);
+      bulk_load_1d(slots + (size_t)sr * PULL_CHUNK, nx.src, nx.bytes, &bar[sr]);
+    }
+  }
+  tma_store_wait_all<0>();   // staged data is in memory before the kernel ends
+}
+
+struct FlagPtrs { unsigned int* p[ONO_MAX_RANKS]; };
+__global__ void stage_signal_kernel2(FlagPtrs f, int nranks, int rank, int bucket, const unsigned int* step) {
+  const int q = threadIdx.x;
+  if (q < nranks && f.p[q]) {
+    __threadfence_system();
+    st_release_sys(f.p[q] + rank * ONO_STAGE_BUCKETS + bucket, *step);
+  }
+}
+__global__ void stage_tick_kernel(unsigned int* step) { *step += 1u; }
+}  // namespace ono
+
+extern "C" int ono_stage_pull(const OnoStagePull* s, ono_stream_t st) {
+  if (!s || s->nranks < 1 || s->nranks > ONO_MAX_RANKS || s->nblocks < 1 || s->bucket < 0 || s->bucket >= ONO_STAGE_BUCKETS ||
+      !s->ready || !s->step || s->n_ranges < 0 || s->n_ranges > ONO_MAX_RANGES) {
+    set_error("bad stage_pull args%s", "", 0, 0);
+    return -1;
+  }
+  for (int r = 0; r < s->n_ranges; ++r)
+    if (s->ranges[r].begin % 4) { set_error("stage_pull ranges must begin at multiples of 4 elements%s", "", 0, 0); return -1; }
+  static bool attr = false;
+  const int smem = PULL_SLOTS * PULL_CHUNK + 128;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(stage_pull_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(stage_pull): %s", cudaGetErrorString(e), 0, 0); return -6; }
+    attr = true;
+  }
+  stage_pull_kernel<<<s->nblocks, 32, smem, (cudaStream_t)st>>>(*s);
+  return check_launch("stage_pull");
+}
+
+extern "C" int ono_stage_signal(unsigned int* const* flags, int nranks, int rank, int bucket, const unsigned int* step,
+                                ono_stream_t st) {
+  if (!flags || nranks < 1 || nranks > ONO_MAX_RANKS || !step) { set_error("bad stage_signal args%s", "", 0, 0); return -1; }
+  FlagPtrs f;
+  for (int q = 0; q < ONO_MAX_RANKS; ++q) f.p[q] = q < nranks ? flags[q] : nullptr;
+  stage_signal_kernel2<<<1, 32, 0, (cudaStream_t)st>>>(f, nranks, rank, bucket, step);
+  return check_launch("stage_signal");
+}
+
+extern "C" int ono_stage_tick(unsigned int* step, ono_stream_t st) {
+  if (!step) return -1;
+  stage_tick_kernel<<<1, 1, 0, (cudaStream_t)st>>>(step);
+  return check_launch("stage_tick");
+}
+
 extern "C" int ono_ring_allreduce(const OnoRing* r, ono_stream_t st) {
   if (!r || r->nranks < 1 || r->nranks > ONO_MAX_RANKS || r->nblocks < 1 || r->n <= 0) {
     set_error("bad ring args%s", "", 0, 0);
@@ -465,6 +593,7 @@ extern "C" int ono_sizeof(int which) {
     case 4: return (int)sizeof(OnoSync);
     case 5: return (int)sizeof(OnoPsAsync);
     case 6: return (int)sizeof(OnoRing);
+    case 7: return (int)sizeof(OnoStagePull);
     default: return -1;
   }
 }

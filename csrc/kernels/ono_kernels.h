@@ -252,6 +252,25 @@ typedef struct OnoRing {
 } OnoRing;
 int ono_ring_allreduce(const OnoRing* r, ono_stream_t stream);
 
+// Staged reduce-scatter: while backward is still running, a few SMs copy the peers' finished gradient ranges (those this
+// rank owns) from their windows into local staging buffers with bulk async copies through shared memory; the fused
+// optimizer kernel then reads every worker's gradient from local HBM. `ready` are this rank's flag words
+// [source rank * ONO_STAGE_BUCKETS + bucket], written by ono_stage_signal on the source once its gradients of that bucket exist.
+#define ONO_STAGE_BUCKETS 64
+typedef struct OnoStagePull {
+  int nranks, rank, nblocks, bucket;
+  const float* src[ONO_MAX_RANKS];           // every rank's gradient window (null = not a worker / self)
+  float* dst[ONO_MAX_RANKS];                 // local staging buffer of each source rank
+  int n_ranges;
+  OnoRange ranges[ONO_MAX_RANGES];           // owned ranges of this bucket (multiples of 4 elements)
+  const unsigned int* ready;                 // local flag words
+  const unsigned int* step;                  // device word holding the current step number
+  int* status; unsigned long long timeout_ns;
+} OnoStagePull;
+int ono_stage_pull(const OnoStagePull* s, ono_stream_t stream);
+// writes *step into flags[q][rank * ONO_STAGE_BUCKETS + bucket] of every rank q (release at system scope)
+int ono_stage_signal(unsigned int* const* flags, int nranks, int rank, int bucket, const unsigned int* step, ono_stream_t stream);
+int ono_stage_tick(unsigned int* step, ono_stream_t stream);
 // dst[i] += src[i] with reductions that need no reply (dst may be a peer GPU's memory).
 int ono_push_add(const float* src, float* dst, long long n, ono_stream_t stream);
 // Flag ping-pong between two GPUs (node/src/stat_service.rs:107-152 rebuilt as a device probe).

@@ -68,6 +68,9 @@ def _declare(lib) -> None:
         "ono_ring_allreduce": [C.POINTER(OnoRing), vp],
         "ono_pingpong": [ci, vp, vp, ci, C.c_uint, vp, vp, vp],
         "ono_push_add": [vp, vp, ll, vp],
+        "ono_stage_pull": [C.POINTER(OnoStagePull), vp],
+        "ono_stage_signal": [C.POINTER(vp), ci, ci, ci, vp, vp],
+        "ono_stage_tick": [vp, vp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)
@@ -76,7 +79,7 @@ def _declare(lib) -> None:
     lib.ono_num_sms.restype = ci
     lib.ono_sizeof.argtypes = [ci]
     lib.ono_sizeof.restype = ci
-    for i, st in enumerate((OnoGemm, OnoLoss, OnoOptim, OnoRows, OnoSync, OnoPsAsync, OnoRing)):
+    for i, st in enumerate((OnoGemm, OnoLoss, OnoOptim, OnoRows, OnoSync, OnoPsAsync, OnoRing, OnoStagePull)):
         if lib.ono_sizeof(i) != C.sizeof(st):
             raise RuntimeError(f"ABI mismatch for {st.__name__}: C {lib.ono_sizeof(i)} vs ctypes {C.sizeof(st)}")
 
@@ -135,6 +138,19 @@ class OnoRows(C.Structure):
 
 class OnoRange(C.Structure):
     _fields_ = [("begin", C.c_longlong), ("end", C.c_longlong)]
+
+
+STAGE_BUCKETS = 64
+
+
+class OnoStagePull(C.Structure):
+    _fields_ = [
+        ("nranks", C.c_int), ("rank", C.c_int), ("nblocks", C.c_int), ("bucket", C.c_int),
+        ("src", C.c_void_p * MAX_RANKS), ("dst", C.c_void_p * MAX_RANKS),
+        ("n_ranges", C.c_int), ("ranges", OnoRange * MAX_RANGES),
+        ("ready", C.c_void_p), ("step", C.c_void_p),
+        ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+    ]
 
 
 class OnoSyncLocal(C.Structure):

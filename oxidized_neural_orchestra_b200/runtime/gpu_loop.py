@@ -52,6 +52,28 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
         st.wait_stream(comm)
         n += e.refresh(stream=st)
         return n
+    if with_sync and getattr(r, "stage_buckets", None):
+        # staged reduce-scatter: every finished bucket is announced to the peers, and the peers' copies of the ranges
+        # this rank owns are pulled into local staging on the communication stream while backward continues
+        n += r.stage_tick(st)
+        comm = r.comm_stream
+
+        def after_layer_stage(l):
+            k = 0
+            for bucket, pull in r.stage_after.get(l, ()):
+                k += r.stage_signal(bucket, st)
+                if pull is not None:
+                    ev = torch.cuda.Event()
+                    ev.record(st)
+                    comm.wait_event(ev)
+                    k += r.stage_pull(pull, comm)
+            return k
+
+        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st, after_layer=after_layer_stage)
+        st.wait_stream(comm)
+        n += r._launch_sync(r.G, st)
+        n += e.refresh(stream=st)
+        return n
     n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
     if r.cadence == "round":
         # sequential.rs:129-141: stateless SGD on the working copy, residual += grad
@@ -93,7 +115,12 @@ def run_batch(r, slot: int, nrows: int) -> None:
 def server_step(r) -> None:
     """A pure server rank takes part in the synchronisation only."""
     with torch.cuda.stream(r.stream):
-        if r.buckets:  # the same launches, in the same order, as the workers issue
+        if getattr(r, "stage_buckets", None):   # a server-only rank pulls the workers' gradients of the ranges it owns
+            r.stage_tick(r.stream)
+            for _, _, pull in r.stage_buckets:
+                r.stage_pull(pull, r.stream)
+            r._launch_sync(r.G, r.stream)
+        elif r.buckets:  # the same launches, in the same order, as the workers issue
             if r.sync_opt.kind == "adam":
                 ew.adam_tick(r.adam_pows, r.sync_opt.b1, r.sync_opt.b2, stream=r.stream)
             for _, bk in r.buckets:

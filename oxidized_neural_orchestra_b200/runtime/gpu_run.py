@@ -202,6 +202,7 @@ def run(r) -> dict:
         "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
     }
     metrics["grad_push"] = bool(getattr(r, "push_active", False))
+    metrics["grad_stage"] = bool(getattr(r, "stage_active", False))
     if r.compress:
         sent = int(r.wire_sent.item())
         metrics["wire"] = ("f16+sparse" if r.sparse_r is not None else "f16")

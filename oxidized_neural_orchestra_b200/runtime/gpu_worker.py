@@ -97,6 +97,12 @@ class GpuRank:
             lay.add("acc", self.n_pad, torch.float32)
         # the ring all-reduce (the reference's algorithm, worker/src/middlewares/worker_ring.rs:112-204) circulates chunks
         # through an accumulation window of its own
+        # Staged reduce-scatter (step cadence, several GPUs): while backward runs, a few SMs copy the peers' finished
+        # gradient ranges this rank owns into local staging buffers (bulk async copies through shared memory), and the
+        # fused optimizer kernel afterwards reads every worker's gradient from local HBM instead of over NVLink.
+        self.stage = self.cadence == "step" and self.b200.get("grad_stage", "auto") == "on" and self.world > 1 and not self.push
+        if self.stage:
+            lay.add("stage_ready", self.world * _lib.STAGE_BUCKETS, torch.int32)
         self.ring_wanted = self.b200.get("allreduce") == "ring" and self.algorithm != "parameter_server"
         if self.ring_wanted:
             lay.add("ring_acc", self.n_pad, torch.float32)
@@ -130,6 +136,10 @@ class GpuRank:
         self.epoch_words = torch.zeros(1024, dtype=torch.int32, device=self.dev)
         self.sync_status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.sumsq = torch.zeros(1, dtype=torch.float64, device=self.dev)
+        if self.stage:
+            self.stage_buf = [None if q == self.rank else torch.zeros(self.n_pad, device=self.dev) for q in range(self.world)]
+            self.stage_step = torch.zeros(1, dtype=torch.int32, device=self.dev)
+            self.stage_sms = max(1, min(int(os.environ.get("ONO_STAGE_SMS", "8")), 32))
 
     def _init_params(self):
         """Every rank generates the whole vector from the per-layer generators: the same Philox
@@ -285,6 +295,7 @@ class GpuRank:
             ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)
         self.buckets, self.bucket_after = [], {}
+        self.stage_buckets, self.stage_after, self.stage_active = [], {}, False
         self.sync_workers = list(workers)
         self.sync_mode = mode
         self.sync_opt = opt
@@ -318,14 +329,21 @@ class GpuRank:
             nvls = getattr(self, "use_nvls", False) and win.mc_ptr != 0 and W > 1
             algo = 1 if nvls else 0
             g_region = self.grad_region
+            stage_active = bool(getattr(self, "stage", False)) and not self.push_active and not self.compress and mode == "fused"
+            self.stage_active = stage_active
             if self.push_active:
                 # gradients arrive already summed in this rank's accumulator: nothing to reduce over the wires, the
                 # kernel averages, applies the optimizer, zeroes the accumulator and distributes the parameters
                 # (through the switch's multicast when there is one)
                 g_region, wmask = "acc", 1 << self.rank
                 algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
+            g_ptrs = win.peer_ptrs(lay.offset(g_region))
+            if stage_active:
+                # every worker's gradient is read from this GPU's memory: its own window, or the staged copy of a peer's
+                g_ptrs = [g_ptrs[q] if q == self.rank else self.stage_buf[q].data_ptr() for q in range(W)]
+                algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
             S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=algo,
-                        g_ptrs=win.peer_ptrs(lay.offset(g_region)), p_f32_ptrs=pf, p_bf16_ptrs=pb,
+                        g_ptrs=g_ptrs, p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
                         g_mc=(win.mc(lay.offset(g_region)) or None) if algo == 1 else None,
@@ -344,6 +362,7 @@ class GpuRank:
                 self.engine.push = None
             self.sync_struct = s
             self._build_buckets()
+            self._build_stage(workers)
         elif mode == "async":
             a = _lib.OnoPsAsync()
             a.nranks, a.rank, a.nblocks = W, self.rank, self.nblocks
@@ -443,6 +462,76 @@ class GpuRank:
                     self.bucket_after.setdefault(l["index"], []).append(s)
                 pending_end = begin
                 cur_end = None
+
+    def _bucket_ranges(self, min_elems: int = 4 << 20):
+        """(layer index after which the bucket is complete, begin, end) in backward order: whole layers grouped until a
+        bucket holds at least `min_elems` parameters; a float4 group straddling two layers goes with the lower layer."""
+        up4 = lambda x: (x + 3) // 4 * 4
+        layers = [l for l in self.plan["layers"] if l["n_params"] > 0]
+        out, pending_end, cur_end = [], self.n_pad, None
+        for idx in range(len(layers) - 1, -1, -1):
+            l = layers[idx]
+            begin = 0 if idx == 0 else up4(l["offset"])
+            if cur_end is None:
+                cur_end = pending_end
+            if cur_end - begin >= min_elems or idx == 0:
+                if cur_end > begin:
+                    out.append((l["index"], begin, cur_end))
+                pending_end, cur_end = begin, None
+        return out
+
+    def _build_stage(self, workers) -> None:
+        """Per bucket: the pull of the peers' gradient ranges this rank owns (launched on the communication stream once
+        the peers have announced the bucket) and the announcement of this rank's own gradients."""
+        from ..ops import gemm as gemm_mod
+
+        self.stage_buckets, self.stage_after = [], {}
+        if not getattr(self, "stage_active", False):
+            return
+        gemm_mod.DEFAULT_MAX_CTAS = _lib.load().ono_num_sms() - self.stage_sms
+        buckets = self._bucket_ranges()
+        while len(buckets) > _lib.STAGE_BUCKETS:                      # merge neighbours until the flag table suffices
+            buckets = [(buckets[i + 1][0] if i + 1 < len(buckets) else buckets[i][0],
+                        buckets[i + 1][1] if i + 1 < len(buckets) else buckets[i][1], buckets[i][2])
+                       for i in range(0, len(buckets), 2)]
+        g_peer = self.win.peer_ptrs(self.layout.offset(self.grad_region))
+        ready = self.layout.tensor(self.win, "stage_ready")
+        self.stage_flag_arr = (C.c_void_p * self.world)(*self.win.peer_ptrs(self.layout.offset("stage_ready")))
+        for k, (layer, begin, end) in enumerate(buckets):
+            mine = []
+            for b, e in self.own[self.rank]:
+                lo, hi = max(b, begin), min(e, end)
+                if hi > lo:
+                    mine.append((lo, hi))
+            pull = None
+            if mine:
+                pull = _lib.OnoStagePull()
+                pull.nranks, pull.rank, pull.nblocks, pull.bucket = self.world, self.rank, self.stage_sms, k
+                for q in range(self.world):
+                    pull.src[q] = g_peer[q] if (q in workers and q != self.rank) else None
+                    pull.dst[q] = self.stage_buf[q].data_ptr() if q != self.rank else None
+                pull.n_ranges = len(mine)
+                for i, (b, e) in enumerate(mine):
+                    pull.ranges[i].begin, pull.ranges[i].end = b, e
+                pull.ready, pull.step = ready.data_ptr(), self.stage_step.data_ptr()
+                pull.status, pull.timeout_ns = self.sync_status.data_ptr(), 10_000_000_000
+            self.stage_buckets.append((layer, k, pull))
+            self.stage_after.setdefault(layer, []).append((k, pull))
+
+    def stage_tick(self, stream) -> int:
+        _lib.check(_lib.load().ono_stage_tick(self.stage_step.data_ptr(), _lib.stream_ptr(stream)), "ono_stage_tick")
+        return 1
+
+    def stage_signal(self, k: int, stream) -> int:
+        _lib.check(_lib.load().ono_stage_signal(self.stage_flag_arr, self.world, self.rank, k, self.stage_step.data_ptr(),
+                                                _lib.stream_ptr(stream)), "ono_stage_signal")
+        return 1
+
+    def stage_pull(self, pull, stream) -> int:
+        if pull is None:
+            return 0
+        _lib.check(_lib.load().ono_stage_pull(C.byref(pull), _lib.stream_ptr(stream)), "ono_stage_pull")
+        return 1
 
     def _launch_sync(self, g_tensor: torch.Tensor, stream) -> int:
         """One synchronisation of `g_tensor` (the window's gradient region) into the parameters."""

@@ -82,6 +82,19 @@ def main():
             a, max(1, world // 2), ds12(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), BarrierSync(),
             BlockingStore(), 6, 48, seed=4, b200={"sync_every": "step", "tile_dtype": t, "colocate": True,
                                                    "sharding": "even", "grad_push": "on"})))
+    # staged reduce-scatter: peers' gradient ranges copied into local staging during backward
+    for tile in ("tf32", "bf16"):
+        push_cases.append((f"stage-ar-{tile}-step", lambda a, t=tile: orchestra.all_reduce(
+            a, ds12(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), 6, 48, seed=4,
+            b200={"sync_every": "step", "tile_dtype": t, "grad_stage": "on"})))
+        push_cases.append((f"stage-ps-{tile}-step", lambda a, t=tile: orchestra.parameter_server(
+            a, max(1, world // 2), ds12(), GradientDescentWithMomentum(0.1, 0.9), CrossEntropy(), BarrierSync(),
+            BlockingStore(), 6, 48, seed=4, b200={"sync_every": "step", "tile_dtype": t, "colocate": True,
+                                                   "sharding": "even", "grad_stage": "on"})))
+    if world >= 2:
+        push_cases.append(("stage-ps-pure-server-step", lambda a: orchestra.parameter_server(
+            a, 1, ds12(), GradientDescent(0.2), CrossEntropy(), BarrierSync(), BlockingStore(), 6, 48, seed=4,
+            b200={"sync_every": "step", "grad_stage": "on"})))
     report = {}
     ok = True
     only = os.environ.get("ONO_PARITY_ONLY", "")
@@ -100,11 +113,13 @@ def main():
             loose = any(k in name for k in ("async", "adam", "switch", "bf16"))
             # closeness to the oracle is the criterion; Adam's first steps move every weight by ~lr whatever the
             # gradient's size, so its loss need not fall within six steps
+            if name.startswith("stage") and not met.get("grad_stage"):
+                same_len = False
             if name.startswith("push") and not met.get("grad_push"):
                 same_len = False          # the case must really have run with pushed gradients
             good = same_len and dl < (0.3 if loose else 0.05) and dw < (0.2 if loose else 2e-2) and (loose or lg[-1] < lg[0])
             report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "loss": [float(lg[0]), float(lg[-1])] if same_len else [], "nvls": met.get("nvls"), "mode": met.get("sync_mode"),
-                            "switched": met.get("switched"), "push": met.get("grad_push")}
+                            "switched": met.get("switched"), "push": met.get("grad_push"), "stage": met.get("grad_stage")}
             ok = ok and good
         dist.barrier()
     if rank == 0:
