@@ -90,7 +90,8 @@ def run_batch(r, slot: int, nrows: int) -> None:
     key = (slot, nrows, r.sync_mode, r.cadence)
     st = r.stream
     st.wait_event(r.feeder.ready[slot])
-    graphable = r.sync_mode != "nccl"
+    # the staged reduce-scatter (experimental) forks onto the communication stream inside the step; it runs uncaptured
+    graphable = r.sync_mode != "nccl" and not getattr(r, "stage_active", False)
     with torch.cuda.stream(st):
         if key not in r.warm or not graphable:
             r.launches_per_step = _batch_body(r, slot, nrows, True)
