@@ -219,12 +219,19 @@ def main() -> None:
         gb = cfg["batch"] * world
         value = gb * K / (m["bench_ms"] / 1e3)
         e2e = gb * K / e["bench_wall_s"]
+        # parameters + gradients + optimizer state touched by every step, against the 126 MB L2
+        widths = [cfg["x"] if not cfg.get("conv") else 3136] + [w for w, _ in cfg["hidden"]] + [cfg["classes"]]
+        n_par = sum(a * b + b for a, b in zip(widths[:-1], widths[1:]))
+        ws_mb = n_par * 4 * 3 / 1e6
+        l2_note = (f"per-step working set (~{ws_mb:.0f} MB of weights, gradients and optimizer state) exceeds the 126 MB L2"
+                   if ws_mb > 126 else
+                   f"per-step working set (~{ws_mb:.0f} MB) fits in L2: steady-state training loop, no flush between steps")
         out = {
             "metric": "samples/sec (device-timed, max over ranks)", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": m["bench_ms"] / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
             "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
-                       "optimizer": cfg["opt"][0], "l2": "per-step working set (weights+grads > 2 GB) exceeds L2",
+                       "optimizer": cfg["opt"][0], "l2": l2_note,
                        "sync": m["sync_mode"], "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
