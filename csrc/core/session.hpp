@@ -304,7 +304,46 @@ class RemoteSession final : public Session {
   std::atomic<bool> failed_{false}, closing_{false};
 };
 
-// Validate + plan + start. `stats_json` optionally carries measured RTTs for the role assignment.
+// All-pairs latency probe (orchestrator/src/configs/stat_requester.rs:32-72): node i pings nodes 0..i-1 and accepts the
+// n-i-1 later ones; the maximum round-trip time per pair feeds the role assignment.
+inline std::map<std::string, std::map<std::string, uint64_t>> obtain_stats(const std::vector<std::string>& addrs, int rounds = 10) {
+  std::vector<wire::Channel> chs;
+  for (auto& a : addrs) {
+    const size_t c = a.rfind(':');
+    if (c == std::string::npos) throw InvalidConfig("address `" + a + "` is not host:port");
+    chs.push_back(wire::connect(a.substr(0, c), std::stoi(a.substr(c + 1))));
+    chs.back().connect_as("Orchestrator");
+  }
+  const size_t n = addrs.size();
+  for (size_t i = 0; i < n; ++i) {
+    Json peers = Json::array();
+    for (size_t j = 0; j < i; ++j) peers.push(addrs[j]);
+    Json body = Json::object();
+    body.set("addrs", peers);
+    body.set("rounds", rounds);
+    body.set("incoming", Json((unsigned long long)(n - i - 1)));
+    chs[i].send_command(Json::tagged("stats_request", Json::tagged("ping", body)));
+  }
+  std::map<std::string, std::map<std::string, uint64_t>> stats;
+  for (auto& a : addrs) stats[a];
+  for (size_t i = 0; i < n; ++i) {
+    wire::Message m = chs[i].recv(120000);
+    if (const Json* resp = m.variant("stats_response"))
+      if (const Json* st = resp->find("stats"); st && st->is_object())
+        if (const Json* ping = st->find("ping"))
+          if (const Json* rtts = ping->find("rtts"))
+            for (auto& [peer, v] : rtts->members()) {
+              const uint64_t mx = (uint64_t)v.at("max").as_double();
+              stats[addrs[i]][peer] = mx;
+              stats[peer][addrs[i]] = mx;
+            }
+    chs[i].send_command(Json("disconnect"));
+    chs[i].close();
+  }
+  return stats;
+}
+
+// Validate + plan + start. With `b200.probe` the nodes' pairwise latency is measured first and used for the plan.
 inline std::unique_ptr<Session> start_session(const ModelConfig& model, const TrainingConfig& training,
                                               oracle::Dataset data, Json* plan_out = nullptr) {
   validate_configs(model, training);
@@ -315,7 +354,9 @@ inline std::unique_ptr<Session> start_session(const ModelConfig& model, const Tr
     any_cpu = any_cpu || cpu;
   }
   if (any_cpu && !all_cpu) throw InvalidConfig("addrs must all be cpu:<i> or all host:port");
-  Json plan = adapt_configs(model, training, Calculator::uniform(training.addrs));
+  Json plan = (!all_cpu && training.b200.probe)
+                  ? adapt_configs(model, training, Calculator(obtain_stats(training.addrs)))
+                  : adapt_configs(model, training, Calculator::uniform(training.addrs));
   if (plan_out) *plan_out = plan;
   if (all_cpu) return std::make_unique<LocalSession>(plan, training, std::move(data));
   return std::make_unique<RemoteSession>(plan, model, training, data);

@@ -120,7 +120,10 @@ def test_nodes_serve_a_single_rank_natively_and_many_ranks_through_rank_processe
     three = _run_orchestrator(bins, mp, tp)
     ref = _python_reference(model, tr, xs, ys)
     assert np.allclose(three["loss_history"], ref.loss_history(), rtol=1e-6)
-    # the nodes went back to listening: a second session on the same processes
+    # the nodes went back to listening: a second session on the same processes, this time planned from a latency probe
+    cfg = json.loads(open(tp).read())
+    cfg["b200"] = {"probe": True}
+    open(tp, "w").write(json.dumps(cfg))
     again = _run_orchestrator(bins, mp, tp)
     assert np.allclose(again["loss_history"], three["loss_history"], rtol=1e-9)
 
