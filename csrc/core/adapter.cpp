@@ -1,5 +1,7 @@
 #include "adapter.hpp"
 
+#include "codec.hpp"
+
 #include <algorithm>
 #include <cmath>
 #include <map>
@@ -281,7 +283,30 @@ std::vector<size_t> per_worker_batch(const TrainingConfig& t, size_t nworkers) {
 }  // namespace
 
 Json adapt_configs(const ModelConfig& model, const TrainingConfig& training, const Calculator& calc) {
-  const auto layers = adapt_layers(model, training.dataset.x_size);
+  auto layers = adapt_layers(model, training.dataset.x_size);
+  if (!training.b200.init_from.empty()) {
+    // Warm start: every layer's generator becomes the checkpoint's values for that layer (weight then bias), the way
+    // promoted servers receive their parameters inline in the spec (worker/src/workers/all_reduce.rs:87-94).
+    std::map<std::string, const NamedTensor*> by_name;
+    const std::vector<NamedTensor> tensors = load_safetensors(training.b200.init_from);
+    for (auto& t : tensors) by_name[t.name] = &t;
+    for (auto& l : layers) {
+      if (l.param_gen.is_null()) continue;
+      const std::string base = "layer_" + std::to_string(l.index);
+      auto w = by_name.find(base + ".weight"), b = by_name.find(base + ".bias");
+      if (w == by_name.end() || b == by_name.end())
+        throw InvalidConfig("b200.init_from: checkpoint has no tensors for " + base);
+      if (w->second->data.size() + b->second->data.size() != l.n_params)
+        throw InvalidConfig("b200.init_from: " + base + " holds " + std::to_string(w->second->data.size() + b->second->data.size()) +
+                            " values, the model needs " + std::to_string(l.n_params));
+      Json vals = Json::array();
+      for (float v : w->second->data) vals.push(Json(v));
+      for (float v : b->second->data) vals.push(Json(v));
+      Json body = Json::object();
+      body.set("params", vals);
+      l.param_gen = Json::tagged("inline", body);
+    }
+  }
   const size_t n_params = layers.empty() ? 0 : layers.back().offset + layers.back().n_params;
   const size_t nrows = dataset_rows(training.dataset);
   const auto kind = training.algorithm.kind;

@@ -392,6 +392,7 @@ Json B200Config::to_json() const {
   o.set("comm_timeout_s", comm_timeout_s);
   o.set("heartbeat_s", heartbeat_s);
   o.set("heartbeat_timeout_s", heartbeat_timeout_s);
+  o.set("init_from", init_from);
   o.set("trace_path", trace_path);
   o.set("metrics_path", metrics_path);
   return o;
@@ -428,6 +429,7 @@ B200Config B200Config::from_json(const Json& j) {
   if (const Json* v = j.find("comm_timeout_s")) c.comm_timeout_s = float_positive(v->as_double(), "b200.comm_timeout_s");
   if (const Json* v = j.find("heartbeat_s")) c.heartbeat_s = float_non_negative(v->as_double(), "b200.heartbeat_s");
   if (const Json* v = j.find("heartbeat_timeout_s")) c.heartbeat_timeout_s = float_non_negative(v->as_double(), "b200.heartbeat_timeout_s");
+  if (const Json* v = j.find("init_from")) c.init_from = v->as_string();
   if (const Json* v = j.find("trace_path")) c.trace_path = v->as_string();
   if (const Json* v = j.find("metrics_path")) c.metrics_path = v->as_string();
   return c;

@@ -113,6 +113,7 @@ struct B200Config {
   double comm_timeout_s = 300.0;          // a collective or device wait that exceeds this ends the run with an error
   double heartbeat_s = 2.0;               // period of a node's liveness messages (0 = none)
   double heartbeat_timeout_s = 0.0;       // the orchestrator drops a node that stayed silent this long (0 = never)
+  std::string init_from;                  // safetensors checkpoint to start from instead of the initialisers (warm start / resume)
   std::string trace_path;                 // chrome-trace JSON of the run's phases (empty = off)
   std::string metrics_path;               // JSONL, one record per round / step window (empty = off)
   bool present = false;

@@ -186,3 +186,36 @@ def test_api_argument_errors_match_the_reference_types():
     # a single worker is a valid ring of one
     m = orchestrate(_model(), orchestra.all_reduce(["cpu:0"], ds, GradientDescent(0.1), CrossEntropy(), 2, 4, seed=1)).wait()
     assert len(m.loss_history()) == 2
+
+
+def test_warm_start_from_a_saved_checkpoint(tmp_path):
+    """b200.init_from replaces the initialisers by a safetensors checkpoint (weights resume where a run stopped)."""
+    import numpy as np
+
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+
+    rng = np.random.default_rng(0)
+    xs = rng.random((40, 6), dtype=np.float32)
+    ys = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 40)]
+    model = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+    addrs = ["cpu:0", "cpu:1"]
+    first = orchestrate(model, orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), GradientDescent(0.5), CrossEntropy(), 5, 5,
+                                                    seed=1)).wait(quiet=True)
+    ckpt = tmp_path / "first.safetensors"
+    first.save_safetensors(ckpt)
+    # a step size of ~0 leaves the loaded weights where they are, and the first reported loss is the saved model's
+    again = orchestrate(model, orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), GradientDescent(1e-12), CrossEntropy(), 1, 5,
+                                                    seed=1, b200={"init_from": str(ckpt)})).wait(quiet=True)
+    assert np.allclose(again.weights_array(), first.weights_array(), atol=1e-7)
+    assert again.loss_history()[0] < first.loss_history()[0]
+    with pytest.raises(ValueError):
+        bad = Sequential([Dense(7, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+        orchestrate(bad, orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), GradientDescent(0.1), CrossEntropy(), 1, 5,
+                                              b200={"init_from": str(ckpt)}))
