@@ -168,7 +168,8 @@ def main() -> None:
     ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
     args = ap.parse_args()
     if args.impl == "reference":
-        reference_arm()
+        if int(os.environ.get("RANK", "0")) == 0:      # one line per job, also when launched once per GPU
+            reference_arm()
         return
     import torch
     import torch.distributed as dist
