@@ -296,6 +296,9 @@ class GpuRank:
         self.own = snap_ranges(ranges, self.n_pad)
         self.buckets, self.bucket_after = [], {}
         self.stage_buckets, self.stage_after, self.stage_active = [], {}, False
+        from ..ops import gemm as _gemm_mod
+
+        _gemm_mod.DEFAULT_MAX_CTAS = 0          # only the overlap modes below leave SMs to communication kernels
         self.sync_workers = list(workers)
         self.sync_mode = mode
         self.sync_opt = opt
