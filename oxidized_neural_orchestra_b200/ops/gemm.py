@@ -29,6 +29,8 @@ def _ptr(t):
 # CTAs a GEMM may use when the caller gives no limit (0 = one per SM). The rank runtime lowers it while gradient
 # buckets are synchronised during backward, so that the communication kernels find free SMs.
 DEFAULT_MAX_CTAS = 0
+# CTA pairs (256-row tiles) for GEMMs whose caller does not choose: 0 = single CTAs, 1 = pairs where the shape allows.
+DEFAULT_PAIR = int(__import__("os").environ.get("ONO_GEMM_PAIR", "0"))
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
@@ -65,7 +67,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     g.dtype = 0 if a.dtype == torch.float32 else 1
     g.a_major, g.b_major = int(a_mn_major), int(b_mn_major)
     g.epi.reduce_out = int(reduce_out)
-    g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas or DEFAULT_MAX_CTAS, split_k, pair
+    g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas or DEFAULT_MAX_CTAS, split_k, pair or DEFAULT_PAIR
     e = g.epi
     ld_out = ld_out_t = 0
     for t in (out, out_bf16, pre):

@@ -145,3 +145,15 @@ def test_gradient_push_through_the_gemm_epilogue_matches_the_plain_path(tile, mo
     # same products, added by reductions instead of stores: equal up to the order of f32 additions
     assert np.allclose(out["on"][0], out["off"][0], rtol=1e-4, atol=1e-6)
     assert np.abs(out["on"][1] - out["off"][1]).max() < 1e-4
+
+
+def test_warm_start_on_the_gpu_loads_the_checkpoint(tmp_path):
+    xs, ys = _data(n=64, x=32, y=12)
+    model = Sequential([Dense(16, XavierUniform(), ReLU(0.0)), Dense(12, XavierUniform(), Softmax())])
+    first = orchestrate(model, orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 32, 12), GradientDescent(0.5), CrossEntropy(),
+                                                    4, 32, seed=1)).wait(quiet=True)
+    ckpt = tmp_path / "m.safetensors"
+    first.save_safetensors(ckpt)
+    again = orchestrate(model, orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 32, 12), GradientDescent(1e-12), CrossEntropy(),
+                                                    1, 32, seed=1, b200={"init_from": str(ckpt)})).wait(quiet=True)
+    assert np.allclose(again.weights_array(), first.weights_array(), atol=1e-6)
