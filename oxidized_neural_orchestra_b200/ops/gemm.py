@@ -29,9 +29,9 @@ def _ptr(t):
 # CTAs a GEMM may use when the caller gives no limit (0 = one per SM). The rank runtime lowers it while gradient
 # buckets are synchronised during backward, so that the communication kernels find free SMs.
 DEFAULT_MAX_CTAS = 0
-# CTA pairs (256-row tiles) for GEMMs whose caller does not choose. "auto": pairs for bf16 tiles with a long reduction
-# (measured on the 8 x 8192 MLP step: 4.61 ms with pairs against 4.76 ms; tf32 and short-K shapes are faster on single CTAs);
-# "1": wherever the shape allows; "0": never.
+# CTA pairs (256-row tiles) for GEMMs whose caller does not choose. "auto": pairs for bf16 tiles (measured three times,
+# alternating, on the 8 x 8192 MLP step: 4.64 / 4.67 / 4.66 ms with pairs against 4.78 / 4.78 / 4.78 ms without; the gain comes
+# from the short-K weight-gradient GEMMs), single CTAs for tf32 tiles; "1": wherever the shape allows; "0": never.
 DEFAULT_PAIR = __import__("os").environ.get("ONO_GEMM_PAIR", "auto")
 
 
@@ -71,7 +71,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     g.epi.reduce_out = int(reduce_out)
     if pair == 0:
         if DEFAULT_PAIR == "auto":
-            pair = 1 if (a.dtype == torch.bfloat16 and M >= 256 and K >= 1024 and not reduce_out) else -1
+            pair = 1 if (a.dtype == torch.bfloat16 and M >= 256 and not reduce_out) else -1
         else:
             pair = 1 if DEFAULT_PAIR == "1" else -1
     g.bn, g.max_ctas, g.split_k, g.pair = bn, max_ctas or DEFAULT_MAX_CTAS, split_k, pair
