@@ -221,7 +221,7 @@ def main():
     g = sub.add_parser("gemm")
     g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=4096); g.add_argument("--dtype", default="bf16")
-    g.add_argument("--bn", type=int, default=0); g.add_argument("--pair", type=int, default=0); g.add_argument("--iters", type=int, default=20)
+    g.add_argument("--bn", type=int, default=0); g.add_argument("--pair", type=int, default=0, choices=(-1, 0, 1), help="CTA pairs: 1 on, -1 off, 0 the library default"); g.add_argument("--iters", type=int, default=20)
     s = sub.add_parser("sync")
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)

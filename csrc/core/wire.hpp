@@ -68,7 +68,7 @@ class Channel {
   }
   Channel(const Channel&) = delete;
   Channel& operator=(const Channel&) = delete;
-  Channel(Channel&& o) noexcept : fd_(o.fd_), peer_entity(std::move(o.peer_entity)), peer_id(std::move(o.peer_id)) { o.fd_ = -1; }
+  Channel(Channel&& o) noexcept : peer_entity(std::move(o.peer_entity)), peer_id(std::move(o.peer_id)), fd_(o.fd_) { o.fd_ = -1; }
   Channel& operator=(Channel&& o) noexcept {
     if (this != &o) { close(); fd_ = o.fd_; o.fd_ = -1; peer_entity = std::move(o.peer_entity); peer_id = std::move(o.peer_id); }
     return *this;

@@ -58,22 +58,6 @@ struct TileCfg {
   static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 };
 
-// Shared-memory plan of one kernel variant. Single CTAs: the operand ring of TileCfg and one 4 KB output staging tile
-// per epilogue warp. CTA pairs stage only half of B each, so the ring is shorter in bytes and every epilogue warp gets
-// two staging tiles: it unloads two 32-column chunks per trip (one TMEM wait, one proxy fence, one store-queue wait for
-// both), which is what bounds the short-K shapes.
-template <int BN, bool PAIR>
-struct PipeCfg {
-  static constexpr int BN_CTA = PAIR ? BN / 2 : BN;
-  static constexpr int CH = PAIR ? 2 : 1;
-  static constexpr int STAGE_BYTES = 128 * 128 + BN_CTA * 128;
-  static constexpr int CSTAGE_BYTES = 8 * 4096 * CH;
-  static constexpr int ROOM = 227 * 1024 - 1024 /*alignment*/ - 512 /*static*/ - CSTAGE_BYTES;
-  static constexpr int FIT = ROOM / STAGE_BYTES;
-  static constexpr int STAGES = PAIR ? (FIT < 8 ? FIT : 8) : TileCfg<BN_CTA>::STAGES;
-  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + CSTAGE_BYTES + 1024;
-};
-
 __device__ __forceinline__ void fail(const GemmDev& p, volatile int* abort_flag, int code) {
   if (p.status) atomicCAS(p.status, 0, code);
   *abort_flag = 1;
@@ -239,8 +223,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int KSTEPS = BK / UMMA_K;  // 4
   constexpr int BN_CTA = PAIR ? BN / 2 : BN;   // rows of B staged by one CTA
   constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_CTA * 128, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = PipeCfg<BN, PAIR>::STAGES;
-  constexpr int CH = PipeCfg<BN, PAIR>::CH;   // 32-column chunks an epilogue warp unloads per trip
+  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
   constexpr uint32_t TMEM_COLS = TileCfg<BN>::TMEM_COLS;
   const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = crank == 0u;
@@ -249,7 +232,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  // output staging tiles (CH per epilogue warp, 4 KB each: 32 rows x 128 B) behind the operand ring, for TMA stores
+  // eight 4 KB output staging tiles (one per epilogue warp: 32 rows x 128 B) behind the operand ring, for TMA stores
   uint8_t* cstage = smem + (size_t)STAGES * STAGE_BYTES;
 
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -412,12 +395,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue warps 0..3 (TMEM lanes 32*warp .. 32*warp+31) ----------------
     int t = 0;
     bool ok = true;
-    // Two groups of four warps (warps 0-3 and 6-9) take alternate runs of CH 32-column chunks of the accumulator.
-    // Every warp owns CH 4 KB staging tiles (32 rows x 32 columns each) and its own TMA-store queue, so eight
-    // queues are in flight per CTA and no warp waits for another.
+    // Two groups of four warps (warps 0-3 and 6-9) take alternate 32-column chunks of the accumulator, each
+    // group. Every warp owns a 4 KB staging tile (its 32 rows x 32 columns) and its own TMA-store queue, so eight
+    // stores are in flight per CTA and no warp waits for another.
     const int grp = warp >= 6 ? 1 : 0;
     const int quad = warp & 3;                 // TMEM lane quadrant this warp may read
-    uint8_t* const wstage = cstage + (size_t)(grp * 4 + quad) * (4096u * CH);
+    uint8_t* const wstage = cstage + (size_t)(grp * 4 + quad) * 4096u;
     const uint32_t tmem_empty_remote[2] = {PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[0]), 0u) : 0u,
                                            PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[1]), 0u) : 0u};
     for (int work = unit; work < total_work && ok; work += units, ++t) {
@@ -437,80 +420,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int m = m0 + row;
       const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
 #pragma unroll 1
-      for (int c = grp * CH; c < BN / 32; c += 2 * CH) {
+      for (int c = grp; c < BN / 32; c += 2) {
         const int nc = n0 + c * 32;
         if (nc >= p.N) break;  // uniform across the CTA
-        // chunks of this trip that hold columns of the matrix (uniform across the CTA)
-        const int live = (CH == 1) ? 1 : min(CH, (p.N - nc + 31) / 32);
-        float v[CH][32];
-        {
-          uint32_t r[CH][32];
+        uint32_t r[32];
+        tmem_ld_x32(t_row + (uint32_t)(c * 32), r);
+        tmem_ld_wait();
+        float v[32];
 #pragma unroll
-          for (int h = 0; h < CH; ++h) tmem_ld_x32(t_row + (uint32_t)((c + h) * 32), r[h]);   // columns stay inside the buffer
-          tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < CH; ++h)
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[h][j] = __uint_as_float(r[h][j]);
-        }
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (SPLITS > 1) {
           // partial product of one K range: accumulate into the (pre-zeroed) f32 output
           if (m < p.M && p.epi.out_f32) {
+            float* o = p.epi.out_f32 + (size_t)m * p.epi.ld_out + nc;
+            const int ncols = min(32, p.N - nc);
 #pragma unroll
-            for (int h = 0; h < CH; ++h) {
-              if (h >= live) break;
-              float* o = p.epi.out_f32 + (size_t)m * p.epi.ld_out + nc + h * 32;
-              const int ncols = min(32, p.N - nc - h * 32);
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncols) atomicAdd(o + j, v[h][j] * p.epi.alpha);
-            }
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) atomicAdd(o + j, v[j] * p.epi.alpha);
           }
           continue;
         }
-#pragma unroll
-        for (int h = 0; h < CH; ++h)
-          if (h < live) epilogue_chunk(p.epi, v[h], m, nc + h * 32, p.M, p.N, p.tma_out);
+        epilogue_chunk(p.epi, v, m, nc, p.M, p.N, p.tma_out);
         if (p.tma_out) {
-          // registers -> swizzled staging tiles -> one TMA store per warp and 32 x 32 chunk; the TMA unit
+          // registers -> swizzled staging tile -> one TMA store per warp and 32 x 32 chunk; the TMA unit
           // clips rows >= M and columns >= N
-          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous stores have read the tiles
+          if (lane == 0) tma_store_wait_read<0>();  // this warp's previous store has read the tile
           __syncwarp();
+          if (p.tma_out != 2) {
+            uint8_t* rp = wstage + lane * 128;
 #pragma unroll
-          for (int h = 0; h < CH; ++h) {
-            if (h >= live) break;
-            if (p.tma_out != 2) {
-              uint8_t* rp = wstage + h * 4096 + lane * 128;
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(rp + ((j ^ (row & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            uint8_t* rp = wstage + lane * 64;
 #pragma unroll
-              for (int j = 0; j < 8; ++j)
-                *reinterpret_cast<float4*>(rp + ((j ^ (row & 7)) << 4)) =
-                    make_float4(v[h][4 * j], v[h][4 * j + 1], v[h][4 * j + 2], v[h][4 * j + 3]);
-            } else {
-              uint8_t* rp = wstage + h * 4096 + lane * 64;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __nv_bfloat162 t0 = __floats2bfloat162_rn(v[h][8 * j], v[h][8 * j + 1]);
-                __nv_bfloat162 t1 = __floats2bfloat162_rn(v[h][8 * j + 2], v[h][8 * j + 3]);
-                __nv_bfloat162 t2 = __floats2bfloat162_rn(v[h][8 * j + 4], v[h][8 * j + 5]);
-                __nv_bfloat162 t3 = __floats2bfloat162_rn(v[h][8 * j + 6], v[h][8 * j + 7]);
-                uint4 pk;
-                pk.x = *reinterpret_cast<uint32_t*>(&t0);
-                pk.y = *reinterpret_cast<uint32_t*>(&t1);
-                pk.z = *reinterpret_cast<uint32_t*>(&t2);
-                pk.w = *reinterpret_cast<uint32_t*>(&t3);
-                *reinterpret_cast<uint4*>(rp + ((j ^ ((row >> 1) & 3)) << 4)) = pk;
-              }
+            for (int j = 0; j < 4; ++j) {
+              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+              uint4 pk;
+              pk.x = *reinterpret_cast<uint32_t*>(&t0);
+              pk.y = *reinterpret_cast<uint32_t*>(&t1);
+              pk.z = *reinterpret_cast<uint32_t*>(&t2);
+              pk.w = *reinterpret_cast<uint32_t*>(&t3);
+              *reinterpret_cast<uint4*>(rp + ((j ^ ((row >> 1) & 3)) << 4)) = pk;
             }
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-#pragma unroll
-            for (int h = 0; h < CH; ++h) {
-              if (h >= live) break;
-              if (p.tma_out == 3) tma_reduce_add_2d(&tmC, wstage + h * 4096, nc + h * 32, m0 + quad * 32);
-              else tma_store_2d(&tmC, wstage + h * 4096, nc + h * 32, m0 + quad * 32);
-            }
+            if (p.tma_out == 3) tma_reduce_add_2d(&tmC, wstage, nc, m0 + quad * 32);
+            else tma_store_2d(&tmC, wstage, nc, m0 + quad * 32);
             tma_store_commit();
           }
         }
@@ -653,8 +615,9 @@ static int num_sms() {
 template <int ESIZE, int BN, bool PAIR>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmDev& p, int max_ctas,
                   cudaStream_t stream) {
-  constexpr size_t smem = PipeCfg<BN, PAIR>::SMEM;
-  static_assert(PipeCfg<BN, PAIR>::STAGES >= 3, "operand ring too short");
+  constexpr int BN_CTA = PAIR ? BN / 2 : BN;
+  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
+  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN_CTA * 128) + 2 * 16384 + 1024;
   static bool attr_set = false;
   static int max_pairs = 0;
   auto kern = gemm_tcgen05_kernel<ESIZE, BN, PAIR>;

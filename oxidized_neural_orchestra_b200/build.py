@@ -105,9 +105,41 @@ def build_core(force: bool = False) -> Path | None:
     return ext
 
 
-def build_bins(force: bool = False) -> list[Path]:
-    """Native executables: every csrc/{node,tui,orch_main}/*.cpp with a main()."""
-    BINDIR.mkdir(parents=True, exist_ok=True)
+SANITIZERS = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}
+
+
+def sanitizer_cxx(kind: str) -> str | None:
+    """A C++ compiler on this machine that can link the given sanitizer's runtime (None if there is none)."""
+    import tempfile
+
+    seen = []
+    for cxx in (CXX, shutil.which("g++"), "/usr/bin/g++", shutil.which("clang++")):
+        if not cxx or cxx in seen or not Path(cxx).exists() and shutil.which(cxx) is None:
+            continue
+        seen.append(cxx)
+        with tempfile.TemporaryDirectory() as d:
+            src = Path(d) / "probe.cpp"
+            src.write_text("int main() { return 0; }\n")
+            r = subprocess.run([cxx, *SANITIZERS[kind], str(src), "-o", str(Path(d) / "probe")], capture_output=True)
+            if r.returncode == 0:
+                return cxx
+    return None
+
+
+def build_bins(force: bool = False, sanitize: str | None = None) -> list[Path]:
+    """Native executables: every csrc/{node,tui,orch_main}/*.cpp with a main().
+
+    ``sanitize="address"`` (ASan + UBSan) or ``"thread"`` (TSan) builds instrumented copies under
+    ``bin/<sanitize>/`` for the host-side race and memory checks of the C++ runtime (control plane, sessions,
+    dynamic barrier, codec); the reference runs no sanitizer in CI (.github/workflows/test.yml:29-30)."""
+    bindir = BINDIR if sanitize is None else BINDIR / sanitize
+    flags = CXX_FLAGS if sanitize is None else ["-O1", "-g", "-fno-omit-frame-pointer", *CXX_FLAGS[1:], *SANITIZERS[sanitize]]
+    cxx = CXX
+    if sanitize is not None:
+        cxx = sanitizer_cxx(sanitize)
+        if cxx is None:
+            raise RuntimeError(f"no C++ compiler here links the {sanitize} sanitizer runtime")
+    bindir.mkdir(parents=True, exist_ok=True)
     out = []
     core_srcs = sorted((CSRC / "core").glob("*.cpp")) + sorted((CSRC / "oracle").glob("*.cpp"))
     hdrs = _headers(CSRC / "core", CSRC / "oracle", CSRC / "node", CSRC / "tui")
@@ -115,9 +147,9 @@ def build_bins(force: bool = False) -> list[Path]:
         mains = sorted((CSRC / sub).glob("*.cpp")) if (CSRC / sub).exists() else []
         if not mains:
             continue
-        exe = BINDIR / name
+        exe = bindir / name
         if force or any(_newer(s, exe, hdrs) for s in mains + core_srcs):
-            _run([CXX, *CXX_FLAGS, "-I", str(CSRC), "-o", str(exe), *map(str, mains),
+            _run([cxx, *flags, "-I", str(CSRC), "-o", str(exe), *map(str, mains),
                   *map(str, core_srcs), "-ldl"])
         out.append(exe)
     return out
