@@ -101,6 +101,7 @@ def cmd_sync_emulated(a):
     from oxidized_neural_orchestra_b200.parallel import sync as S
 
     R, n = a.emulate_ranks, a.elems
+    torch.manual_seed(0)
     z = lambda dt=torch.float32: torch.zeros(n, device="cuda", dtype=dt)
     g, p, m, v = [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)]
     for t in g:
@@ -123,8 +124,16 @@ def cmd_sync_emulated(a):
     ms = _time(lambda: S.launch_sync(s, emulated=True), a.iters)
     assert status.item() == 0
     per = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + 4 * R + 4 * R     # owner state + R gradient reads + R parameter writes
-    print(json.dumps({"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "ms": ms,
-                      "GBs_local_hbm": per * n / ms / 1e6, "blocks_per_rank": nblocks}))
+    rec = {"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "ms": ms,
+           "GBs_local_hbm": per * n / ms / 1e6, "blocks_per_rank": nblocks}
+    if a.checksum:      # bits of every rank's parameters and optimizer state: equal between runs (fixed summation order)
+        import hashlib
+
+        h = hashlib.sha256()
+        for t in p + m + v:
+            h.update(t.cpu().numpy().tobytes())
+        rec["checksum"] = h.hexdigest()
+    print(json.dumps(rec))
 
 
 def cmd_sweep(a):
@@ -226,6 +235,7 @@ def main():
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
     s.add_argument("--emulate-ranks", type=int, default=0, help="run R ranks as one cooperative launch on this GPU")
+    s.add_argument("--checksum", action="store_true", help="with --emulate-ranks: print a hash of the resulting state")
     w = sub.add_parser("sweep")
     w.add_argument("--max-bytes", type=int, default=1 << 30)
     w.add_argument("--min-bytes", type=int, default=1024)

@@ -387,6 +387,7 @@ Json B200Config::to_json() const {
   o.set("colocate", colocate);
   o.set("data", data);
   o.set("probe", probe);
+  o.set("phase_timing", phase_timing);
   o.set("grad_stage", grad_stage);
   o.set("grad_push", grad_push);
   o.set("comm_timeout_s", comm_timeout_s);
@@ -426,6 +427,7 @@ B200Config B200Config::from_json(const Json& j) {
   if (const Json* v = j.find("switch_resets_progress")) c.switch_resets_progress = v->as_bool();
   if (const Json* v = j.find("colocate")) c.colocate = v->as_bool();
   if (const Json* v = j.find("probe")) c.probe = v->as_bool();
+  if (const Json* v = j.find("phase_timing")) c.phase_timing = v->as_bool();
   if (const Json* v = j.find("comm_timeout_s")) c.comm_timeout_s = float_positive(v->as_double(), "b200.comm_timeout_s");
   if (const Json* v = j.find("heartbeat_s")) c.heartbeat_s = float_non_negative(v->as_double(), "b200.heartbeat_s");
   if (const Json* v = j.find("heartbeat_timeout_s")) c.heartbeat_timeout_s = float_non_negative(v->as_double(), "b200.heartbeat_timeout_s");

@@ -107,6 +107,7 @@ struct B200Config {
   bool switch_resets_progress = false;
   bool colocate = false;                  // server ranks also train (B200 extension)
   std::string data = "host";              // "host": per-step H2D from pinned memory | "device"
+  bool phase_timing = false;              // run steps uncaptured with CUDA events + NVTX ranges around compute / exchange / refresh
   bool probe = false;                     // measure pairwise node latency before planning (host:port sessions)
   std::string grad_stage = "auto";        // "auto" | "on" | "off": copy peers' finished gradient ranges into local staging during backward
   std::string grad_push = "auto";         // "auto" | "on" | "off": weight-gradient GEMMs add their tiles into the owner's accumulator

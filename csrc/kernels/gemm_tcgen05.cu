@@ -751,11 +751,14 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
     p.tma_out = 3;
   } else if (p.split_k > 1) {
     // atomics path, no TMA store
-  } else if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0) {
+  } else if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0 && g->N % 4 == 0) {
     if (encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out) == 0) p.tma_out = 1;
-  } else if (e.out_bf16 && ((uintptr_t)e.out_bf16 & 15) == 0) {
+  } else if (e.out_bf16 && ((uintptr_t)e.out_bf16 & 15) == 0 && g->N % 8 == 0) {
     if (encode_out_map(&tc, e.out_bf16, 2, g->M, g->N, e.ld_out) == 0) p.tma_out = 2;
   }
+  // (A TMA store writes whole 16-byte units: with a row of N elements that ends inside a unit it would put the
+  // zero-filled rest of the unit into the columns after N, which belong to the caller when the output is a view of a
+  // wider matrix. Such shapes leave through thread stores. The reduce-add form adds those zeros, which changes nothing.)
   const uint32_t fmt = g->dtype == ONO_TF32 ? 2u : 1u;  // TF32 / BF16
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
             ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);

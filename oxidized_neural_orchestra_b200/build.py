@@ -126,7 +126,7 @@ def sanitizer_cxx(kind: str) -> str | None:
     return None
 
 
-def build_bins(force: bool = False, sanitize: str | None = None) -> list[Path]:
+def build_bins(force: bool = False, sanitize: str | None = None, only: tuple | None = None) -> list[Path]:
     """Native executables: every csrc/{node,tui,orch_main}/*.cpp with a main().
 
     ``sanitize="address"`` (ASan + UBSan) or ``"thread"`` (TSan) builds instrumented copies under
@@ -145,7 +145,7 @@ def build_bins(force: bool = False, sanitize: str | None = None) -> list[Path]:
     hdrs = _headers(CSRC / "core", CSRC / "oracle", CSRC / "node", CSRC / "tui")
     for name, sub in (("ono-node", "node"), ("orchestui", "tui"), ("ono-orchestrator", "orch_main")):
         mains = sorted((CSRC / sub).glob("*.cpp")) if (CSRC / sub).exists() else []
-        if not mains:
+        if not mains or (only is not None and name not in only):
             continue
         exe = bindir / name
         if force or any(_newer(s, exe, hdrs) for s in mains + core_srcs):

@@ -74,14 +74,31 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
         n += r._launch_sync(r.G, st)
         n += e.refresh(stream=st)
         return n
+    ph = r.phase_events if getattr(r, "phase_timing", False) else None
+
+    def mark(name):     # phase boundary: a timed event on the stream and an NVTX range for external profilers
+        if ph is None:
+            return
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(st)
+        if ph and ph[-1][0] != "end":
+            torch.cuda.nvtx.range_pop()
+        ph.append((name, ev))
+        if name != "end":
+            torch.cuda.nvtx.range_push(name)
+
+    mark("compute")
     n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
+    mark("exchange")
     if r.cadence == "round":
         # sequential.rs:129-141: stateless SGD on the working copy, residual += grad
         ew.local_sgd(r.W[:r.n], r.g[:r.n], r.G[:r.n], r.local_lr, p_bf16=r.shadow, stream=st)
         n += 1
     elif with_sync:
         n += r._launch_sync(r.G, st)
+    mark("refresh")
     n += e.refresh(stream=st)
+    mark("end")
     return n
 
 
@@ -91,7 +108,7 @@ def run_batch(r, slot: int, nrows: int) -> None:
     st = r.stream
     st.wait_event(r.feeder.ready[slot])
     # the staged reduce-scatter (experimental) forks onto the communication stream inside the step; it runs uncaptured
-    graphable = r.sync_mode != "nccl" and not getattr(r, "stage_active", False)
+    graphable = r.sync_mode != "nccl" and not getattr(r, "stage_active", False) and not getattr(r, "phase_timing", False)
     with torch.cuda.stream(st):
         if key not in r.warm or not graphable:
             r.launches_per_step = _batch_body(r, slot, nrows, True)

@@ -69,6 +69,20 @@ def _record_epoch(r, tracer, sink, ev_first: int, epoch_first: int, epoch_now: i
     wall = time.perf_counter() - t_epoch
     tracer.events.append({"name": "epoch", "ph": "X", "pid": r.rank, "tid": 0, "ts": (t_epoch - tracer.t0) * 1e6,
                           "dur": wall * 1e6, "args": {"epoch": epoch_first, "losses": losses}}) if tracer.on else None
+    phase_ms: dict = {}
+    ph = getattr(r, "phase_events", None)
+    if ph:
+        ph[-1][1].synchronize()
+        count: dict = {}
+        for (name, a), (_, b) in zip(ph[:-1], ph[1:]):
+            if name == "end":
+                continue
+            phase_ms[name] = phase_ms.get(name, 0.0) + a.elapsed_time(b)
+            count[name] = count.get(name, 0) + 1
+            tracer.device_span(name, a, b, epoch=epoch_first)
+        phase_ms = {k: v / count[k] for k, v in phase_ms.items()}
+        r.phase_ms_last = phase_ms
+        ph.clear()
     steps = max(0, len(evs) - 1)
     rows = steps * int(getattr(r.engine, "B", 0) or 0)
     sink.write(epoch=epoch_now, epochs_in_record=max(1, epoch_now - epoch_first), loss=(losses[-1] if losses else None),
@@ -76,6 +90,7 @@ def _record_epoch(r, tracer, sink, ev_first: int, epoch_first: int, epoch_now: i
                samples_per_sec=(rows / (dev_ms / 1e3) if dev_ms > 0 else None),
                epochs_per_sec=(max(1, epoch_now - epoch_first) / wall if wall > 0 else None),
                strategy=("parameter_server" if r.switched else r.algorithm), sync_mode=r.sync_mode,
+               **({"phase_ms": phase_ms} if phase_ms else {}),
                h2d_bytes_per_step=(r.feeder.h2d_bytes_per_step if r.feeder is not None else 0))
 
 
@@ -91,6 +106,8 @@ def run(r) -> dict:
     pending = [False, False]
     norm_hist: list = []
     check_every = int(r.b200.get("switch_check_every", 10))
+    r.phase_timing = bool(r.b200.get("phase_timing", False)) and r.engine is not None
+    r.phase_events = []
     tracer = r.tracer = Tracer(r.b200.get("trace_path") or None, r.rank)
     sink = MetricsSink(r.b200.get("metrics_path") or None, r.rank)
     tracer.device_anchor(r.stream)
@@ -162,7 +179,7 @@ def run(r) -> dict:
                 ev.record(r.stream)
             r.round_events = getattr(r, "round_events", []) + [ev]
             epoch += nep
-        if tracer.on or sink.on:
+        if tracer.on or sink.on or r.phase_timing:
             _record_epoch(r, tracer, sink, ev_first, epoch_first, epoch, epoch_losses, t_epoch)
         if decision != 2:
             with tracer.span("report_and_decide", epoch=epoch):
@@ -201,6 +218,8 @@ def run(r) -> dict:
         "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
         "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
     }
+    if r.phase_timing:
+        metrics["phase_ms"] = getattr(r, "phase_ms_last", {})     # means over the steps of the last record
     metrics["grad_push"] = bool(getattr(r, "push_active", False))
     metrics["grad_stage"] = bool(getattr(r, "stage_active", False))
     if r.compress:

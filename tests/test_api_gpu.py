@@ -125,6 +125,27 @@ def test_trace_and_metrics_files_of_a_gpu_run(tmp_path):
     assert len(recs) == 3 and all(r["steps"] >= 1 and r["device_ms"] > 0 and r["samples_per_sec"] > 0 for r in recs)
 
 
+def test_phase_timing_reports_compute_exchange_and_refresh_per_step(tmp_path):
+    import json
+
+    rng = np.random.default_rng(0)
+    xs = rng.random((128, 16), dtype=np.float32)
+    ys = np.eye(4, dtype=np.float32)[rng.integers(0, 4, 128)]
+    model = Sequential([Dense(32, XavierUniform(), ReLU(0.0)), Dense(4, XavierUniform(), Softmax())])
+    tp, mp = tmp_path / "trace.json", tmp_path / "metrics.jsonl"
+    tr = orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 16, 4), GradientDescent(0.1), CrossEntropy(), 2, 32, seed=1,
+                              b200={"sync_every": "step", "phase_timing": True, "trace_path": str(tp), "metrics_path": str(mp)})
+    m = orchestrate(model, tr).wait(quiet=True)
+    recs = [json.loads(l) for l in open(mp)]
+    assert len(recs) == 2
+    for r in recs:
+        assert set(r["phase_ms"]) == {"compute", "exchange", "refresh"} and all(v > 0 for v in r["phase_ms"].values())
+        assert sum(r["phase_ms"].values()) <= r["max_step_ms"] * 1.5
+    names = [e["name"] for e in json.load(open(tp))["traceEvents"]]
+    assert names.count("compute") == 8 and names.count("exchange") == 8      # 4 steps per epoch, device rows
+    assert set(m.metrics()["phase_ms"]) == {"compute", "exchange", "refresh"}
+
+
 @pytest.mark.parametrize("tile", ["tf32", "bf16"])
 def test_gradient_push_through_the_gemm_epilogue_matches_the_plain_path(tile, monkeypatch):
     """Weight-gradient tiles added into the owner's accumulator by TMA reductions (here the owner is this GPU)."""
