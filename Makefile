@@ -3,7 +3,7 @@ PY ?= python
 NODES ?= 3
 BASE_PORT ?= 40000
 
-.PHONY: build test test-gpu node orchestui orchestrator cluster-up bench bench-nccl bench-kernels clean
+.PHONY: build test test-gpu sanitize node orchestui orchestrator cluster-up bench bench-nccl bench-kernels clean
 
 build:            ## CUDA kernels (sm_100a), the C++ core extension and the native executables
 	$(PY) -c "import __graft_entry__ as g; g.build()"
@@ -13,6 +13,9 @@ test: build       ## CPU test-suite
 
 test-gpu: build   ## needs a B200
 	$(PY) -m pytest tests -x -q -m gpu
+
+sanitize:         ## sessions through ASan+UBSan and TSan builds of the native executables
+	$(PY) -m pytest tests/test_sanitizers_cpu.py -x -q
 
 node: build       ## one listening node: make node PORT=40000 [GPU=0]
 	PORT=$(PORT) ./bin/ono-node $(if $(GPU),--gpu $(GPU),--device cpu)
