@@ -395,6 +395,9 @@ Json B200Config::to_json() const {
   o.set("heartbeat_timeout_s", heartbeat_timeout_s);
   o.set("init_from", init_from);
   o.set("trace_path", trace_path);
+  o.set("state_path", state_path);
+  o.set("init_state_from", init_state_from);
+  o.set("start_epoch", (long long)start_epoch);
   o.set("metrics_path", metrics_path);
   return o;
 }
@@ -433,6 +436,9 @@ B200Config B200Config::from_json(const Json& j) {
   if (const Json* v = j.find("heartbeat_timeout_s")) c.heartbeat_timeout_s = float_non_negative(v->as_double(), "b200.heartbeat_timeout_s");
   if (const Json* v = j.find("init_from")) c.init_from = v->as_string();
   if (const Json* v = j.find("trace_path")) c.trace_path = v->as_string();
+  if (const Json* v = j.find("state_path")) c.state_path = v->as_string();
+  if (const Json* v = j.find("init_state_from")) c.init_state_from = v->as_string();
+  if (const Json* v = j.find("start_epoch")) c.start_epoch = v->as_int();
   if (const Json* v = j.find("metrics_path")) c.metrics_path = v->as_string();
   return c;
 }

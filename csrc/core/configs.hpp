@@ -115,6 +115,9 @@ struct B200Config {
   double heartbeat_s = 2.0;               // period of a node's liveness messages (0 = none)
   double heartbeat_timeout_s = 0.0;       // the orchestrator drops a node that stayed silent this long (0 = never)
   std::string init_from;                  // safetensors checkpoint to start from instead of the initialisers (warm start / resume)
+  std::string state_path;                 // GPU ranks: rank 0 writes the optimizer state (m, v, Adam powers) here at the end of the run
+  long long start_epoch = -1;             // GPU ranks: first epoch number for the shuffle sequence (-1: 0, or the epochs recorded in init_state_from)
+  std::string init_state_from;            // GPU ranks: optimizer state to resume from (a file written through state_path)
   std::string trace_path;                 // chrome-trace JSON of the run's phases (empty = off)
   std::string metrics_path;               // JSONL, one record per round / step window (empty = off)
   bool present = false;

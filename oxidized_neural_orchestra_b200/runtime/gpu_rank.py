@@ -153,6 +153,7 @@ class BatchFeeder:
         return (self.rows + self.batch - 1) // self.batch
 
     def _indices(self, epoch: int, step: int) -> torch.Tensor:
+        epoch += getattr(self, "epoch_offset", 0)
         if epoch != self._epoch:
             g = torch.Generator()
             g.manual_seed((self.seed * 1000003 + epoch) & 0x7FFFFFFFFFFFFFFF)

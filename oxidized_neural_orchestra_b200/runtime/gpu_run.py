@@ -94,6 +94,46 @@ def _record_epoch(r, tracer, sink, ev_first: int, epoch_first: int, epoch_now: i
                h2d_bytes_per_step=(r.feeder.h2d_bytes_per_step if r.feeder is not None else 0))
 
 
+def _state_tensors(r):
+    """Where this rank keeps the optimizer moments of the ranges it owns (asynchronous PS: in the window)."""
+    if r.sync_mode == "async" and hasattr(r, "m_win"):
+        return r.m_win, r.v_win
+    return r.m_loc, r.v_loc
+
+
+def _load_state(r, path: str) -> int:
+    """Copy a saved optimizer state into this rank's buffers; returns the number of epochs the file records."""
+    from ..utils.state import load_state
+
+    st = load_state(path, r.n)
+    targets = [(r.m_loc, "m"), (r.v_loc, "v")]
+    if hasattr(r, "m_win"):
+        targets += [(r.m_win, "m"), (r.v_win, "v")]
+    with torch.cuda.stream(r.stream):
+        for dst, k in targets:
+            dst[:r.n].copy_(torch.from_numpy(st[k].copy()).to(r.dev))
+        r.adam_pows.copy_(torch.from_numpy(st["adam_pows"].copy()).to(r.dev))
+    r.stream.synchronize()
+    return int(st["meta"].get("epochs", 0))
+
+
+def _save_state(r, path: str, epochs: int) -> None:
+    """Owners' moments -> rank 0 -> ``path`` (same gather as the final parameters)."""
+    from ..utils.state import save_state
+
+    m, v = _state_tensors(r)
+    if r.world > 1 and r.sync_mode not in ("oneshot", "ring"):
+        both = torch.zeros(2, r.n_pad, device=r.dev)
+        for b, e in r.own[r.rank]:
+            both[0, b:e] = m[b:e]
+            both[1, b:e] = v[b:e]
+        dist.all_reduce(both, group=r.group)
+        m, v = both[0], both[1]
+    if r.rank == 0:
+        save_state(path, m[:r.n].cpu().numpy(), v[:r.n].cpu().numpy(), r.adam_pows.cpu().numpy(),
+                   optimizer=r.sync_opt.kind, epochs=epochs, n_params=r.n)
+
+
 def run(r) -> dict:
     import os
 
@@ -111,6 +151,13 @@ def run(r) -> dict:
     tracer = r.tracer = Tracer(r.b200.get("trace_path") or None, r.rank)
     sink = MetricsSink(r.b200.get("metrics_path") or None, r.rank)
     tracer.device_anchor(r.stream)
+    first_epoch = int(r.b200.get("start_epoch", -1))
+    if r.b200.get("init_state_from"):
+        recorded = _load_state(r, r.b200["init_state_from"])
+        first_epoch = recorded if first_epoch < 0 else first_epoch
+    r.first_epoch = max(0, first_epoch)
+    if r.feeder is not None:
+        r.feeder.epoch_offset = r.first_epoch       # the shuffle sequence continues where the saved run stopped
     while epoch < r.max_epochs:
         decision = 0
         epoch_losses: list[float] = []
@@ -208,6 +255,8 @@ def run(r) -> dict:
     else:
         final = r.C
     params = final[:r.n].cpu().numpy() if r.rank == 0 else None
+    if r.b200.get("state_path"):
+        _save_state(r, r.b200["state_path"], r.first_epoch + epoch)
     ms = []
     evs = r.step_events
     for a, b in zip(evs[:-1], evs[1:]):

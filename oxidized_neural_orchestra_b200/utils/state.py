@@ -1,0 +1,55 @@
+"""Optimizer-state sidecar of a checkpoint.
+
+The reference exports final weights only (orchestrator/src/sessions/trained_model.rs:36-121): no optimizer state,
+no resume; at a strategy switch the state is reset (worker/src/builder.rs:179-181). Here a run can additionally
+write ``<name>.state.safetensors`` (``b200.state_path``) and a later run can start from it
+(``b200.init_state_from``, together with ``b200.init_from`` for the weights), which continues momentum / Adam
+exactly where the first run stopped.
+
+The file is a safetensors container (8-byte little-endian header length, JSON header, raw little-endian data):
+``optimizer.m`` and ``optimizer.v`` F32 ``[n_params]`` in the flat parameter order of the weights file,
+``optimizer.adam_pows`` F32 ``[2]`` (running b1^t, b2^t), and string metadata (optimizer kind, epochs done).
+"""
+from __future__ import annotations
+
+import json
+import struct
+
+import numpy as np
+
+
+def save_state(path: str, m: np.ndarray, v: np.ndarray, adam_pows: np.ndarray, **meta) -> None:
+    tensors = [("optimizer.m", np.ascontiguousarray(m, dtype="<f4")), ("optimizer.v", np.ascontiguousarray(v, dtype="<f4")),
+               ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))]
+    header: dict = {"__metadata__": {k: str(val) for k, val in meta.items()}}
+    off = 0
+    for name, t in tensors:
+        header[name] = {"dtype": "F32", "shape": list(t.shape), "data_offsets": [off, off + t.nbytes]}
+        off += t.nbytes
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for _, t in tensors:
+            f.write(t.tobytes())
+
+
+def load_state(path: str, n_params: int) -> dict:
+    with open(path, "rb") as f:
+        (hlen,) = struct.unpack("<Q", f.read(8))
+        if hlen > (1 << 26):
+            raise ValueError(f"{path}: implausible header length {hlen}")
+        header = json.loads(f.read(hlen))
+        data = f.read()
+    out: dict = {"meta": header.get("__metadata__", {})}
+    for name in ("optimizer.m", "optimizer.v", "optimizer.adam_pows"):
+        e = header.get(name)
+        if e is None or e.get("dtype") != "F32":
+            raise ValueError(f"{path}: no F32 tensor {name}")
+        b, en = e["data_offsets"]
+        arr = np.frombuffer(data[b:en], dtype="<f4").reshape(e["shape"])
+        out[name.split(".", 1)[1]] = arr
+    if out["m"].shape != (n_params,) or out["v"].shape != (n_params,) or out["adam_pows"].shape != (2,):
+        raise ValueError(f"{path}: state of {out['m'].shape[0]} parameters does not fit a model of {n_params}")
+    return out
