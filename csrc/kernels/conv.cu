@@ -297,6 +297,124 @@ __global__ void conv1_wgrad_kernel(const OnoConvGeom g, int F, const T* x, int l
   if (threadIdx.x == 0 && threadIdx.y == 0) g_c1_ticket = 0u;
 }
 
+// Image-tiled variants of the two kernels above for k = 3 and k = 5 (compile-time taps): a block keeps one
+// zero-padded image in shared memory, lane = filter, a warp walks output rows; a tap is one broadcast shared-memory
+// load and one FMA, with no bounds test and no division in the pixel loop. Output and dy rows are 128-byte coalesced.
+template <typename T>
+__device__ __forceinline__ void c1_stage_image(const OnoConvGeom& g, const T* x, int ldx, int img, float* tile, int TW, int TH) {
+  for (int i = threadIdx.x; i < TH * TW; i += 256) {
+    const int ty = i / TW, tx = i - ty * TW;
+    const int iy = ty - g.P, ix = tx - g.P;
+    tile[i] = (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) ? to_f32(x[(long long)((img * g.H + iy) * g.W + ix) * ldx]) : 0.f;
+  }
+}
+
+template <typename T, int K>
+__global__ void __launch_bounds__(256) conv1_fwd_img_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const float* kparams,
+                                                            const float* bias, int act, float act_param, T* y, int ldy) {
+  extern __shared__ float c1_tile[];
+  const int TW = g.W + 2 * g.P, TH = g.H + 2 * g.P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int f = blockIdx.y * 32 + lane;
+  float w[K * K];
+#pragma unroll
+  for (int i = 0; i < K * K; ++i) w[i] = f < F ? kparams[(long long)f * (K * K) + i] : 0.f;
+  const float bv = (bias && f < F) ? bias[f] : 0.f;
+  for (int img = blockIdx.x; img < g.B; img += gridDim.x) {
+    __syncthreads();   // the previous image has been read by every warp
+    c1_stage_image(g, x, ldx, img, c1_tile, TW, TH);
+    __syncthreads();
+    for (int oy = warp; oy < g.OH; oy += 8) {
+      const float* trow = c1_tile + oy * g.S * TW;
+      T* yrow = y + (long long)(img * g.OH + oy) * g.OW * ldy + f;
+#pragma unroll 4
+      for (int ox = 0; ox < g.OW; ++ox) {
+        const float* t0 = trow + ox * g.S;
+        float acc = bv;
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) acc += w[ky * K + kx] * t0[ky * TW + kx];
+        if (f < F) yrow[(long long)ox * ldy] = from_f32<T>(act_fwd(act, act_param, acc));
+      }
+    }
+  }
+}
+
+// Partial sums of block b for (filter f, slot i; slot K*K = bias) go to g_c1_part[(f * (K*K+1) + i) * gridDim.x + b];
+// conv1_wgrad_reduce_kernel then adds a pair's partials with one warp in a fixed order.
+template <typename T, int K>
+__global__ void __launch_bounds__(256) conv1_wgrad_img_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const T* dy, int ld_dy) {
+  extern __shared__ float c1_tile[];   // the padded image; afterwards the cross-warp reduction scratch
+  constexpr int KK = K * K;
+  const int TW = g.W + 2 * g.P, TH = g.H + 2 * g.P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nfb = (F + 31) / 32;
+  for (int fb = 0; fb < nfb; ++fb) {
+    const int f = fb * 32 + lane;
+    float acc[KK + 1];
+#pragma unroll
+    for (int i = 0; i <= KK; ++i) acc[i] = 0.f;
+    for (int img = blockIdx.x; img < g.B; img += gridDim.x) {
+      __syncthreads();
+      c1_stage_image(g, x, ldx, img, c1_tile, TW, TH);
+      __syncthreads();
+      for (int oy = warp; oy < g.OH; oy += 8) {
+        const float* trow = c1_tile + oy * g.S * TW;
+        const T* drow = dy + (long long)(img * g.OH + oy) * g.OW * ld_dy + f;
+#pragma unroll 4
+        for (int ox = 0; ox < g.OW; ++ox) {
+          const float d = f < F ? to_f32(drow[(long long)ox * ld_dy]) : 0.f;
+          const float* t0 = trow + ox * g.S;
+#pragma unroll
+          for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < K; ++kx) acc[ky * K + kx] += d * t0[ky * TW + kx];
+          acc[KK] += d;
+        }
+      }
+    }
+    __syncthreads();   // the image is no longer needed: its space takes the warps' sums
+#pragma unroll
+    for (int i = 0; i <= KK; ++i) c1_tile[(warp * 32 + lane) * (KK + 1) + i] = acc[i];
+    __syncthreads();
+    if (warp == 0 && f < F) {
+#pragma unroll
+      for (int i = 0; i <= KK; ++i) {
+        float t = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < 8; ++wq) t += c1_tile[(wq * 32 + lane) * (KK + 1) + i];
+        g_c1_part[((size_t)f * (KK + 1) + i) * gridDim.x + blockIdx.x] = t;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) conv1_wgrad_reduce_kernel(int F, int kk, int nblocks, float* gk, float* gb, float beta) {
+  const int lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (pair >= F * (kk + 1)) return;
+  const float* p = g_c1_part + (size_t)pair * nblocks;
+  float t = 0.f;
+  for (int b = lane; b < nblocks; b += 32) t += p[b];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  if (lane == 0) {
+    const int f = pair / (kk + 1), i = pair - f * (kk + 1);
+    float* dst = i < kk ? gk + (long long)f * kk + i : gb + f;
+    *dst = beta != 0.f ? beta * (*dst) + t : t;
+  }
+}
+
+// Shared memory of the image-tiled kernels, or 0 when the shape has to take the generic kernels.
+static size_t c1_img_smem(const OnoConvGeom* g) {
+  if (g->K != 3 && g->K != 5) return 0;
+  const size_t tile = (size_t)(g->H + 2 * g->P) * (g->W + 2 * g->P);
+  const size_t red = (size_t)256 * (g->K * g->K + 1);
+  const size_t bytes = std::max(tile, red) * sizeof(float);
+  return bytes <= 48 * 1024 ? bytes : 0;
+}
+
 // y[(b,oy,ox), c] = max over the window of the zero-padded input; arg[...] = input pixel (iy*W+ix) of the
 // maximum or -1 when the maximum is a padding zero. Ties: the last element in scan order.
 template <typename T>
@@ -428,6 +546,20 @@ extern "C" int ono_conv1_fwd(const OnoConvGeom* g, int F, int dtype, const void*
   if (!g || g->C != 1 || g->K * g->K > C1_MAXKK || F <= 0) { set_error("conv1_fwd: needs one input channel and k <= 5%s", "", 0, 0); return -1; }
   const long long rows = (long long)g->B * g->OH * g->OW;
   if (rows >= (1ll << 31)) { set_error("conv1_fwd: too many output pixels%s", "", 0, 0); return -1; }
+  if (const size_t sm = c1_img_smem(g)) {
+    const dim3 grid((unsigned)std::min(g->B, 148 * 8), (F + 31) / 32);
+    cudaStream_t s = (cudaStream_t)st;
+    if (g->K == 3) {
+      ONO_DISPATCH(dtype,
+                   (conv1_fwd_img_kernel<float, 3><<<grid, 256, sm, s>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
+                   (conv1_fwd_img_kernel<bf16, 3><<<grid, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))
+    } else {
+      ONO_DISPATCH(dtype,
+                   (conv1_fwd_img_kernel<float, 5><<<grid, 256, sm, s>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
+                   (conv1_fwd_img_kernel<bf16, 5><<<grid, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))
+    }
+    return done("conv1_fwd");
+  }
   const dim3 blk(32, 8), grid((unsigned)std::min<long long>((rows + 255) / 256, 148 * 8), (F + 31) / 32);
   ONO_DISPATCH(dtype,
                (conv1_fwd_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
@@ -441,6 +573,22 @@ extern "C" int ono_conv1_wgrad(const OnoConvGeom* g, int F, int dtype, const voi
   const long long rows = (long long)g->B * g->OH * g->OW;
   const dim3 blk(32, 8);
   if (rows >= (1ll << 31)) { set_error("conv1_wgrad: too many output pixels%s", "", 0, 0); return -1; }
+  if (const size_t sm = c1_img_smem(g)) {
+    const int nb = std::min(g->B, C1_MAXBLOCKS);
+    cudaStream_t s = (cudaStream_t)st;
+    if (g->K == 3) {
+      ONO_DISPATCH(dtype,
+                   (conv1_wgrad_img_kernel<float, 3><<<nb, 256, sm, s>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy)),
+                   (conv1_wgrad_img_kernel<bf16, 3><<<nb, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy)))
+    } else {
+      ONO_DISPATCH(dtype,
+                   (conv1_wgrad_img_kernel<float, 5><<<nb, 256, sm, s>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy)),
+                   (conv1_wgrad_img_kernel<bf16, 5><<<nb, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy)))
+    }
+    const int pairs = F * (g->K * g->K + 1);
+    conv1_wgrad_reduce_kernel<<<(pairs + 7) / 8, 256, 0, s>>>(F, g->K * g->K, nb, gk, gb, beta);
+    return done("conv1_wgrad");
+  }
   const int grid = (int)std::min<long long>((rows + 255) / 256, C1_MAXBLOCKS);
   ONO_DISPATCH(dtype,
                (conv1_wgrad_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy, gk, gb, beta)),

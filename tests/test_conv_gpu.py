@@ -135,3 +135,43 @@ def test_single_channel_first_layer_uses_direct_kernels_and_tracks_the_oracle():
     assert lg[-1] < lg[0]
     assert np.allclose(lc, lg, rtol=5e-2, atol=1e-5)
     assert np.abs(wc - wg).max() < 5e-2 * max(1.0, np.abs(wc).max())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(5, 28, 28, 3, 1, 1, 32), (7, 28, 28, 3, 2, 1, 40), (3, 28, 28, 5, 1, 0, 6),
+                                   (4, 12, 17, 5, 2, 2, 33), (3, 9, 9, 2, 1, 0, 8), (2, 120, 120, 3, 1, 1, 16)])
+def test_direct_single_channel_kernels_match_conv2d(dtype, shape):
+    """Image-tiled kernels (k = 3, 5; image fits shared memory) and the generic ones (k = 2; 120 x 120) against PyTorch."""
+    from oxidized_neural_orchestra_b200.ops import conv as CV
+
+    B, H, W, K, S, P, Fo = shape
+    torch.manual_seed(3)
+    g = CV.geom(B, 1, H, W, K, S, P)
+    x = torch.randn(B * H * W, 4, device="cuda").to(dtype)[:, :1]          # pixel-major, one channel, padded rows
+    kp = torch.randn(Fo, K, K, device="cuda") * 0.3
+    bias = torch.randn(Fo, device="cuda")
+    rows = B * g.OH * g.OW
+    y = torch.full((rows, Fo + 8), 7.0, device="cuda", dtype=dtype)[:, :Fo]
+    CV.conv1_fwd(g, Fo, x, kp, bias, y, act="tanh", act_param=1.0)
+    xi = x.double().reshape(B, 1, H, W)       # float64 reference: cuDNN's fp32 convolutions may run on tf32
+    ref = torch.tanh(F.conv2d(xi, kp.double().view(Fo, 1, K, K), bias.double(), stride=S, padding=P))
+    ref_rows = ref.permute(0, 2, 3, 1).reshape(rows, Fo)
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert (y.float() - ref_rows).abs().max().item() <= tol
+    assert bool((y._base[:, Fo:] == 7.0).all())
+    dy = (torch.randn(rows, Fo + 8, device="cuda") * 0.1).to(dtype)[:, :Fo]
+    gk, gb = torch.full((Fo, K, K), 3.0, device="cuda"), torch.full((Fo,), 3.0, device="cuda")
+    CV.conv1_wgrad(g, Fo, x, dy, gk, gb, beta=0.0)
+    again_k, again_b = torch.empty_like(gk), torch.empty_like(gb)
+    CV.conv1_wgrad(g, Fo, x, dy, again_k, again_b, beta=0.0)
+    kr = kp.double().view(Fo, 1, K, K).requires_grad_(True)
+    br = bias.double().requires_grad_(True)
+    out = F.conv2d(xi, kr, br, stride=S, padding=P)
+    out.backward(dy.double().reshape(B, g.OH, g.OW, Fo).permute(0, 3, 1, 2))
+    scale = max(1.0, kr.grad.abs().max().item())
+    wtol = (3e-2 if dtype == torch.bfloat16 else 2e-4) * scale
+    assert (gk - kr.grad.view(Fo, K, K)).abs().max().item() <= wtol
+    assert (gb - br.grad).abs().max().item() <= wtol * 4
+    assert torch.equal(gk, again_k) and torch.equal(gb, again_b)      # fixed summation order
+    CV.conv1_wgrad(g, Fo, x, dy, gk, gb, beta=1.0)                     # accumulate
+    assert (gk - 2 * kr.grad.view(Fo, K, K)).abs().max().item() <= 2 * wtol
