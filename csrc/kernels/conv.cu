@@ -155,6 +155,84 @@ __global__ void col2im_kernel(const OnoConvGeom g, const T* dcols, int ld_dcols,
   }
 }
 
+// Four consecutive channels at once (16-byte loads of f32, 8-byte loads of bf16).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<const uint32_t*>(&a);
+  u.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// col2im with compile-time kernel size and stride, four channels per thread: a block takes 32 pixels x 32 channels
+// (thread = pixel x channel quad), the K x K taps unroll into independent predicated vector loads, so a thread has all
+// its loads in flight at once instead of walking data-dependent loops. Needs C % 4 == 0 and 4-element aligned rows.
+template <typename T, int K, int S>
+__global__ void __launch_bounds__(256) col2im_vec_kernel(const OnoConvGeom g, const T* dcols, int ld_dcols, const T* aux, int ld_aux,
+                                                         int dact, float dact_param, int relu_quirk, T* dx, int ld_dx, T* dxT, int ld_dxT) {
+  __shared__ float tile[32][33];
+  const long long npix = (long long)g.B * g.H * g.W;
+  const int ctiles = (g.C + 31) / 32;
+  const long long ntiles = ((npix + 31) / 32) * ctiles;
+  const int q = threadIdx.x & 7, pp = threadIdx.x >> 3;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long p0 = (t / ctiles) * 32;
+    const int c0 = (int)(t % ctiles) * 32;
+    const int c = c0 + 4 * q;
+    const long long pix = p0 + pp;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (pix < npix && c < g.C) {
+      const int ixp = (int)(pix % g.W) + g.P;
+      const long long rest = pix / g.W;
+      const int iyp = (int)(rest % g.H) + g.P;
+      const long long img_row = (rest / g.H) * g.OH;
+#pragma unroll
+      for (int ky = 0; ky < K; ++ky) {
+        const int ty = iyp - ky;
+        const int oy = ty / S;
+        const bool oky = ty >= 0 && (ty % S) == 0 && oy < g.OH;
+#pragma unroll
+        for (int kx = 0; kx < K; ++kx) {
+          const int tx = ixp - kx;
+          const int ox = tx / S;
+          if (oky && tx >= 0 && (tx % S) == 0 && ox < g.OW) {
+            const float4 v = load4(dcols + ((img_row + oy) * g.OW + ox) * (long long)ld_dcols + (ky * K + kx) * g.C + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+          }
+        }
+      }
+      if (dact != ACT_NONE) {
+        const float4 a = load4(aux + pix * ld_aux + c);
+        acc.x = act_bwd(dact, dact_param, relu_quirk, a.x, acc.x);
+        acc.y = act_bwd(dact, dact_param, relu_quirk, a.y, acc.y);
+        acc.z = act_bwd(dact, dact_param, relu_quirk, a.z, acc.z);
+        acc.w = act_bwd(dact, dact_param, relu_quirk, a.w, acc.w);
+      }
+      store4(dx + pix * ld_dx + c, acc);
+    }
+    if (dxT) {
+      tile[pp][4 * q] = acc.x; tile[pp][4 * q + 1] = acc.y; tile[pp][4 * q + 2] = acc.z; tile[pp][4 * q + 3] = acc.w;
+      __syncthreads();
+      const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int cc = wy + 8 * j;
+        const long long px = p0 + lane;
+        if (px < npix && c0 + cc < g.C) dxT[(long long)(c0 + cc) * ld_dxT + px] = from_f32<T>(tile[lane][cc]);
+      }
+      __syncthreads();
+    }
+  }
+}
+
 // Kernel tensor between the parameter layout K[F][C][k][k] (f32, contiguous) and the operand layout
 // [F][(ky,kx,c)] used by the GEMMs. dir 0: parameters -> operand (dst, dtype T, leading dimension ld_dst) and
 // optionally its transpose dstT[(ky,kx,c)][F]; dir 1: f32 operand-ordered gradient (src, ld_src) -> parameter
@@ -535,6 +613,21 @@ extern "C" int ono_col2im(const OnoConvGeom* g, int dtype, const void* dcols, in
   const long long n = (long long)g->B * g->H * g->W * ((g->C + 31) / 32 * 32);
   const dim3 blk(32, 8);
   const int grid = grid_of(n / 4);
+  const int esz = dtype == 0 ? 4 : 2;
+  const bool vec = g->C % 4 == 0 && ld_dcols % 4 == 0 && ld_dx % 4 == 0 && (!aux || ld_aux % 4 == 0) &&
+                   (((uintptr_t)dcols | (uintptr_t)dx | (uintptr_t)aux) & (uintptr_t)(4 * esz - 1)) == 0 && (aux || dact == ACT_NONE);
+#define ONO_COL2IM_VEC(KK, SS)                                                                                                   \
+  if (vec && g->K == KK && g->S == SS) {                                                                                          \
+    ONO_DISPATCH(dtype,                                                                                                           \
+                 (col2im_vec_kernel<float, KK, SS><<<grid, 256, 0, (cudaStream_t)st>>>(*g, (const float*)dcols, ld_dcols, (const float*)aux, ld_aux, dact, dact_param, relu_quirk, (float*)dx, ld_dx, (float*)dxT, ld_dxT)), \
+                 (col2im_vec_kernel<bf16, KK, SS><<<grid, 256, 0, (cudaStream_t)st>>>(*g, (const bf16*)dcols, ld_dcols, (const bf16*)aux, ld_aux, dact, dact_param, relu_quirk, (bf16*)dx, ld_dx, (bf16*)dxT, ld_dxT))) \
+    return done("col2im");                                                                                                        \
+  }
+  ONO_COL2IM_VEC(3, 1)
+  ONO_COL2IM_VEC(3, 2)
+  ONO_COL2IM_VEC(5, 1)
+  ONO_COL2IM_VEC(5, 2)
+#undef ONO_COL2IM_VEC
   ONO_DISPATCH(dtype,
                (col2im_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const float*)dcols, ld_dcols, (const float*)aux, ld_aux, dact, dact_param, relu_quirk, (float*)dx, ld_dx, (float*)dxT, ld_dxT)),
                (col2im_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const bf16*)dcols, ld_dcols, (const bf16*)aux, ld_aux, dact, dact_param, relu_quirk, (bf16*)dx, ld_dx, (bf16*)dxT, ld_dxT)))
