@@ -172,6 +172,49 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
   *reinterpret_cast<uint2*>(p) = u;
 }
 
+// im2col, four channels per thread (C % 4 == 0, so four consecutive columns share one tap): a block takes a
+// 32 x 32 tile of (r, q) in one pass; one vector load, one vector store, the transposed copy through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) im2col_vec_kernel(const OnoConvGeom g, const T* x, int ldx, T* cols, int ld_cols, T* colsT,
+                                                         int ld_colsT) {
+  __shared__ float tile[32][33];
+  const int ckk = g.C * g.K * g.K;
+  const long long rows = (long long)g.B * g.OH * g.OW;
+  const int qtiles = (ckk + 31) / 32;
+  const long long ntiles = ((rows + 31) / 32) * qtiles;
+  const int qd = threadIdx.x & 7, rr = threadIdx.x >> 3;
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    const long long r0 = (t / qtiles) * 32;
+    const int q0 = (int)(t % qtiles) * 32;
+    const int q = q0 + 4 * qd;
+    const long long r = r0 + rr;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows && q < ckk) {
+      const int tap = q / g.C, c = q - tap * g.C;
+      const int ky = tap / g.K, kx = tap - ky * g.K;
+      const int ox = (int)(r % g.OW);
+      const long long rest = r / g.OW;
+      const int oy = (int)(rest % g.OH);
+      const long long img = rest / g.OH;
+      const int iy = oy * g.S - g.P + ky, ix = ox * g.S - g.P + kx;
+      if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) v = load4(x + ((img * g.H + iy) * g.W + ix) * (long long)ldx + c);
+      store4(cols + r * ld_cols + q, v);
+    }
+    if (colsT) {
+      tile[rr][4 * qd] = v.x; tile[rr][4 * qd + 1] = v.y; tile[rr][4 * qd + 2] = v.z; tile[rr][4 * qd + 3] = v.w;
+      __syncthreads();
+      const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int qq = wy + 8 * j;
+        const long long rw = r0 + lane;
+        if (rw < rows && q0 + qq < ckk) colsT[(long long)(q0 + qq) * ld_colsT + rw] = from_f32<T>(tile[lane][qq]);
+      }
+      __syncthreads();
+    }
+  }
+}
+
 // col2im with compile-time kernel size and stride, four channels per thread: a block takes 32 pixels x 32 channels
 // (thread = pixel x channel quad), the K x K taps unroll into independent predicated vector loads, so a thread has all
 // its loads in flight at once instead of walking data-dependent loops. Needs C % 4 == 0 and 4-element aligned rows.
@@ -602,6 +645,17 @@ extern "C" int ono_im2col(const OnoConvGeom* g, int dtype, const void* x, int ld
   const long long n = (long long)g->B * g->OH * g->OW * g->C * g->K * g->K;
   const dim3 blk(32, 8);
   const int grid = grid_of(n / 4);
+  {
+    const int esz = dtype == 0 ? 4 : 2;
+    const bool vec = g->C % 4 == 0 && ldx % 4 == 0 && ld_cols % 4 == 0 &&
+                     (((uintptr_t)x | (uintptr_t)cols) & (uintptr_t)(4 * esz - 1)) == 0;
+    if (vec) {
+      ONO_DISPATCH(dtype,
+                   (im2col_vec_kernel<float><<<grid, 256, 0, (cudaStream_t)st>>>(*g, (const float*)x, ldx, (float*)cols, ld_cols, (float*)colsT, ld_colsT)),
+                   (im2col_vec_kernel<bf16><<<grid, 256, 0, (cudaStream_t)st>>>(*g, (const bf16*)x, ldx, (bf16*)cols, ld_cols, (bf16*)colsT, ld_colsT)))
+      return done("im2col");
+    }
+  }
   ONO_DISPATCH(dtype,
                (im2col_kernel<float><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const float*)x, ldx, (float*)cols, ld_cols, (float*)colsT, ld_colsT)),
                (im2col_kernel<bf16><<<grid, blk, 0, (cudaStream_t)st>>>(*g, (const bf16*)x, ldx, (bf16*)cols, ld_cols, (bf16*)colsT, ld_colsT)))
