@@ -102,6 +102,8 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
         b200["grad_push"] = cfg["grad_push"]
     if cfg.get("grad_stage"):
         b200["grad_stage"] = cfg["grad_stage"]
+    if cfg.get("phase_timing"):
+        b200["phase_timing"] = True
     strat = cfg["strategy"]
     if strat.startswith("ps") or strat.startswith("ss"):
         ns = min(int(strat[2:] or 2), n_gpus)
@@ -165,6 +167,9 @@ def main() -> None:
     ap.add_argument("--config", default="deep", choices=sorted(CONFIGS))
     ap.add_argument("--push", default=None, choices=("on", "off", "auto"), help="gradient push through the GEMM epilogues")
     ap.add_argument("--stage", default=None, choices=("on", "off", "auto"), help="staged reduce-scatter during backward")
+    ap.add_argument("--phases", action="store_true",
+                    help="diagnostic: run the steps uncaptured with CUDA events around compute / exchange / refresh and add "
+                         "their mean durations (phase_ms) to the line; such a line is not a benchmark value")
     ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -190,6 +195,8 @@ def main() -> None:
         cfg["grad_push"] = args.push
     if args.stage:
         cfg["grad_stage"] = args.stage
+    if args.phases:
+        cfg["phase_timing"] = True
     W, K = max(3, args.warmup), args.steps
     if args.impl == "nccl":
         sys.path.insert(0, os.path.join(ROOT, "baseline"))
@@ -240,6 +247,9 @@ def main() -> None:
                     "device_ms_per_step": e["bench_ms"] / K},
             "gpu_launches": int(m["launches_per_step"]) * K,
         }
+        if m.get("phase_ms"):
+            out["phase_ms"] = m["phase_ms"]
+            out["config"]["phase_timing"] = "steps ran uncaptured with per-phase events: diagnostic line, not a benchmark value"
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
