@@ -3,7 +3,7 @@ PY ?= python
 NODES ?= 3
 BASE_PORT ?= 40000
 
-.PHONY: build test test-gpu sanitize node orchestui orchestrator cluster-up bench bench-nccl bench-kernels clean
+.PHONY: build test test-gpu sanitize node orchestui orchestrator cluster-up cluster-down compose-up compose-down bench bench-nccl bench-kernels bench-suites bench-plots lint check clean
 
 build:            ## CUDA kernels (sm_100a), the C++ core extension and the native executables
 	$(PY) -c "import __graft_entry__ as g; g.build()"
@@ -27,10 +27,31 @@ orchestrator: build   ## make orchestrator MODEL=model.json TRAINING=training.js
 	./bin/ono-orchestrator $(MODEL) $(TRAINING)
 
 cluster-up: build ## NODES listening nodes on BASE_PORT.. (foreground; ctrl-c stops them)
-	$(PY) -m oxidized_neural_orchestra_b200.runtime.launch --nodes $(NODES) --base-port $(BASE_PORT)
+	$(PY) -m oxidized_neural_orchestra_b200.runtime.launch --nodes $(NODES) --base-port $(BASE_PORT) --pid-file .cluster.pid
+
+cluster-down:     ## stop the nodes of a running `make cluster-up` (from another shell)
+	@if [ -f .cluster.pid ]; then kill `cat .cluster.pid` && rm -f .cluster.pid; else echo "no .cluster.pid: nothing to stop"; fi
+
+compose-up:       ## NODES node containers, one GPU each: make compose-up NODES=8 [RATE=10mbit]
+	$(PY) docker/compose_up.py --nodes $(NODES) --base-port $(BASE_PORT) $(if $(RATE),--rate $(RATE),)
+
+compose-down:
+	$(PY) docker/compose_up.py --down
 
 bench:
 	$(PY) bench.py
+
+bench-suites:     ## the reference's benchmark suites (strategies; SUITE=scalability|offline) -> bench/results/
+	$(PY) bench/suites.py --suite $(or $(SUITE),strategies)
+
+bench-plots:      ## SVG charts + plots.md from bench/results/history.jsonl
+	$(PY) bench/plots.py
+
+lint:             ## syntax check of every Python file, warnings-as-errors compile of the C++ core headers
+	$(PY) -m compileall -q oxidized_neural_orchestra_b200 orchestra bench baseline examples docker tests bench.py __graft_entry__.py
+	$(CXX) -std=c++17 -Wall -Wextra -Werror -Wno-unused-parameter -Wno-unused-function -fsyntax-only -I csrc csrc/core/configs.cpp csrc/core/codec.cpp
+
+check: lint test  ## what CI runs
 
 bench-nccl:
 	$(PY) bench.py --impl nccl

@@ -31,15 +31,32 @@ SERVICE = """  node-{i}:
 """
 
 
+# Optional traffic shaping of the control plane, as the reference's benchmark clusters do with Pumba
+# (docker/gen_compose.py:15-41: `netem --duration ... rate 10mbit` on every node container). It touches the
+# containers' TCP interfaces only; gradients between GPUs travel over NVLink and are not shaped.
+PUMBA = """  pumba:
+    image: gaiaadm/pumba
+    volumes:
+      - /var/run/docker.sock:/var/run/docker.sock
+    command: netem --duration {duration} --tc-image gaiadocker/iproute2 rate --rate {rate} {targets}
+    depends_on: [{deps}]
+"""
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--nodes", type=int, default=8)
     ap.add_argument("--base-port", type=int, default=40000)
     ap.add_argument("--log", default="info")
+    ap.add_argument("--rate", default=None, help="shape every node's network to this rate with a Pumba container, e.g. 10mbit")
+    ap.add_argument("--rate-duration", default="24h")
     a = ap.parse_args()
     out = ["services:"]
     for i in range(a.nodes):
         out.append(SERVICE.format(i=i, port=a.base_port + i, log=a.log))
+    if a.rate:
+        names = [f"node-{i}" for i in range(a.nodes)]
+        out.append(PUMBA.format(duration=a.rate_duration, rate=a.rate, targets=" ".join(names), deps=", ".join(names)))
     sys.stdout.write("\n".join(out))
     addrs = ", ".join(f'"node-{i}:{a.base_port + i}"' for i in range(a.nodes))
     print(f"# addrs for training.json (from a container on the same network): [{addrs}]", file=sys.stderr)

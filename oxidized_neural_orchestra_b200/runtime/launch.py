@@ -107,7 +107,11 @@ def main(argv=None) -> None:
     ap.add_argument("--base-port", type=int, default=40000)
     ap.add_argument("--device", choices=("cpu", "gpu"), default=None)
     ap.add_argument("--native", action="store_true", help="start the C++ ono-node executable instead of the Python node")
+    ap.add_argument("--pid-file", default=None, help="write this launcher's pid here (SIGTERM to it stops the nodes it started)")
     a = ap.parse_args(argv)
+    if a.pid_file:
+        with open(a.pid_file, "w") as f:
+            f.write(str(os.getpid()))
     device = a.device
     if device is None:
         import torch
@@ -136,6 +140,8 @@ def main(argv=None) -> None:
         for p in procs:      # exactly the children started above
             if p.poll() is None:
                 p.terminate()
+        if a.pid_file and os.path.exists(a.pid_file):
+            os.remove(a.pid_file)
         for p in procs:
             try:
                 p.wait(timeout=10)
