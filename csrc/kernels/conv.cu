@@ -511,6 +511,76 @@ __global__ void __launch_bounds__(256) conv1_wgrad_img_kernel(const OnoConvGeom 
   }
 }
 
+// The same with 16-byte loads of dy (F % 4 == 0): a lane holds four consecutive filters of one of four pixels the warp
+// works on at a time, so a warp instruction brings in 512 bytes and the pixel loop has a quarter of the load
+// instructions; the four pixel groups are folded with shuffles before the cross-warp reduction.
+template <typename T, int K>
+__global__ void __launch_bounds__(256) conv1_wgrad_img4_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const T* dy, int ld_dy) {
+  extern __shared__ float c1_tile[];
+  constexpr int KK = K * K;
+  const int TW = g.W + 2 * g.P, TH = g.H + 2 * g.P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int fq = lane & 7, pg = lane >> 3;
+  const int nfb = (F + 31) / 32;
+  for (int fb = 0; fb < nfb; ++fb) {
+    const int f4 = fb * 32 + 4 * fq;          // first of this lane's four filters
+    const bool live = f4 < F;
+    float acc[KK + 1][4];
+#pragma unroll
+    for (int i = 0; i <= KK; ++i) { acc[i][0] = 0.f; acc[i][1] = 0.f; acc[i][2] = 0.f; acc[i][3] = 0.f; }
+    for (int img = blockIdx.x; img < g.B; img += gridDim.x) {
+      __syncthreads();
+      c1_stage_image(g, x, ldx, img, c1_tile, TW, TH);
+      __syncthreads();
+      for (int oy = warp; oy < g.OH; oy += 8) {
+        const float* trow = c1_tile + oy * g.S * TW;
+        const T* drow = dy + (long long)(img * g.OH + oy) * g.OW * ld_dy + f4;
+#pragma unroll 2
+        for (int ox = pg; ox < g.OW; ox += 4) {
+          const float4 d = live ? load4(drow + (long long)ox * ld_dy) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float* t0 = trow + ox * g.S;
+#pragma unroll
+          for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+            for (int kx = 0; kx < K; ++kx) {
+              const float t = t0[ky * TW + kx];
+              acc[ky * K + kx][0] += d.x * t; acc[ky * K + kx][1] += d.y * t;
+              acc[ky * K + kx][2] += d.z * t; acc[ky * K + kx][3] += d.w * t;
+            }
+          acc[KK][0] += d.x; acc[KK][1] += d.y; acc[KK][2] += d.z; acc[KK][3] += d.w;
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i <= KK; ++i)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float v = acc[i][c];
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        acc[i][c] = v;
+      }
+    __syncthreads();   // the image is no longer needed: its space takes the warps' sums, [warp][filter][slot]
+    if (pg == 0) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i <= KK; ++i) c1_tile[(warp * 32 + 4 * fq + c) * (KK + 1) + i] = acc[i][c];
+    }
+    __syncthreads();
+    const int f = fb * 32 + lane;
+    if (warp == 0 && f < F) {
+#pragma unroll
+      for (int i = 0; i <= KK; ++i) {
+        float t = 0.f;
+#pragma unroll
+        for (int wq = 0; wq < 8; ++wq) t += c1_tile[(wq * 32 + lane) * (KK + 1) + i];
+        g_c1_part[((size_t)f * (KK + 1) + i) * gridDim.x + blockIdx.x] = t;
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) conv1_wgrad_reduce_kernel(int F, int kk, int nblocks, float* gk, float* gb, float beta) {
   const int lane = threadIdx.x & 31;
   const int pair = blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -723,7 +793,17 @@ extern "C" int ono_conv1_wgrad(const OnoConvGeom* g, int F, int dtype, const voi
   if (const size_t sm = c1_img_smem(g)) {
     const int nb = std::min(g->B, C1_MAXBLOCKS);
     cudaStream_t s = (cudaStream_t)st;
-    if (g->K == 3) {
+    const int esz = dtype == 0 ? 4 : 2;
+    const bool v4 = F % 4 == 0 && ld_dy % 4 == 0 && ((uintptr_t)dy & (uintptr_t)(4 * esz - 1)) == 0;
+    if (v4 && g->K == 3) {
+      ONO_DISPATCH(dtype,
+                   (conv1_wgrad_img4_kernel<float, 3><<<nb, 256, sm, s>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy)),
+                   (conv1_wgrad_img4_kernel<bf16, 3><<<nb, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy)))
+    } else if (v4) {
+      ONO_DISPATCH(dtype,
+                   (conv1_wgrad_img4_kernel<float, 5><<<nb, 256, sm, s>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy)),
+                   (conv1_wgrad_img4_kernel<bf16, 5><<<nb, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy)))
+    } else if (g->K == 3) {
       ONO_DISPATCH(dtype,
                    (conv1_wgrad_img_kernel<float, 3><<<nb, 256, sm, s>>>(*g, F, (const float*)x, ldx, (const float*)dy, ld_dy)),
                    (conv1_wgrad_img_kernel<bf16, 3><<<nb, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, (const bf16*)dy, ld_dy)))
