@@ -462,6 +462,51 @@ __global__ void __launch_bounds__(256) conv1_fwd_img_kernel(const OnoConvGeom g,
   }
 }
 
+// Forward with 16-byte stores (F % 4 == 0): a lane holds four consecutive filters of one of the four pixels the warp
+// works on at a time.
+template <typename T, int K>
+__global__ void __launch_bounds__(256) conv1_fwd_img4_kernel(const OnoConvGeom g, int F, const T* x, int ldx, const float* kparams,
+                                                             const float* bias, int act, float act_param, T* y, int ldy) {
+  extern __shared__ float c1_tile[];
+  constexpr int KK = K * K;
+  const int TW = g.W + 2 * g.P, TH = g.H + 2 * g.P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int fq = lane & 7, pg = lane >> 3;
+  const int f4 = blockIdx.y * 32 + 4 * fq;
+  const bool live = f4 < F;
+  float w[KK][4], bv[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    bv[c] = (bias && live) ? bias[f4 + c] : 0.f;
+#pragma unroll
+    for (int i = 0; i < KK; ++i) w[i][c] = live ? kparams[(long long)(f4 + c) * KK + i] : 0.f;
+  }
+  for (int img = blockIdx.x; img < g.B; img += gridDim.x) {
+    __syncthreads();
+    c1_stage_image(g, x, ldx, img, c1_tile, TW, TH);
+    __syncthreads();
+    for (int oy = warp; oy < g.OH; oy += 8) {
+      const float* trow = c1_tile + oy * g.S * TW;
+      T* yrow = y + (long long)(img * g.OH + oy) * g.OW * ldy + f4;
+#pragma unroll 2
+      for (int ox = pg; ox < g.OW; ox += 4) {
+        const float* t0 = trow + ox * g.S;
+        float a0 = bv[0], a1 = bv[1], a2 = bv[2], a3 = bv[3];
+#pragma unroll
+        for (int ky = 0; ky < K; ++ky)
+#pragma unroll
+          for (int kx = 0; kx < K; ++kx) {
+            const float t = t0[ky * TW + kx];
+            a0 += w[ky * K + kx][0] * t; a1 += w[ky * K + kx][1] * t; a2 += w[ky * K + kx][2] * t; a3 += w[ky * K + kx][3] * t;
+          }
+        if (live)
+          store4(yrow + (long long)ox * ldy, make_float4(act_fwd(act, act_param, a0), act_fwd(act, act_param, a1),
+                                                         act_fwd(act, act_param, a2), act_fwd(act, act_param, a3)));
+      }
+    }
+  }
+}
+
 // Partial sums of block b for (filter f, slot i; slot K*K = bias) go to g_c1_part[(f * (K*K+1) + i) * gridDim.x + b];
 // conv1_wgrad_reduce_kernel then adds a pair's partials with one warp in a fixed order.
 template <typename T, int K>
@@ -766,7 +811,17 @@ extern "C" int ono_conv1_fwd(const OnoConvGeom* g, int F, int dtype, const void*
   if (const size_t sm = c1_img_smem(g)) {
     const dim3 grid((unsigned)std::min(g->B, 148 * 8), (F + 31) / 32);
     cudaStream_t s = (cudaStream_t)st;
-    if (g->K == 3) {
+    const int esz = dtype == 0 ? 4 : 2;
+    const bool v4 = F % 4 == 0 && ldy % 4 == 0 && ((uintptr_t)y & (uintptr_t)(4 * esz - 1)) == 0;
+    if (v4 && g->K == 3) {
+      ONO_DISPATCH(dtype,
+                   (conv1_fwd_img4_kernel<float, 3><<<grid, 256, sm, s>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
+                   (conv1_fwd_img4_kernel<bf16, 3><<<grid, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))
+    } else if (v4) {
+      ONO_DISPATCH(dtype,
+                   (conv1_fwd_img4_kernel<float, 5><<<grid, 256, sm, s>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
+                   (conv1_fwd_img4_kernel<bf16, 5><<<grid, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))
+    } else if (g->K == 3) {
       ONO_DISPATCH(dtype,
                    (conv1_fwd_img_kernel<float, 3><<<grid, 256, sm, s>>>(*g, F, (const float*)x, ldx, kparams, bias, act, act_param, (float*)y, ldy)),
                    (conv1_fwd_img_kernel<bf16, 3><<<grid, 256, sm, s>>>(*g, F, (const bf16*)x, ldx, kparams, bias, act, act_param, (bf16*)y, ldy)))

@@ -37,6 +37,9 @@ class ConvNetEngine:
         self.bf16 = tile_dtype == "bf16"
         self.dev = params.device
         self.sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        # tf32 weight gradients read dy and the columns in place as MN-major operands (no transposed copies of either);
+        # ONO_CONV_TF32_T=1 brings back the K-major operands with their transposed copies
+        self.wgrad_t = tile_dtype != "bf16" and __import__("os").environ.get("ONO_CONV_TF32_T", "0") == "1"
         self.B = batch_size
         self.relu_quirk = not leaky_relu_exact
         self.params, self.grads, self.params_bf16 = params, grads, params_bf16
@@ -87,9 +90,10 @@ class ConvNetEngine:
                 d["cols"] = z(Mout, _up(ckk))
                 d["dcols"] = z(Mout, _up(ckk)) if j > 0 else None
                 d["gk_tmp"] = z(d["F"], _up(ckk), torch.float32)
-                if not self.bf16:
+                if self.wgrad_t:
                     d["colsT"] = z(ckk, _up(Mout))
                     d["dyT"] = z(d["F"], _up(Mout))
+                if not self.bf16:
                     d["kt"] = z(ckk, _up(d["F"]))                     # K^T for dgrad
                 # the kernel tensor as a GEMM operand: rows in (ky, kx, c) order, rebuilt at every refresh
                 d["kop"] = z(d["F"], _up(ckk))[:, :ckk]
@@ -141,7 +145,7 @@ class ConvNetEngine:
                 cv.conv1_fwd(g, d["F"], cur, self._k_view(d), self._kb_view(d), d["y"], act=act, act_param=ap, stream=stream)
                 n += 1
             elif d["kind"] == "conv":
-                cv.im2col(g, cur, d["cols"], None if self.bf16 else d["colsT"], stream=stream)
+                cv.im2col(g, cur, d["cols"], d["colsT"] if self.wgrad_t else None, stream=stream)
                 kw = dict(bias=self._kb_view(d), act=act, act_param=ap, status=self.status, stream=stream)
                 if self.bf16:
                     kw["out_bf16"] = d["y"][:Mout, :d["F"]]
@@ -164,7 +168,7 @@ class ConvNetEngine:
         de = self.dense
         last = self.front[-1]
         act, ap = self._act(last) if last["kind"] == "conv" else (None, 0.0)
-        want_t = (not self.bf16) and last["kind"] == "conv" and not last.get("direct")
+        want_t = self.wgrad_t and last["kind"] == "conv" and not last.get("direct")
         cv.nchw_flat(nrows, last["F"], last["OH"] * last["OW"], False, last["dy"], de.d[0],
                      out_t=last["dyT"] if want_t else None, aux=last["y"], dact=act, dact_param=ap,
                      relu_quirk=self.relu_quirk, stream=stream)
@@ -175,7 +179,7 @@ class ConvNetEngine:
             Mout, Min = nrows * d["OH"] * d["OW"], nrows * d["H"] * d["W"]
             g = cv.geom(nrows, d["C"], d["H"], d["W"], d["K"], d["S"], d["P"])
             pact, pap = (self._act(prev) if (prev is not None and prev["kind"] == "conv") else (None, 0.0))
-            prev_t = prev is not None and prev["kind"] == "conv" and not self.bf16 and not prev.get("direct")
+            prev_t = prev is not None and prev["kind"] == "conv" and self.wgrad_t and not prev.get("direct")
             if d["kind"] == "conv" and d.get("direct"):
                 F, ckk = d["F"], d["ckk"]
                 cv.conv1_wgrad(g, F, self.x0, d["dy"], self.grads[d["off"]:d["off"] + F * ckk],
@@ -200,7 +204,7 @@ class ConvNetEngine:
                 kb = -(-Mout // (64 if self.bf16 else 32))
                 tiles = -(-F // 128) * (1 if ckk <= 128 else -(-ckk // 128))
                 split = max(1, min(kb, -(-self.sms // tiles)))
-                if self.bf16:
+                if not self.wgrad_t:
                     gemm(dy, d["cols"][:Mout, :ckk], a_mn_major=True, b_mn_major=True, out=tmp[:, :ckk], split_k=split,
                          status=self.status, stream=stream)
                 else:
