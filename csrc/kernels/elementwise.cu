@@ -417,8 +417,46 @@ extern "C" int ono_init(float* out, long long n, unsigned long long off, unsigne
   return launch_ok("init");
 }
 
+// f32 copy and/or transpose of an aligned matrix with 16-byte accesses on both sides: 64 x 64 tiles, rows read as
+// float4, the transpose written as float4 along the source's rows (R % 4 == 0, W % 4 == 0, 16-byte aligned rows).
+__global__ void __launch_bounds__(256) rows_vec_kernel(const OnoRows r) {
+  __shared__ float tile[64][65];
+  const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int row = r0 + ty + 16 * p, col = c0 + 4 * tx;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < r.R && col < r.W) {
+      v = *reinterpret_cast<const float4*>(r.src + (size_t)row * r.ld_src + col);
+      if (r.dst_f32) *reinterpret_cast<float4*>(r.dst_f32 + (size_t)row * r.ld_dst + col) = v;
+    }
+    float* t = &tile[ty + 16 * p][4 * tx];
+    t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
+  }
+  if (!r.dstT_f32) return;
+  __syncthreads();
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int col = c0 + ty + 16 * p, row = r0 + 4 * tx;   // output row = source column
+    if (col < r.W && row < r.R) {
+      const int cl = ty + 16 * p;
+      *reinterpret_cast<float4*>(r.dstT_f32 + (size_t)col * r.ld_dstT + row) =
+          make_float4(tile[4 * tx][cl], tile[4 * tx + 1][cl], tile[4 * tx + 2][cl], tile[4 * tx + 3][cl]);
+    }
+  }
+}
+
 extern "C" int ono_rows(const OnoRows* r, ono_stream_t st) {
   if (!r || !r->src || r->R <= 0 || r->W <= 0) { set_error("bad rows args%s", "", 0, 0); return -1; }
+  const bool vec = !r->idx && !r->dst_bf16 && !r->dstT_bf16 && (r->dst_f32 || r->dstT_f32) && r->R % 4 == 0 && r->W % 4 == 0 &&
+                   r->ld_src % 4 == 0 && (!r->dst_f32 || r->ld_dst % 4 == 0) && (!r->dstT_f32 || r->ld_dstT % 4 == 0) &&
+                   (((uintptr_t)r->src | (uintptr_t)r->dst_f32 | (uintptr_t)r->dstT_f32) & 15) == 0 && (long long)r->R * r->W >= (1 << 16);
+  if (vec) {
+    dim3 grid((r->W + 63) / 64, (r->R + 63) / 64);
+    rows_vec_kernel<<<grid, 256, 0, (cudaStream_t)st>>>(*r);
+    return launch_ok("rows");
+  }
   dim3 block(32, 8), grid((r->W + 31) / 32, (r->R + 31) / 32);
   rows_kernel<<<grid, block, 0, (cudaStream_t)st>>>(*r);
   return launch_ok("rows");

@@ -135,3 +135,22 @@ def test_column_sums_and_gemm_repeat_bit_for_bit():
     torch.cuda.synchronize()
     assert torch.equal(sums[0], sums[1])
     assert torch.allclose(sums[0].double(), d.double().sum(0), atol=1e-3)
+
+
+@pytest.mark.parametrize("shape", [(256, 516), (260, 1000), (4096, 784), (64, 1024)])
+@pytest.mark.parametrize("which", ["both", "copy", "transpose"])
+def test_vector_copy_and_transpose_match_and_stay_inside(shape, which):
+    from oxidized_neural_orchestra_b200.ops.elementwise import rows
+
+    R, W = shape
+    torch.manual_seed(4)
+    src = torch.randn(R, W + 12, device="cuda")[:, :W]
+    dst, dst_w, dst_g = _guarded(R, W)
+    dt, dt_w, dt_g = _guarded(W, R)
+    rows(src, dst=dst if which != "transpose" else None, dst_t=dt if which != "copy" else None)
+    torch.cuda.synchronize()
+    if which != "transpose":
+        assert torch.equal(dst, src)
+    if which != "copy":
+        assert torch.equal(dt, src.t())
+    assert _intact(dst_w, dst_g | (which == "transpose")) and _intact(dt_w, dt_g | (which == "copy"))
