@@ -495,6 +495,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// Two-pass form for problems with a handful of output tiles and a long reduction (e.g. 342 x 128 x 3136: three tiles,
+// i.e. three SMs streaming 98 k-blocks each): the reduction is split over the SMs into a scratch accumulator with
+// atomic adds, then this pass runs the regular epilogue (bias, activation, derivative, every output form) on the sums.
+// The scratch is one static buffer: such GEMMs must not overlap on the device (one compute stream).
+constexpr long long SPLIT_SCRATCH_ELEMS = 1ll << 20;
+__device__ float g_split_scratch[SPLIT_SCRATCH_ELEMS];
+
+__global__ void __launch_bounds__(128) gemm_finish_kernel(const float* scratch, int ld, int M, int N, const OnoEpilogue e) {
+  const int m = blockIdx.x * 128 + threadIdx.x;
+  const int n0 = blockIdx.y * 32;
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = 0.f;
+  if (m < M) {
+    const float* src = scratch + (size_t)m * ld + n0;
+    if (n0 + 32 <= ld) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(src + j);
+        v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (n0 + j < ld) v[j] = src[j];
+    }
+  }
+  epilogue_chunk(e, v, m, n0, M, N, 0);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------------
@@ -716,6 +746,9 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   const bool pair = g->pair > 0 && bn >= 128 && g->M > 128;
   rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, pair ? bn / 2 : bn);
   if (rc) return rc;
+  bool two_pass = false;
+  int scratch_ld = 0;
+  float* scratch = nullptr;
   // split-K (g->split_k > 1, or 0 = automatic for tall-K problems with few output tiles): only the
   // plain accumulate-into-f32 epilogue is supported, and the caller zeroes the output first.
   {
@@ -734,14 +767,42 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
       }
     }
     p.split_k = sk > 1 ? sk : 1;
-    (void)tiles0;
+    // automatic two-pass split (see gemm_finish_kernel)
+    const long long ldn = ((long long)g->N + 3) / 4 * 4;
+    if (g->split_k == 0 && !e.reduce_out && !pair && tiles0 * 8 <= num_sms() && KBh >= 32 && (long long)g->M * ldn <= SPLIT_SCRATCH_ELEMS) {
+      int want = std::min<long long>(KBh / 4, num_sms() / tiles0);
+      if (want >= 2) {
+        const int per = (KBh + want - 1) / want;
+        p.split_k = (KBh + per - 1) / per;
+        two_pass = true;
+        scratch_ld = (int)ldn;
+      }
+    }
+  }
+  if (two_pass) {
+    static float* scratch_ptr = nullptr;
+    if (!scratch_ptr && cudaGetSymbolAddress((void**)&scratch_ptr, g_split_scratch) != cudaSuccess) {
+      set_error("split scratch address unavailable%s", "");
+      return -6;
+    }
+    if (cudaMemsetAsync(scratch_ptr, 0, (size_t)g->M * scratch_ld * sizeof(float), stream) != cudaSuccess) {
+      set_error("split scratch memset failed%s", "");
+      return -6;
+    }
+    memset(&p.epi, 0, sizeof(p.epi));
+    p.epi.out_f32 = scratch_ptr;
+    p.epi.ld_out = scratch_ld;
+    p.epi.alpha = 1.0f;
+    scratch = scratch_ptr;
   }
   // One row-major output may leave through TMA stores (coalesced, off the LSU path): the f32 output
   // when it is not accumulated into, else the bf16 output.
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_out = 0;
-  if (e.reduce_out) {
+  if (two_pass) {
+    // atomics into the scratch, no TMA store
+  } else if (e.reduce_out) {
     if (p.split_k > 1 || !e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || ((uintptr_t)e.out_f32 & 15)) {
       set_error("reduce_out supports a plain, 16-byte aligned f32 output only%s", "");
       return -1;
@@ -763,18 +824,26 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
             ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
 
-  if (pair) {
-    if (esize == 4) return bn == 128 ? launch<4, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
-                                     : launch<4, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
-    return bn == 128 ? launch<2, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
-                     : launch<2, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
-  }
-  if (esize == 4) {
-    if (bn == 32) return launch<4, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
-    if (bn == 128) return launch<4, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
-    return launch<4, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
-  }
-  if (bn == 32) return launch<2, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
-  if (bn == 128) return launch<2, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
-  return launch<2, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
+  auto run = [&]() -> int {
+    if (pair) {
+      if (esize == 4) return bn == 128 ? launch<4, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
+                                       : launch<4, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
+      return bn == 128 ? launch<2, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
+                       : launch<2, 256, true>(ta, tb, tc, p, g->max_ctas, stream);
+    }
+    if (esize == 4) {
+      if (bn == 32) return launch<4, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
+      if (bn == 128) return launch<4, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
+      return launch<4, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
+    }
+    if (bn == 32) return launch<2, 32, false>(ta, tb, tc, p, g->max_ctas, stream);
+    if (bn == 128) return launch<2, 128, false>(ta, tb, tc, p, g->max_ctas, stream);
+    return launch<2, 256, false>(ta, tb, tc, p, g->max_ctas, stream);
+  };
+  rc = run();
+  if (rc || !two_pass) return rc;
+  const dim3 fgrid((g->M + 127) / 128, (g->N + 31) / 32);
+  gemm_finish_kernel<<<fgrid, 128, 0, stream>>>(scratch, scratch_ld, g->M, g->N, g->epi);
+  if (cudaGetLastError() != cudaSuccess) { set_error("gemm_finish launch failed%s", ""); return -7; }
+  return 0;
 }

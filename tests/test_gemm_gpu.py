@@ -186,3 +186,31 @@ def test_gemm_reduce_add_output_and_push_add(dtype):
     x, y = torch.arange(1000, device="cuda", dtype=torch.float32), torch.ones(1000, device="cuda")
     push_add(x, y)
     assert torch.equal(y, x + 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(342, 128, 3136), (100, 10, 4096), (1024, 10, 4096), (342, 130, 3140)])
+def test_gemm_few_tiles_long_reduction_takes_the_two_pass_split(dtype, shape):
+    """Three tiles and 98 k-blocks: the reduction is split over the SMs and a finishing pass applies the whole epilogue."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(5)
+    ld = lambda n: (n + 15) // 16 * 16
+    a = (torch.randn(M, ld(K), device="cuda") / 8).to(dtype)[:, :K]
+    b = (torch.randn(N, ld(K), device="cuda") / 8).to(dtype)[:, :K]
+    bias = torch.randn(N, device="cuda")
+    out = torch.full((M, ld(N)), 9.0, device="cuda")[:, :N]
+    pre = torch.full((M, ld(N)), 9.0, device="cuda")[:, :N]
+    out_t = torch.full((N, ld(M)), 9.0, device="cuda")[:, :M]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):      # the scratch accumulator is cleared by every call
+        gemm(a, b, out=out, out_t=out_t, pre=pre, bias=bias, act="relu", pair=-1, status=status)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    z = a.double() @ b.double().t() + bias.double()
+    tol = (4e-3 if dtype == torch.float32 else 2e-3) * z.abs().max().item()
+    assert (pre.double() - z).abs().max().item() <= tol
+    assert (out.double() - z.clamp_min(0)).abs().max().item() <= tol
+    assert (out_t.double() - z.clamp_min(0).t()).abs().max().item() <= tol
+    assert bool((out._base[:, N:] == 9.0).all()) and bool((out_t._base[:, M:] == 9.0).all())
