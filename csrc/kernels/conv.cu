@@ -190,14 +190,16 @@ __global__ void __launch_bounds__(256) im2col_vec_kernel(const OnoConvGeom g, co
     const long long r = r0 + rr;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < rows && q < ckk) {
+      // 32-bit coordinate arithmetic (the launcher checks that pixel counts fit): 64-bit divisions cost ~50 instructions each
+      const unsigned ri = (unsigned)r;
       const int tap = q / g.C, c = q - tap * g.C;
       const int ky = tap / g.K, kx = tap - ky * g.K;
-      const int ox = (int)(r % g.OW);
-      const long long rest = r / g.OW;
-      const int oy = (int)(rest % g.OH);
-      const long long img = rest / g.OH;
+      const unsigned rest = ri / (unsigned)g.OW;
+      const int ox = (int)(ri - rest * (unsigned)g.OW);
+      const unsigned img = rest / (unsigned)g.OH;
+      const int oy = (int)(rest - img * (unsigned)g.OH);
       const int iy = oy * g.S - g.P + ky, ix = ox * g.S - g.P + kx;
-      if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) v = load4(x + ((img * g.H + iy) * g.W + ix) * (long long)ldx + c);
+      if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) v = load4(x + (long long)((img * g.H + iy) * g.W + ix) * ldx + c);
       store4(cols + r * ld_cols + q, v);
     }
     if (colsT) {
@@ -233,10 +235,12 @@ __global__ void __launch_bounds__(256) col2im_vec_kernel(const OnoConvGeom g, co
     const long long pix = p0 + pp;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (pix < npix && c < g.C) {
-      const int ixp = (int)(pix % g.W) + g.P;
-      const long long rest = pix / g.W;
-      const int iyp = (int)(rest % g.H) + g.P;
-      const long long img_row = (rest / g.H) * g.OH;
+      const unsigned pi = (unsigned)pix;               // 32-bit coordinate arithmetic, see im2col_vec_kernel
+      const unsigned rest = pi / (unsigned)g.W;
+      const int ixp = (int)(pi - rest * (unsigned)g.W) + g.P;
+      const unsigned img = rest / (unsigned)g.H;
+      const int iyp = (int)(rest - img * (unsigned)g.H) + g.P;
+      const long long img_row = (long long)img * g.OH;
 #pragma unroll
       for (int ky = 0; ky < K; ++ky) {
         const int ty = iyp - ky;
@@ -762,7 +766,8 @@ extern "C" int ono_im2col(const OnoConvGeom* g, int dtype, const void* x, int ld
   const int grid = grid_of(n / 4);
   {
     const int esz = dtype == 0 ? 4 : 2;
-    const bool vec = g->C % 4 == 0 && ldx % 4 == 0 && ld_cols % 4 == 0 &&
+    const bool vec = g->C % 4 == 0 && ldx % 4 == 0 && ld_cols % 4 == 0 && (long long)g->B * g->H * g->W < (1ll << 31) &&
+                     (long long)g->B * g->OH * g->OW < (1ll << 31) &&
                      (((uintptr_t)x | (uintptr_t)cols) & (uintptr_t)(4 * esz - 1)) == 0;
     if (vec) {
       ONO_DISPATCH(dtype,
@@ -784,6 +789,7 @@ extern "C" int ono_col2im(const OnoConvGeom* g, int dtype, const void* dcols, in
   const int grid = grid_of(n / 4);
   const int esz = dtype == 0 ? 4 : 2;
   const bool vec = g->C % 4 == 0 && ld_dcols % 4 == 0 && ld_dx % 4 == 0 && (!aux || ld_aux % 4 == 0) &&
+                   (long long)g->B * g->H * g->W < (1ll << 31) && (long long)g->B * g->OH * g->OW < (1ll << 31) &&
                    (((uintptr_t)dcols | (uintptr_t)dx | (uintptr_t)aux) & (uintptr_t)(4 * esz - 1)) == 0 && (aux || dact == ACT_NONE);
 #define ONO_COL2IM_VEC(KK, SS)                                                                                                   \
   if (vec && g->K == KK && g->S == SS) {                                                                                          \
