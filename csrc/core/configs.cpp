@@ -396,6 +396,8 @@ Json B200Config::to_json() const {
   o.set("init_from", init_from);
   o.set("trace_path", trace_path);
   o.set("state_path", state_path);
+  o.set("checkpoint_path", checkpoint_path);
+  o.set("checkpoint_every", (long long)checkpoint_every);
   o.set("init_state_from", init_state_from);
   o.set("start_epoch", (long long)start_epoch);
   o.set("metrics_path", metrics_path);
@@ -437,6 +439,11 @@ B200Config B200Config::from_json(const Json& j) {
   if (const Json* v = j.find("init_from")) c.init_from = v->as_string();
   if (const Json* v = j.find("trace_path")) c.trace_path = v->as_string();
   if (const Json* v = j.find("state_path")) c.state_path = v->as_string();
+  if (const Json* v = j.find("checkpoint_path")) c.checkpoint_path = v->as_string();
+  if (const Json* v = j.find("checkpoint_every")) {
+    c.checkpoint_every = v->as_int();
+    if (c.checkpoint_every < 0) throw InvalidConfig("b200.checkpoint_every must be >= 0");
+  }
   if (const Json* v = j.find("init_state_from")) c.init_state_from = v->as_string();
   if (const Json* v = j.find("start_epoch")) c.start_epoch = v->as_int();
   if (const Json* v = j.find("metrics_path")) c.metrics_path = v->as_string();

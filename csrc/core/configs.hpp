@@ -115,6 +115,8 @@ struct B200Config {
   double heartbeat_s = 2.0;               // period of a node's liveness messages (0 = none)
   double heartbeat_timeout_s = 0.0;       // the orchestrator drops a node that stayed silent this long (0 = never)
   std::string init_from;                  // safetensors checkpoint to start from instead of the initialisers (warm start / resume)
+  std::string checkpoint_path;            // GPU ranks: periodic checkpoint (weights here, optimizer state beside it); "{epoch}" is replaced
+  long long checkpoint_every = 0;         // epochs between periodic checkpoints (0 = off)
   std::string state_path;                 // GPU ranks: rank 0 writes the optimizer state (m, v, Adam powers) here at the end of the run
   long long start_epoch = -1;             // GPU ranks: first epoch number for the shuffle sequence (-1: 0, or the epochs recorded in init_state_from)
   std::string init_state_from;            // GPU ranks: optimizer state to resume from (a file written through state_path)

@@ -134,6 +134,37 @@ def _save_state(r, path: str, epochs: int) -> None:
                    optimizer=r.sync_opt.kind, epochs=epochs, n_params=r.n)
 
 
+def _gather_params(r):
+    """The authoritative parameters on rank 0: owners' ranges where ownership is partitioned (session.rs:293-359),
+    rank 0's replica otherwise (session.rs:371-412). Collective."""
+    if r.world > 1 and r.sync_mode not in ("oneshot", "ring"):
+        tmp = torch.zeros_like(r.C)
+        for b, e in r.own[r.rank]:
+            tmp[b:e] = r.C[b:e]
+        dist.all_reduce(tmp, group=r.group)
+        return tmp
+    return r.C
+
+
+def _checkpoint(r, epochs_done: int) -> None:
+    """Periodic checkpoint: weights in the reference's layout plus the optimizer-state sidecar (collective; rank 0 writes)."""
+    from ..utils.state import save_tensors, weight_tensors
+    from .gpu_rank import engine_layers_from_plan
+
+    torch.cuda.synchronize(r.dev)
+    path = r.b200["checkpoint_path"]
+    path = path.replace("{epoch}", str(epochs_done)) if "{epoch}" in path else f"{path}.epoch{epochs_done}"
+    with torch.cuda.stream(r.stream):
+        params = _gather_params(r)
+        host = params[:r.n].cpu().numpy() if r.rank == 0 else None
+    if r.rank == 0:
+        save_tensors(path, weight_tensors(engine_layers_from_plan(r.plan), host))
+    base = path[:-len(".safetensors")] if path.endswith(".safetensors") else path
+    with torch.cuda.stream(r.stream):
+        _save_state(r, base + ".state.safetensors", epochs_done)
+    torch.cuda.synchronize(r.dev)
+
+
 def run(r) -> dict:
     import os
 
@@ -156,6 +187,7 @@ def run(r) -> dict:
         recorded = _load_state(r, r.b200["init_state_from"])
         first_epoch = recorded if first_epoch < 0 else first_epoch
     r.first_epoch = max(0, first_epoch)
+    ckpt_mark = r.first_epoch // max(1, int(r.b200.get("checkpoint_every", 0) or 1))
     if r.feeder is not None:
         r.feeder.epoch_offset = r.first_epoch       # the shuffle sequence continues where the saved run stopped
     while epoch < r.max_epochs:
@@ -232,6 +264,10 @@ def run(r) -> dict:
             with tracer.span("report_and_decide", epoch=epoch):
                 decision = L.report_and_decide(r, epoch_losses)
         L.check_status(r)
+        every = int(r.b200.get("checkpoint_every", 0) or 0)
+        if every > 0 and r.b200.get("checkpoint_path") and decision == 0 and (r.first_epoch + epoch) // every > ckpt_mark:
+            ckpt_mark = (r.first_epoch + epoch) // every      # a round of several epochs may cross more than one multiple
+            _checkpoint(r, r.first_epoch + epoch)
         if decision == 1:
             break
         if decision == 2 and r.algorithm == "strategy_switch" and not r.switched:

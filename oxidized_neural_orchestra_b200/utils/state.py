@@ -18,6 +18,57 @@ import struct
 import numpy as np
 
 
+def weight_tensors(engine_layers: list[dict], params: np.ndarray) -> list:
+    """(name, array) pairs of a weights checkpoint in the reference's layout
+    (orchestrator/src/sessions/trained_model.rs:36-121): for layer i in model order ``layer_{i}.weight`` F32 [in, out]
+    (dense) / [F, C, K, K] (conv) / [0] (max-pool), then ``layer_{i}.bias`` F32 [out] / [F] / [0]; the data are consecutive
+    slices of the flat parameter vector."""
+    out, off = [], 0
+    shapes = []
+    for l in engine_layers:
+        if l["kind"] == "dense":
+            shapes.append(((l["in"], l["out"]), (l["out"],)))
+        elif l["kind"] == "conv":
+            f, c, k = l["kernel_dim"]
+            shapes.append(((f, c, k, k), (f,)))
+        else:
+            shapes.append(((0,), (0,)))
+    total = sum(int(np.prod(w)) + int(np.prod(b)) for w, b in shapes)
+    if total != params.shape[0]:
+        raise ValueError(f"model layout covers {total} parameters, the vector has {params.shape[0]}")
+    for i, l in enumerate(engine_layers):
+        if l["kind"] == "dense":
+            wshape, bshape = (l["in"], l["out"]), (l["out"],)
+        elif l["kind"] == "conv":
+            f, c, k = l["kernel_dim"]
+            wshape, bshape = (f, c, k, k), (f,)
+        else:
+            wshape, bshape = (0,), (0,)
+        for name, shape in ((f"layer_{i}.weight", wshape), (f"layer_{i}.bias", bshape)):
+            n = int(np.prod(shape))
+            out.append((name, np.ascontiguousarray(params[off:off + n], dtype="<f4").reshape(shape)))
+            off += n
+    return out
+
+
+def save_tensors(path: str, tensors: list, meta: dict | None = None) -> None:
+    """Write (name, f32 array) pairs as a safetensors file (no metadata block unless ``meta`` is given)."""
+    header: dict = {}
+    if meta is not None:
+        header["__metadata__"] = {k: str(val) for k, val in meta.items()}
+    off = 0
+    for name, t in tensors:
+        header[name] = {"dtype": "F32", "shape": list(t.shape), "data_offsets": [off, off + t.nbytes]}
+        off += t.nbytes
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for _, t in tensors:
+            f.write(t.tobytes())
+
+
 def save_state(path: str, m: np.ndarray, v: np.ndarray, adam_pows: np.ndarray, **meta) -> None:
     tensors = [("optimizer.m", np.ascontiguousarray(m, dtype="<f4")), ("optimizer.v", np.ascontiguousarray(v, dtype="<f4")),
                ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))]

@@ -207,3 +207,27 @@ def test_resume_with_optimizer_state_continues_the_uninterrupted_run(tmp_path):
     assert err_resumed < 1e-5, err_resumed
     assert err_cold > 20 * max(err_resumed, 1e-7), (err_cold, err_resumed)
     assert np.allclose(resumed.loss_history(), whole.loss_history()[3:], rtol=1e-4, atol=1e-6)
+
+
+def test_periodic_checkpoints_load_back_and_continue_the_run(tmp_path):
+    from orchestra.optimizers import Adam
+
+    xs, ys = _data(n=128, x=32, y=12)
+    model = Sequential([Dense(24, XavierUniform(), ReLU(0.0)), Dense(12, XavierUniform(), Softmax())])
+
+    def run(epochs, **b200):
+        tr = orchestra.all_reduce(["gpu:0"], InlineDataset(xs, ys, 32, 12), Adam(0.01), CrossEntropy(), epochs, 32, seed=4,
+                                  b200={"sync_every": "step", **b200})
+        return orchestrate(model, tr).wait(quiet=True)
+
+    pat = str(tmp_path / "ck_{epoch}.safetensors")
+    whole = run(4, checkpoint_path=pat, checkpoint_every=2)
+    files = sorted(p.name for p in tmp_path.iterdir())
+    assert files == ["ck_2.safetensors", "ck_2.state.safetensors", "ck_4.safetensors", "ck_4.state.safetensors"]
+    from orchestra import _orchestra as core
+
+    last = np.concatenate([np.asarray(t[2]).reshape(-1) for t in sorted(core.load_safetensors(str(tmp_path / "ck_4.safetensors")),
+                                                                       key=lambda t: (int(t[0].split("_")[1].split(".")[0]), t[0].endswith("bias")))])
+    assert np.allclose(last, whole.weights_array(), atol=1e-7)
+    resumed = run(2, init_from=str(tmp_path / "ck_2.safetensors"), init_state_from=str(tmp_path / "ck_2.state.safetensors"))
+    assert np.abs(resumed.weights_array() - whole.weights_array()).max() < 1e-5

@@ -34,3 +34,31 @@ def test_state_of_another_model_is_rejected(tmp_path):
     save_state(str(path), np.zeros(10, np.float32), np.zeros(10, np.float32), np.ones(2, np.float32))
     with pytest.raises(ValueError, match="does not fit"):
         load_state(str(path), 11)
+
+
+def test_weight_checkpoint_writer_matches_the_core_writer(tmp_path):
+    """The Python writer used for periodic checkpoints produces what the core library's exporter produces."""
+    import json
+
+    from orchestra import _orchestra as core
+    from oxidized_neural_orchestra_b200.utils.state import save_tensors, weight_tensors
+
+    model = {"layers": [{"conv": {"input_dim": [1, 8, 8], "kernel_dim": [4, 1, 3], "stride": 1, "padding": 1, "init": "xavier", "act_fn": {"tanh": {"amp": 1.0}}}},
+                        {"max_pooling": {"input_dim": [4, 8, 8], "filter_size": 2, "stride": 2, "padding": 0}},
+                        {"dense": {"output_size": 5, "init": "xavier_uniform", "act_fn": "softmax"}}]}
+    n = 4 * 9 + 4 + 64 * 5 + 5
+    params = np.arange(n, dtype=np.float32) / 7
+    a, b = tmp_path / "core.safetensors", tmp_path / "py.safetensors"
+    try:
+        core.save_safetensors(str(a), json.dumps(model), 64, params)
+    except Exception as exc:      # the model document above must be valid for the core: fail loudly if the schema moved
+        pytest.fail(f"core writer rejected the model: {exc}")
+    layers = [{"kind": "conv", "kernel_dim": [4, 1, 3]}, {"kind": "pool"}, {"kind": "dense", "in": 64, "out": 5}]
+    save_tensors(str(b), weight_tensors(layers, params))
+    ta = {t[0]: (list(t[1]), np.asarray(t[2])) for t in core.load_safetensors(str(a))}
+    tb = {t[0]: (list(t[1]), np.asarray(t[2])) for t in core.load_safetensors(str(b))}
+    assert sorted(ta) == sorted(tb) == sorted(f"layer_{i}.{k}" for i in range(3) for k in ("weight", "bias"))
+    for k in ta:
+        assert ta[k][0] == tb[k][0] and np.array_equal(ta[k][1], tb[k][1]), k
+    with pytest.raises(ValueError, match="covers"):
+        weight_tensors(layers, params[:-1])
