@@ -133,14 +133,14 @@ def build_bins(force: bool = False, sanitize: str | None = None, only: tuple | N
     ``bin/<sanitize>/`` for the host-side race and memory checks of the C++ runtime (control plane, sessions,
     dynamic barrier, codec); the reference runs no sanitizer in CI (.github/workflows/test.yml:29-30)."""
     bindir = BINDIR if sanitize is None else BINDIR / sanitize
-    flags = CXX_FLAGS if sanitize is None else ["-O1", "-g", "-fno-omit-frame-pointer", *CXX_FLAGS[1:], *SANITIZERS[sanitize]]
+    flags = CXX_FLAGS if sanitize is None else ["-O1", "-g1", "-fno-omit-frame-pointer", *CXX_FLAGS[1:], *SANITIZERS[sanitize]]
     cxx = CXX
     if sanitize is not None:
         cxx = sanitizer_cxx(sanitize)
         if cxx is None:
             raise RuntimeError(f"no C++ compiler here links the {sanitize} sanitizer runtime")
     bindir.mkdir(parents=True, exist_ok=True)
-    out = []
+    out, jobs = [], []
     core_srcs = sorted((CSRC / "core").glob("*.cpp")) + sorted((CSRC / "oracle").glob("*.cpp"))
     hdrs = _headers(CSRC / "core", CSRC / "oracle", CSRC / "node", CSRC / "tui")
     for name, sub in (("ono-node", "node"), ("orchestui", "tui"), ("ono-orchestrator", "orch_main")):
@@ -149,9 +149,10 @@ def build_bins(force: bool = False, sanitize: str | None = None, only: tuple | N
             continue
         exe = bindir / name
         if force or any(_newer(s, exe, hdrs) for s in mains + core_srcs):
-            _run([cxx, *flags, "-I", str(CSRC), "-o", str(exe), *map(str, mains),
-                  *map(str, core_srcs), "-ldl"])
+            jobs.append([cxx, *flags, "-I", str(CSRC), "-o", str(exe), *map(str, mains), *map(str, core_srcs), "-ldl"])
         out.append(exe)
+    with cf.ThreadPoolExecutor(max_workers=min(4, os.cpu_count() or 2)) as ex:      # one compiler process per executable
+        list(ex.map(_run, jobs))
     return out
 
 

@@ -23,8 +23,21 @@ def _bins(kind):
     return {p.name: str(p) for p in build.build_bins(sanitize=kind, only=("ono-node", "ono-orchestrator"))}
 
 
+@pytest.fixture(scope="module")
+def _both_built():
+    """Build the address and the thread variants side by side (they are independent compiler runs)."""
+    import concurrent.futures as cf
+
+    from oxidized_neural_orchestra_b200 import build
+
+    kinds = [k for k in ("address", "thread") if build.sanitizer_cxx(k) is not None]
+    with cf.ThreadPoolExecutor(max_workers=2) as ex:
+        list(ex.map(lambda k: build.build_bins(sanitize=k, only=("ono-node", "ono-orchestrator")), kinds))
+    return kinds
+
+
 @pytest.fixture(scope="module", params=["address", "thread"])
-def san(request):
+def san(request, _both_built):
     env = dict(os.environ, ONO_LOG="warn", ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1",
                TSAN_OPTIONS="halt_on_error=0:second_deadlock_stack=1")
     return request.param, _bins(request.param), env
