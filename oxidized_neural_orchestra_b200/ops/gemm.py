@@ -43,7 +43,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          aux: torch.Tensor | None = None, dact: str | None = None, dact_param: float = 0.0,
          relu_quirk: bool = False, alpha: float = 1.0, beta: float = 0.0, bn: int = 0,
          max_ctas: int = 0, split_k: int = 0, pair: int = 0, reduce_out: bool = False, status: torch.Tensor | None = None, stream=None) -> None:
-    """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride."""
+    """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride.
+
+    With ``split_k=0`` the library decides: a shape with a handful of output tiles and a long reduction (e.g. 342 x 128 x
+    3136) is split over the SMs into a library-owned scratch accumulator and finished by a second small kernel that applies
+    the whole epilogue. That scratch is one buffer per process, so such GEMMs must be issued on one stream (or otherwise
+    not overlap on the device); pass ``split_k=1`` to keep a call on the single-pass path."""
     if not a.is_cuda:
         raise RuntimeError("ono gemm needs CUDA tensors (there is no CPU fallback on this path)")
     lib = _lib.load()
