@@ -14,35 +14,11 @@
 #include <string.h>
 
 #include "ono_kernels.h"
+#include "opt.cuh"
 #include "ptx.cuh"
 
 namespace ono {
 void set_error(const char* fmt, const char* a, long long b, long long c);
-
-struct OptScal {
-  int kind;
-  float lr, mu, b1, b2, eps, gs, adam_step;
-};
-
-__device__ __forceinline__ float opt_apply(const OptScal& s, float p, float g, float& m, float& v) {
-  g *= s.gs;
-  if (s.kind == 0) return p - s.lr * g;
-  if (s.kind == 1) {
-    m = s.mu * m + g;
-    return p - s.lr * m;
-  }
-  m = s.b1 * m + (1.0f - s.b1) * g;
-  v = s.b2 * v + (1.0f - s.b2) * g * g;
-  return p - s.adam_step * m / (sqrtf(v) + s.eps);
-}
-
-__device__ __forceinline__ uint2 pack_bf16x4(float4 p) {
-  __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
-  uint2 pk;
-  pk.x = *reinterpret_cast<uint32_t*>(&lo);
-  pk.y = *reinterpret_cast<uint32_t*>(&hi);
-  return pk;
-}
 
 // Barrier between block `blk` of every member rank. Thread t (< nranks) talks to rank t.
 __device__ __forceinline__ bool rank_barrier(unsigned int* const* flags, int nranks, int rank, int blk,
@@ -94,7 +70,20 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
           const long long i4 = base + (long long)u * blockDim.x;
           g[u] = p[u] = m[u] = v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
           if (i4 >= e4) continue;
-          if (a.algo == 1) {
+          if (a.g_dtype != 0) {
+            // 16-bit gradient wire (bf16 or f16): four values per 8-byte load, summed in f32 in rank order
+            if (a.algo == 1) {
+              g[u] = unpack16x4(multimem_ld_reduce_add_16x4(reinterpret_cast<const uint2*>(a.g_mc) + i4, a.g_dtype == 2),
+                                a.g_dtype == 2);
+            } else {
+#pragma unroll
+              for (int q = 0; q < ONO_MAX_RANKS; ++q)
+                if (q < a.nranks && ((workers >> q) & 1u)) {
+                  const float4 x = unpack16x4(ld_relaxed_sys_v2(reinterpret_cast<const uint2*>(a.g[q]) + i4), a.g_dtype == 2);
+                  g[u].x += x.x; g[u].y += x.y; g[u].z += x.z; g[u].w += x.w;
+                }
+            }
+          } else if (a.algo == 1) {
             g[u] = multimem_ld_reduce_add_v4(reinterpret_cast<const float4*>(a.g_mc) + i4);
           } else {
 #pragma unroll
@@ -145,8 +134,10 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
               if (q < a.nranks && a.p_out_bf16[q])
                 *(reinterpret_cast<uint2*>(a.p_out_bf16[q]) + i4) = pb;
           }
-          if (a.zero_grad && ((workers >> rank) & 1u))
-            *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (a.zero_grad && ((workers >> rank) & 1u)) {
+            if (a.g_dtype != 0) *(reinterpret_cast<uint2*>(const_cast<float*>(a.g[rank])) + i4) = make_uint2(0u, 0u);
+            else *(reinterpret_cast<float4*>(const_cast<float*>(a.g[rank])) + i4) = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
         }
       }
     }
@@ -401,6 +392,7 @@ static int validate_sync(const OnoSync* s) {
     return -1;
   }
   if (s->algo == 1 && !s->g_mc) { set_error("NVLS needs multicast addresses%s", "", 0, 0); return -1; }
+  if (s->g_dtype < 0 || s->g_dtype > 2) { set_error("g_dtype must be 0 (f32), 1 (bf16) or 2 (f16)%s", "", 0, 0); return -1; }
   return 0;
 }
 
@@ -640,6 +632,11 @@ extern "C" int ono_sync_step_noalloc(const OnoNoAllocStep* s, ono_stream_t st) {
     set_error("buffers must be 16-byte aligned%s", "", 0, 0);
     return -1;
   }
+  if (((uintptr_t)s->p_bf16 & 7) || ((uintptr_t)s->sumsq & 7) || ((uintptr_t)s->adam_pows & 3) || ((uintptr_t)s->status & 3)) {
+    set_error("p_bf16 and sumsq must be 8-byte aligned, adam_pows and status 4-byte aligned%s", "", 0, 0);
+    return -1;
+  }
+  if (s->n % 4 != 0) { set_error("n must be padded to a multiple of 4 elements%s", "", 0, 0); return -1; }
   if (s->nblocks > ONO_NOALLOC_MAX_BLOCKS) {
     set_error("nblocks %s%lld exceeds the built-in scratch (max %lld blocks)", "", (long long)s->nblocks,
               (long long)ONO_NOALLOC_MAX_BLOCKS);

@@ -12,6 +12,7 @@
 #include "../core/philox.h"
 #include "act.cuh"
 #include "ono_kernels.h"
+#include "opt.cuh"
 
 namespace ono {
 void set_error(const char* fmt, const char* a, long long b, long long c);
@@ -356,6 +357,31 @@ __global__ void push_add_kernel(const float* src, float* dst, long long n) {
     atomicAdd(dst + i, src[i]);   // result unused: compiled to a reduction that needs no reply
 }
 }  // namespace ono
+
+namespace ono {
+__global__ void cast16_kernel(const float* src, uint16_t* dst, long long n, int f16, int vec) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n4 = vec ? n >> 2 : 0;
+  for (long long i = tid; i < n4; i += stride) {
+    const float4 x = __ldcs(reinterpret_cast<const float4*>(src) + i);
+    *(reinterpret_cast<uint2*>(dst) + i) = make_uint2(pack16x2(x.x, x.y, f16), pack16x2(x.z, x.w, f16));
+  }
+  for (long long i = (n4 << 2) + tid; i < n; i += stride) {
+    const uint32_t w = pack16x2(src[i], 0.0f, f16);
+    dst[i] = (uint16_t)(w & 0xffffu);
+  }
+}
+}  // namespace ono
+
+extern "C" int ono_cast16(const float* src, void* dst, long long n, int f16, ono_stream_t st) {
+  if (!src || !dst || n < 0) { set_error("bad cast16 args%s", "", 0, 0); return -1; }
+  if (((uintptr_t)dst & 1) != 0) { set_error("cast16 destination must be 2-byte aligned%s", "", 0, 0); return -1; }
+  if (n == 0) return 0;
+  const int vec = (((uintptr_t)src & 15) == 0 && ((uintptr_t)dst & 7) == 0) ? 1 : 0;
+  ono::cast16_kernel<<<grid_for(n, 256, 8), 256, 0, (cudaStream_t)st>>>(src, (uint16_t*)dst, n, f16 ? 1 : 0, vec);
+  return launch_ok("cast16");
+}
 
 extern "C" int ono_push_add(const float* src, float* dst, long long n, ono_stream_t st) {
   if (!src || !dst || n < 0) { set_error("bad push_add args%s", "", 0, 0); return -1; }

@@ -25,6 +25,7 @@
 
 #include "act.cuh"
 #include "ono_kernels.h"
+#include "opt.cuh"
 #include "ptx.cuh"
 
 namespace ono {
@@ -48,8 +49,12 @@ struct GemmDev {
   OnoEpilogue epi;
   int* status;
   unsigned long long timeout_ns;
-  int split_k;  // > 1: K is split over that many work items per tile, partials added with atomics
+  int split_k;  // > 1: K is split over that many work items per tile; split s writes its partial product to slab s of `slabs`
   int tma_out;  // 0: thread stores only; 1: out_f32 leaves through a TMA store; 2: out_bf16 does; 3: out_f32 += through TMA reduce-add
+  float* slabs;            // split-K partial products: [split_k][M][slab_ld] f32
+  long long slab_elems;    // M * slab_ld
+  int slab_ld;
+  OnoApply apply;          // optimizer applied to the result tile in the epilogue (apply.p != nullptr)
 };
 
 template <int BN>
@@ -180,16 +185,15 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
         uint4 pk;
-        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-        __nv_bfloat162 t1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-        __nv_bfloat162 t3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-        pk.x = *reinterpret_cast<uint32_t*>(&t0);
-        pk.y = *reinterpret_cast<uint32_t*>(&t1);
-        pk.z = *reinterpret_cast<uint32_t*>(&t2);
-        pk.w = *reinterpret_cast<uint32_t*>(&t3);
+        pk.x = pack16x2(v[j], v[j + 1], e.out16_f16);
+        pk.y = pack16x2(v[j + 2], v[j + 3], e.out16_f16);
+        pk.z = pack16x2(v[j + 4], v[j + 5], e.out16_f16);
+        pk.w = pack16x2(v[j + 6], v[j + 7], e.out16_f16);
         *reinterpret_cast<uint4*>(o + j) = pk;
       }
+    } else if (e.out16_f16) {
+      __half* oh = reinterpret_cast<__half*>(o);
+      ONO_TAIL_LOOP(j) oh[j] = __float2half_rn(v[j]);
     } else {
       ONO_TAIL_LOOP(j) o[j] = __float2bfloat16_rn(v[j]);
     }
@@ -430,13 +434,59 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         if (SPLITS > 1) {
-          // partial product of one K range: accumulate into the (pre-zeroed) f32 output
-          if (m < p.M && p.epi.out_f32) {
-            float* o = p.epi.out_f32 + (size_t)m * p.epi.ld_out + nc;
-            const int ncols = min(32, p.N - nc);
+          // partial product of one K range: plain stores into this split's own slab; the finishing pass adds the
+          // slabs in split order, so the sum does not depend on which CTA finished first
+          if (m < p.M) {
+            float* o = p.slabs + (size_t)(work % SPLITS) * p.slab_elems + (size_t)m * p.slab_ld + nc;
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) atomicAdd(o + j, v[j] * p.epi.alpha);
+            for (int j = 0; j < 32; j += 4)
+              if (nc + j < p.slab_ld) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          }
+          continue;
+        }
+        if (p.apply.p) {
+          // Optimizer in the epilogue. The warp stages its 32 x 32 tile of dW, then walks the tile so that eight
+          // lanes cover one 128-byte row segment: every access to the master, the state and the shadow is a full line.
+          __syncwarp();                       // the previous chunk's reads of the staging tile are done
+          {
+            uint8_t* rp = wstage + lane * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<float4*>(rp + ((j ^ (lane & 7)) << 4)) =
+                  make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
+          __syncwarp();
+          const OnoApply& ap = p.apply;
+          OptScal os{ap.kind, ap.lr, ap.mu, ap.b1, ap.b2, ap.eps, ap.grad_scale, 0.0f};
+          if (ap.kind == 2) os.adam_step = ap.lr * sqrtf(1.0f - __ldg(ap.adam_pows + 1)) / (1.0f - __ldg(ap.adam_pows));
+          const int c4 = lane & 7, rsub = lane >> 3;
+          const int col = nc + c4 * 4;
+          const int mbase = m0 + quad * 32 + rsub;
+          float4 P[8], Mo[8], Vo[8];
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int mr = mbase + it * 4;
+            P[it] = Mo[it] = Vo[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col < p.N && mr < p.M) {
+              const size_t off = (size_t)mr * ap.ld + col;
+              P[it] = __ldcs(reinterpret_cast<const float4*>(ap.p + off));
+              if (ap.kind >= 1) Mo[it] = __ldcs(reinterpret_cast<const float4*>(ap.m + off));
+              if (ap.kind == 2) Vo[it] = __ldcs(reinterpret_cast<const float4*>(ap.v + off));
+            }
+          }
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + rsub;
+            const int mr = mbase + it * 4;
+            if (col < p.N && mr < p.M) {
+              const size_t off = (size_t)mr * ap.ld + col;
+              const float4 g = *reinterpret_cast<const float4*>(wstage + r * 128 + ((c4 ^ (r & 7)) << 4));
+              const float4 pp = opt_apply4(os, P[it], g, Mo[it], Vo[it]);
+              __stcs(reinterpret_cast<float4*>(ap.p + off), pp);
+              if (ap.kind >= 1) __stcs(reinterpret_cast<float4*>(ap.m + off), Mo[it]);
+              if (ap.kind == 2) __stcs(reinterpret_cast<float4*>(ap.v + off), Vo[it]);
+              if (ap.p_bf16) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(ap.p_bf16) + off) = pack_bf16x4(pp);
+            }
           }
           continue;
         }
@@ -456,15 +506,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             uint8_t* rp = wstage + lane * 64;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-              __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-              __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
               uint4 pk;
-              pk.x = *reinterpret_cast<uint32_t*>(&t0);
-              pk.y = *reinterpret_cast<uint32_t*>(&t1);
-              pk.z = *reinterpret_cast<uint32_t*>(&t2);
-              pk.w = *reinterpret_cast<uint32_t*>(&t3);
+              pk.x = pack16x2(v[8 * j], v[8 * j + 1], p.epi.out16_f16);
+              pk.y = pack16x2(v[8 * j + 2], v[8 * j + 3], p.epi.out16_f16);
+              pk.z = pack16x2(v[8 * j + 4], v[8 * j + 5], p.epi.out16_f16);
+              pk.w = pack16x2(v[8 * j + 6], v[8 * j + 7], p.epi.out16_f16);
               *reinterpret_cast<uint4*>(rp + ((j ^ ((row >> 1) & 3)) << 4)) = pk;
             }
           }
@@ -495,31 +541,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-// Two-pass form for problems with a handful of output tiles and a long reduction (e.g. 342 x 128 x 3136: three tiles,
-// i.e. three SMs streaming 98 k-blocks each): the reduction is split over the SMs into a scratch accumulator with
-// atomic adds, then this pass runs the regular epilogue (bias, activation, derivative, every output form) on the sums.
-// The scratch is one static buffer: such GEMMs must not overlap on the device (one compute stream).
-constexpr long long SPLIT_SCRATCH_ELEMS = 1ll << 20;
+// Two-pass form (split-K). Used for problems with a handful of output tiles and a long reduction (e.g. 342 x 128 x 3136:
+// three tiles, i.e. three SMs streaming 98 k-blocks each) and whenever the caller asks for a split: the reduction is
+// split over the SMs, split s stores its partial product into slab s of a workspace, and this pass adds the slabs in
+// split order and runs the regular epilogue (bias, activation, derivative, every output form) on the sums. The result
+// is the same to the bit from run to run. The workspace comes from the caller (OnoGemm::workspace, e.g. one per
+// stream); without one a static buffer is used, and such GEMMs must then not overlap on the device.
+constexpr long long SPLIT_SCRATCH_ELEMS = 4ll << 20;
 __device__ float g_split_scratch[SPLIT_SCRATCH_ELEMS];
 
-__global__ void __launch_bounds__(128) gemm_finish_kernel(const float* scratch, int ld, int M, int N, const OnoEpilogue e) {
+__global__ void __launch_bounds__(128) gemm_finish_kernel(const float* slabs, long long slab_elems, int nslabs, int ld, int M,
+                                                          int N, const OnoEpilogue e) {
   const int m = blockIdx.x * 128 + threadIdx.x;
   const int n0 = blockIdx.y * 32;
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = 0.f;
   if (m < M) {
-    const float* src = scratch + (size_t)m * ld + n0;
-    if (n0 + 32 <= ld) {
+    for (int sidx = 0; sidx < nslabs; ++sidx) {
+      const float* src = slabs + (size_t)sidx * slab_elems + (size_t)m * ld + n0;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float4 q = *reinterpret_cast<const float4*>(src + j);
-        v[j] = q.x; v[j + 1] = q.y; v[j + 2] = q.z; v[j + 3] = q.w;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (n0 + j < ld) v[j] = src[j];
+      for (int j = 0; j < 32; j += 4)
+        if (n0 + j < ld) {
+          const float4 q = __ldcs(reinterpret_cast<const float4*>(src + j));
+          v[j] += q.x; v[j + 1] += q.y; v[j + 2] += q.z; v[j + 3] += q.w;
+        }
     }
   }
   epilogue_chunk(e, v, m, n0, M, N, 0);
@@ -631,15 +677,21 @@ static int make_operand(OperandDev* od, CUtensorMap* map, const void* ptr, int e
   return encode_map_2d(map, ptr, esize, K, MN, ld, chunk, BK);
 }
 
-static int g_num_sms = 0;
+// cudaFuncSetAttribute, symbol addresses and SM counts belong to a device: caches are kept per device.
+constexpr int kMaxDevices = 64;
+static int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  return dev;
+}
 static int num_sms() {
-  if (g_num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
-    if (g_num_sms <= 0) g_num_sms = 148;
+  static int sms[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (sms[dev] == 0) {
+    cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (sms[dev] <= 0) sms[dev] = 148;
   }
-  return g_num_sms;
+  return sms[dev];
 }
 
 template <int ESIZE, int BN, bool PAIR>
@@ -648,8 +700,11 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   constexpr int BN_CTA = PAIR ? BN / 2 : BN;
   constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
   constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN_CTA * 128) + 2 * 16384 + 1024;
-  static bool attr_set = false;
-  static int max_pairs = 0;
+  static bool attr_done[kMaxDevices] = {false};
+  static int max_pairs_dev[kMaxDevices] = {0};
+  const int dev = current_device();
+  bool& attr_set = attr_done[dev];
+  int& max_pairs = max_pairs_dev[dev];
   auto kern = gemm_tcgen05_kernel<ESIZE, BN, PAIR>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -746,72 +801,85 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   const bool pair = g->pair > 0 && bn >= 128 && g->M > 128;
   rc = make_operand(&p.b, &tb, g->B, esize, g->b_major, g->N, g->K, g->ldb, pair ? bn / 2 : bn);
   if (rc) return rc;
+  // Optimizer in the epilogue: the result tile updates the master / state tiles and is not stored.
+  const OnoApply& ap = g->apply;
+  if (ap.p) {
+    if (e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || e.bias || e.bias_bf16 ||
+        e.act != ACT_NONE || e.dact != ACT_NONE || e.reduce_out) {
+      set_error("apply: the epilogue optimizer excludes every other output%s", "");
+      return -1;
+    }
+    if (ap.kind < 0 || ap.kind > 2 || (ap.kind >= 1 && !ap.m) || (ap.kind == 2 && (!ap.v || !ap.adam_pows))) {
+      set_error("apply: optimizer kind or state missing%s", "");
+      return -1;
+    }
+    if (g->N % 4 != 0 || ap.ld % 4 != 0 || ap.ld < g->N || (((uintptr_t)ap.p | (uintptr_t)ap.m | (uintptr_t)ap.v) & 15) ||
+        ((uintptr_t)ap.p_bf16 & 7)) {
+      set_error("apply: N and ld must be multiples of 4 and the matrices 16-byte aligned%s", "");
+      return -1;
+    }
+    if (g->split_k > 1) { set_error("apply: split-K is not supported%s", ""); return -1; }
+    p.apply = ap;
+  }
+  // split-K (g->split_k > 1, or 0 = automatic for long-K problems with few output tiles): see gemm_finish_kernel.
   bool two_pass = false;
-  int scratch_ld = 0;
-  float* scratch = nullptr;
-  // split-K (g->split_k > 1, or 0 = automatic for tall-K problems with few output tiles): only the
-  // plain accumulate-into-f32 epilogue is supported, and the caller zeroes the output first.
   {
     const int BKe = 128 / esize;
     const int KBh = (g->K + BKe - 1) / BKe;
-    const long long tiles0 = (long long)((g->M + 127) / 128) * ((g->N + bn - 1) / bn);
-    int sk = g->split_k;
-    if (sk > KBh) sk = KBh;
-    if (sk > 1) {
-      const int per = (KBh + sk - 1) / sk;
-      sk = (KBh + per - 1) / per;  // no empty split
-      if (!e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || e.bias || e.bias_bf16 ||
-          e.act != ACT_NONE || e.dact != ACT_NONE || e.beta != 0.0f) {
-        set_error("split-K supports a plain f32 output only%s", "");
+    const long long tiles0 = (long long)((g->M + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((g->N + bn - 1) / bn);
+    const long long ldn = ((long long)g->N + 3) / 4 * 4;
+    int want = g->split_k > 1 ? g->split_k : 0;
+    if (g->split_k == 0 && !ap.p && !e.reduce_out && !pair && tiles0 * 8 <= num_sms() && KBh >= 32)
+      want = (int)std::min<long long>(KBh / 4, num_sms() / tiles0);
+    if (want > KBh) want = KBh;
+    if (want >= 2) {
+      if (e.reduce_out) { set_error("split-K cannot be combined with reduce_out%s", ""); return -1; }
+      float* ws = g->workspace;
+      long long ws_elems = g->workspace_elems;
+      if (!ws) {
+        static float* scratch_dev[kMaxDevices] = {nullptr};
+        float*& sp = scratch_dev[current_device()];
+        if (!sp && cudaGetSymbolAddress((void**)&sp, g_split_scratch) != cudaSuccess) {
+          set_error("split scratch address unavailable%s", "");
+          return -6;
+        }
+        ws = sp;
+        ws_elems = SPLIT_SCRATCH_ELEMS;
+      } else if (((uintptr_t)ws & 15) != 0) {
+        set_error("split-K workspace must be 16-byte aligned%s", "");
+        return -1;
+      }
+      const long long slab = (long long)g->M * ldn;
+      if (want > ws_elems / slab) want = (int)(ws_elems / slab);   // as many slabs as the workspace holds
+      if (want >= 2) {
+        const int per = (KBh + want - 1) / want;
+        p.split_k = (KBh + per - 1) / per;                         // no empty split
+        p.slabs = ws;
+        p.slab_elems = slab;
+        p.slab_ld = (int)ldn;
+        two_pass = p.split_k > 1;
+      } else if (g->split_k > 1 && slab > ws_elems) {
+        set_error("split-K workspace too small for one slab (%s%lld elements needed)", "", slab);
         return -1;
       }
     }
-    p.split_k = sk > 1 ? sk : 1;
-    // automatic two-pass split (see gemm_finish_kernel)
-    const long long ldn = ((long long)g->N + 3) / 4 * 4;
-    if (g->split_k == 0 && !e.reduce_out && !pair && tiles0 * 8 <= num_sms() && KBh >= 32 && (long long)g->M * ldn <= SPLIT_SCRATCH_ELEMS) {
-      int want = std::min<long long>(KBh / 4, num_sms() / tiles0);
-      if (want >= 2) {
-        const int per = (KBh + want - 1) / want;
-        p.split_k = (KBh + per - 1) / per;
-        two_pass = true;
-        scratch_ld = (int)ldn;
-      }
-    }
-  }
-  if (two_pass) {
-    static float* scratch_ptr = nullptr;
-    if (!scratch_ptr && cudaGetSymbolAddress((void**)&scratch_ptr, g_split_scratch) != cudaSuccess) {
-      set_error("split scratch address unavailable%s", "");
-      return -6;
-    }
-    if (cudaMemsetAsync(scratch_ptr, 0, (size_t)g->M * scratch_ld * sizeof(float), stream) != cudaSuccess) {
-      set_error("split scratch memset failed%s", "");
-      return -6;
-    }
-    memset(&p.epi, 0, sizeof(p.epi));
-    p.epi.out_f32 = scratch_ptr;
-    p.epi.ld_out = scratch_ld;
-    p.epi.alpha = 1.0f;
-    scratch = scratch_ptr;
+    if (!two_pass) p.split_k = 1;
   }
   // One row-major output may leave through TMA stores (coalesced, off the LSU path): the f32 output
-  // when it is not accumulated into, else the bf16 output.
+  // when it is not accumulated into, else the 16-bit output.
   CUtensorMap tc;
   memset(&tc, 0, sizeof(tc));
   p.tma_out = 0;
-  if (two_pass) {
-    // atomics into the scratch, no TMA store
+  if (two_pass || ap.p) {
+    // plain stores into the slabs / updates in place, no TMA store
   } else if (e.reduce_out) {
-    if (p.split_k > 1 || !e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || ((uintptr_t)e.out_f32 & 15)) {
+    if (!e.out_f32 || e.out_bf16 || e.outT_f32 || e.outT_bf16 || e.pre_f32 || e.pre_bf16 || ((uintptr_t)e.out_f32 & 15)) {
       set_error("reduce_out supports a plain, 16-byte aligned f32 output only%s", "");
       return -1;
     }
     rc = encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out);
     if (rc) return rc;
     p.tma_out = 3;
-  } else if (p.split_k > 1) {
-    // atomics path, no TMA store
   } else if (e.out_f32 && e.beta == 0.0f && ((uintptr_t)e.out_f32 & 15) == 0 && g->N % 4 == 0) {
     if (encode_out_map(&tc, e.out_f32, 4, g->M, g->N, e.ld_out) == 0) p.tma_out = 1;
   } else if (e.out_bf16 && ((uintptr_t)e.out_bf16 & 15) == 0 && g->N % 8 == 0) {
@@ -843,7 +911,7 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   rc = run();
   if (rc || !two_pass) return rc;
   const dim3 fgrid((g->M + 127) / 128, (g->N + 31) / 32);
-  gemm_finish_kernel<<<fgrid, 128, 0, stream>>>(scratch, scratch_ld, g->M, g->N, g->epi);
+  gemm_finish_kernel<<<fgrid, 128, 0, stream>>>(p.slabs, p.slab_elems, p.split_k, p.slab_ld, g->M, g->N, g->epi);
   if (cudaGetLastError() != cudaSuccess) { set_error("gemm_finish launch failed%s", ""); return -7; }
   return 0;
 }

@@ -41,7 +41,23 @@ typedef struct OnoEpilogue {
   float alpha, beta;
   int reduce_out;            // out_f32 += result through TMA reduce-add (out_f32 may be a peer GPU's memory: the GEMM pushes its
                              // tiles into the owner's accumulator over NVLink); plain f32 output only, beta ignored
+  int out16_f16;             // 1: out_bf16 receives IEEE f16 values instead of bf16 (a 16-bit gradient wire in either format);
+                             //    out_bf16 may be a peer GPU's memory: the tiles leave through TMA stores over NVLink
 } OnoEpilogue;
+
+// Optimizer step applied by the weight-gradient GEMM's own epilogue, for a layer that one rank owns outright: the
+// tile of dW is never written to memory. The epilogue reads the matching tile of the f32 master and of the optimizer
+// state, updates them in place and writes the bf16 shadow (optional). p, m, v and p_bf16 are [M, ld] matrices with the
+// geometry of the GEMM result; ld and N must be multiples of 4 and the pointers 16-byte aligned (p_bf16: 8).
+// p == NULL switches it off. No other output and no bias / activation may be requested together with it.
+typedef struct OnoApply {
+  float* p; float* m; float* v; void* p_bf16;
+  int ld;
+  int kind;                  // OnoOptim kinds: 0 SGD, 1 momentum, 2 Adam
+  float lr, mu, b1, b2, eps;
+  float grad_scale;          // the gradient is multiplied by this first
+  const float* adam_pows;    // device float[2] = {b1^t, b2^t} after this step's tick (Adam)
+} OnoApply;
 
 // D[M,N] = A[M,K] * B[K,N] with f32 accumulation in TMEM.
 //   A: a_major == K_MAJOR  -> memory is [M, lda] with K contiguous
@@ -58,11 +74,15 @@ typedef struct OnoGemm {
   int a_major, b_major;
   int bn;          // tile N: 0 = auto, else 32 / 128 / 256
   int max_ctas;    // 0 = one per SM
-  int split_k;     // > 1: split K over that many CTAs per tile; out_f32 must be zero on entry and is
-                   //      accumulated with atomics (plain f32 output only). 0 / 1 = off
+  int split_k;     // > 1: split K over (at most) that many work items per tile, each storing its partial product into its
+                   //      own slab of the workspace; a finishing pass adds the slabs in order and runs the whole epilogue
+                   //      (run-to-run deterministic). 0 = the library decides, 1 = never split
   int pair;        // CTA pairs (256-row tiles, tcgen05 cta_group::2): 0 = automatic, 1 = on, -1 = off
   OnoEpilogue epi;
   int* status;     // device int, set non-zero on an in-kernel timeout; may be null
+  OnoApply apply;  // optimizer fused into the epilogue (apply.p == NULL: off)
+  float* workspace;           // split-K slabs, 16-byte aligned; NULL = a static buffer of the library, which GEMMs that overlap
+  long long workspace_elems;  // on the device would share: give each stream its own workspace. Size in floats.
 } OnoGemm;
 
 int ono_gemm(const OnoGemm* g, ono_stream_t stream);
@@ -210,6 +230,8 @@ typedef struct OnoSync {
   int kind; float lr, mu, b1, b2, eps;       // optimizer (OnoOptim kinds)
   int divide;                                // 1: scale by 1/n_workers (0 reproduces WildStore)
   int zero_grad;                             // 1: owners zero the summed gradient ranges afterwards
+  int g_dtype;                               // element type of the g windows: 0 f32, 1 bf16, 2 f16 (16-bit gradient wire:
+                                             // g[q] and g_mc then address 2-byte elements with the same indices)
   unsigned long long timeout_ns;
   OnoSyncLocal loc[ONO_MAX_RANKS];           // a real launch reads loc[rank] only
 } OnoSync;
@@ -273,6 +295,9 @@ int ono_stage_signal(unsigned int* const* flags, int nranks, int rank, int bucke
 int ono_stage_tick(unsigned int* step, ono_stream_t stream);
 // dst[i] += src[i] with reductions that need no reply (dst may be a peer GPU's memory).
 int ono_push_add(const float* src, float* dst, long long n, ono_stream_t stream);
+// dst[i] = 16-bit float of src[i] (bf16, or f16 when f16 != 0); dst may be a peer GPU's memory (the 16-bit gradient
+// wire for values that do not leave through a GEMM epilogue: bias gradients, unaligned layers, convolution kernels).
+int ono_cast16(const float* src, void* dst, long long n, int f16, ono_stream_t stream);
 // Flag ping-pong between two GPUs (node/src/stat_service.rs:107-152 rebuilt as a device probe).
 // role 0 pings, role 1 answers; rtt_ns[rounds] is written by role 0.
 int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base_epoch,

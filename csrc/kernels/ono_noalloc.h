@@ -41,13 +41,13 @@ typedef struct OnoNoAllocStep {
   const float* g;          // [n] gradient
   float* m;                // [n] first-moment / velocity state (momentum, Adam), else null
   float* v;                // [n] second-moment state (Adam), else null
-  void* p_bf16;            // optional [n] bf16 copy of the updated parameters
-  long long n;             // element count; buffers must be 16-byte aligned and padded to 4 elements
+  void* p_bf16;            // optional [n] bf16 copy of the updated parameters, 8-byte aligned
+  long long n;             // element count, a multiple of 4 (pad the buffers); p, g, m, v 16-byte aligned
   int kind;                // 0 SGD, 1 momentum, 2 Adam
   float lr, mu, b1, b2, eps;
   int n_workers;           // the gradient is divided by this first (values below 1 mean 1)
   const float* adam_pows;  // device float[2] = {b1^t, b2^t} for this step (Adam only)
-  double* sumsq;           // optional device double, += sum of squares of the scaled gradient
+  double* sumsq;           // optional device double (8-byte aligned), += sum of squares of the scaled gradient
   int* status;             // optional device int, set non-zero if an in-kernel wait gave up
   int nblocks;             // 0 = choose; at most ONO_NOALLOC_MAX_BLOCKS
 } OnoNoAllocStep;

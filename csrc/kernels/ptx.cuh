@@ -347,6 +347,23 @@ __device__ __forceinline__ float4 ld_global_v4_volatile(const float4* p) {
                : "memory");
   return v;
 }
+// Four 16-bit values (two packed 32-bit words) from memory another GPU may have written.
+__device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// NVLS: the sum over every GPU of four 16-bit floats (bf16, or f16), accumulated in f32 inside the switch.
+__device__ __forceinline__ uint2 multimem_ld_reduce_add_16x4(const uint2* mc_ptr, int f16) {
+  uint2 v;
+  if (f16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.f16x2 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y) : "l"(mc_ptr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v2.bf16x2 {%0,%1}, [%2];"
+                 : "=r"(v.x), "=r"(v.y) : "l"(mc_ptr) : "memory");
+  return v;
+}
 // NVLS: one load that returns the sum over every GPU bound to the multicast address.
 __device__ __forceinline__ float4 multimem_ld_reduce_add_v4(const float4* mc_ptr) {
   float4 v;

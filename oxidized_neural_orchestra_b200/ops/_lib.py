@@ -20,6 +20,15 @@ class OnoEpilogue(C.Structure):
         ("ld_out", C.c_int), ("ld_outT", C.c_int), ("ld_aux", C.c_int),
         ("act", C.c_int), ("act_param", C.c_float), ("dact", C.c_int), ("dact_param", C.c_float),
         ("relu_quirk", C.c_int), ("alpha", C.c_float), ("beta", C.c_float), ("reduce_out", C.c_int),
+        ("out16_f16", C.c_int),
+    ]
+
+
+class OnoApply(C.Structure):
+    _fields_ = [
+        ("p", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p), ("p_bf16", C.c_void_p), ("ld", C.c_int),
+        ("kind", C.c_int), ("lr", C.c_float), ("mu", C.c_float), ("b1", C.c_float), ("b2", C.c_float),
+        ("eps", C.c_float), ("grad_scale", C.c_float), ("adam_pows", C.c_void_p),
     ]
 
 
@@ -28,7 +37,7 @@ class OnoGemm(C.Structure):
         ("A", C.c_void_p), ("B", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
         ("lda", C.c_int), ("ldb", C.c_int), ("dtype", C.c_int), ("a_major", C.c_int),
         ("b_major", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int), ("split_k", C.c_int), ("pair", C.c_int), ("epi", OnoEpilogue),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("apply", OnoApply), ("workspace", C.c_void_p), ("workspace_elems", C.c_longlong),
     ]
 
 
@@ -68,6 +77,7 @@ def _declare(lib) -> None:
         "ono_ring_allreduce": [C.POINTER(OnoRing), vp],
         "ono_pingpong": [ci, vp, vp, ci, C.c_uint, vp, vp, vp],
         "ono_push_add": [vp, vp, ll, vp],
+        "ono_cast16": [vp, vp, ll, ci, vp],
         "ono_stage_pull": [C.POINTER(OnoStagePull), vp],
         "ono_stage_signal": [C.POINTER(vp), ci, ci, ci, vp, vp],
         "ono_stage_tick": [vp, vp],
@@ -172,7 +182,7 @@ class OnoSync(C.Structure):
         ("n_workers", C.c_int),
         ("kind", C.c_int), ("lr", C.c_float), ("mu", C.c_float), ("b1", C.c_float), ("b2", C.c_float),
         ("eps", C.c_float),
-        ("divide", C.c_int), ("zero_grad", C.c_int), ("timeout_ns", C.c_ulonglong),
+        ("divide", C.c_int), ("zero_grad", C.c_int), ("g_dtype", C.c_int), ("timeout_ns", C.c_ulonglong),
         ("loc", OnoSyncLocal * MAX_RANKS),
     ]
 

@@ -34,6 +34,23 @@ DEFAULT_MAX_CTAS = 0
 # from the short-K weight-gradient GEMMs), single CTAs for tf32 tiles; "1": wherever the shape allows; "0": never.
 DEFAULT_PAIR = __import__("os").environ.get("ONO_GEMM_PAIR", "auto")
 
+# Split-K workspaces, one per (device, stream): GEMMs on different streams may overlap on the device, so each stream
+# gets its own slabs. 8 Mi floats hold e.g. 148 slabs of a 64 x 576 weight gradient or 49 of a 342 x 128 product.
+WORKSPACE_ELEMS = 8 << 20
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, stream) -> torch.Tensor | None:
+    s = stream if stream is not None else torch.cuda.current_stream(device)
+    key = (device.index, s.cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None      # never allocate inside a capture; the library's static buffer serves this call
+        ws = torch.empty(WORKSPACE_ELEMS, dtype=torch.float32, device=device)
+        _workspaces[key] = ws
+    return ws
+
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_major: bool = False,
          out: torch.Tensor | None = None, out_t: torch.Tensor | None = None,
@@ -42,18 +59,30 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          act: str | None = None, act_param: float = 0.0,
          aux: torch.Tensor | None = None, dact: str | None = None, dact_param: float = 0.0,
          relu_quirk: bool = False, alpha: float = 1.0, beta: float = 0.0, bn: int = 0,
-         max_ctas: int = 0, split_k: int = 0, pair: int = 0, reduce_out: bool = False, status: torch.Tensor | None = None, stream=None) -> None:
+         max_ctas: int = 0, split_k: int = 0, pair: int = 0, reduce_out: bool = False, out_f16: torch.Tensor | None = None,
+         apply: dict | None = None, status: torch.Tensor | None = None, stream=None) -> None:
     """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride.
 
-    With ``split_k=0`` the library decides: a shape with a handful of output tiles and a long reduction (e.g. 342 x 128 x
-    3136) is split over the SMs into a library-owned scratch accumulator and finished by a second small kernel that applies
-    the whole epilogue. That scratch is one buffer per process, so such GEMMs must be issued on one stream (or otherwise
-    not overlap on the device); pass ``split_k=1`` to keep a call on the single-pass path."""
+    ``split_k``: 0 lets the library decide (a shape with a handful of output tiles and a long reduction, e.g. 342 x 128 x
+    3136, is split over the SMs), ``> 1`` asks for that many splits, 1 keeps the call single-pass. Every split stores its
+    partial product into its own slab of a per-stream workspace and a small finishing kernel adds the slabs in order and
+    applies the whole epilogue, so the result is the same to the bit from run to run.
+
+    ``out_f16``: like ``out_bf16`` but the values are IEEE f16 (a 16-bit gradient wire in the reference's format). Either
+    16-bit output may be a view of a peer GPU's window: aligned tiles then leave through TMA stores over NVLink.
+
+    ``apply``: optimizer applied by the epilogue to the tile it has just computed (the weight gradient of a layer this
+    rank owns outright), which is then never written to memory: ``dict(p=, m=, v=, p_bf16=, kind=, lr=, mu=, b1=, b2=,
+    eps=, grad_scale=, adam_pows=)`` with ``p``/``m``/``v``/``p_bf16`` shaped like the result."""
     if not a.is_cuda:
         raise RuntimeError("ono gemm needs CUDA tensors (there is no CPU fallback on this path)")
     lib = _lib.load()
     if a.dtype != b.dtype or a.dtype not in (torch.float32, torch.bfloat16):
         raise TypeError("a and b must both be float32 (tf32 tiles) or bfloat16")
+    if out_f16 is not None:
+        if out_bf16 is not None or out_f16.dtype != torch.float16:
+            raise ValueError("out_f16 must be float16 and excludes out_bf16")
+        out_bf16 = out_f16
     for t in (a, b, out, out_t, out_bf16, out_t_bf16, pre, aux):
         if t is not None and (t.dim() != 2 or t.stride(1) != 1):
             raise ValueError("tensors must be 2-D with unit inner stride")
@@ -74,6 +103,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     g.dtype = 0 if a.dtype == torch.float32 else 1
     g.a_major, g.b_major = int(a_mn_major), int(b_mn_major)
     g.epi.reduce_out = int(reduce_out)
+    g.epi.out16_f16 = int(out_f16 is not None)
+    if split_k != 1 and apply is None and not reduce_out:
+        ws = _workspace(a.device, stream)
+        if ws is not None:
+            g.workspace, g.workspace_elems = ws.data_ptr(), ws.numel()
+    if apply is not None:
+        ap, pm = g.apply, apply["p"]
+        if pm.dim() != 2 or pm.stride(1) != 1 or tuple(pm.shape) != (M, N) or pm.dtype != torch.float32:
+            raise ValueError("apply['p'] must be an f32 [M, N] matrix with unit inner stride")
+        ap.p, ap.ld = pm.data_ptr(), pm.stride(0)
+        for k in ("m", "v", "p_bf16"):
+            t = apply.get(k)
+            if t is not None and (t.stride(0) != pm.stride(0) or tuple(t.shape) != (M, N)):
+                raise ValueError(f"apply[{k!r}] must share the shape and leading dimension of apply['p']")
+        ap.m, ap.v, ap.p_bf16 = _ptr(apply.get("m")), _ptr(apply.get("v")), _ptr(apply.get("p_bf16"))
+        ap.kind = {"sgd": 0, "momentum": 1, "adam": 2}[apply["kind"]]
+        ap.lr, ap.mu = apply["lr"], apply.get("mu", 0.0)
+        ap.b1, ap.b2, ap.eps = apply.get("b1", 0.9), apply.get("b2", 0.999), apply.get("eps", 1e-8)
+        ap.grad_scale = apply.get("grad_scale", 1.0)
+        ap.adam_pows = _ptr(apply.get("adam_pows"))
     if pair == 0:
         if DEFAULT_PAIR == "auto":
             pair = 1 if (a.dtype == torch.bfloat16 and M >= 256 and not reduce_out) else -1

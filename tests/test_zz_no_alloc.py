@@ -77,10 +77,10 @@ def test_noalloc_step_matches_regular_entry_point_twice(kind):
         if kind == "adam":
             adam_tick(ref["pows"], 0.9, 0.999)
             adam_tick(new["pows"], 0.9, 0.999)
-        _regular(lib, S, _lib, ref, kind, n, nblocks)
+        _regular(lib, S, _lib, ref, kind, npad, nblocks)
         a = OnoNoAllocStep()
         a.p, a.g, a.m, a.v, a.p_bf16 = (new[k].data_ptr() for k in ("p", "g", "m", "v", "pb"))
-        a.n, a.kind = n, OPT_KIND[kind]
+        a.n, a.kind = npad, OPT_KIND[kind]      # the padded length: the entry point rejects a length that is not a multiple of 4
         a.lr, a.mu, a.b1, a.b2, a.eps = 0.05, 0.9, 0.9, 0.999, 1e-8
         a.n_workers = 4
         a.adam_pows, a.sumsq, a.status = new["pows"].data_ptr(), new["sumsq"].data_ptr(), new["status"].data_ptr()
@@ -115,6 +115,17 @@ def test_noalloc_step_rejects_requests_beyond_its_scratch():
     assert b"exceeds the built-in scratch" in lib.ono_last_error()
     torch.cuda.synchronize()
     assert torch.count_nonzero(p).item() == 0  # nothing ran
+    # a length that is not padded to 4 elements, or a bf16 shadow that is not 8-byte aligned, is an argument error too
+    a.nblocks = 0
+    a.n = 1022
+    assert fn(C.byref(a), _lib.stream_ptr()) != 0 and b"multiple of 4" in lib.ono_last_error()
+    a.n = 1024
+    shadow = torch.zeros(1028, device="cuda", dtype=torch.bfloat16)
+    a.p_bf16 = shadow.data_ptr() + 2
+    assert fn(C.byref(a), _lib.stream_ptr()) != 0 and b"8-byte aligned" in lib.ono_last_error()
+    a.p_bf16 = None
+    torch.cuda.synchronize()
+    assert torch.count_nonzero(p).item() == 0
     a.nblocks = 0  # the library picks a grid within its scratch
     assert fn(C.byref(a), _lib.stream_ptr()) == 0
     torch.cuda.synchronize()
