@@ -376,6 +376,8 @@ Json B200Config::to_json() const {
   o.set("sync_every", sync_every);
   o.set("tile_dtype", tile_dtype);
   o.set("wire_dtype", wire_dtype);
+  o.set("wgrad_apply", wgrad_apply);
+  o.set("switch_check_every", Json((unsigned long long)switch_check_every));
   o.set("allreduce", allreduce);
   o.set("sharding", sharding);
   o.set("switch_metric", switch_metric);
@@ -418,12 +420,14 @@ B200Config B200Config::from_json(const Json& j) {
   };
   str("sync_every", c.sync_every, {"round", "step"});
   str("tile_dtype", c.tile_dtype, {"tf32", "bf16"});
-  str("wire_dtype", c.wire_dtype, {"f32", "f16", "bf16"});
+  str("wire_dtype", c.wire_dtype, {"auto", "f32", "f16", "bf16"});
   str("allreduce", c.allreduce, {"auto", "ring", "oneshot", "twoshot", "nvls", "nccl"});
   str("sharding", c.sharding, {"layer", "even"});
   str("switch_metric", c.switch_metric, {"loss", "grad_norm"});
   str("data", c.data, {"host", "device"});
-  str("grad_push", c.grad_push, {"auto", "on", "off"});
+  str("grad_push", c.grad_push, {"auto", "on", "off", "reduce"});
+  str("wgrad_apply", c.wgrad_apply, {"auto", "off"});
+  if (const Json* v = j.find("switch_check_every")) c.switch_check_every = nonzero(*v, "b200.switch_check_every");
   str("grad_stage", c.grad_stage, {"auto", "on", "off"});
   if (const Json* v = j.find("switch_window")) { c.switch_window = nonzero(*v, "b200.switch_window"); if (c.switch_window < 2) throw InvalidConfig("b200.switch_window must be at least 2"); }
   if (const Json* v = j.find("switch_threshold")) c.switch_threshold = float_non_negative(v->as_double(), "b200.switch_threshold");

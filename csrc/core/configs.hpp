@@ -96,7 +96,7 @@ struct SerializerConfig {
 struct B200Config {
   std::string sync_every = "round";       // "round" (reference cadence) | "step"
   std::string tile_dtype = "tf32";        // "tf32" | "bf16"
-  std::string wire_dtype = "f32";         // "f32" | "f16" | "bf16"
+  std::string wire_dtype = "auto";        // "auto" | "f32" | "f16" | "bf16": gradients between ranks (auto: bf16 between GPUs in step cadence, else f32)
   std::string allreduce = "auto";         // "auto" | "ring" | "oneshot" | "twoshot" | "nvls"
   std::string sharding = "layer";         // "layer" (reference LPT) | "even"
   std::string switch_metric = "loss";     // "loss" | "grad_norm"
@@ -110,7 +110,10 @@ struct B200Config {
   bool phase_timing = false;              // run steps uncaptured with CUDA events + NVTX ranges around compute / exchange / refresh
   bool probe = false;                     // measure pairwise node latency before planning (host:port sessions)
   std::string grad_stage = "auto";        // "auto" | "on" | "off": copy peers' finished gradient ranges into local staging during backward
-  std::string grad_push = "auto";         // "auto" | "on" | "off": weight-gradient GEMMs add their tiles into the owner's accumulator
+  std::string grad_push = "auto";         // "auto" | "on" | "off" | "reduce": weight-gradient GEMMs store their 16-bit tiles into the owner's slab
+                                          // ("reduce": add f32 tiles into the owner's accumulator instead)
+  std::string wgrad_apply = "auto";       // "auto" | "off": on one GPU the weight-gradient GEMMs apply the optimizer in their epilogues
+  size_t switch_check_every = 10;         // step cadence: steps between two evaluations of the gradient-norm switch metric
   double comm_timeout_s = 300.0;          // a collective or device wait that exceeds this ends the run with an error
   double heartbeat_s = 2.0;               // period of a node's liveness messages (0 = none)
   double heartbeat_timeout_s = 0.0;       // the orchestrator drops a node that stayed silent this long (0 = never)

@@ -62,6 +62,10 @@ class GpuEngine:
                  input_grad: bool = False):
         self.bias_from_shadow = bias_from_shadow
         self.input_grad = input_grad  # also produce d[0], the gradient w.r.t. the input batch
+        self.max_ctas = 0             # CTAs a GEMM of this engine may use (0 = one per SM); lowered while other kernels need SMs
+        self.push = None              # weight-gradient tiles added into the owners' f32 accumulators (see backward)
+        self.wire16 = None            # weight-gradient tiles stored as 16-bit values into the owners' slabs
+        self.apply_plan = None        # optimizer applied by the weight-gradient GEMM's epilogue, per layer
         if tile_dtype not in ("tf32", "bf16"):
             raise ValueError("tile_dtype must be 'tf32' or 'bf16'")
         self.dev = device or params.device
@@ -140,6 +144,9 @@ class GpuEngine:
             self.w_t.append(None if self.mn else z(o, _up(i), f32)[:, :i])
             g_direct = o % 4 == 0 and pl.w_off % 4 == 0 and (self.grads.data_ptr() + 4 * pl.w_off) % 16 == 0
             self.gw_tmp.append(None if g_direct else z(i, _up(o), f32)[:, :o])
+
+    def _gemm(self, *args, **kw) -> None:
+        gemm(*args, max_ctas=self.max_ctas, **kw)
 
     def w_view(self, l: int) -> torch.Tensor:
         pl = self.plans[l]
@@ -220,9 +227,9 @@ class GpuEngine:
                 if self.zpre[l + 1] is not None:
                     kw["pre"] = self.zpre[l + 1][:nrows, :pl.out_features]
             if self.mn:
-                gemm(a_in, self.w_k[l], b_mn_major=True, **kw)
+                self._gemm(a_in, self.w_k[l], b_mn_major=True, **kw)
             else:
-                gemm(a_in, self.w_t[l], **kw)
+                self._gemm(a_in, self.w_t[l], **kw)
             n += 1
         return n
 
@@ -252,9 +259,9 @@ class GpuEngine:
         that layer's parameters while the layers below are still running."""
         L, n = self.plans, 0
         beta = 1.0 if accumulate else 0.0
-        push = getattr(self, "push", None)
-        if push is not None and accumulate:
-            raise RuntimeError("gradient push cannot accumulate over several batches")
+        push, wire, app = self.push, self.wire16, self.apply_plan
+        if (push is not None or wire is not None or app is not None) and accumulate:
+            raise RuntimeError("pushed / fused weight gradients cannot accumulate over several batches")
         for l in range(len(L) - 1, -1, -1):
             pl = L[l]
             i, o = pl.in_features, pl.out_features
@@ -270,23 +277,60 @@ class GpuEngine:
                     kw.update(aux=stored[:nrows, :i], dact=prev.act, dact_param=prev.act_param,
                               relu_quirk=self.relu_quirk)
                 if self.bf16:
-                    gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
+                    self._gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
                 elif self.mn:
-                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], **kw)
+                    self._gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], **kw)
                 else:
-                    gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
-                         out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
+                    self._gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
+                               out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
                 n += 1
+
+            def wgrad(r0, r1, **out_kw):     # rows [r0, r1) of dW = A_l^T d
+                if self.mn:
+                    self._gemm(self.a[l][:nrows, r0:r1], d_out, a_mn_major=True, b_mn_major=True, status=self.status,
+                               stream=stream, **out_kw)
+                else:
+                    self._gemm(self.at[l][r0:r1, :nrows], self.dt[l + 1][:, :nrows], status=self.status, stream=stream,
+                               **out_kw)
+
+            if wire is not None:
+                # 16-bit gradient wire: every tile of dW leaves the epilogue as bf16 / f16 through a TMA store into
+                # the slab the owner of those rows keeps for this rank (its window over NVLink, or local memory); the
+                # exchange rides on backward and the owner later reduces its slabs from local memory
+                pieces = wire["w"][l]
+                if pieces is not None:
+                    for r0, r1, dst in pieces:
+                        wgrad(r0, r1, **{"out_f16" if wire["f16"] else "out_bf16": dst})
+                        n += 1
+                else:
+                    tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
+                    wgrad(0, i, out=tgt)
+                    n += 1
+                    if self.gw_tmp[l] is not None:
+                        ew.rows(tgt, dst=self.gw_view(l), stream=stream)
+                        n += 1
+                ew.colsum(d_out, self.gb_view(l), beta=0.0, stream=stream)
+                n += 1
+                for src, dst in wire["cast"][l]:
+                    ew.cast16(src, dst, f16=wire["f16"], stream=stream)
+                    n += 1
+                if after_layer is not None:
+                    n += after_layer(l) or 0
+                continue
+            if app is not None and app.get(l) is not None:
+                # this rank owns the whole layer: the epilogue applies the optimizer to the tile it has just
+                # computed (master, state, bf16 shadow); the weight gradient itself is never stored
+                wgrad(0, i, apply=app[l])
+                ew.colsum(d_out, self.gb_view(l), beta=0.0, stream=stream)
+                n += 2
+                if after_layer is not None:
+                    n += after_layer(l) or 0
+                continue
             if push is not None:
                 # weight gradient tiles are added straight into the accumulator of the rank that owns those rows (its
                 # window, over NVLink): the reduce-scatter happens inside the GEMM epilogue, tile by tile
                 for r0, r1, dst in push["w"][l]:
-                    if self.mn:
-                        gemm(self.a[l][:nrows, r0:r1], d_out, a_mn_major=True, b_mn_major=True, out=dst, reduce_out=True,
-                             status=self.status, stream=stream)
-                    else:
-                        gemm(self.at[l][r0:r1, :nrows], self.dt[l + 1][:, :nrows], out=dst, reduce_out=True,
-                             status=self.status, stream=stream)
+                    wgrad(r0, r1, out=dst, reduce_out=True)
                     n += 1
                 ew.colsum(d_out, self.gb_view(l), beta=0.0, stream=stream)
                 ew.push_add(self.gb_view(l), push["b"][l], stream=stream)
@@ -297,12 +341,7 @@ class GpuEngine:
             # wgrad: dW[in,out] = A_{l}^T d
             tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)
             wbeta = beta if self.gw_tmp[l] is None else 0.0
-            if self.mn:
-                gemm(self.a[l][:nrows, :i], d_out, a_mn_major=True, b_mn_major=True, out=tgt, beta=wbeta,
-                     status=self.status, stream=stream)
-            else:
-                gemm(self.at[l][:, :nrows], self.dt[l + 1][:, :nrows], out=tgt, beta=wbeta, status=self.status,
-                     stream=stream)
+            wgrad(0, i, out=tgt, beta=wbeta)
             n += 1
             if self.gw_tmp[l] is not None:
                 if accumulate:

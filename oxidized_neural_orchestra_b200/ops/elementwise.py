@@ -72,6 +72,15 @@ def push_add(src: torch.Tensor, dst: torch.Tensor, stream=None) -> None:
     _lib.check(lib.ono_push_add(src.data_ptr(), dst.data_ptr(), src.numel(), _lib.stream_ptr(stream)), "ono_push_add")
 
 
+def cast16(src: torch.Tensor, dst: torch.Tensor, f16: bool = False, stream=None) -> None:
+    """``dst[i] = bf16(src[i])`` (IEEE f16 with ``f16=True``); ``dst`` may be a view of a peer GPU's window."""
+    _need_cuda(src)
+    if dst.numel() != src.numel() or dst.element_size() != 2 or src.dtype != torch.float32:
+        raise ValueError("cast16 needs an f32 source and a 16-bit destination of the same length")
+    _lib.check(_lib.load().ono_cast16(src.data_ptr(), dst.data_ptr(), src.numel(), int(f16), _lib.stream_ptr(stream)),
+               "ono_cast16")
+
+
 def optim_step(p: torch.Tensor, g: torch.Tensor, *, kind: str, lr: float, mu: float = 0.0, b1: float = 0.9,
                b2: float = 0.999, eps: float = 1e-8, m: torch.Tensor | None = None,
                v: torch.Tensor | None = None, adam_pows: torch.Tensor | None = None,

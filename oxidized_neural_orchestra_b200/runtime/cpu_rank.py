@@ -29,7 +29,9 @@ class CpuRank:
         self.n = plan["n_params"]
         self.b200 = plan["b200"]
         self.algorithm = plan["algorithm"]
-        self.seed = plan["seed"] if plan.get("seed") is not None else int(time.time())
+        from .gpu_rank import resolve_seed
+
+        self.seed = resolve_seed(plan, rank, world, None, group)      # one seed for every rank, drawn by rank 0 if the plan has none
         self.worker_ranks = [w["rank"] for w in plan["workers"]]
         self.sync_workers = list(self.worker_ranks)
         self.widx = self.worker_ranks.index(rank) if rank in self.worker_ranks else None

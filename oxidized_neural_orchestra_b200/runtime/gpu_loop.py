@@ -30,6 +30,10 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
     f, e = r.feeder, r.engine
     e.loss_sum.zero_()
     n = 1
+    if with_sync and r.apply_active and r.sync_opt.kind == "adam":
+        # the weight-gradient GEMMs apply Adam in their epilogues: the step's powers must exist before backward
+        ew.adam_tick(r.adam_pows, r.sync_opt.b1, r.sync_opt.b2, stream=st)
+        n += 1
     if with_sync and r.buckets:
         # bucketed: each layer's gradients are synchronised on the communication stream as soon as
         # they exist, while backward continues below that layer
@@ -52,7 +56,7 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
         st.wait_stream(comm)
         n += e.refresh(stream=st)
         return n
-    if with_sync and getattr(r, "stage_buckets", None):
+    if with_sync and r.stage_buckets:
         # staged reduce-scatter: every finished bucket is announced to the peers, and the peers' copies of the ranges
         # this rank owns are pulled into local staging on the communication stream while backward continues
         n += r.stage_tick(st)
@@ -108,7 +112,7 @@ def run_batch(r, slot: int, nrows: int) -> None:
     st = r.stream
     st.wait_event(r.feeder.ready[slot])
     # the staged reduce-scatter (experimental) forks onto the communication stream inside the step; it runs uncaptured
-    graphable = r.sync_mode != "nccl" and not getattr(r, "stage_active", False) and not getattr(r, "phase_timing", False)
+    graphable = r.sync_mode != "nccl" and not r.stage_active and not getattr(r, "phase_timing", False)
     with torch.cuda.stream(st):
         if key not in r.warm or not graphable:
             r.launches_per_step = _batch_body(r, slot, nrows, True)
@@ -133,7 +137,7 @@ def run_batch(r, slot: int, nrows: int) -> None:
 def server_step(r) -> None:
     """A pure server rank takes part in the synchronisation only."""
     with torch.cuda.stream(r.stream):
-        if getattr(r, "stage_buckets", None):   # a server-only rank pulls the workers' gradients of the ranges it owns
+        if r.stage_buckets:   # a server-only rank pulls the workers' gradients of the ranges it owns
             r.stage_tick(r.stream)
             for _, _, pull in r.stage_buckets:
                 r.stage_pull(pull, r.stream)

@@ -70,6 +70,21 @@ def optimizer_cfg(spec: dict) -> S.OptimizerCfg:
                           eps=b.get("epsilon", b.get("eps", 1e-8)))
 
 
+def resolve_seed(plan: dict, rank: int, world: int, device=None, group=None) -> int:
+    """The run's seed, the same on every rank. A plan without a seed (the public API's default) gets one drawn by
+    rank 0 and broadcast: initial parameters are generated per rank from (seed, element index), so ranks that each
+    picked their own would start from different models."""
+    if plan.get("seed") is not None:
+        return int(plan["seed"])
+    seed = int.from_bytes(__import__("os").urandom(4), "little") if rank == 0 else 0
+    if world > 1 and dist.is_initialized():
+        box = [seed]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group,
+                                   device=device)
+        seed = int(box[0])
+    return seed
+
+
 def snap_ranges(ranges_per_rank: list[list[tuple[int, int]]], n_pad: int) -> list[list[tuple[int, int]]]:
     """Move every interior boundary down to a multiple of 4 elements (the kernels work on float4), the
     same rule on both sides of a boundary so the ranges still partition ``[0, n_pad)``."""

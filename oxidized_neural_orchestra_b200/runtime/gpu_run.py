@@ -301,12 +301,15 @@ def run(r) -> dict:
         "step_ms": ms, "steps": len(evs), "step_wall": r.step_wall, "launches_per_step": r.launches_per_step,
         "h2d_bytes_per_step": r.feeder.h2d_bytes_per_step if r.feeder is not None else 0,
         "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
-        "nvls": bool(getattr(r, "use_nvls", False) and r.win.mc_ptr),
+        "nvls": bool(r.use_nvls and r.win.mc_ptr),
+        # what travels between GPUs: the 16-bit wire applies to the fused kernels of step cadence
+        "wire": (r.wire16 if (r.wire16 is not None and r.sync_mode in ("fused", "oneshot")) else "f32") if r.world > 1 else "none",
+        "wire_push": bool(r.wire16_push), "wgrad_apply": bool(r.apply_active),
     }
     if r.phase_timing:
         metrics["phase_ms"] = getattr(r, "phase_ms_last", {})     # means over the steps of the last record
-    metrics["grad_push"] = bool(getattr(r, "push_active", False))
-    metrics["grad_stage"] = bool(getattr(r, "stage_active", False))
+    metrics["grad_push"] = bool(r.push_active)
+    metrics["grad_stage"] = bool(r.stage_active)
     if r.compress:
         sent = int(r.wire_sent.item())
         metrics["wire"] = ("f16+sparse" if r.sparse_r is not None else "f16")

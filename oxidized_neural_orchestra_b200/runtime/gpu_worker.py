@@ -19,7 +19,8 @@ from ..ops import _lib
 from ..ops import elementwise as ew
 from ..parallel import sync as S
 from ..parallel.symmetric import SymmetricWindow, WindowLayout
-from .gpu_rank import BatchFeeder, engine_layers_from_plan, optimizer_cfg, snap_ranges, snap_to_row_blocks
+from .gpu_rank import (BatchFeeder, engine_layers_from_plan, optimizer_cfg, resolve_seed, snap_ranges,
+                       snap_to_row_blocks)
 
 
 def _up(n, m=16):
@@ -38,7 +39,7 @@ class GpuRank:
         self.algorithm = plan["algorithm"]
         self.n = plan["n_params"]
         self.n_pad = _up(self.n, 16)
-        self.seed = plan["seed"] if plan.get("seed") is not None else int(time.time())
+        self.seed = resolve_seed(plan, rank, world, device, group)
         self.x_size = plan["layers"][0]["input_size"]
         self.y_size = plan["layers"][-1]["output_size"]
         self.worker_ranks = [w["rank"] for w in plan["workers"]]
@@ -49,6 +50,9 @@ class GpuRank:
         self.step_events: list[torch.cuda.Event] = []
         self.step_wall: list[float] = []
         self.switched = False
+        self.use_nvls = False
+        self.push_active = self.stage_active = self.wire16_push = self.apply_active = False
+        self.buckets, self.bucket_after, self.stage_buckets, self.stage_after = [], {}, [], {}
         self.stream = torch.cuda.Stream(device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
         wspec = plan["workers"][self.widx if self.widx is not None else 0]["spec"]
@@ -84,15 +88,33 @@ class GpuRank:
         self.compress = self.cadence == "round" and (self.b200.get("wire_dtype") == "f16" or self.sparse_r is not None)
         if self.compress:
             lay.add("wire", self.n_pad, torch.float32)
-        # Gradient push (step cadence, dense models whose weight blocks are 16-byte aligned): the weight-gradient GEMMs
-        # add their output tiles into the accumulator of the rank that owns those rows, so the reduce-scatter rides on
-        # the GEMM epilogues instead of a separate pass over NVLink after backward.
+        # Gradient wire between GPUs. The reference always ships gradients as f16 (comms/src/handles/compressor.rs:104-118,
+        # decoded at comms/src/handles/worker.rs:84-101). In step cadence the default here is a bf16 wire (f32 range, so
+        # the small gradients of a loss normalised by batch x outputs do not underflow); "f16" gives the reference's
+        # format, "f32" the uncompressed wire. One GPU has no wire: its gradients stay f32.
+        wd = self.b200.get("wire_dtype", "auto")
+        self.wire16 = None
         gp = self.b200.get("grad_push", "auto")
+        if self.cadence == "step" and self.world > 1 and wd != "f32" and gp != "reduce":
+            self.wire16 = "f16" if wd == "f16" else "bf16"
         lays = engine_layers_from_plan(self.plan)
-        aligned = all(l["kind"] == "dense" and l["out"] % 4 == 0 for l in lays) and \
-            all(pl["offset"] % 4 == 0 for pl in self.plan["layers"])
+        dense_only = all(l["kind"] == "dense" for l in lays)
+        ar_mode = self.b200.get("allreduce", "auto")
+        # 16-bit push (the default data path of a dense model on several GPUs): the weight-gradient GEMMs store their
+        # tiles as 16-bit values straight into the slab that the owner of those rows keeps for this rank, so the
+        # reduce-scatter rides on backward and the owner reduces `world` local slabs. Slab q of a window holds rank q's
+        # gradients, indexed like the flat parameter vector.
+        self.push16 = (self.wire16 is not None and gp in ("auto", "on") and dense_only and not self.async_ps and
+                       ar_mode in ("auto", "twoshot", "nvls"))
+        if self.wire16 is not None:
+            self.nslabs = self.world if self.push16 else 1
+            lay.add("slab16", self.nslabs * self.n_pad, torch.float16 if self.wire16 == "f16" else torch.bfloat16)
+        # f32 gradient push (opt-in, "reduce"): the weight-gradient GEMMs add their output tiles into the f32 accumulator
+        # of the rank that owns those rows with TMA reduce-adds
+        aligned = dense_only and all(l["out"] % 4 == 0 for l in lays) and all(pl["offset"] % 4 == 0 for pl in self.plan["layers"])
         forced_single = os.environ.get("ONO_PUSH_SINGLE", "0") == "1"
-        self.push = self.cadence == "step" and gp == "on" and aligned and (self.world > 1 or forced_single)
+        self.push = (self.cadence == "step" and not self.push16 and gp in ("on", "reduce") and aligned and
+                     (self.world > 1 or forced_single))
         if self.push:
             lay.add("acc", self.n_pad, torch.float32)
         # the ring all-reduce (the reference's algorithm, worker/src/middlewares/worker_ring.rs:112-204) circulates chunks
@@ -100,7 +122,8 @@ class GpuRank:
         # Staged reduce-scatter (step cadence, several GPUs): while backward runs, a few SMs copy the peers' finished
         # gradient ranges this rank owns into local staging buffers (bulk async copies through shared memory), and the
         # fused optimizer kernel afterwards reads every worker's gradient from local HBM instead of over NVLink.
-        self.stage = self.cadence == "step" and self.b200.get("grad_stage", "auto") == "on" and self.world > 1 and not self.push
+        self.stage = (self.cadence == "step" and self.b200.get("grad_stage", "auto") == "on" and self.world > 1 and
+                      not self.push and self.wire16 is None)
         if self.stage:
             lay.add("stage_ready", self.world * _lib.STAGE_BUCKETS, torch.int32)
         self.ring_wanted = self.b200.get("allreduce") == "ring" and self.algorithm != "parameter_server"
@@ -283,22 +306,114 @@ class GpuRank:
             w[li] = sorted(pieces, key=lambda t: t[0])
         return {"w": w, "b": b}
 
+    def _all_ranks_agree(self, mine: bool) -> bool:
+        """True when every rank says yes (ranks without an engine always do)."""
+        if self.world == 1:
+            return mine
+        flag = torch.tensor([1.0 if mine else 0.0], device=self.dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        return bool(flag.item() > 0)
+
+    def _build_wire16(self):
+        """Per layer: where this rank's 16-bit gradients go. ``w[l]``: (row range, destination matrix) pieces of the
+        weight gradient, one per owner, each a view of slab `rank` in the owner's window (None for a layer whose rows
+        are not 16-byte aligned as 16-bit values: its gradient is computed in f32 locally and cast). ``cast[l]``:
+        (f32 source, 16-bit destination) pairs for the bias gradient and for such unaligned layers."""
+        dt = torch.float16 if self.wire16 == "f16" else torch.bfloat16
+        slab_elems0 = self.layout.offset("slab16") // 2 + self.rank * self.n_pad
+        local = self.layout.tensor(self.win, "slab16")
+
+        def flat(owner, begin, count):
+            if owner == self.rank or self.win.handle is None:
+                return local[self.rank * self.n_pad + begin:self.rank * self.n_pad + begin + count]
+            return self.win.handle.get_buffer(owner, (count,), dt, slab_elems0 + begin)
+
+        w, cast = {}, {}
+        for li, pl in enumerate(self.engine.plans):
+            i, o = pl.in_features, pl.out_features
+            direct = o % 8 == 0 and pl.w_off % 8 == 0
+            pieces, casts = [], []
+            for owner, rs in enumerate(self.own):
+                for lo, hi in rs:
+                    a0, a1 = max(lo, pl.w_off), min(hi, pl.w_off + i * o)
+                    if a1 > a0:
+                        if direct:
+                            assert (a0 - pl.w_off) % o == 0 and (a1 - pl.w_off) % o == 0, "ownership must follow whole rows"
+                            r0, r1 = (a0 - pl.w_off) // o, (a1 - pl.w_off) // o
+                            pieces.append((r0, r1, flat(owner, a0, (r1 - r0) * o).view(r1 - r0, o)))
+                        else:
+                            casts.append((self.G[a0:a1], flat(owner, a0, a1 - a0)))
+                    b0, b1 = max(lo, pl.b_off), min(hi, pl.b_off + o)
+                    if b1 > b0:
+                        casts.append((self.G[b0:b1], flat(owner, b0, b1 - b0)))
+            w[li] = sorted(pieces, key=lambda t: t[0]) if direct else None
+            cast[li] = casts
+        return {"f16": self.wire16 == "f16", "w": w, "cast": cast}
+
+    def _build_apply(self, opt, n_workers: int, wild: bool):
+        """Layers whose weight-gradient GEMM applies the optimizer itself, and the ranges left to the fused kernel."""
+        e = self.engine
+        kind = {"sgd": "sgd", "momentum": "momentum", "adam": "adam"}[opt.kind]
+        cand = []
+        for li, pl in enumerate(e.plans):
+            i, o = pl.in_features, pl.out_features
+            if o % 4 == 0 and (self.C.data_ptr() + 4 * pl.w_off) % 16 == 0 and i * o >= 1 << 16:
+                cand.append((i * o, li))
+        cand.sort(reverse=True)
+
+        def rest_of(chosen):
+            cuts = sorted((e.plans[li].w_off, e.plans[li].w_off + e.plans[li].in_features * e.plans[li].out_features)
+                          for li in chosen)
+            out, at = [], 0
+            for b, en in cuts:
+                if b > at:
+                    out.append((at, b))
+                at = en
+            if at < self.n_pad:
+                out.append((at, self.n_pad))
+            return out
+
+        chosen = [li for _, li in cand]
+        while chosen and len(rest_of(chosen)) > _lib.MAX_RANGES:
+            chosen.pop()                                    # the smallest layer goes back to the fused kernel
+        plan = {}
+        for li in chosen:
+            pl = e.plans[li]
+            i, o = pl.in_features, pl.out_features
+            sl = slice(pl.w_off, pl.w_off + i * o)
+            shadow = None
+            if e.bf16 and not e.w_copy_needed[li] and self.shadow is not None:
+                shadow = self.shadow[sl].view(i, o)
+            plan[li] = dict(p=self.C[sl].view(i, o), m=self.m_loc[sl].view(i, o), v=self.v_loc[sl].view(i, o), p_bf16=shadow,
+                            kind=kind, lr=opt.lr, mu=opt.mu, b1=opt.b1, b2=opt.b2, eps=opt.eps,
+                            grad_scale=1.0 if wild else 1.0 / max(1, n_workers), adam_pows=self.adam_pows)
+        return plan, rest_of(chosen)
+
     def _set_ownership(self, ranges, workers, opt, mode, wild):
         W = self.world
-        push = self.push and mode == "fused" and self.engine is not None and getattr(self.engine, "plans", None) is not None
-        if self.push and W > 1:       # every rank must take the same decision
-            flag = torch.tensor([1.0 if (push or self.engine is None) else 0.0], device=self.dev)
-            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
-            push = push and bool(flag.item() > 0)
-        self.push_active = bool(self.push and mode == "fused" and (push or self.engine is None))
-        if self.push_active:
+        dense_engine = self.engine is not None and isinstance(self.engine, GpuEngine)
+        can = mode == "fused" and (dense_engine or self.engine is None)
+        self.push_active = bool(self.push) and self._all_ranks_agree(can) if self.push else False
+        self.wire16_push = bool(self.push16) and self._all_ranks_agree(can) if self.push16 else False
+        if self.push_active or self.wire16_push:
             ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)
         self.buckets, self.bucket_after = [], {}
         self.stage_buckets, self.stage_after, self.stage_active = [], {}, False
-        from ..ops import gemm as _gemm_mod
-
-        _gemm_mod.DEFAULT_MAX_CTAS = 0          # only the overlap modes below leave SMs to communication kernels
+        if self.engine is not None:
+            self.engine.max_ctas = 0            # only the overlap modes below leave SMs to communication kernels
+            if dense_engine:
+                self.engine.push = self.engine.wire16 = self.engine.apply_plan = None
+        # One GPU that owns every layer: the weight-gradient GEMMs apply the optimizer in their epilogues and the fused
+        # kernel afterwards only handles what is left (biases, layers whose rows are not 16-byte aligned)
+        self.apply_active = False
+        if (W == 1 and dense_engine and self.cadence == "step" and mode in ("fused", "oneshot") and not self.grad_norm_switch
+                and self.b200.get("wgrad_apply", "auto") != "off" and os.environ.get("ONO_WGRAD_APPLY", "1") != "0"):
+            plan_, rest = self._build_apply(opt, len(workers), wild)
+            if plan_:
+                self.engine.apply_plan = plan_
+                self.own = [rest]
+                self.apply_active = True
         self.sync_workers = list(workers)
         self.sync_mode = mode
         self.sync_opt = opt
@@ -329,10 +444,11 @@ class GpuRank:
                       for r, p in enumerate(win.peer_ptrs(lay.offset("params_bf16")))]
             else:
                 pb = [None] * W
-            nvls = getattr(self, "use_nvls", False) and win.mc_ptr != 0 and W > 1
+            nvls = self.use_nvls and win.mc_ptr != 0 and W > 1
             algo = 1 if nvls else 0
             g_region = self.grad_region
-            stage_active = bool(getattr(self, "stage", False)) and not self.push_active and not self.compress and mode == "fused"
+            g_dtype = 0
+            stage_active = bool(self.stage) and not self.push_active and not self.compress and mode == "fused"
             self.stage_active = stage_active
             if self.push_active:
                 # gradients arrive already summed in this rank's accumulator: nothing to reduce over the wires, the
@@ -345,11 +461,21 @@ class GpuRank:
                 # every worker's gradient is read from this GPU's memory: its own window, or the staged copy of a peer's
                 g_ptrs = [g_ptrs[q] if q == self.rank else self.stage_buf[q].data_ptr() for q in range(W)]
                 algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
+            if self.wire16 is not None:
+                g_dtype = 2 if self.wire16 == "f16" else 1
+                slab0 = lay.offset("slab16")
+                if self.wire16_push:
+                    # slab q of this rank's own window holds what worker q's GEMMs stored here during backward
+                    g_ptrs = [win.ptrs[self.rank] + slab0 + 2 * q * self.n_pad for q in range(W)]
+                    algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
+                else:
+                    # pull form: every worker casts its gradient into slab 0 of its own window, owners read the peers'
+                    g_ptrs = win.peer_ptrs(slab0)
             S.fill_sync(s, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=algo,
                         g_ptrs=g_ptrs, p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
-                        g_mc=(win.mc(lay.offset(g_region)) or None) if algo == 1 else None,
+                        g_mc=(win.mc(lay.offset("slab16" if g_dtype else g_region)) or None) if algo == 1 else None,
                         p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
                         p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
@@ -357,12 +483,13 @@ class GpuRank:
                          epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
                          sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
                          status=self.sync_status.data_ptr())
+            s.g_dtype = g_dtype
             if self.push_active:
                 s.zero_grad = 1
                 if self.engine is not None:
                     self.engine.push = self._build_push()
-            elif self.engine is not None and hasattr(self.engine, "push"):
-                self.engine.push = None
+            if self.wire16_push and self.engine is not None:
+                self.engine.wire16 = self._build_wire16()
             self.sync_struct = s
             self._build_buckets()
             self._build_stage(workers)
@@ -424,16 +551,14 @@ class GpuRank:
         # issued per thread, and NVLink throughput grows with the number of SMs issuing them (about 4-5 GB/s per SM):
         # 16 / 32 SMs left to the bucket kernels moved gradients at roughly 70 / 140 GB/s on 4 GPUs, against 650 GB/s
         # when the fused kernel owns the whole GPU after backward.
-        from ..ops import gemm as gemm_mod
-
-        gemm_mod.DEFAULT_MAX_CTAS = 0
         if (self.sync_mode != "fused" or self.cadence != "step" or os.environ.get("ONO_OVERLAP", "0") == "0"):
             return
         # The persistent GEMM (one CTA per SM, all of its shared memory and most registers) and a 512-thread
         # synchronisation block do not fit on one SM together, so the SMs are split: `comm_sms` of them are left to the
         # bucket kernels, the GEMMs run on the rest.
         comm_sms = max(1, min(int(os.environ.get("ONO_OVERLAP_SMS", "24")), _lib.load().ono_num_sms() // 2))
-        gemm_mod.DEFAULT_MAX_CTAS = _lib.load().ono_num_sms() - comm_sms
+        if self.engine is not None:
+            self.engine.max_ctas = _lib.load().ono_num_sms() - comm_sms
         up4 = lambda x: (x + 3) // 4 * 4
         layers = [l for l in self.plan["layers"] if l["n_params"] > 0]
         min_elems = 4 << 20
@@ -486,12 +611,11 @@ class GpuRank:
     def _build_stage(self, workers) -> None:
         """Per bucket: the pull of the peers' gradient ranges this rank owns (launched on the communication stream once
         the peers have announced the bucket) and the announcement of this rank's own gradients."""
-        from ..ops import gemm as gemm_mod
-
         self.stage_buckets, self.stage_after = [], {}
-        if not getattr(self, "stage_active", False):
+        if not self.stage_active:
             return
-        gemm_mod.DEFAULT_MAX_CTAS = _lib.load().ono_num_sms() - self.stage_sms
+        if self.engine is not None:
+            self.engine.max_ctas = _lib.load().ono_num_sms() - self.stage_sms
         buckets = self._bucket_ranges()
         while len(buckets) > _lib.STAGE_BUCKETS:                      # merge neighbours until the flag table suffices
             buckets = [(buckets[i + 1][0] if i + 1 < len(buckets) else buckets[i][0],
@@ -552,8 +676,13 @@ class GpuRank:
                 n += 1
             self.wire_rounds += 1
             g_tensor = self.wire
-        if self.sync_opt.kind == "adam":
+        if self.sync_opt.kind == "adam" and not self.apply_active:   # with the optimizer in the GEMM epilogues the step ticks first
             ew.adam_tick(self.adam_pows, self.sync_opt.b1, self.sync_opt.b2, stream=stream)
+            n += 1
+        if (self.wire16 is not None and not self.wire16_push and self.sync_mode in ("fused", "oneshot")
+                and self.widx is not None and self.rank in self.sync_workers):
+            # 16-bit wire, pull form: this worker's gradient goes to slab 0 of its own window as 16-bit values
+            ew.cast16(g_tensor, self.layout.tensor(self.win, "slab16")[:self.n_pad], f16=self.wire16 == "f16", stream=stream)
             n += 1
         if self.sync_mode in ("fused", "oneshot"):
             S.launch_sync(self.sync_struct, stream=stream)

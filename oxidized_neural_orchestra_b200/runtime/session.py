@@ -38,7 +38,7 @@ class CpuHandle:
         sparse = isinstance(ser, dict)
         self.n_workers = len(plan["workers"])
         self._cluster = core.LocalCluster(json.dumps(plan), xs, ys, x_size, y_size,
-                                          wire=b.get("wire_dtype", "f32") if b.get("wire_dtype") != "bf16" else "f32",
+                                          wire="f16" if b.get("wire_dtype") == "f16" else "f32",
                                           sparse=sparse, sparse_r=ser["sparse_capable"]["r"] if sparse else 0.0,
                                           leaky_relu_exact=b.get("leaky_relu_exact", True),
                                           switch_resets_progress=b.get("switch_resets_progress", False))

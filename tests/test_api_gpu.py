@@ -231,3 +231,27 @@ def test_periodic_checkpoints_load_back_and_continue_the_run(tmp_path):
     assert np.allclose(last, whole.weights_array(), atol=1e-7)
     resumed = run(2, init_from=str(tmp_path / "ck_2.safetensors"), init_state_from=str(tmp_path / "ck_2.state.safetensors"))
     assert np.abs(resumed.weights_array() - whole.weights_array()).max() < 1e-5
+
+
+@pytest.mark.parametrize("tile", ["bf16", "tf32"])
+@pytest.mark.parametrize("opt", [GradientDescentWithMomentum(0.1, 0.9), Adam(0.005), GradientDescent(0.2)])
+def test_optimizer_in_the_weight_gradient_epilogue_matches_the_separate_pass(tile, opt):
+    """On one GPU the weight-gradient GEMMs update master, state and shadow in their epilogues; the run must follow the
+    run whose optimizer is the separate fused pass (same arithmetic per element, only the GEMM's f32 result is not
+    rounded through memory in between: the two are equal to rounding)."""
+    xs, ys = _data(n=256, x=512, y=16, seed=4)
+    model = Sequential([Dense(1024, XavierUniform(), GELU()), Dense(512, XavierUniform(), ReLU(0.0)),
+                        Dense(16, XavierUniform(), Softmax())])
+    got = {}
+    for mode in ("auto", "off"):
+        tr = orchestra.parameter_server(["gpu:0"], 1, InlineDataset(xs, ys, 512, 16), opt, CrossEntropy(), BarrierSync(),
+                                        BlockingStore(), max_epochs=5, batch_size=64, seed=3,
+                                        b200={"sync_every": "step", "tile_dtype": tile, "colocate": True, "sharding": "even",
+                                              "wgrad_apply": mode})
+        m = orchestrate(model, tr).wait(quiet=True)
+        assert m.metrics()["wgrad_apply"] == (mode == "auto")
+        got[mode] = (np.array(m.loss_history()), m.weights_array())
+    (la, wa), (lo, wo) = got["auto"], got["off"]
+    assert la[-1] < la[0]
+    assert np.allclose(la, lo, rtol=2e-3, atol=1e-6)
+    assert np.abs(wa - wo).max() < 2e-3 * max(1.0, np.abs(wo).max())

@@ -214,3 +214,123 @@ def test_gemm_few_tiles_long_reduction_takes_the_two_pass_split(dtype, shape):
     assert (out.double() - z.clamp_min(0)).abs().max().item() <= tol
     assert (out_t.double() - z.clamp_min(0).t()).abs().max().item() <= tol
     assert bool((out._base[:, N:] == 9.0).all()) and bool((out_t._base[:, M:] == 9.0).all())
+
+
+def _opt_ref(kind, p, g, m, v, lr, mu, b1, b2, eps, gs, pows):
+    g = g * gs
+    if kind == "sgd":
+        return p - lr * g, m, v
+    if kind == "momentum":
+        m = mu * m + g
+        return p - lr * m, m, v
+    m = b1 * m + (1 - b1) * g
+    v = b2 * v + (1 - b2) * g * g
+    step = lr * (1 - pows[1]) ** 0.5 / (1 - pows[0])
+    return p - step * m / (v.sqrt() + eps), m, v
+
+
+@pytest.mark.parametrize("kind", ["sgd", "momentum", "adam"])
+@pytest.mark.parametrize("dtype,pair", [(torch.bfloat16, 1), (torch.bfloat16, -1), (torch.float32, -1)])
+@pytest.mark.parametrize("shape", [(512, 768, 256), (300, 260, 96), (1024, 1000, 512)])
+def test_gemm_epilogue_applies_the_optimizer_to_its_own_tile(kind, dtype, pair, shape):
+    """Weight-gradient form dW = A^T d with the optimizer in the epilogue: master, state and bf16 shadow are updated in place,
+    nothing else is written (the matrices are views into wider buffers whose other columns must stay untouched)."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(7)
+    ld = (N + 15) // 16 * 16 + 16
+    a = (torch.randn(K, M, device="cuda") / 4).to(dtype)       # MN-major operands, as the engines pass them
+    d = (torch.randn(K, N, device="cuda") / 4).to(dtype)
+    wide = lambda dt=torch.float32: torch.full((M, ld), 3.0, device="cuda", dtype=dt)
+    pw, mw, vw, sw = wide(), wide(), wide(), wide(torch.bfloat16)
+    p, m, v, sh = pw[:, :N], mw[:, :N], vw[:, :N], sw[:, :N]
+    p.copy_(torch.randn(M, N, device="cuda"))
+    m.copy_(torch.randn(M, N, device="cuda") * 0.1)
+    v.copy_(torch.rand(M, N, device="cuda") * 0.1)
+    pows = torch.tensor([0.9 ** 3, 0.999 ** 3], device="cuda")
+    p0, m0, v0 = p.double().clone(), m.double().clone(), v.double().clone()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, d, a_mn_major=True, b_mn_major=True, pair=pair, status=status,
+         apply=dict(p=p, m=m, v=v, p_bf16=sh, kind=kind, lr=0.05, mu=0.9, b1=0.9, b2=0.999, eps=1e-8, grad_scale=0.25,
+                    adam_pows=pows))
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    g = a.double().t() @ d.double()
+    rp, rm, rv = _opt_ref(kind, p0, g, m0, v0, 0.05, 0.9, 0.9, 0.999, 1e-8, 0.25, pows.double().tolist())
+    gtol = (4e-3 if dtype == torch.float32 else 2e-3) * g.abs().max().item()
+    # Adam normalises the step: an error of gtol in g moves p by at most ~lr * gtol / sqrt(v)
+    ptol = 0.05 * gtol * (40 if kind == "adam" else 1.5) + 1e-6
+    assert (p.double() - rp).abs().max().item() <= ptol
+    if kind != "sgd":
+        assert (m.double() - rm).abs().max().item() <= gtol
+    else:
+        assert torch.equal(m.double(), m0)
+    if kind == "adam":
+        assert (v.double() - rv).abs().max().item() <= 2 * gtol * g.abs().max().item()
+    else:
+        assert torch.equal(v.double(), v0)
+    assert (sh.float() - p).abs().max().item() <= 2 ** -8 * p.abs().max().item()
+    for w in (pw, mw, vw):
+        assert bool((w[:, N:] == 3.0).all())
+    assert bool((sw[:, N:] == 3.0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("fmt", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (384, 264, 200), (130, 72, 64)])
+def test_gemm_sixteen_bit_wire_output(dtype, fmt, shape):
+    """The 16-bit output in both wire formats, through TMA stores (aligned rows) and thread stores (the rest)."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(8)
+    a = (torch.randn(K, M, device="cuda") / 4).to(dtype)
+    b = (torch.randn(K, N, device="cuda") / 4).to(dtype)
+    odt = torch.float16 if fmt == "f16" else torch.bfloat16
+    wide = torch.full((M, N + 24), 5.0, device="cuda", dtype=odt)
+    out = wide[:, :N]
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    gemm(a, b, a_mn_major=True, b_mn_major=True, status=status, **{"out_f16" if fmt == "f16" else "out_bf16": out})
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    ref = a.double().t() @ b.double()
+    tol = (2 ** -10 if fmt == "f16" else 2 ** -7) * ref.abs().max().item() + 4e-3 * ref.abs().max().item()
+    assert (out.double() - ref).abs().max().item() <= tol
+    assert bool((wide[:, N:] == 5.0).all())
+
+
+@pytest.mark.parametrize("shape,split,pair", [((64, 576, 8192), 37, -1), ((342, 128, 3136), 0, -1), ((512, 768, 2048), 4, 1)])
+def test_split_k_repeats_bit_for_bit_and_is_safe_on_two_streams(shape, split, pair):
+    """Every split writes its own slab and the finishing pass adds the slabs in order: two runs give the same bits, and two
+    such GEMMs on two streams (each with its own workspace) do not disturb one another."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    torch.manual_seed(9)
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    a2 = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    ref, ref2 = a.double().t() @ b.double(), a2.double().t() @ b.double()
+    outs = []
+    for _ in range(3):
+        out = torch.full((M, N), 7.0, device="cuda")
+        gemm(a, b, a_mn_major=True, b_mn_major=True, out=out, split_k=split, pair=pair)
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert (outs[0].double() - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    o1 = [torch.empty(M, N, device="cuda") for _ in range(8)]
+    o2 = [torch.empty(M, N, device="cuda") for _ in range(8)]
+    for i in range(8):
+        with torch.cuda.stream(s1):
+            gemm(a, b, a_mn_major=True, b_mn_major=True, out=o1[i], split_k=split, pair=pair, stream=s1)
+        with torch.cuda.stream(s2):
+            gemm(a2, b, a_mn_major=True, b_mn_major=True, out=o2[i], split_k=split, pair=pair, stream=s2)
+    torch.cuda.synchronize()
+    for i in range(8):
+        assert torch.equal(o1[i], outs[0])
+        assert (o2[i].double() - ref2).abs().max().item() <= 2e-3 * ref2.abs().max().item()
+        assert torch.equal(o2[i], o2[0])

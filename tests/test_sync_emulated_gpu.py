@@ -101,3 +101,62 @@ def test_layer_granular_ranges():
 
     offs = [(0, 0, 1000), (1, 1000, 5000), (0, 5000, 5200), (0, 5200, 9000)]
     _run(2, 9000, lambda n, N: layer_ranges(offs, N), "momentum")
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "f16"])
+@pytest.mark.parametrize("kind", ["momentum", "adam"])
+def test_sixteen_bit_gradient_windows(fmt, kind):
+    """Four ranks whose gradient windows hold 16-bit values (the wire format of step cadence): the owners sum them in f32
+    in rank order, average, apply the optimizer and publish f32 + bf16 parameters."""
+    from oxidized_neural_orchestra_b200.ops import _lib
+    from oxidized_neural_orchestra_b200.ops.elementwise import adam_tick, cast16
+    from oxidized_neural_orchestra_b200.parallel import sync as S
+    from oxidized_neural_orchestra_b200.parallel.sync import even_ranges
+
+    torch.manual_seed(3)
+    N, n, nblocks = 4, 70004, 4
+    dt = torch.float16 if fmt == "f16" else torch.bfloat16
+    g16 = [torch.zeros(n, device="cuda", dtype=dt) for _ in range(N)]
+    p0 = torch.randn(n, device="cuda")
+    p = [p0.clone() for _ in range(N)]
+    pb = [torch.zeros(n, device="cuda", dtype=torch.bfloat16) for _ in range(N)]
+    m = [torch.zeros(n, device="cuda") for _ in range(N)]
+    v = [torch.zeros(n, device="cuda") for _ in range(N)]
+    flags = [torch.zeros(nblocks * 8, device="cuda", dtype=torch.int32) for _ in range(N)]
+    epoch = [torch.zeros(nblocks, device="cuda", dtype=torch.int32) for _ in range(N)]
+    status = [torch.zeros(1, device="cuda", dtype=torch.int32) for _ in range(N)]
+    pows = torch.ones(2, device="cuda")
+    ranges = even_ranges(n, list(range(N)), N)
+    s = _lib.OnoSync()
+    S.fill_sync(s, nranks=N, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=[t.data_ptr() for t in g16],
+                p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[t.data_ptr() for t in pb],
+                flag_ptrs=[t.data_ptr() for t in flags], worker_mask=(1 << N) - 1, member_mask=(1 << N) - 1, n_workers=N,
+                opt=S.OptimizerCfg(kind=kind, lr=0.05, mu=0.9))
+    s.g_dtype = 2 if fmt == "f16" else 1
+    for r in range(N):
+        S.fill_local(s.loc[r], p_master=p[r].data_ptr(), m=m[r].data_ptr(), v=v[r].data_ptr(), state_off=0,
+                     adam_pows=pows.data_ptr(), epoch=epoch[r].data_ptr(), ranges=ranges[r], status=status[r].data_ptr())
+    ref_p, ref_m, ref_v = p0.double().clone(), torch.zeros(n, device="cuda").double(), torch.zeros(n, device="cuda").double()
+    b1t = b2t = 1.0
+    for step in range(2):
+        gs = [torch.randn(n, device="cuda") * 0.01 for _ in range(N)]
+        for r in range(N):
+            cast16(gs[r], g16[r], f16=fmt == "f16")
+            assert torch.equal(g16[r], gs[r].to(dt))          # the cast kernel rounds like PyTorch does
+        if kind == "adam":
+            adam_tick(pows, 0.9, 0.999)
+        S.launch_sync(s, emulated=True)
+        avg = sum(t.double() for t in g16) / N
+        if kind == "momentum":
+            ref_m = 0.9 * ref_m + avg
+            ref_p -= 0.05 * ref_m
+        else:
+            b1t *= 0.9; b2t *= 0.999
+            ref_m = 0.9 * ref_m + 0.1 * avg
+            ref_v = 0.999 * ref_v + 0.001 * avg * avg
+            ref_p -= 0.05 * math.sqrt(1 - b2t) / (1 - b1t) * ref_m / (ref_v.sqrt() + 1e-8)
+    torch.cuda.synchronize()
+    for r in range(N):
+        assert status[r].item() == 0
+        assert (p[r].double() - ref_p).abs().max().item() < (2e-3 if kind == "adam" else 1e-5), f"rank {r}"
+        assert (pb[r].float() - p[r]).abs().max().item() <= 2 ** -7 * p[r].abs().max().item()
