@@ -240,7 +240,9 @@ def main() -> None:
             "vs_baseline": None, "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
             "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
                        "optimizer": cfg["opt"][0], "l2": l2_note,
-                       "sync": m["sync_mode"], "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
+                       "sync": m["sync_mode"], "wire": m.get("wire"), "wire_push": bool(m.get("wire_push", False)),
+                       "wgrad_apply": bool(m.get("wgrad_apply", False)),
+                       "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "samples/s", "h2d_bytes_per_step": e["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": e["d2h_bytes_per_step"], "ms_per_step": e["bench_wall_s"] * 1e3 / K,

@@ -2,6 +2,7 @@
 """Kernel-level benchmarks (CUDA-event timed, warm-up excluded, max over ranks).
 
     python bench/kernels.py gemm  [--m 4096 --n 4096 --k 4096 --dtype bf16 --iters 20]
+    python bench/kernels.py wgrad [--m 8192 --n 8192 --k 512 --dtype bf16 --opt momentum]   (weight-gradient output forms)
     python bench/kernels.py sync  [--elems 67108864 --opt adam --iters 20]            (1 GPU: fused optimizer pass)
     torchrun --nproc-per-node N bench/kernels.py sweep [--max-bytes 1073741824]        (all-reduce sweep)
 
@@ -64,6 +65,46 @@ def cmd_gemm(a):
     fl = 2.0 * a.m * a.n * a.k
     print(json.dumps({"kernel": "gemm_tcgen05", "m": a.m, "n": a.n, "k": a.k, "dtype": a.dtype, "pair": a.pair, "ms": ms,
                       "tflops": fl / ms / 1e9, "cublas_ms": ref, "cublas_tflops": fl / ref / 1e9}))
+
+
+def cmd_wgrad(a):
+    """The weight-gradient GEMM dW[in,out] = X^T d (operands as the engines store them: [batch, in] and [batch, out]) in its
+    three output forms: f32 store, 16-bit wire store, optimizer applied in the epilogue (master + state + bf16 shadow updated
+    in place), the last one against the f32 store followed by the separate fused optimizer pass."""
+    from oxidized_neural_orchestra_b200.ops import elementwise as ew
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    dt = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    M, N, K = a.m, a.n, a.k
+    x = (torch.randn(K, M, device="cuda") / 8).to(dt)
+    d = (torch.randn(K, N, device="cuda") / 8).to(dt)
+    g32 = torch.zeros(M, N, device="cuda")
+    g16 = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    p, m, v = torch.randn(M, N, device="cuda"), torch.zeros(M, N, device="cuda"), torch.zeros(M, N, device="cuda")
+    sh = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16)
+    pows = torch.full((2,), 0.5, device="cuda")
+    ap = dict(p=p, m=m, v=v, p_bf16=sh if a.dtype == "bf16" else None, kind=a.opt, lr=1e-3, mu=0.9, adam_pows=pows)
+    kw = dict(a_mn_major=True, b_mn_major=True, pair=a.pair)
+    forms = {
+        "store_f32": lambda: gemm(x, d, out=g32, **kw),
+        "store_bf16": lambda: gemm(x, d, out_bf16=g16, **kw),
+        "apply": lambda: gemm(x, d, apply=ap, **kw),
+        "store_f32+optimizer_pass": lambda: (gemm(x, d, out=g32, **kw),
+                                             ew.optim_step(p.view(-1), g32.view(-1), kind=a.opt, lr=1e-3, mu=0.9, m=m.view(-1),
+                                                           v=v.view(-1), adam_pows=pows, p_bf16=sh.view(-1) if a.dtype == "bf16" else None)),
+    }
+    state = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + (2 if a.dtype == "bf16" else 0)
+    fl = 2.0 * M * N * K
+    flush = torch.empty(64 << 20, device="cuda")
+    for name, fn in forms.items():
+        for _ in range(3):
+            fn()
+        ms = _time(fn, a.iters, flush=flush if M * N * 4 < (256 << 20) else None)
+        rec = {"kernel": "gemm_tcgen05 wgrad", "form": name, "m": M, "n": N, "k": K, "dtype": a.dtype, "opt": a.opt, "ms": ms,
+               "tflops": fl / ms / 1e9}
+        if name == "apply":
+            rec["state_GBs"] = state * M * N / ms / 1e6
+        print(json.dumps(rec))
 
 
 def cmd_sync(a):
@@ -231,6 +272,11 @@ def main():
     g.add_argument("--m", type=int, default=4096); g.add_argument("--n", type=int, default=4096)
     g.add_argument("--k", type=int, default=4096); g.add_argument("--dtype", default="bf16")
     g.add_argument("--bn", type=int, default=0); g.add_argument("--pair", type=int, default=0, choices=(-1, 0, 1), help="CTA pairs: 1 on, -1 off, 0 the library default"); g.add_argument("--iters", type=int, default=20)
+    wg = sub.add_parser("wgrad")
+    wg.add_argument("--m", type=int, default=8192); wg.add_argument("--n", type=int, default=8192)
+    wg.add_argument("--k", type=int, default=512); wg.add_argument("--dtype", default="bf16")
+    wg.add_argument("--opt", default="momentum"); wg.add_argument("--pair", type=int, default=0, choices=(-1, 0, 1))
+    wg.add_argument("--iters", type=int, default=10)
     s = sub.add_parser("sync")
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
@@ -242,7 +288,7 @@ def main():
     a = ap.parse_args()
     if a.cmd == "sync" and a.emulate_ranks > 1:
         return cmd_sync_emulated(a)
-    {"gemm": cmd_gemm, "sync": cmd_sync, "sweep": cmd_sweep}[a.cmd](a)
+    {"gemm": cmd_gemm, "wgrad": cmd_wgrad, "sync": cmd_sync, "sweep": cmd_sweep}[a.cmd](a)
 
 
 if __name__ == "__main__":

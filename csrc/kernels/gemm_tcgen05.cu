@@ -216,10 +216,16 @@ __device__ __forceinline__ void epilogue_chunk(const OnoEpilogue& e, float (&v)[
 // PAIR = true: two CTAs of a cluster work on one 256 x BN tile (tcgen05 cta_group::2). Each CTA stages its own
 // 128 rows of A and its own BN/2 rows of B, so every byte of B crosses L2 -> SM once per pair instead of
 // once per CTA; the leader CTA (cluster rank 0) issues the MMAs for both, each CTA drains its own TMEM.
-template <int ESIZE, int BN, bool PAIR>
+// APPLY = true: the instantiation whose epilogue applies the optimizer through TMA: the operand ring shrinks to two
+// stages and every epilogue warp gets APPLY_WARP_BYTES of shared memory for the tiles of the master, the optimizer state
+// and the bf16 shadow that belong to the 32 x 32 accumulator chunk it is working on (see the epilogue below).
+struct ApplyMaps { CUtensorMap p, m, v, s; };
+constexpr uint32_t APPLY_WARP_BYTES = 20480;
+
+template <int ESIZE, int BN, bool PAIR, bool APPLY>
 __global__ void __launch_bounds__(320, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const GemmDev p) {
+                    const __grid_constant__ CUtensorMap tmC, const __grid_constant__ ApplyMaps am, const GemmDev p) {
   constexpr int BM = 128;              // rows per CTA
   constexpr int TILE_M = PAIR ? 256 : 128;
   constexpr int BK = 128 / ESIZE;      // one 128-byte swizzle row of K per stage
@@ -227,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int KSTEPS = BK / UMMA_K;  // 4
   constexpr int BN_CTA = PAIR ? BN / 2 : BN;   // rows of B staged by one CTA
   constexpr uint32_t A_BYTES = BM * 128, B_BYTES = BN_CTA * 128, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
+  constexpr int STAGES = APPLY ? 2 : TileCfg<BN_CTA>::STAGES;
   constexpr uint32_t TMEM_COLS = TileCfg<BN>::TMEM_COLS;
   const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
   const bool leader = crank == 0u;
@@ -244,6 +250,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __shared__ __align__(8) uint64_t tmem_full_bar[2];
   __shared__ __align__(8) uint64_t tmem_empty_bar[2];
   __shared__ __align__(8) uint64_t drain_bar;
+  __shared__ __align__(8) uint64_t apply_bar[APPLY ? 16 : 1];   // [epilogue warp][buffer]: tiles of a chunk have landed
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
 
@@ -261,6 +268,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       mbar_init(&tmem_empty_bar[b], PAIR ? 512 : 256);   // 8 epilogue warps; a pair's leader counts both CTAs'
     }
     mbar_init(&drain_bar, 1);
+    if (APPLY)
+      for (int b = 0; b < 16; ++b) mbar_init(&apply_bar[b], 1);
     abort_flag = 0;
     mbar_fence_init();
   }
@@ -268,6 +277,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
     if (p.tma_out) tma_prefetch_desc(&tmC);
+    if (APPLY) { tma_prefetch_desc(&am.p); tma_prefetch_desc(&am.m); tma_prefetch_desc(&am.v); tma_prefetch_desc(&am.s); }
   }
   if (warp == 5) {
     if (PAIR) { tmem_alloc_pair(&tmem_base_smem, TMEM_COLS); tmem_relinquish_pair(); }
@@ -407,6 +417,133 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint8_t* const wstage = cstage + (size_t)(grp * 4 + quad) * 4096u;
     const uint32_t tmem_empty_remote[2] = {PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[0]), 0u) : 0u,
                                            PAIR ? mapa_shared(smem_u32(&tmem_empty_bar[1]), 0u) : 0u};
+    if constexpr (APPLY) {
+      // ---------------- optimizer in the epilogue, tiles moved by TMA ----------------
+      // For every 32 x 32 chunk of dW the warp brings the matching tiles of the f32 master and of the optimizer state
+      // into shared memory with TMA loads (issued one chunk ahead when two buffers fit, also across output tiles, since
+      // they do not depend on the MMAs), updates them in place with the gradient values it reads from TMEM (a lane
+      // holds one row in both), writes the bf16 shadow tile next to them and sends everything back with TMA stores.
+      // Out-of-range rows and columns are zero-filled by the loads and clipped by the stores.
+      const OnoApply& ap = p.apply;
+      const int narr = 1 + (ap.kind >= 1 ? 1 : 0) + (ap.kind == 2 ? 1 : 0);
+      const uint32_t slot_bytes = (uint32_t)narr * 4096u + 2048u;
+      const int nbuf = APPLY_WARP_BYTES / slot_bytes >= 2 ? 2 : 1;
+      const int ew = grp * 4 + quad;                                   // epilogue warp index 0..7
+      uint8_t* const wbase = cstage + (size_t)ew * APPLY_WARP_BYTES;
+      uint64_t* const bars = &apply_bar[ew * 2];
+      OptScal os{ap.kind, ap.lr, ap.mu, ap.b1, ap.b2, ap.eps, ap.grad_scale, 0.0f};
+      if (ap.kind == 2) os.adam_step = ap.lr * sqrtf(1.0f - __ldg(ap.adam_pows + 1)) / (1.0f - __ldg(ap.adam_pows));
+      // chunk iterator over this warp's (work item, column chunk) sequence
+      // (each group of four warps walks its own contiguous half of the tile's columns, so that a warp's successive
+      // chunks continue the same rows in memory)
+      constexpr int CPG = BN / 64;                 // chunks per group and tile
+      auto first_chunk = [&](int& w, int& c) {
+        c = grp * CPG;
+        while (w < total_work && (w / num_m) * BN + c * 32 >= p.N) w += units;
+      };
+      auto next_chunk = [&](int& w, int& c) {
+        c += 1;
+        if (c >= (grp + 1) * CPG || (w / num_m) * BN + c * 32 >= p.N) { w += units; first_chunk(w, c); }
+      };
+      auto issue = [&](int w, int c, int b) {      // lane 0: loads of chunk (w, c) into buffer b
+        const int y = (w % num_m) * TILE_M + (int)crank * BM + quad * 32;
+        const int x = (w / num_m) * BN + c * 32;
+        uint8_t* dst = wbase + (size_t)b * slot_bytes;
+        mbar_expect_tx(&bars[b], (uint32_t)narr * 4096u);
+        tma_load_2d(dst, &am.p, &bars[b], x, y);
+        if (ap.kind >= 1) tma_load_2d(dst + 4096, &am.m, &bars[b], x, y);
+        if (ap.kind == 2) tma_load_2d(dst + 8192, &am.v, &bars[b], x, y);
+      };
+      int pw = unit, pc = 0;                       // next chunk to prefetch
+      first_chunk(pw, pc);
+      long long issued = 0, done = 0;
+      if (lane == 0)
+        for (; issued < nbuf && pw < total_work; ++issued) { issue(pw, pc, (int)issued); next_chunk(pw, pc); }
+      for (int work = unit; work < total_work && ok; work += units, ++t) {
+        const int m0 = (work % num_m) * TILE_M + (int)crank * BM;
+        const int n0 = (work / num_m) * BN;
+        const int buf = t & 1;
+        const uint32_t acc_phase = (t >> 1) & 1;
+        const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+        for (int c = grp * CPG; c < (grp + 1) * CPG; ++c) {
+          const int nc = n0 + c * 32;
+          if (nc >= p.N) break;
+          const int b = (int)(done % nbuf);
+          const bool landed = mbar_wait_bounded(&bars[b], (uint32_t)((done / nbuf) & 1), abortp, budget);
+          if (!__all_sync(0xffffffffu, landed)) {
+            if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          uint32_t r[32];
+          tmem_ld_x32(t_row + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          uint8_t* const tp = wbase + (size_t)b * slot_bytes + lane * 128;      // this lane's row of the master tile
+          uint8_t* const ts = wbase + (size_t)b * slot_bytes + (size_t)narr * 4096u + lane * 64;   // and of the shadow tile
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            float4 out[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int j = 2 * jj + h;
+              const uint32_t o = (uint32_t)((j ^ (lane & 7)) << 4);
+              const float4 g = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                           __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              float4 P = *reinterpret_cast<const float4*>(tp + o);
+              float4 Mo = make_float4(0.f, 0.f, 0.f, 0.f), Vo = Mo;
+              if (ap.kind >= 1) Mo = *reinterpret_cast<const float4*>(tp + 4096 + o);
+              if (ap.kind == 2) Vo = *reinterpret_cast<const float4*>(tp + 8192 + o);
+              P = opt_apply4(os, P, g, Mo, Vo);
+              *reinterpret_cast<float4*>(tp + o) = P;
+              if (ap.kind >= 1) *reinterpret_cast<float4*>(tp + 4096 + o) = Mo;
+              if (ap.kind == 2) *reinterpret_cast<float4*>(tp + 8192 + o) = Vo;
+              out[h] = P;
+            }
+            if (ap.p_bf16) {
+              const uint2 lo = pack_bf16x4(out[0]), hi = pack_bf16x4(out[1]);
+              *reinterpret_cast<uint4*>(ts + ((jj ^ ((lane >> 1) & 3)) << 4)) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int y = m0 + quad * 32;
+            uint8_t* src = wbase + (size_t)b * slot_bytes;
+            tma_store_2d(&am.p, src, nc, y);
+            if (ap.kind >= 1) tma_store_2d(&am.m, src + 4096, nc, y);
+            if (ap.kind == 2) tma_store_2d(&am.v, src + 8192, nc, y);
+            if (ap.p_bf16) tma_store_2d(&am.s, src + (size_t)narr * 4096u, nc, y);
+            tma_store_commit();
+            if (pw < total_work) {                  // refill this buffer once its stores have read it
+              tma_store_wait_read<0>();
+              issue(pw, pc, b);
+              next_chunk(pw, pc);
+              ++issued;
+            }
+          }
+          __syncwarp();
+          ++done;
+        }
+        tc_fence_before();
+        if (PAIR) mbar_arrive_cluster(tmem_empty_remote[buf]);
+        else mbar_arrive(&tmem_empty_bar[buf]);
+      }
+      if (lane == 0) {
+        tma_store_wait_all<0>();
+        if (!ok) {      // loads already issued into this warp's buffers must land before the CTA retires its shared memory
+          const uint64_t t0 = globaltimer_ns();
+          while (globaltimer_ns() - t0 < 200000ull) { __nanosleep(1000); }
+        }
+      }
+    } else
     for (int work = unit; work < total_work && ok; work += units, ++t) {
       const int tile = work / SPLITS;
       const int m0 = (tile % num_m) * TILE_M + (int)crank * BM;
@@ -527,7 +664,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (PAIR) mbar_arrive_cluster(tmem_empty_remote[buf]);
       else mbar_arrive(&tmem_empty_bar[buf]);
     }
-    if (p.tma_out && lane == 0) tma_store_wait_all<0>();  // global writes done before exit
+    if (!APPLY && p.tma_out && lane == 0) tma_store_wait_all<0>();  // global writes done before exit
   }
 
   tc_fence_before();
@@ -694,18 +831,20 @@ static int num_sms() {
   return sms[dev];
 }
 
-template <int ESIZE, int BN, bool PAIR>
+static ApplyMaps g_no_apply_maps;   // zero-filled: instantiations without the TMA optimizer epilogue never touch it
+
+template <int ESIZE, int BN, bool PAIR, bool APPLY = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmDev& p, int max_ctas,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const ApplyMaps& am = g_no_apply_maps) {
   constexpr int BN_CTA = PAIR ? BN / 2 : BN;
-  constexpr int STAGES = TileCfg<BN_CTA>::STAGES;
-  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN_CTA * 128) + 2 * 16384 + 1024;
+  constexpr int STAGES = APPLY ? 2 : TileCfg<BN_CTA>::STAGES;
+  constexpr size_t smem = (size_t)STAGES * (128 * 128 + BN_CTA * 128) + (APPLY ? 8 * APPLY_WARP_BYTES : 2 * 16384) + 1024;
   static bool attr_done[kMaxDevices] = {false};
   static int max_pairs_dev[kMaxDevices] = {0};
   const int dev = current_device();
   bool& attr_set = attr_done[dev];
   int& max_pairs = max_pairs_dev[dev];
-  auto kern = gemm_tcgen05_kernel<ESIZE, BN, PAIR>;
+  auto kern = gemm_tcgen05_kernel<ESIZE, BN, PAIR, APPLY>;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return -6; }
@@ -731,7 +870,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
   if (!PAIR) {
     int grid = max_ctas > 0 ? max_ctas : num_sms();
     if (grid > tiles) grid = tiles;
-    kern<<<grid, 320, smem, stream>>>(ta, tb, tc, p);
+    kern<<<grid, 320, smem, stream>>>(ta, tb, tc, am, p);
   } else {
     int pairs = max_ctas > 0 ? std::max(1, max_ctas / 2) : max_pairs;
     if (pairs > max_pairs) pairs = max_pairs;
@@ -746,7 +885,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMa
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, am, p);
     if (le != cudaSuccess) { set_error("gemm pair launch: %s", cudaGetErrorString(le)); return -7; }
   }
   cudaError_t e = cudaGetLastError();
@@ -892,7 +1031,27 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)p.a.mn_major << 15) |
             ((uint32_t)p.b.mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((pair ? 256 : 128) >> 4) << 24);
 
+  // The TMA form of the optimizer epilogue: bf16 CTA pairs with 256-column tiles (the weight gradients of wide layers),
+  // a reduction short enough for the two-stage operand ring, shadow rows that a bf16 tensor map can address.
+  ApplyMaps am;
+  // Momentum and SGD fit two chunk buffers per warp (loads run one chunk ahead); Adam's three state tiles fit only one,
+  // which measured slower than reading them from registers (8192 x 8192 x 512: 0.48 ms against 0.44 ms), so Adam stays
+  // on the register form. A TMA store writes whole 16-byte units, hence the shadow needs N % 8 == 0 here.
+  const bool apply_tma = ap.p && pair && esize == 2 && bn == 256 && g->K <= 2048 && ap.kind <= 1 &&
+                         (!ap.p_bf16 || (g->N % 8 == 0 && ap.ld % 8 == 0 && ((uintptr_t)ap.p_bf16 & 15) == 0));
+  if (apply_tma) {
+    memset(&am, 0, sizeof(am));
+    if ((rc = encode_out_map(&am.p, ap.p, 4, g->M, g->N, ap.ld))) return rc;
+    if (ap.kind >= 1 && (rc = encode_out_map(&am.m, ap.m, 4, g->M, g->N, ap.ld))) return rc;
+    if (ap.kind == 2 && (rc = encode_out_map(&am.v, ap.v, 4, g->M, g->N, ap.ld))) return rc;
+    if (ap.p_bf16 && (rc = encode_out_map(&am.s, ap.p_bf16, 2, g->M, g->N, ap.ld))) return rc;
+    // unused maps still get prefetched by the kernel: point them at the master's map
+    if (ap.kind < 1) am.m = am.p;
+    if (ap.kind < 2) am.v = am.p;
+    if (!ap.p_bf16) am.s = am.p;
+  }
   auto run = [&]() -> int {
+    if (apply_tma) return launch<2, 256, true, true>(ta, tb, tc, p, g->max_ctas, stream, am);
     if (pair) {
       if (esize == 4) return bn == 128 ? launch<4, 128, true>(ta, tb, tc, p, g->max_ctas, stream)
                                        : launch<4, 256, true>(ta, tb, tc, p, g->max_ctas, stream);

@@ -408,6 +408,7 @@ class GpuRank:
         # kernel afterwards only handles what is left (biases, layers whose rows are not 16-byte aligned)
         self.apply_active = False
         if (W == 1 and dense_engine and self.cadence == "step" and mode in ("fused", "oneshot") and not self.grad_norm_switch
+                and not self.push_active and not self.compress
                 and self.b200.get("wgrad_apply", "auto") != "off" and os.environ.get("ONO_WGRAD_APPLY", "1") != "0"):
             plan_, rest = self._build_apply(opt, len(workers), wild)
             if plan_:

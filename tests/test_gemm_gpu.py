@@ -230,18 +230,21 @@ def _opt_ref(kind, p, g, m, v, lr, mu, b1, b2, eps, gs, pows):
 
 
 @pytest.mark.parametrize("kind", ["sgd", "momentum", "adam"])
-@pytest.mark.parametrize("dtype,pair", [(torch.bfloat16, 1), (torch.bfloat16, -1), (torch.float32, -1)])
+@pytest.mark.parametrize("dtype,pair,bn", [(torch.bfloat16, 1, 0), (torch.bfloat16, 1, 256), (torch.bfloat16, -1, 0), (torch.float32, -1, 0)])
 @pytest.mark.parametrize("shape", [(512, 768, 256), (300, 260, 96), (1024, 1000, 512)])
-def test_gemm_epilogue_applies_the_optimizer_to_its_own_tile(kind, dtype, pair, shape):
+def test_gemm_epilogue_applies_the_optimizer_to_its_own_tile(kind, dtype, pair, bn, shape):
     """Weight-gradient form dW = A^T d with the optimizer in the epilogue: master, state and bf16 shadow are updated in place,
-    nothing else is written (the matrices are views into wider buffers whose other columns must stay untouched)."""
+    nothing else is written (the matrices are views into wider buffers whose other columns must stay untouched). bf16 CTA
+    pairs with 256-column tiles take the form that moves the master / state / shadow tiles with TMA, the rest the form that
+    reads and writes them from registers."""
     from oxidized_neural_orchestra_b200.ops.gemm import gemm
 
     M, N, K = shape
     torch.manual_seed(7)
     ld = (N + 15) // 16 * 16 + 16
-    a = (torch.randn(K, M, device="cuda") / 4).to(dtype)       # MN-major operands, as the engines pass them
-    d = (torch.randn(K, N, device="cuda") / 4).to(dtype)
+    up = lambda n: (n + 15) // 16 * 16
+    a = (torch.randn(K, up(M), device="cuda") / 4).to(dtype)[:, :M]       # MN-major operands, as the engines pass them
+    d = (torch.randn(K, up(N), device="cuda") / 4).to(dtype)[:, :N]
     wide = lambda dt=torch.float32: torch.full((M, ld), 3.0, device="cuda", dtype=dt)
     pw, mw, vw, sw = wide(), wide(), wide(), wide(torch.bfloat16)
     p, m, v, sh = pw[:, :N], mw[:, :N], vw[:, :N], sw[:, :N]
@@ -251,7 +254,7 @@ def test_gemm_epilogue_applies_the_optimizer_to_its_own_tile(kind, dtype, pair, 
     pows = torch.tensor([0.9 ** 3, 0.999 ** 3], device="cuda")
     p0, m0, v0 = p.double().clone(), m.double().clone(), v.double().clone()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    gemm(a, d, a_mn_major=True, b_mn_major=True, pair=pair, status=status,
+    gemm(a, d, a_mn_major=True, b_mn_major=True, pair=pair, bn=bn, status=status,
          apply=dict(p=p, m=m, v=v, p_bf16=sh, kind=kind, lr=0.05, mu=0.9, b1=0.9, b2=0.999, eps=1e-8, grad_scale=0.25,
                     adam_pows=pows))
     torch.cuda.synchronize()
@@ -285,8 +288,9 @@ def test_gemm_sixteen_bit_wire_output(dtype, fmt, shape):
 
     M, N, K = shape
     torch.manual_seed(8)
-    a = (torch.randn(K, M, device="cuda") / 4).to(dtype)
-    b = (torch.randn(K, N, device="cuda") / 4).to(dtype)
+    up = lambda n: (n + 15) // 16 * 16
+    a = (torch.randn(K, up(M), device="cuda") / 4).to(dtype)[:, :M]
+    b = (torch.randn(K, up(N), device="cuda") / 4).to(dtype)[:, :N]
     odt = torch.float16 if fmt == "f16" else torch.bfloat16
     wide = torch.full((M, N + 24), 5.0, device="cuda", dtype=odt)
     out = wide[:, :N]
@@ -308,9 +312,10 @@ def test_split_k_repeats_bit_for_bit_and_is_safe_on_two_streams(shape, split, pa
 
     M, N, K = shape
     torch.manual_seed(9)
-    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
-    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
-    a2 = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+    up = lambda n: (n + 15) // 16 * 16
+    a = torch.randn(K, up(M), device="cuda", dtype=torch.bfloat16)[:, :M]
+    b = torch.randn(K, up(N), device="cuda", dtype=torch.bfloat16)[:, :N]
+    a2 = torch.randn(K, up(M), device="cuda", dtype=torch.bfloat16)[:, :M]
     ref, ref2 = a.double().t() @ b.double(), a2.double().t() @ b.double()
     outs = []
     for _ in range(3):
