@@ -103,6 +103,7 @@ class _Update:
         self.m = torch.zeros_like(self.p) if self.kind != "sgd" else None
         self.v = torch.zeros_like(self.p) if self.kind == "adam" else None
         self.pows = torch.ones(2, device=master.device)
+        self.betas = torch.tensor([0.9, 0.999], device=master.device)
         self.tmp = torch.empty_like(self.p) if self.kind == "adam" else None
 
     def step(self):
@@ -114,7 +115,7 @@ class _Update:
             p.add_(self.m, alpha=-self.lr)
         else:
             b1, b2, eps = 0.9, 0.999, 1e-8
-            self.pows.mul_(torch.tensor([b1, b2], device=p.device))
+            self.pows.mul_(self.betas)
             self.m.mul_(b1).add_(g, alpha=(1 - b1) * self.scale)
             self.tmp.copy_(g).mul_(self.scale)
             self.v.mul_(b2).addcmul_(self.tmp, self.tmp, value=1 - b2)
@@ -170,7 +171,6 @@ def run(cfg, strategy, n_servers, steps, warmup, data_mode, switch=None, wire="b
     shard_upd = None
     if is_server:
         lo = rank * piece
-        shard_upd = _Update(cfg, master, comp, torch.zeros(1), 0, 0, 1.0)     # placeholder, rebuilt below
         shard_upd = _Update(cfg, master, comp, _Shift(shard_g, lo), lo, lo + piece * group_sz, 1.0 / world)
 
     def exchange_ps():

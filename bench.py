@@ -14,6 +14,10 @@ Two measurements, both through the public API (``orchestra.orchestrate(...).wait
   value  device-timed K steps with the dataset resident in HBM (inputs gathered on the device)
   e2e    the same run with the dataset in pinned host memory: every step's inputs cross PCIe inside
          the timed region and the step's loss is read back to the host
+The reference publishes no number for this configuration (its figures are CPU runs of LeNet-5 / Nielsen), so
+``vs_baseline`` is measured in the same invocation: the NCCL + cuBLAS arm (``baseline/torch_nccl.py``: the same model,
+strategy, batch and wire width written with library calls only) runs right after ours with the same N, K and W, and
+``vs_baseline`` = our value / that arm's value (``baseline`` holds its numbers; ``--no-baseline`` skips it).
 Timing: CUDA events on the training stream, after W warm-up steps, with synchronize + barrier on both
 sides, max over ranks. Every step reads inputs (8 MB+ activations) and 2.7 GB of weights/gradients,
 far above the 126 MB L2, so no explicit L2 flush is needed between steps.
@@ -104,6 +108,8 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
         b200["grad_stage"] = cfg["grad_stage"]
     if cfg.get("phase_timing"):
         b200["phase_timing"] = True
+    if cfg.get("wire"):
+        b200["wire_dtype"] = cfg["wire"]
     strat = cfg["strategy"]
     if strat.startswith("ps") or strat.startswith("ss"):
         ns = min(int(strat[2:] or 2), n_gpus)
@@ -171,6 +177,8 @@ def main() -> None:
                     help="diagnostic: run the steps uncaptured with CUDA events around compute / exchange / refresh and add "
                          "their mean durations (phase_ms) to the line; such a line is not a benchmark value")
     ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
+    ap.add_argument("--no-baseline", action="store_true", help="do not run the NCCL + cuBLAS arm after ours (vs_baseline: null)")
+    ap.add_argument("--wire", default=None, choices=("auto", "f32", "f16", "bf16"), help="gradient wire between GPUs")
     args = ap.parse_args()
     if args.impl == "reference":
         if int(os.environ.get("RANK", "0")) == 0:      # one line per job, also when launched once per GPU
@@ -197,12 +205,16 @@ def main() -> None:
         cfg["grad_stage"] = args.stage
     if args.phases:
         cfg["phase_timing"] = True
+    if args.wire:
+        cfg["wire"] = args.wire
     W, K = max(3, args.warmup), args.steps
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import torch_nccl
+    st = cfg["strategy"]
+    nccl_args = (cfg, args.config, st[:2], int(st[2:] or 2) if st != "ar" else 1, K, W, SWITCH)
+    nccl_wire = "f32" if cfg.get("wire") == "f32" else "bf16"
     if args.impl == "nccl":
-        sys.path.insert(0, os.path.join(ROOT, "baseline"))
-        import torch_nccl
-        st = cfg["strategy"]
-        torch_nccl.main(cfg, args.config, st[:2], int(st[2:] or 2) if st != "ar" else 1, K, W, SWITCH, ClockSampler)
+        torch_nccl.main(*nccl_args, ClockSampler, nccl_wire)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -222,6 +234,9 @@ def main() -> None:
         torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
+    base = None
+    if not args.no_baseline and not args.phases:
+        base = torch_nccl.measure(*nccl_args, None, nccl_wire)       # every rank takes part; rank 0 gets the line
     if rank == 0:
         m, e = results["device"], results["host"]
         gb = cfg["batch"] * world
@@ -237,7 +252,8 @@ def main() -> None:
         out = {
             "metric": "samples/sec (device-timed, max over ranks)", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": m["bench_ms"] / K, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
+            "vs_baseline": (value / base["value"]) if base else None,
+            "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
             "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
                        "optimizer": cfg["opt"][0], "l2": l2_note,
                        "sync": m["sync_mode"], "wire": m.get("wire"), "wire_push": bool(m.get("wire_push", False)),
@@ -249,6 +265,11 @@ def main() -> None:
                     "device_ms_per_step": e["bench_ms"] / K},
             "gpu_launches": int(m["launches_per_step"]) * K,
         }
+        if base:
+            out["baseline"] = {"impl": base["impl"], "what": "same model / strategy / batch / wire with NCCL + cuBLAS (baseline/torch_nccl.py), "
+                               "run in this invocation right after ours", "value": base["value"], "ms_per_step": base["ms_per_step"],
+                               "e2e_value": base["e2e"]["value"], "e2e_ratio": e2e / base["e2e"]["value"],
+                               "cuda_graph": base["config"]["cuda_graph"], "wire": base["config"]["wire"]}
         if m.get("phase_ms"):
             out["phase_ms"] = m["phase_ms"]
             out["config"]["phase_timing"] = "steps ran uncaptured with per-phase events: diagnostic line, not a benchmark value"

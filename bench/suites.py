@@ -2,7 +2,7 @@
 """Strategy benchmark suites over the public API, in the spirit of the reference's harness
 (benchmarks/run_issue_benchmarks.py:64-229, benchmarks/issue/{suites,runner,metrics,results}.py).
 
-    python bench/suites.py [--suite strategies|scalability|offline] [--model lenet5|nielsen|both]
+    python bench/suites.py [--suite strategies|scalability|offline|published] [--model lenet5|nielsen|both]
                            [--nodes gpu|cpu] [--rows 4096] [--epochs 4] [--repeats 1] [--out bench/results]
 
 Every run trains LeNet-5 or the Nielsen network on seeded MNIST-shaped synthetic data (class prototypes plus
@@ -86,7 +86,24 @@ def suites(kind: str, n_nodes: int):
                [(f"ps_{w}w_2s", "ps", w, min(2, w), {}) for w in sorted({cap(3), cap(5)})]
     if kind == "offline":
         return [(f"all_reduce_offline{e}", "ar", cap(3), 0, {"offline_epochs": e}) for e in (0, 1, 4)]
+    if kind == "published":
+        # the throughput rows the reference publishes (benchmarks/README.md:80-85 execution speed, :116-125 scalability):
+        # 4 000 samples, 8 epochs, plain SGD; servers are separate nodes, so a PS row uses workers + 2 nodes
+        rows = [("AR 3w offline 0 b64", "ar", 3, 0, {}), ("AR 3w offline 4 b64", "ar", 3, 0, {"offline_epochs": 4}),
+                ("AR 3w offline 0 b256", "ar", 3, 0, {"batch": 256}), ("AR 5w", "ar", 5, 0, {}), ("AR 7w", "ar", 7, 0, {}),
+                ("PS blocking 3w+2s", "ps", 3, 2, {"pure_servers": True}), ("PS blocking 5w+2s", "ps", 5, 2, {"pure_servers": True})]
+        return [r for r in rows if r[2] + (r[3] if r[4].get("pure_servers") else 0) <= n_nodes]
     raise SystemExit(f"unknown suite {kind}")
+
+
+# samples/s the reference publishes for the rows of the `published` suite (benchmarks/README.md:80-85,116-125; CPU
+# containers on one ~8-core host)
+PUBLISHED = {
+    ("lenet5", "AR 3w offline 0 b64"): 9675, ("lenet5", "AR 3w offline 4 b64"): 9827, ("lenet5", "AR 3w offline 0 b256"): 8928,
+    ("nielsen", "AR 3w offline 0 b64"): 8353, ("nielsen", "AR 3w offline 4 b64"): 8527, ("nielsen", "AR 3w offline 0 b256"): 7721,
+    ("lenet5", "AR 5w"): 10012, ("lenet5", "AR 7w"): 10899, ("lenet5", "PS blocking 3w+2s"): 9970, ("lenet5", "PS blocking 5w+2s"): 11356,
+    ("nielsen", "AR 5w"): 8404, ("nielsen", "AR 7w"): 8605, ("nielsen", "PS blocking 3w+2s"): 8227, ("nielsen", "PS blocking 5w+2s"): 8920,
+}
 
 
 def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, epochs, batch):
@@ -100,18 +117,22 @@ def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, 
     from orchestra.sync import BarrierSync, NonBlockingSync
 
     xtr, ytr, xte, lte = data
-    addrs = [f"{prefix}:{i}" for i in range(workers)]
+    extra = dict(extra)
+    pure = extra.pop("pure_servers", False)
+    batch = extra.pop("batch", batch)
+    lr = extra.pop("lr", 0.5)
+    addrs = [f"{prefix}:{i}" for i in range(workers + (servers if pure else 0))]
     ds = InlineDataset(xtr, ytr, 784, 10)
     common = dict(max_epochs=epochs, batch_size=batch, seed=42, **extra)
-    b200 = {"colocate": True} if prefix == "gpu" else None
-    opt, loss = GradientDescent(0.5), CrossEntropy()   # the loss is normalised by batch x classes (cross_entropy.rs:35-47)
+    b200 = {"colocate": True} if (prefix == "gpu" and not pure) else None
+    opt, loss = GradientDescent(lr), CrossEntropy()   # the loss is normalised by batch x classes (cross_entropy.rs:35-47)
     if strategy == "ar":
         cfg = orchestra.all_reduce(addrs, ds, opt, loss, **common)
     else:
         sync = NonBlockingSync() if strategy == "ps_async" else BarrierSync()
         fn = orchestra.strategy_switch if strategy == "ss" else orchestra.parameter_server
         kw = dict(common, b200=b200) if b200 and servers >= workers else (dict(common, b200=b200) if b200 else common)
-        if prefix == "cpu" and servers >= workers:
+        if prefix == "cpu" and servers >= workers and not pure:
             return None                      # the reference needs at least one pure worker
         cfg = fn(addrs, servers, ds, opt, loss, sync, BlockingStore(), **kw)
     model = {"lenet5": lenet5, "nielsen": nielsen}[model_name]()
@@ -121,7 +142,14 @@ def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, 
     hist = trained.loss_history()
     acc = torch_accuracy(model_name, trained.weights_array(), xte, lte)
     done = len(hist)
-    return {"suite_label": label, "model": model_name, "strategy": strategy, "workers": workers, "servers": servers,
+    met = trained.metrics() or {}
+    # device time of the training steps alone (CUDA events; GPU ranks): the wall clock above also holds the start-up
+    # of one process per GPU, which the reference's figure (nodes already running) does not
+    step_ms = met.get("step_ms") or []
+    dev_s = sum(step_ms) / 1e3 if step_ms else None
+    return {"device_seconds": dev_s,
+            "samples_per_sec_device": (len(xtr) * done / dev_s * (len(step_ms) / (len(step_ms) + 1.0))) if dev_s else None,
+            "batch": batch, "nodes": len(addrs), "suite_label": label, "model": model_name, "strategy": strategy, "workers": workers, "servers": servers,
             "backend": prefix, "epochs": done, "samples": len(xtr), "train_seconds": secs,
             "samples_per_sec": len(xtr) * done / secs, "epochs_per_sec": done / secs, "final_loss": hist[-1] if hist else None,
             "accuracy": acc, "loss_per_sec": (hist[0] - hist[-1]) / secs if len(hist) > 1 else 0.0,
@@ -143,6 +171,8 @@ def main():
 
     prefix = a.nodes or ("gpu" if torch.cuda.is_available() else "cpu")
     n_nodes = torch.cuda.device_count() if prefix == "gpu" else 7
+    if a.suite == "published" and a.rows == 4096 and a.epochs == 4:
+        a.rows, a.epochs = 4000, 8               # the reference's budget for these rows
     os.makedirs(a.out, exist_ok=True)
     data = make_data(a.rows, 42)
     records = []
@@ -150,6 +180,8 @@ def main():
         for model_name in (("lenet5", "nielsen") if a.model == "both" else (a.model,)):
             for label, strategy, workers, servers, extra in suites(a.suite, n_nodes):
                 for rep in range(a.repeats):
+                    if a.suite == "published":      # the models' recipes: benchmarks/issue/suites.py:148-178
+                        extra = dict(extra, lr=0.05 if model_name == "lenet5" else 0.1)
                     rec = run_one(model_name, label, strategy, workers, servers, extra, prefix, data, a.epochs, a.batch)
                     if rec is None:
                         continue
@@ -159,6 +191,19 @@ def main():
                     records.append(rec)
                     print(f"{model_name:8s} {label:22s} {rec['samples_per_sec']:12.0f} samples/s  loss {rec['final_loss']:.5f}  "
                           f"acc {rec['accuracy']:.3f}", file=sys.stderr)
+    if a.suite == "published":
+        with open(os.path.join(a.out, f"published_{prefix}.md"), "w") as f:
+            f.write(f"# The reference's published throughput rows on `{prefix}` nodes ({a.rows} samples, {a.epochs} epochs, SGD)\n\n"
+                    "samples/s = samples x epochs / wall seconds of `orchestrate(...).wait()` (the reference's definition); "
+                    "`device` = the same count over the CUDA-event time of the training steps (GPU ranks only).\n\n"
+                    "| model | run | nodes | batch | samples/s (wall) | samples/s (device) | reference, published | wall / published | final loss | accuracy |\n"
+                    "|---|---|---|---|---|---|---|---|---|---|\n")
+            for r in records:
+                pub = PUBLISHED.get((r["model"], r["suite_label"]))
+                dev = f"{r['samples_per_sec_device']:.0f}" if r.get("samples_per_sec_device") else "-"
+                f.write(f"| {r['model']} | {r['suite_label']} | {r['nodes']} | {r['batch']} | {r['samples_per_sec']:.0f} | {dev} | "
+                        f"{pub if pub else '-'} | {(r['samples_per_sec'] / pub):.2f}x | {r['final_loss']:.5f} | {r['accuracy']:.3f} |\n"
+                        if pub else "")
     with open(os.path.join(a.out, "summary.md"), "w") as f:
         f.write(f"# Suite `{a.suite}` on `{prefix}` nodes ({a.rows} samples, {a.epochs} epochs, batch {a.batch})\n\n")
         f.write("| model | run | workers | servers | samples/s | epochs/s | final loss | accuracy | switched |\n|---|---|---|---|---|---|---|---|---|\n")

@@ -131,8 +131,12 @@ def philox_init(out: torch.Tensor, *, seed: int, index_offset: int, kind: str, a
 def rows(src: torch.Tensor, *, idx: torch.Tensor | None = None, n_rows: int | None = None,
          dst: torch.Tensor | None = None, dst_t: torch.Tensor | None = None,
          dst_bf16: torch.Tensor | None = None, dst_t_bf16: torch.Tensor | None = None, stream=None) -> None:
-    """Gather rows (optionally by int32 ``idx``), cast and/or transpose in one pass."""
-    _need_cuda(src)
+    """Gather rows (optionally by int32 ``idx``), cast and/or transpose in one pass.
+
+    ``src`` may be a pinned host tensor: under unified addressing the kernel then reads the selected rows straight out of
+    host memory over PCIe (the host-to-device copy and the gather are one pass; ``idx`` and the outputs are on the GPU)."""
+    if not src.is_cuda and not src.is_pinned():
+        raise RuntimeError("rows() needs a CUDA tensor or a pinned host tensor as its source")
     lib = _lib.load()
     r = _lib.OnoRows()
     r.src, r.ld_src = src.data_ptr(), src.stride(0)

@@ -45,10 +45,14 @@ class SymmetricWindow:
             import torch.distributed._symmetric_memory as symm_mem
 
             grp = group if group is not None else dist.group.WORLD
-            try:  # needed by older builds, a no-op (deprecated) on newer ones
-                symm_mem.enable_symm_mem_for_group(grp.group_name)
-            except Exception:
-                pass
+            import warnings
+
+            with warnings.catch_warnings():       # needed by older builds; newer ones only warn that it is a no-op
+                warnings.simplefilter("ignore")
+                try:
+                    symm_mem.enable_symm_mem_for_group(grp.group_name)
+                except Exception:
+                    pass
             self.buf = symm_mem.empty(total, dtype=torch.uint8, device=device)
             self.handle = symm_mem.rendezvous(self.buf, grp)
             self.ptrs = [int(p) for p in self.handle.buffer_ptrs]

@@ -48,8 +48,14 @@ class CpuRank:
         self.policy = core.SessionPolicy(len(self.worker_ranks))
         if plan.get("early_stopping"):
             self.policy.enable_early_stopping(plan["early_stopping"]["window"], plan["early_stopping"]["tolerance"])
+        self.grad_norm_switch = False
         if plan.get("switch"):
             self.policy.enable_switch(plan["switch"]["window"], plan["switch"]["threshold"])
+            # the switch may watch the norm of the averaged gradient instead of the losses
+            # (orchestrator/src/sessions/switch_tracker.rs:48-62 applied to a different series)
+            self.grad_norm_switch = plan["switch"].get("metric", "loss") == "grad_norm"
+            self.policy.set_switch_on_metric(self.grad_norm_switch)
+        self.last_norm = None
         self.switched = False
         self.stop_reason = "max_epochs"
         if self.algorithm == "parameter_server":
@@ -95,6 +101,7 @@ class CpuRank:
         else:
             total = self._all_reduce(mine.copy())
             avg = total / nw
+            self.last_norm = float(np.sqrt(np.sum(avg.astype(np.float64) ** 2)))     # every rank holds the same vector
             for k, (b, e) in enumerate(self.own[self.rank]):
                 self.C[b:e] = self.opts[k].step(self.C[b:e], avg[b:e])
         fresh = np.zeros_like(self.C)
@@ -195,6 +202,8 @@ class CpuRank:
             decision = self._decide(losses)
             if decision == 1:
                 break
+            if decision == 0 and self.grad_norm_switch and not self.switched and self.last_norm is not None:
+                decision = int(self.policy.on_metric(self.last_norm))
             if decision == 2 and self.algorithm == "strategy_switch" and not self.switched:
                 self._switch()
         if self.rank == 0:

@@ -135,9 +135,9 @@ def snap_to_row_blocks(ranges_per_rank, plan_layers, engine_layers, n, n_pad, ro
 class BatchFeeder:
     """Stages mini-batches from pinned host memory to the device on a copy stream, one step ahead.
 
-    The dataset partition stays in host memory (as on the reference's workers); every step's inputs
-    cross PCIe inside the timed region. A background thread gathers the next batch's rows into a
-    pinned staging buffer while the GPU works on the current one.
+    The dataset partition stays in (pinned) host memory, as on the reference's workers; every step's inputs
+    cross PCIe inside the timed region: the host sends the shuffled row indices of the next batch, and a gather
+    kernel on the copy stream pulls exactly those rows out of host memory while the GPU works on the current batch.
     """
 
     def __init__(self, xs: np.ndarray, ys: np.ndarray, x_size: int, y_size: int, batch: int, device, seed: int,
@@ -149,12 +149,14 @@ class BatchFeeder:
         self.host_x = torch.from_numpy(np.ascontiguousarray(xs.reshape(self.rows, x_size)))
         self.host_y = torch.from_numpy(np.ascontiguousarray(ys.reshape(self.rows, y_size)))
         self.device_resident = device_resident
+        self.nslots = 2
         if device_resident:
             self.dev_all_x = self.host_x.to(device)
             self.dev_all_y = self.host_y.to(device)
-        self.nslots = 2
-        self.pin_x = [torch.empty(batch, x_size).pin_memory() for _ in range(self.nslots)]
-        self.pin_y = [torch.empty(batch, y_size).pin_memory() for _ in range(self.nslots)]
+        else:
+            self.host_x, self.host_y = self.host_x.pin_memory(), self.host_y.pin_memory()
+            self.pin_idx = [torch.empty(batch, dtype=torch.int32).pin_memory() for _ in range(self.nslots)]
+            self.dev_idx = [torch.zeros(batch, dtype=torch.int32, device=device) for _ in range(self.nslots)]
         self.dev_x = [torch.zeros(batch, x_size, device=device) for _ in range(self.nslots)]
         self.dev_y = [torch.zeros(batch, y_size, device=device) for _ in range(self.nslots)]
         self.copy_stream = torch.cuda.Stream(device=device)
@@ -189,12 +191,15 @@ class BatchFeeder:
                 torch.index_select(self.dev_all_y, 0, di, out=self.dev_y[slot][:n])
                 self.ready[slot].record(self.copy_stream)
             return n
-        self.consumed[slot].synchronize()  # the pinned buffer's previous copy has been issued and read
-        torch.index_select(self.host_x, 0, idx, out=self.pin_x[slot][:n])
-        torch.index_select(self.host_y, 0, idx, out=self.pin_y[slot][:n])
+        # The dataset partition is pinned: the gather kernel reads the batch's rows straight out of host memory over
+        # PCIe on the copy stream (host-to-device copy and gather in one pass), so the host thread only ships the index
+        # vector and never touches the rows themselves.
+        self.consumed[slot].synchronize()  # the slot's index buffer is free again
+        self.pin_idx[slot][:n].copy_(idx)
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self.consumed[slot])
-            self.dev_x[slot][:n].copy_(self.pin_x[slot][:n], non_blocking=True)
-            self.dev_y[slot][:n].copy_(self.pin_y[slot][:n], non_blocking=True)
+            self.dev_idx[slot][:n].copy_(self.pin_idx[slot][:n], non_blocking=True)
+            ew.rows(self.host_x, idx=self.dev_idx[slot], n_rows=n, dst=self.dev_x[slot], stream=self.copy_stream)
+            ew.rows(self.host_y, idx=self.dev_idx[slot], n_rows=n, dst=self.dev_y[slot], stream=self.copy_stream)
             self.ready[slot].record(self.copy_stream)
         return n

@@ -154,14 +154,13 @@ def _checkpoint(r, epochs_done: int) -> None:
     torch.cuda.synchronize(r.dev)
     path = r.b200["checkpoint_path"]
     path = path.replace("{epoch}", str(epochs_done)) if "{epoch}" in path else f"{path}.epoch{epochs_done}"
+    base = path[:-len(".safetensors")] if path.endswith(".safetensors") else path
     with torch.cuda.stream(r.stream):
         params = _gather_params(r)
         host = params[:r.n].cpu().numpy() if r.rank == 0 else None
+        _save_state(r, base + ".state.safetensors", epochs_done)   # the sidecar is complete before the weights file appears
     if r.rank == 0:
         save_tensors(path, weight_tensors(engine_layers_from_plan(r.plan), host))
-    base = path[:-len(".safetensors")] if path.endswith(".safetensors") else path
-    with torch.cuda.stream(r.stream):
-        _save_state(r, base + ".state.safetensors", epochs_done)
     torch.cuda.synchronize(r.dev)
 
 

@@ -52,7 +52,13 @@ def weight_tensors(engine_layers: list[dict], params: np.ndarray) -> list:
 
 
 def save_tensors(path: str, tensors: list, meta: dict | None = None) -> None:
-    """Write (name, f32 array) pairs as a safetensors file (no metadata block unless ``meta`` is given)."""
+    """Write (name, f32 array) pairs as a safetensors file (no metadata block unless ``meta`` is given). Entries are
+    laid out in name order, like the core exporter (csrc/core/codec.cpp) and the reference's, so the files are equal
+    byte for byte. The file appears under its final name only when complete (temporary file, fsync, rename): a crash
+    during a periodic checkpoint leaves the previous file in place, never a truncated one."""
+    import os
+
+    tensors = sorted(tensors, key=lambda nt: nt[0])
     header: dict = {}
     if meta is not None:
         header["__metadata__"] = {k: str(val) for k, val in meta.items()}
@@ -62,28 +68,20 @@ def save_tensors(path: str, tensors: list, meta: dict | None = None) -> None:
         off += t.nbytes
     blob = json.dumps(header, separators=(",", ":")).encode()
     blob += b" " * ((8 - len(blob) % 8) % 8)
-    with open(path, "wb") as f:
+    tmp = path + ".tmp"
+    with open(tmp, "wb") as f:
         f.write(struct.pack("<Q", len(blob)))
         f.write(blob)
         for _, t in tensors:
             f.write(t.tobytes())
+        f.flush()
+        os.fsync(f.fileno())
+    os.replace(tmp, path)
 
 
 def save_state(path: str, m: np.ndarray, v: np.ndarray, adam_pows: np.ndarray, **meta) -> None:
-    tensors = [("optimizer.m", np.ascontiguousarray(m, dtype="<f4")), ("optimizer.v", np.ascontiguousarray(v, dtype="<f4")),
-               ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))]
-    header: dict = {"__metadata__": {k: str(val) for k, val in meta.items()}}
-    off = 0
-    for name, t in tensors:
-        header[name] = {"dtype": "F32", "shape": list(t.shape), "data_offsets": [off, off + t.nbytes]}
-        off += t.nbytes
-    blob = json.dumps(header, separators=(",", ":")).encode()
-    blob += b" " * ((8 - len(blob) % 8) % 8)
-    with open(path, "wb") as f:
-        f.write(struct.pack("<Q", len(blob)))
-        f.write(blob)
-        for _, t in tensors:
-            f.write(t.tobytes())
+    save_tensors(path, [("optimizer.m", np.ascontiguousarray(m, dtype="<f4")), ("optimizer.v", np.ascontiguousarray(v, dtype="<f4")),
+                        ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))], meta)
 
 
 def load_state(path: str, n_params: int) -> dict:

@@ -68,6 +68,54 @@ def test_nodes_strategy_switch_and_stop(nodes):
     assert m.stop_reason == "stopped" and len(m.loss_history()) < 100000
 
 
+def test_runs_without_a_seed_start_every_rank_from_the_same_parameters(nodes):
+    """No seed in the configuration (the public API's default): rank 0 draws one and every rank uses it. With a zero
+    learning rate nothing moves, so what comes back is the initial vector. Parameter-server ranks own disjoint slices
+    and the final gather takes each slice from its owner: the result equals the all-reduce run's (rank 0's replica)
+    only if all ranks generated the same vector... which also needs the same seed in both runs, so each run is instead
+    checked against its own loss: identical replicas give every worker the loss of the same model on its partition,
+    and two epochs at zero learning rate give the same losses twice."""
+    model, xs, ys = _setup()
+    tr = orchestra.parameter_server(nodes, 2, InlineDataset(xs, ys, 6, 3), GradientDescent(1e-30), CrossEntropy(), BarrierSync(),
+                                    BlockingStore(), 2, 40, b200={"colocate": True, "sharding": "even"})
+    s = orchestrate(model, tr)
+    per_worker = {}
+    for ev in s.events():
+        if ev["kind"] == "losses":
+            per_worker.setdefault(ev["worker"], []).extend(ev["losses"])
+    m = s.wait(quiet=True)
+    w = m.weights_array()
+    assert len(per_worker) == 3 and np.isfinite(w).all() and np.abs(w).max() > 0
+    # the gathered vector is a patchwork of the three owners' slices; evaluate it on each worker's partition with the
+    # CPU engine: a worker whose replica differed from the patchwork would have reported a different loss
+    from orchestra import _orchestra as core
+    import json
+
+    plan = json.loads(core.adapt_configs(json.dumps(model.to_config()), tr.to_json()))
+    for wk in plan["workers"]:
+        b, e = wk["partition"]
+        spec = dict(wk["spec"]["trainer"])
+        t = core.RoundTrainer(json.dumps(spec), xs[b:e].reshape(-1), ys[b:e].reshape(-1), True)
+        _, _, losses, _ = t.train(w.copy(), np.zeros_like(w))
+        got = per_worker[plan["workers"].index(wk)]
+        assert abs(losses[0] - got[0]) < 1e-6 and abs(got[0] - got[1]) < 1e-6
+
+
+def test_gradient_norm_switch_on_cpu_ranks(nodes):
+    """switch_metric "grad_norm": the norm of the averaged gradient drives the switch instead of the losses."""
+    model, xs, ys = _setup()
+    tr = orchestra.strategy_switch(nodes, 1, InlineDataset(xs, ys, 6, 3), Adam(0.01), CrossEntropy(), BarrierSync(),
+                                   BlockingStore(), 12, 5, seed=3,
+                                   b200={"switch_metric": "grad_norm", "switch_window": 3, "switch_threshold": 10.0})
+    s = orchestrate(model, tr)
+    evs = list(s.events())
+    kinds = [ev["kind"] for ev in evs]
+    m = s.wait(quiet=True)
+    assert "switch" in kinds and "upgraded" in kinds
+    w0 = [l for ev in evs if ev["kind"] == "losses" and ev["worker"] == 0 for l in ev["losses"]]
+    assert m.metrics()["switched"] is True and len(w0) == 12 and w0[-1] < w0[0]        # training went on after the switch
+
+
 def test_latency_probe_feeds_the_planner(nodes):
     """All-pairs ping between the node processes, then a session planned from the measured round-trip times."""
     from oxidized_neural_orchestra_b200.runtime.node import obtain_stats
