@@ -171,7 +171,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--config", default="deep", choices=sorted(CONFIGS))
-    ap.add_argument("--push", default=None, choices=("on", "off", "auto"), help="gradient push through the GEMM epilogues")
+    ap.add_argument("--push", default=None, choices=("on", "off", "auto", "direct", "reduce"),
+                    help="gradient push: auto/on = 16-bit tiles + copy engines, direct = epilogue stores into the owner's window, "
+                         "reduce = f32 reduce-adds, off = the fused kernel pulls")
     ap.add_argument("--stage", default=None, choices=("on", "off", "auto"), help="staged reduce-scatter during backward")
     ap.add_argument("--phases", action="store_true",
                     help="diagnostic: run the steps uncaptured with CUDA events around compute / exchange / refresh and add "
@@ -256,7 +258,7 @@ def main() -> None:
             "dtype": "bf16" if cfg["tile"] == "bf16" else "tf32", "data": "synthetic",
             "config": {"model": cfg["model"], "global_batch": gb, "seq_len": None, "parallelism": par,
                        "optimizer": cfg["opt"][0], "l2": l2_note,
-                       "sync": m["sync_mode"], "wire": m.get("wire"), "wire_push": bool(m.get("wire_push", False)),
+                       "sync": m["sync_mode"], "wire": m.get("wire"), "wire_push": bool(m.get("wire_push", False)), "wire_transport": m.get("wire_transport"),
                        "wgrad_apply": bool(m.get("wgrad_apply", False)),
                        "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
             "clocks": clocks,

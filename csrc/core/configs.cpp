@@ -425,7 +425,7 @@ B200Config B200Config::from_json(const Json& j) {
   str("sharding", c.sharding, {"layer", "even"});
   str("switch_metric", c.switch_metric, {"loss", "grad_norm"});
   str("data", c.data, {"host", "device"});
-  str("grad_push", c.grad_push, {"auto", "on", "off", "reduce"});
+  str("grad_push", c.grad_push, {"auto", "on", "off", "reduce", "direct"});
   str("wgrad_apply", c.wgrad_apply, {"auto", "off"});
   if (const Json* v = j.find("switch_check_every")) c.switch_check_every = nonzero(*v, "b200.switch_check_every");
   str("grad_stage", c.grad_stage, {"auto", "on", "off"});

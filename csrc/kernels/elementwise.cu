@@ -125,6 +125,45 @@ __global__ void loss_kernel(const OnoLoss l) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Softmax layer (forward and Jacobian-vector product): one warp per row, three passes over the row.
+// ------------------------------------------------------------------------------------------------
+__global__ void softmax_kernel(const OnoSoftmax a) {
+  const int wpb = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __nv_bfloat16* ob = reinterpret_cast<__nv_bfloat16*>(a.out_bf16);
+  __nv_bfloat16* otb = reinterpret_cast<__nv_bfloat16*>(a.outT_bf16);
+  const __nv_bfloat16* pb = reinterpret_cast<const __nv_bfloat16*>(a.p_bf16);
+  for (int row = blockIdx.x * wpb + warp; row < a.B; row += gridDim.x * wpb) {
+    const float* x = a.x + (size_t)row * a.ld_x;
+    float mx = -INFINITY, inv_z = 1.0f, dot = 0.0f;
+    if (!a.backward) {
+      for (int j = lane; j < a.C; j += 32) mx = fmaxf(mx, x[j]);
+      mx = warp_max(mx);
+      float z = 0.0f;
+      for (int j = lane; j < a.C; j += 32) z += expf(x[j] - mx);
+      inv_z = 1.0f / warp_sum(z);
+    } else {
+      for (int j = lane; j < a.C; j += 32) {
+        const float p = a.p_f32 ? a.p_f32[(size_t)row * a.ld_p + j] : __bfloat162float(pb[(size_t)row * a.ld_p + j]);
+        dot += p * x[j];
+      }
+      dot = warp_sum(dot);
+    }
+    for (int j = lane; j < a.C; j += 32) {
+      float v;
+      if (!a.backward) v = expf(x[j] - mx) * inv_z;
+      else {
+        const float p = a.p_f32 ? a.p_f32[(size_t)row * a.ld_p + j] : __bfloat162float(pb[(size_t)row * a.ld_p + j]);
+        v = p * (x[j] - dot);      // softmax.rs:44-64
+      }
+      if (a.out_f32) a.out_f32[(size_t)row * a.ld_out + j] = v;
+      if (ob) ob[(size_t)row * a.ld_out + j] = __float2bfloat16_rn(v);
+      if (a.outT_f32) a.outT_f32[(size_t)j * a.ld_outT + row] = v;
+      if (otb) otb[(size_t)j * a.ld_outT + row] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Column sums (bias gradient). Block = 32 columns x 8 row-lanes.
 // ------------------------------------------------------------------------------------------------
 // Rows are split into `nchunks` slabs (grid.y) so that a tall, narrow matrix (the bias gradient of a
@@ -358,6 +397,18 @@ __global__ void push_add_kernel(const float* src, float* dst, long long n) {
 }
 }  // namespace ono
 
+extern "C" int ono_softmax(const OnoSoftmax* a, ono_stream_t st) {
+  if (!a || !a->x || a->B <= 0 || a->C <= 0 || (a->backward && !a->p_f32 && !a->p_bf16)) {
+    set_error("bad softmax args%s", "", 0, 0);
+    return -1;
+  }
+  const int wpb = 8;
+  int grid = (a->B + wpb - 1) / wpb;
+  if (grid > 148 * 8) grid = 148 * 8;
+  softmax_kernel<<<grid, wpb * 32, 0, (cudaStream_t)st>>>(*a);
+  return launch_ok("softmax");
+}
+
 namespace ono {
 __global__ void cast16_kernel(const float* src, uint16_t* dst, long long n, int f16, int vec) {
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -373,6 +424,14 @@ __global__ void cast16_kernel(const float* src, uint16_t* dst, long long n, int 
   }
 }
 }  // namespace ono
+
+extern "C" int ono_copy_async(void* dst, const void* src, long long bytes, ono_stream_t st) {
+  if (!dst || !src || bytes < 0) { set_error("bad copy args%s", "", 0, 0); return -1; }
+  if (bytes == 0) return 0;
+  const cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)st);
+  if (e != cudaSuccess) { set_error("cudaMemcpyAsync failed: %s", cudaGetErrorString(e), 0, 0); return -7; }
+  return 0;
+}
 
 extern "C" int ono_cast16(const float* src, void* dst, long long n, int f16, ono_stream_t st) {
   if (!src || !dst || n < 0) { set_error("bad cast16 args%s", "", 0, 0); return -1; }

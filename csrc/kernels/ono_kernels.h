@@ -117,6 +117,19 @@ typedef struct OnoLoss {
 } OnoLoss;
 int ono_loss(const OnoLoss* l, ono_stream_t stream);
 
+// Softmax as a layer's activation anywhere in a network (arch/layers/softmax.rs:24-64), one warp per row.
+//   backward == 0: out = softmax(x) row-wise (x: pre-activations)
+//   backward == 1: out = p * (x - sum_k p_k x_k) (x: gradient w.r.t. the softmax output, p: the stored output, f32 or bf16)
+// Any of the four output forms may be requested (row-major / transposed, f32 / bf16).
+typedef struct OnoSoftmax {
+  const float* x; int ld_x;
+  const float* p_f32; const void* p_bf16; int ld_p;
+  int B, C, backward;
+  float* out_f32; void* out_bf16; float* outT_f32; void* outT_bf16;
+  int ld_out, ld_outT;
+} OnoSoftmax;
+int ono_softmax(const OnoSoftmax* s, ono_stream_t stream);
+
 // out[n] = beta*out[n] + sum_m d[m][n]   (bias gradient, dense.rs:58). dtype: 0 f32, 1 bf16.
 int ono_colsum(const void* d, int dtype, int M, int N, int ld, float* out, float beta, ono_stream_t stream);
 
@@ -295,6 +308,9 @@ int ono_stage_signal(unsigned int* const* flags, int nranks, int rank, int bucke
 int ono_stage_tick(unsigned int* step, ono_stream_t stream);
 // dst[i] += src[i] with reductions that need no reply (dst may be a peer GPU's memory).
 int ono_push_add(const float* src, float* dst, long long n, ono_stream_t stream);
+// cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, stream): a copy-engine transfer (no SM involved); dst or src may be a
+// peer GPU's window. One call per copy.
+int ono_copy_async(void* dst, const void* src, long long bytes, ono_stream_t stream);
 // dst[i] = 16-bit float of src[i] (bf16, or f16 when f16 != 0); dst may be a peer GPU's memory (the 16-bit gradient
 // wire for values that do not leave through a GEMM epilogue: bias gradients, unaligned layers, convolution kernels).
 int ono_cast16(const float* src, void* dst, long long n, int f16, ono_stream_t stream);

@@ -91,9 +91,8 @@ class GpuEngine:
         self.n_params = off
         if params.numel() < off or grads.numel() < off:
             raise ValueError("flat parameter/gradient buffers are too small")
-        for i, pl in enumerate(self.plans[:-1]):
-            if pl.act == "softmax":
-                raise NotImplementedError("softmax is supported as the last activation only on the GPU engine")
+        # softmax on the last layer is fused into the loss kernel; on any other layer it is a row-wise pass of its own
+        # after the GEMM (forward) and before the next GEMM's operand is formed (Jacobian-vector product in backward)
         self.softmax_last = self.plans[-1].act == "softmax"
         self._alloc()
 
@@ -111,9 +110,12 @@ class GpuEngine:
         self.logits = z(B, self.lds[-1], f32)
         self.d = [z(B, self.lds[0], cd) if self.input_grad else None] + [z(B, self.lds[i], cd) for i in range(1, len(feats))]
         self.zpre = [None] * len(feats)
+        self.soft_tmp = [None] * len(feats)       # f32 scratch of an inner softmax layer: pre-activations, then d/d(output)
         for l, pl in enumerate(L):
             if pl.act == "gelu":
                 self.zpre[l + 1] = z(B, self.lds[l + 1], cd)
+            if pl.act == "softmax" and l < len(L) - 1:
+                self.soft_tmp[l + 1] = z(B, self.lds[l + 1], f32)
         # MN-major operands let every GEMM read activations, deltas and weights as they are stored. bf16 always does;
         # for tf32 the MN-major tiles (32-element rows, twelve small TMA boxes per stage) measured slower than K-major
         # tiles fed from transposed compute copies (wide MLP step 1.20 ms against 1.13 ms), so it is opt-in: ONO_TF32_MN=1
@@ -212,8 +214,20 @@ class GpuEngine:
         for l, pl in enumerate(L):
             last = l == len(L) - 1
             a_in = self.a[l][:nrows, :pl.in_features]
-            act = None if (last and self.softmax_last) else pl.act
+            inner_softmax = pl.act == "softmax" and not last
+            act = None if (pl.act == "softmax") else pl.act
             kw = dict(bias=self.b_view(l), act=act, act_param=pl.act_param, status=self.status, stream=stream)
+            if inner_softmax:
+                o = pl.out_features
+                kw["out"] = self.soft_tmp[l + 1][:nrows, :o]
+                if self.mn:
+                    self._gemm(a_in, self.w_k[l], b_mn_major=True, **kw)
+                else:
+                    self._gemm(a_in, self.w_t[l], **kw)
+                ew.softmax_layer(self.soft_tmp[l + 1][:nrows, :o], out=self.a[l + 1][:nrows, :o],
+                                 out_t=None if self.mn else self.at[l + 1][:, :nrows], stream=stream)
+                n += 2
+                continue
             if last:
                 kw["out"] = self.logits[:nrows, :pl.out_features]
             elif self.bf16:
@@ -273,17 +287,27 @@ class GpuEngine:
                 prev = L[l - 1] if l > 0 else LayerPlan("input", 0, i)
                 stored = self.zpre[l] if prev.act == "gelu" else self.a[l]
                 kw = dict(status=self.status, stream=stream)
-                if prev.act is not None:
+                if prev.act == "softmax":
+                    # the GEMM leaves d/d(softmax output) in f32; the Jacobian-vector product needs whole rows
+                    tmp = self.soft_tmp[l][:nrows, :i]
+                    self._gemm(d_out, self.w_k[l], out=tmp, **kw)
+                    ew.softmax_layer(tmp, p=self.a[l][:nrows, :i], out=self.d[l][:nrows, :i],
+                                     out_t=None if (self.mn or l == 0) else self.dt[l][:, :nrows], stream=stream)
+                    n += 2
+                elif prev.act is not None:
                     kw.update(aux=stored[:nrows, :i], dact=prev.act, dact_param=prev.act_param,
                               relu_quirk=self.relu_quirk)
-                if self.bf16:
+                if prev.act == "softmax":
+                    pass
+                elif self.bf16:
                     self._gemm(d_out, self.w_k[l], out_bf16=self.d[l][:nrows, :i], **kw)
                 elif self.mn:
                     self._gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i], **kw)
                 else:
                     self._gemm(d_out, self.w_k[l], out=self.d[l][:nrows, :i],
                                out_t=self.dt[l][:, :nrows] if l > 0 else None, **kw)
-                n += 1
+                if prev.act != "softmax":
+                    n += 1
 
             def wgrad(r0, r1, **out_kw):     # rows [r0, r1) of dW = A_l^T d
                 if self.mn:
@@ -294,13 +318,15 @@ class GpuEngine:
                                **out_kw)
 
             if wire is not None:
-                # 16-bit gradient wire: every tile of dW leaves the epilogue as bf16 / f16 through a TMA store into
-                # the slab the owner of those rows keeps for this rank (its window over NVLink, or local memory); the
-                # exchange rides on backward and the owner later reduces its slabs from local memory
+                # 16-bit gradient wire. "staged": dW leaves the epilogue as bf16 / f16 into this rank's own 16-bit
+                # gradient vector (TMA stores to local memory); the caller's after_layer hook then ships the ranges other
+                # ranks own with copy-engine transfers while backward goes on. "direct": the epilogue's TMA stores go
+                # straight into the slab the owner of those rows keeps for this rank (its window over NVLink).
+                k16 = "out_f16" if wire["f16"] else "out_bf16"
                 pieces = wire["w"][l]
                 if pieces is not None:
                     for r0, r1, dst in pieces:
-                        wgrad(r0, r1, **{"out_f16" if wire["f16"] else "out_bf16": dst})
+                        wgrad(r0, r1, **{k16: dst})
                         n += 1
                 else:
                     tgt = self.gw_tmp[l] if self.gw_tmp[l] is not None else self.gw_view(l)

@@ -65,6 +65,7 @@ def _declare(lib) -> None:
     sigs = {
         "ono_loss": [C.POINTER(OnoLoss), vp],
         "ono_colsum": [vp, ci, ci, ci, ci, vp, cf, vp],
+        "ono_softmax": [C.POINTER(OnoSoftmax), vp],
         "ono_optim": [C.POINTER(OnoOptim), vp],
         "ono_adam_tick": [vp, cf, cf, vp],
         "ono_local_sgd": [vp, vp, vp, ll, cf, vp, vp],
@@ -78,6 +79,7 @@ def _declare(lib) -> None:
         "ono_pingpong": [ci, vp, vp, ci, C.c_uint, vp, vp, vp],
         "ono_push_add": [vp, vp, ll, vp],
         "ono_cast16": [vp, vp, ll, ci, vp],
+        "ono_copy_async": [vp, vp, ll, vp],
         "ono_stage_pull": [C.POINTER(OnoStagePull), vp],
         "ono_stage_signal": [C.POINTER(vp), ci, ci, ci, vp, vp],
         "ono_stage_tick": [vp, vp],
@@ -125,6 +127,15 @@ class OnoLoss(C.Structure):
         ("d_bf16", C.c_void_p), ("dT_bf16", C.c_void_p),
         ("ld_d", C.c_int), ("ld_dT", C.c_int),
         ("loss_sum", C.c_void_p), ("correct", C.c_void_p),
+    ]
+
+
+class OnoSoftmax(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("ld_x", C.c_int), ("p_f32", C.c_void_p), ("p_bf16", C.c_void_p), ("ld_p", C.c_int),
+        ("B", C.c_int), ("C", C.c_int), ("backward", C.c_int),
+        ("out_f32", C.c_void_p), ("out_bf16", C.c_void_p), ("outT_f32", C.c_void_p), ("outT_bf16", C.c_void_p),
+        ("ld_out", C.c_int), ("ld_outT", C.c_int),
     ]
 
 

@@ -56,6 +56,37 @@ def loss_backward(a: torch.Tensor, y: torch.Tensor, *, kind: str, softmax: bool,
     _lib.check(lib.ono_loss(C.byref(l), _lib.stream_ptr(stream)), "ono_loss")
 
 
+def softmax_layer(x: torch.Tensor, *, p: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                  out_t: torch.Tensor | None = None, stream=None) -> None:
+    """Softmax as a layer activation. Forward (``p`` is None): ``out = softmax(x)`` row-wise. Backward: ``x`` is the gradient
+    w.r.t. the softmax output, ``p`` the stored output (f32 or bf16), ``out = p * (x - sum_k p_k x_k)``
+    (arch/layers/softmax.rs:44-64). ``out`` / ``out_t`` (transposed copy) may be f32 or bf16; ``x`` is f32."""
+    _need_cuda(x)
+    a = _lib.OnoSoftmax()
+    a.x, a.ld_x = x.data_ptr(), x.stride(0)
+    a.B, a.C = x.shape
+    a.backward = int(p is not None)
+    if p is not None:
+        if p.dtype == torch.float32:
+            a.p_f32 = p.data_ptr()
+        else:
+            a.p_bf16 = p.data_ptr()
+        a.ld_p = p.stride(0)
+    if out is not None:
+        if out.dtype == torch.float32:
+            a.out_f32 = out.data_ptr()
+        else:
+            a.out_bf16 = out.data_ptr()
+        a.ld_out = out.stride(0)
+    if out_t is not None:
+        if out_t.dtype == torch.float32:
+            a.outT_f32 = out_t.data_ptr()
+        else:
+            a.outT_bf16 = out_t.data_ptr()
+        a.ld_outT = out_t.stride(0)
+    _lib.check(_lib.load().ono_softmax(C.byref(a), _lib.stream_ptr(stream)), "ono_softmax")
+
+
 def colsum(d: torch.Tensor, out: torch.Tensor, beta: float = 0.0, stream=None) -> None:
     """``out[n] = beta*out[n] + sum_m d[m, n]`` (bias gradient)."""
     _need_cuda(d)

@@ -92,7 +92,13 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
             torch.cuda.nvtx.range_push(name)
 
     mark("compute")
-    n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
+    if with_sync and r.wire_copies:
+        # 16-bit gradients leave for their owners layer by layer on the communication stream (copy engines) while the
+        # layers below are still in backward; the fused kernel starts once the last transfer has been issued and done
+        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st, after_layer=lambda l: r.wire_ship(l, st))
+        st.wait_stream(r.comm_stream)
+    else:
+        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
     mark("exchange")
     if r.cadence == "round":
         # sequential.rs:129-141: stateless SGD on the working copy, residual += grad

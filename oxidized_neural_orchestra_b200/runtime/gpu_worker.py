@@ -52,6 +52,7 @@ class GpuRank:
         self.switched = False
         self.use_nvls = False
         self.push_active = self.stage_active = self.wire16_push = self.apply_active = False
+        self.wire_copies, self.wire_transport = None, "staged"
         self.buckets, self.bucket_after, self.stage_buckets, self.stage_after = [], {}, [], {}
         self.stream = torch.cuda.Stream(device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
@@ -104,7 +105,10 @@ class GpuRank:
         # tiles as 16-bit values straight into the slab that the owner of those rows keeps for this rank, so the
         # reduce-scatter rides on backward and the owner reduces `world` local slabs. Slab q of a window holds rank q's
         # gradients, indexed like the flat parameter vector.
-        self.push16 = (self.wire16 is not None and gp in ("auto", "on") and dense_only and not self.async_ps and
+        # transport of the pushed tiles: "staged" = local 16-bit gradient vector + copy-engine transfers that overlap with
+        # backward (default); "direct" = the epilogues' TMA stores target the owner's window themselves
+        self.wire_transport = "direct" if gp == "direct" else "staged"
+        self.push16 = (self.wire16 is not None and gp in ("auto", "on", "direct") and dense_only and not self.async_ps and
                        ar_mode in ("auto", "twoshot", "nvls"))
         if self.wire16 is not None:
             self.nslabs = self.world if self.push16 else 1
@@ -315,40 +319,75 @@ class GpuRank:
         return bool(flag.item() > 0)
 
     def _build_wire16(self):
-        """Per layer: where this rank's 16-bit gradients go. ``w[l]``: (row range, destination matrix) pieces of the
-        weight gradient, one per owner, each a view of slab `rank` in the owner's window (None for a layer whose rows
-        are not 16-byte aligned as 16-bit values: its gradient is computed in f32 locally and cast). ``cast[l]``:
-        (f32 source, 16-bit destination) pairs for the bias gradient and for such unaligned layers."""
+        """Where this rank's 16-bit gradients go, per layer.
+
+        ``w[l]``: (row range, destination matrix) pieces of the weight gradient (None for a layer whose rows are not
+        16-byte aligned as 16-bit values: its gradient is computed in f32 locally and cast); ``cast[l]``: (f32 source,
+        16-bit destination) pairs for the bias gradient and for such unaligned layers.
+
+        Staged transport (default): every destination is slab `rank` of this rank's OWN window; ``self.wire_copies[l]``
+        then lists the (destination address in the owner's window, local source address, bytes) transfers that carry
+        the ranges other ranks own, issued on the communication stream as copy-engine transfers as soon as layer l's
+        gradients exist. Direct transport: the destinations are views of slab `rank` in the owners' windows and the
+        GEMM epilogues store over NVLink themselves (one GEMM per owner and layer)."""
         dt = torch.float16 if self.wire16 == "f16" else torch.bfloat16
-        slab_elems0 = self.layout.offset("slab16") // 2 + self.rank * self.n_pad
+        slab0 = self.layout.offset("slab16")
+        slab_elems0 = slab0 // 2 + self.rank * self.n_pad
         local = self.layout.tensor(self.win, "slab16")
+        direct_transport = self.wire_transport == "direct"
 
         def flat(owner, begin, count):
-            if owner == self.rank or self.win.handle is None:
+            if owner == self.rank or self.win.handle is None or not direct_transport:
                 return local[self.rank * self.n_pad + begin:self.rank * self.n_pad + begin + count]
             return self.win.handle.get_buffer(owner, (count,), dt, slab_elems0 + begin)
 
-        w, cast = {}, {}
+        w, cast, copies = {}, {}, {}
         for li, pl in enumerate(self.engine.plans):
             i, o = pl.in_features, pl.out_features
-            direct = o % 8 == 0 and pl.w_off % 8 == 0
-            pieces, casts = [], []
+            aligned = o % 8 == 0 and pl.w_off % 8 == 0
+            pieces, casts, cps = [], [], []
             for owner, rs in enumerate(self.own):
                 for lo, hi in rs:
+                    a0, a1 = max(lo, pl.w_off), min(hi, pl.b_off + o)      # the layer's whole block: weights then bias
+                    if a1 > a0 and owner != self.rank and not direct_transport:
+                        off = 2 * (self.rank * self.n_pad + a0)
+                        cps.append((self.win.ptrs[owner] + slab0 + off, self.win.ptrs[self.rank] + slab0 + off, 2 * (a1 - a0)))
                     a0, a1 = max(lo, pl.w_off), min(hi, pl.w_off + i * o)
-                    if a1 > a0:
-                        if direct:
+                    if a1 > a0 and direct_transport:
+                        if aligned:
                             assert (a0 - pl.w_off) % o == 0 and (a1 - pl.w_off) % o == 0, "ownership must follow whole rows"
                             r0, r1 = (a0 - pl.w_off) // o, (a1 - pl.w_off) // o
                             pieces.append((r0, r1, flat(owner, a0, (r1 - r0) * o).view(r1 - r0, o)))
                         else:
                             casts.append((self.G[a0:a1], flat(owner, a0, a1 - a0)))
                     b0, b1 = max(lo, pl.b_off), min(hi, pl.b_off + o)
-                    if b1 > b0:
+                    if b1 > b0 and direct_transport:
                         casts.append((self.G[b0:b1], flat(owner, b0, b1 - b0)))
-            w[li] = sorted(pieces, key=lambda t: t[0]) if direct else None
+            if not direct_transport:
+                if aligned:
+                    pieces = [(0, i, flat(self.rank, pl.w_off, i * o).view(i, o))]
+                else:
+                    casts.append((self.G[pl.w_off:pl.w_off + i * o], flat(self.rank, pl.w_off, i * o)))
+                casts.append((self.G[pl.b_off:pl.b_off + o], flat(self.rank, pl.b_off, o)))
+            w[li] = sorted(pieces, key=lambda t: t[0]) if aligned else None
             cast[li] = casts
+            copies[li] = cps
+        self.wire_copies = copies
         return {"f16": self.wire16 == "f16", "w": w, "cast": cast}
+
+    def wire_ship(self, l: int, stream) -> int:
+        """Ship layer l's finished 16-bit gradients to their owners: copy-engine transfers on the communication stream,
+        ordered after the kernels that produced them. Returns the number of transfers."""
+        cps = self.wire_copies.get(l) if self.wire_copies else None
+        if not cps:
+            return 0
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        self.comm_stream.wait_event(ev)
+        lib, cs = _lib.load(), _lib.stream_ptr(self.comm_stream)
+        for dst, src, nbytes in cps:
+            _lib.check(lib.ono_copy_async(dst, src, nbytes, cs), "ono_copy_async")
+        return len(cps)
 
     def _build_apply(self, opt, n_workers: int, wild: bool):
         """Layers whose weight-gradient GEMM applies the optimizer itself, and the ranges left to the fused kernel."""
@@ -395,7 +434,8 @@ class GpuRank:
         can = mode == "fused" and (dense_engine or self.engine is None)
         self.push_active = bool(self.push) and self._all_ranks_agree(can) if self.push else False
         self.wire16_push = bool(self.push16) and self._all_ranks_agree(can) if self.push16 else False
-        if self.push_active or self.wire16_push:
+        self.wire_copies = None
+        if self.push_active or (self.wire16_push and self.wire_transport == "direct"):
             ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)
         self.buckets, self.bucket_after = [], {}

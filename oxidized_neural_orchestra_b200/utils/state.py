@@ -51,14 +51,15 @@ def weight_tensors(engine_layers: list[dict], params: np.ndarray) -> list:
     return out
 
 
-def save_tensors(path: str, tensors: list, meta: dict | None = None) -> None:
+def save_tensors(path: str, tensors: list, meta: dict | None = None, sort: bool = True) -> None:
     """Write (name, f32 array) pairs as a safetensors file (no metadata block unless ``meta`` is given). Entries are
     laid out in name order, like the core exporter (csrc/core/codec.cpp) and the reference's, so the files are equal
     byte for byte. The file appears under its final name only when complete (temporary file, fsync, rename): a crash
     during a periodic checkpoint leaves the previous file in place, never a truncated one."""
     import os
 
-    tensors = sorted(tensors, key=lambda nt: nt[0])
+    if sort:
+        tensors = sorted(tensors, key=lambda nt: nt[0])
     header: dict = {}
     if meta is not None:
         header["__metadata__"] = {k: str(val) for k, val in meta.items()}
@@ -81,7 +82,7 @@ def save_tensors(path: str, tensors: list, meta: dict | None = None) -> None:
 
 def save_state(path: str, m: np.ndarray, v: np.ndarray, adam_pows: np.ndarray, **meta) -> None:
     save_tensors(path, [("optimizer.m", np.ascontiguousarray(m, dtype="<f4")), ("optimizer.v", np.ascontiguousarray(v, dtype="<f4")),
-                        ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))], meta)
+                        ("optimizer.adam_pows", np.ascontiguousarray(adam_pows, dtype="<f4"))], meta, sort=False)
 
 
 def load_state(path: str, n_params: int) -> dict:

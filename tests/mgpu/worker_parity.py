@@ -67,14 +67,20 @@ def main():
     for mode in ("twoshot", "auto"):
         ar(f"bf16-ar-{mode}-step", model, 10, {"sync_every": "step", "tile_dtype": "bf16", "allreduce": mode})
     ps("bf16-ps-colocated-even-step", model, 10, {"sync_every": "step", "tile_dtype": "bf16", "colocate": True, "sharding": "even"})
-    # 16-bit gradient wire in step cadence, both formats: tiles stored into the owners' slabs by the GEMM epilogues
-    # (push), or cast and read over NVLink by the fused kernel (pull), also through the in-switch reduction
+    # 16-bit gradient wire in step cadence, both formats: 16-bit tiles written by the GEMM epilogues and shipped to the
+    # owners' slabs by copy engines during backward (push, staged), stored into the owners' slabs by the epilogues
+    # themselves (push, direct), or cast and read over NVLink by the fused kernel (pull), also through the in-switch reduction
     for tile in ("tf32", "bf16"):
         for fmt in ("bf16", "f16"):
             base = {"sync_every": "step", "tile_dtype": tile, "wire_dtype": fmt}
-            ar(f"ar-{tile}-wire16-{fmt}-push-step", model12, 16, dict(base), expect={"wire": fmt, "wire_push": True})
+            ar(f"ar-{tile}-wire16-{fmt}-push-step", model12, 16, dict(base), expect={"wire": fmt, "wire_push": True, "wire_transport": "staged"})
             ps(f"ps-{tile}-wire16-{fmt}-push-step", model12, 16, dict(base, colocate=True, sharding="even"),
                expect={"wire": fmt, "wire_push": True})
+        ar(f"ar-{tile}-wire16-direct-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "direct"},
+           expect={"wire": "bf16", "wire_push": True, "wire_transport": "direct"})
+        ps(f"ps-{tile}-wire16-direct-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "direct",
+                                                           "colocate": True, "sharding": "even"},
+           expect={"wire": "bf16", "wire_push": True, "wire_transport": "direct"})
         ar(f"ar-{tile}-wire16-pull-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "off"},
            expect={"wire": "bf16", "wire_push": False})
         ar(f"ar-{tile}-wire16-pull-nvls-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "off",

@@ -48,6 +48,14 @@ CASES = [
     ([dict(kind="dense", **{"in": 256, "out": 512}, act=("gelu", 0.0)),
       dict(kind="dense", **{"in": 512, "out": 256}, act=("relu", 0.1)),
       dict(kind="dense", **{"in": 256, "out": 16}, act=("softmax", 0.0))], "cross_entropy", 200),
+    # softmax as an inner layer's activation (arch/layers/softmax.rs:24-64 allows it anywhere), first and middle layer
+    ([dict(kind="dense", **{"in": 64, "out": 48}, act=("softmax", 0.0)),
+      dict(kind="dense", **{"in": 48, "out": 40}, act=("tanh", 1.0)),
+      dict(kind="dense", **{"in": 40, "out": 24}, act=("softmax", 0.0)),
+      dict(kind="dense", **{"in": 24, "out": 8}, act=("softmax", 0.0))], "cross_entropy", 96),
+    ([dict(kind="dense", **{"in": 30, "out": 20}, act=("relu", 0.0)),
+      dict(kind="dense", **{"in": 20, "out": 12}, act=("softmax", 0.0)),
+      dict(kind="dense", **{"in": 12, "out": 5}, act=None)], "mse", 40),
 ]
 
 

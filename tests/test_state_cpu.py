@@ -58,6 +58,7 @@ def test_weight_checkpoint_writer_matches_the_core_writer(tmp_path):
     ta = {t[0]: (list(t[1]), np.asarray(t[2])) for t in core.load_safetensors(str(a))}
     tb = {t[0]: (list(t[1]), np.asarray(t[2])) for t in core.load_safetensors(str(b))}
     assert sorted(ta) == sorted(tb) == sorted(f"layer_{i}.{k}" for i in range(3) for k in ("weight", "bias"))
+    assert a.read_bytes() == b.read_bytes()        # same entry order (by name) and layout: equal byte for byte
     for k in ta:
         assert ta[k][0] == tb[k][0] and np.array_equal(ta[k][1], tb[k][1]), k
     with pytest.raises(ValueError, match="covers"):
