@@ -11,6 +11,7 @@
 //   compact     the same selection as (index, f16 value) pairs in ascending index order plus their count
 //               (three passes: per-block counts, scan of the counts, ordered write) and
 //   lift        acc[index] += value, the receiver's side (protocol.rs:96-144).
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -70,13 +71,24 @@ __global__ void __launch_bounds__(1024) sparse_threshold_kernel(const float* x, 
   }
 }
 
-__global__ void sparse_mask_kernel(float* residual, long long n, const float* thr, float* wire, unsigned long long* sent) {
-  const float t = thr ? *thr : -1.0f;   // no threshold: everything is sent (plain f16 wire)
+// wire_f32 (optional): the selection as f32 values rounded through f16; wire16 (optional): the same as 16-bit values
+// (f16, or bf16 when f16 == 0), which is what crosses NVLink. Entries that are not sent are zero on the wire.
+__global__ void sparse_mask_kernel(float* residual, long long n, const float* thr, float* wire_f32, uint16_t* wire16, int f16,
+                                   unsigned long long* sent) {
+  const float t = thr ? *thr : -1.0f;   // no threshold: everything is sent (plain 16-bit wire)
   unsigned long long mine = 0;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float v = residual[i];
     const bool send = fabsf(v) >= t;
-    wire[i] = send ? f16_round(v) : 0.0f;
+    if (wire_f32) wire_f32[i] = send ? f16_round(v) : 0.0f;
+    if (wire16) {
+      uint16_t w = 0;
+      if (send) {
+        if (f16) { const __half h = __float2half_rn(v); w = *reinterpret_cast<const uint16_t*>(&h); }
+        else { const __nv_bfloat16 h = __float2bfloat16_rn(v); w = *reinterpret_cast<const uint16_t*>(&h); }
+      }
+      wire16[i] = w;
+    }
     if (send) { residual[i] = 0.0f; ++mine; }
   }
   if (sent) {
@@ -175,6 +187,50 @@ __global__ void sparse_lift_kernel(float* acc, long long n, const unsigned int* 
   }
 }
 
+// The receiving side of the sparse wire for one sender and one owned range [begin, end): if the sender's message fits its
+// list (count <= capacity) the owner looks up the part of the ascending index list that falls into its range (two binary
+// searches) and adds exactly those (index, f16) pairs; otherwise the sender fell back to the dense 16-bit wire
+// (protocol.rs:57-86 falls back when the sparse encoding is the larger one) and the owner adds that range of it.
+// idx / val / count / dense16 may live in the sender's window (peer memory). *bytes += what was read from the sender.
+__global__ void sparse_lift_range_kernel(float* acc, long long begin, long long end, const unsigned int* idx, const __half* val,
+                                         const unsigned int* count, unsigned int capacity, const uint16_t* dense16, int dense_f16,
+                                         unsigned long long* bytes) {
+  __shared__ unsigned int s_lo, s_hi, s_cnt;
+  if (threadIdx.x == 0) {
+    const unsigned int c = *reinterpret_cast<const volatile unsigned int*>(count);
+    s_cnt = c;
+    if (c <= capacity) {
+      auto lower = [&](unsigned int key) {
+        unsigned int lo = 0, hi = c;
+        while (lo < hi) {
+          const unsigned int mid = (lo + hi) >> 1;
+          if (reinterpret_cast<const volatile unsigned int*>(idx)[mid] < key) lo = mid + 1; else hi = mid;
+        }
+        return lo;
+      };
+      s_lo = lower((unsigned int)begin);
+      s_hi = lower((unsigned int)end);
+    }
+  }
+  __syncthreads();
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x, stride = (long long)gridDim.x * blockDim.x;
+  if (s_cnt <= capacity) {
+    // (volatile loads: the sender rewrote these buffers this round, nothing cached from an earlier round may be used)
+    for (long long i = s_lo + tid; i < s_hi; i += stride) {
+      const unsigned int at = __ldcv(idx + i);
+      const unsigned short w = __ldcv(reinterpret_cast<const unsigned short*>(val) + i);
+      acc[at] += __half2float(*reinterpret_cast<const __half*>(&w));            // the indices of one message are distinct
+    }
+    if (bytes && tid == 0) atomicAdd(bytes, (unsigned long long)(s_hi - s_lo) * 6ull + 4ull);
+  } else {
+    for (long long i = begin + tid; i < end; i += stride) {
+      const uint16_t w = __ldcv(dense16 + i);
+      acc[i] += dense_f16 ? __half2float(*reinterpret_cast<const __half*>(&w)) : __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&w));
+    }
+    if (bytes && tid == 0) atomicAdd(bytes, (unsigned long long)(end - begin) * 2ull + 4ull);
+  }
+}
+
 static int done(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { set_error("%s launch failed (%lld)", what, (long long)e, 0); return -7; }
@@ -194,10 +250,24 @@ extern "C" int ono_sparse_threshold(const float* x, long long n, float r, unsign
   return done("sparse_threshold");
 }
 
-extern "C" int ono_sparse_mask(float* residual, long long n, const float* thr, float* wire, unsigned long long* sent, ono_stream_t st) {
-  if (!residual || !wire || n <= 0) { set_error("bad sparse_mask args%s", "", 0, 0); return -1; }
-  sparse_mask_kernel<<<grid_for(n), 256, 0, (cudaStream_t)st>>>(residual, n, thr, wire, sent);
+extern "C" int ono_sparse_mask(float* residual, long long n, const float* thr, float* wire_f32, void* wire16, int wire16_f16,
+                               unsigned long long* sent, ono_stream_t st) {
+  if (!residual || (!wire_f32 && !wire16) || n <= 0) { set_error("bad sparse_mask args%s", "", 0, 0); return -1; }
+  sparse_mask_kernel<<<grid_for(n), 256, 0, (cudaStream_t)st>>>(residual, n, thr, wire_f32, (uint16_t*)wire16, wire16_f16, sent);
   return done("sparse_mask");
+}
+
+extern "C" int ono_sparse_lift_range(float* acc, long long begin, long long end, const unsigned int* idx, const void* val_f16,
+                                     const unsigned int* count, unsigned int capacity, const void* dense16, int dense_f16,
+                                     unsigned long long* bytes, ono_stream_t st) {
+  if (!acc || !idx || !val_f16 || !count || !dense16 || begin < 0 || end < begin || end >= (1ll << 32)) {
+    set_error("bad sparse_lift_range args%s", "", 0, 0);
+    return -1;
+  }
+  if (end == begin) return 0;
+  sparse_lift_range_kernel<<<grid_for(end - begin), 256, 0, (cudaStream_t)st>>>(acc, begin, end, idx, (const __half*)val_f16, count, capacity,
+                                                                            (const uint16_t*)dense16, dense_f16, bytes);
+  return done("sparse_lift_range");
 }
 
 // scratch: at least ceil(n / 1024) unsigned ints. count receives the number of selected elements (it may exceed

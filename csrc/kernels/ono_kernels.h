@@ -324,14 +324,24 @@ int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int r
 // ---------------------------------------------------------------------------------------------
 // threshold = k-th smallest |x| of a seeded sample of <= 16384 elements, k = floor(sample * (1 - r)), >= min positive f16
 int ono_sparse_threshold(const float* x, long long n, float r, unsigned long long seed, float* thr_out, ono_stream_t st);
-// wire[i] = f16(x[i]) if |x[i]| >= *thr else 0, sent entries zeroed in x; thr == NULL sends everything (f16 wire);
+// What a rank puts on the wire and what it keeps: entries with |x[i]| >= *thr are sent and zeroed in x, the rest stays as the
+// residual; thr == NULL sends everything (plain 16-bit wire). The sent values (0 elsewhere) are written as f32 rounded through
+// f16 to wire_f32 and / or as 16-bit values (f16, or bf16 when wire16_f16 == 0) to wire16, the buffer peers read over NVLink;
 // *sent (optional) is incremented by the number of entries sent
-int ono_sparse_mask(float* x, long long n, const float* thr, float* wire, unsigned long long* sent, ono_stream_t st);
+int ono_sparse_mask(float* x, long long n, const float* thr, float* wire_f32, void* wire16, int wire16_f16, unsigned long long* sent,
+                    ono_stream_t st);
 // (index, f16) pairs of the selected entries in ascending index order; scratch holds ceil(n/1024) unsigned ints
 int ono_sparse_compact(float* x, long long n, const float* thr, unsigned int* scratch, unsigned int* idx, void* val_f16,
                        unsigned int capacity, unsigned int* count, int zero_sent, ono_stream_t st);
 int ono_sparse_lift(float* acc, long long n, const unsigned int* idx, const void* val_f16, const unsigned int* count,
                     unsigned int capacity, ono_stream_t st);
+// One sender's contribution to the range [begin, end) an owner holds: the pairs of the sender's ascending (index, f16) list that
+// fall into the range (found by binary search, so only those cross NVLink), or, if the sender's selection did not fit its list
+// (*count > capacity), that range of its dense 16-bit wire. acc is local; the other pointers may be the sender's window.
+// *bytes (optional) += the bytes read from the sender.
+int ono_sparse_lift_range(float* acc, long long begin, long long end, const unsigned int* idx, const void* val_f16,
+                          const unsigned int* count, unsigned int capacity, const void* dense16, int dense_f16,
+                          unsigned long long* bytes, ono_stream_t st);
 
 #ifdef __cplusplus
 }

@@ -312,8 +312,18 @@ def run(r) -> dict:
     metrics["grad_stage"] = bool(r.stage_active)
     if r.compress:
         sent = int(r.wire_sent.item())
-        metrics["wire"] = ("f16+sparse" if r.sparse_r is not None else "f16")
+        metrics["wire"] = (r.cwire + "+sparse") if r.sparse_r is not None else r.cwire
         metrics["wire_sent_fraction"] = sent / max(1, r.wire_rounds * r.n_pad) if r.widx is not None else None
+        if r.world > 1 and r.sync_mode in ("fused", "oneshot"):
+            # bytes this rank read from its peers per round, against what the dense 16-bit wire moves for the same ranges
+            owned = sum(e - b for b, e in r.own[r.rank])
+            senders = len([q for q in r.sync_workers if q != r.rank])
+            dense = 2 * owned * senders
+            got = int(r.wire_bytes.item()) / max(1, r.wire_rounds) if r.sparse_r is not None else dense
+            t = torch.tensor([got, dense], dtype=torch.float64, device=r.dev)
+            dist.all_reduce(t, group=r.group)
+            metrics["wire_bytes_per_round"], metrics["wire_dense16_bytes_per_round"] = float(t[0]), float(t[1])
+            metrics["wire_dense32_bytes_per_round"] = 2.0 * float(t[1])
     if len(r.bench_events) == 2:
         metrics["bench_ms"] = r.bench_events[0].elapsed_time(r.bench_events[1])
         metrics["bench_wall_s"] = r.bench_wall[1] - r.bench_wall[0]

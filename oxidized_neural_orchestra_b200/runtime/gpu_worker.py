@@ -81,14 +81,23 @@ class GpuRank:
         lay = WindowLayout()
         lay.add("params", self.n_pad, torch.float32)
         lay.add("grads", self.n_pad, torch.float32)
-        # Compressed gradient wire (reference cadence only): peers reduce the `wire` region, which holds the f16-rounded
-        # entries a rank sends this round; what it does not send stays in `grads` as its residual
-        # (comms/src/handles/compressor.rs:71-118, worker/src/middlewares/server_cluster.rs:85-104).
+        # Compressed gradient wire of the reference's cadence (comms/src/handles/compressor.rs:71-118,
+        # worker/src/middlewares/server_cluster.rs:85-104, comms/src/sparse/protocol.rs:57-86): what a rank sends this
+        # round leaves `grads` (its residual keeps the rest) and is published in its window as 16-bit values: the dense
+        # `wire16` region and, with the sparse serializer, an ascending (index, f16) list that owners read instead
+        # whenever it is the smaller encoding (at most a third of the entries: 6 bytes per pair against 2 per element).
         ser = self.plan.get("serializer", "base")
         self.sparse_r = float(ser["sparse_capable"]["r"]) if isinstance(ser, dict) else None
-        self.compress = self.cadence == "round" and (self.b200.get("wire_dtype") == "f16" or self.sparse_r is not None)
+        wd_round = self.b200.get("wire_dtype", "auto")
+        self.compress = self.cadence == "round" and (wd_round in ("f16", "bf16") or self.sparse_r is not None)
+        self.cwire = "bf16" if wd_round == "bf16" else "f16"
         if self.compress:
-            lay.add("wire", self.n_pad, torch.float32)
+            lay.add("wire16", self.n_pad, torch.bfloat16 if self.cwire == "bf16" else torch.float16)
+            if self.sparse_r is not None:
+                self.sp_cap = max(16, self.n_pad // 3)
+                lay.add("sp_idx", self.sp_cap, torch.int32)
+                lay.add("sp_val", self.sp_cap, torch.float16)
+                lay.add("sp_cnt", 64, torch.int32)
         # Gradient wire between GPUs. The reference always ships gradients as f16 (comms/src/handles/compressor.rs:104-118,
         # decoded at comms/src/handles/worker.rs:84-101). In step cadence the default here is a bf16 wire (f32 range, so
         # the small gradients of a loss normalised by batch x outputs do not underflow); "f16" gives the reference's
@@ -148,12 +157,20 @@ class GpuRank:
         self.win = SymmetricWindow(lay.size, self.dev, self.group)
         self.C = lay.tensor(self.win, "params")
         self.G = lay.tensor(self.win, "grads")
-        self.grad_region = "wire" if self.compress else "grads"
+        self.grad_region = "grads"
         if self.compress:
-            self.wire = lay.tensor(self.win, "wire")
+            self.wire16_t = lay.tensor(self.win, "wire16")
+            self.wire = None                      # f32 form of the wire, only for the exchanges that read a local buffer
             self.wire_thr = torch.zeros(1, device=self.dev)
             self.wire_sent = torch.zeros(1, dtype=torch.int64, device=self.dev)
+            self.wire_bytes = torch.zeros(1, dtype=torch.int64, device=self.dev)     # read from peers by this rank's lifts
             self.wire_rounds = 0
+            if self.sparse_r is not None:
+                self.sp_idx, self.sp_val = lay.tensor(self.win, "sp_idx"), lay.tensor(self.win, "sp_val")
+                self.sp_cnt = lay.tensor(self.win, "sp_cnt")
+                self.sp_acc = torch.zeros(self.n_pad, device=self.dev)
+                self.sp_scratch = torch.zeros((self.n_pad + 1023) // 1024, dtype=torch.int32, device=self.dev)
+                self.sp_tick = torch.zeros(1, device=self.dev)
         self.shadow = lay.tensor(self.win, "params_bf16") if self.tile == "bf16" else None
         if needs_async:
             self.m_win, self.v_win = lay.tensor(self.win, "m"), lay.tensor(self.win, "v")
@@ -372,7 +389,9 @@ class GpuRank:
             w[li] = sorted(pieces, key=lambda t: t[0]) if aligned else None
             cast[li] = casts
             copies[li] = cps
-        self.wire_copies = copies
+        # (a rank with nothing to ship must not touch the communication stream: under graph capture a stream that was never
+        # forked from the capturing one cannot be joined)
+        self.wire_copies = copies if any(copies.values()) else None
         return {"f16": self.wire16 == "f16", "w": w, "cast": cast}
 
     def wire_ship(self, l: int, stream) -> int:
@@ -502,6 +521,14 @@ class GpuRank:
                 # every worker's gradient is read from this GPU's memory: its own window, or the staged copy of a peer's
                 g_ptrs = [g_ptrs[q] if q == self.rank else self.stage_buf[q].data_ptr() for q in range(W)]
                 algo = 2 if (win.mc_ptr != 0 and W > 2) else 0
+            if self.compress and self.sparse_r is not None:
+                # sparse wire: every sender's selection is lifted into this rank's own f32 accumulator first (see
+                # _launch_sync); the fused kernel then averages it, applies the optimizer and clears it
+                g_ptrs = [self.sp_acc.data_ptr()] * W
+                wmask, algo = 1 << self.rank, (2 if algo == 1 else algo)
+            elif self.compress:
+                g_dtype = 1 if self.cwire == "bf16" else 2
+                g_ptrs = win.peer_ptrs(lay.offset("wire16"))
             if self.wire16 is not None:
                 g_dtype = 2 if self.wire16 == "f16" else 1
                 slab0 = lay.offset("slab16")
@@ -516,7 +543,8 @@ class GpuRank:
                         g_ptrs=g_ptrs, p_f32_ptrs=pf, p_bf16_ptrs=pb,
                         flag_ptrs=win.flag_ptrs, worker_mask=wmask, member_mask=allmask, n_workers=len(workers),
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
-                        g_mc=(win.mc(lay.offset("slab16" if g_dtype else g_region)) or None) if algo == 1 else None,
+                        g_mc=(win.mc(lay.offset(("wire16" if self.compress else "slab16") if g_dtype else g_region)) or None)
+                        if algo == 1 else None,
                         p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
                         p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
@@ -525,6 +553,8 @@ class GpuRank:
                          sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
                          status=self.sync_status.data_ptr())
             s.g_dtype = g_dtype
+            if self.compress and self.sparse_r is not None:
+                s.zero_grad = 1
             if self.push_active:
                 s.zero_grad = 1
                 if self.engine is not None:
@@ -707,16 +737,37 @@ class GpuRank:
         if self.compress and g_tensor is self.G:
             from ..ops import compress as cp
 
+            fused = self.sync_mode in ("fused", "oneshot")
+            sparse = self.sparse_r is not None
+            if not fused and self.wire is None:
+                self.wire = torch.zeros(self.n_pad, device=self.dev)
             if self.widx is not None:
                 thr = None
-                if self.sparse_r is not None:
+                if sparse:
                     thr = cp.sparse_threshold(self.G[:self.n], self.sparse_r, self.seed + self.wire_rounds, out=self.wire_thr,
                                               stream=stream)
                     n += 1
-                cp.wire_mask(self.G, self.wire, thr, self.wire_sent, stream=stream)
+                    if fused:     # the (index, f16) list of the selection, before the mask takes it out of the residual
+                        cp.sparse_compact(self.G, thr, self.sp_cap, zero_sent=False, stream=stream,
+                                          out=(self.sp_idx, self.sp_val, self.sp_cnt[:1]), scratch=self.sp_scratch)
+                        n += 3
+                cp.wire_mask(self.G, None if fused else self.wire, thr, self.wire_sent, wire16=self.wire16_t if fused else None,
+                             stream=stream)
                 n += 1
             self.wire_rounds += 1
-            g_tensor = self.wire
+            if fused and sparse:
+                if self.world > 1:      # every sender's list is complete before anyone reads it
+                    with torch.cuda.stream(stream):
+                        dist.all_reduce(self.sp_tick, group=self.group)
+                lay, win = self.layout, self.win
+                idx_p, val_p = win.peer_ptrs(lay.offset("sp_idx")), win.peer_ptrs(lay.offset("sp_val"))
+                cnt_p, w16_p = win.peer_ptrs(lay.offset("sp_cnt")), win.peer_ptrs(lay.offset("wire16"))
+                for q in self.sync_workers:
+                    for b, e in self.own[self.rank]:
+                        cp.sparse_lift_range(self.sp_acc, b, min(e, self.n_pad), idx_p[q], val_p[q], cnt_p[q], self.sp_cap, w16_p[q],
+                                             self.cwire == "f16", self.wire_bytes if q != self.rank else None, stream=stream)
+                        n += 1
+            g_tensor = self.wire if not fused else self.G
         if self.sync_opt.kind == "adam" and not self.apply_active:   # with the optimizer in the GEMM epilogues the step ticks first
             ew.adam_tick(self.adam_pows, self.sync_opt.b1, self.sync_opt.b2, stream=stream)
             n += 1

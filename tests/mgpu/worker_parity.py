@@ -48,14 +48,15 @@ def main():
     mom = lambda: GradientDescentWithMomentum(0.1, 0.9)
     cases = []          # (name, model, builder(addrs), expectations on the metrics)
 
-    def ar(name, mdl, classes, b200, opt=mom, expect=None):
-        cases.append((name, mdl, lambda a: orchestra.all_reduce(a, ds(classes), opt(), CrossEntropy(), 6, 48, seed=4, b200=b200),
-                      expect or {}))
+    def ar(name, mdl, classes, b200, opt=mom, expect=None, ser=None):
+        cases.append((name, mdl, lambda a: orchestra.all_reduce(a, ds(classes), opt(), CrossEntropy(), 6, 48, seed=4, b200=b200,
+                                                                serializer=ser), expect or {}))
 
     def ps(name, mdl, classes, b200, opt=mom, nserv=max(1, world // 2), expect=None, sync=BarrierSync, store=BlockingStore,
-           nworkers=world, epochs=6):
+           nworkers=world, epochs=6, ser=None):
         cases.append((name, mdl, lambda a: orchestra.parameter_server(a, nserv, ds(classes, nworkers), opt(), CrossEntropy(), sync(),
-                                                                      store(), epochs, 48, seed=4, b200=b200), expect or {}))
+                                                                      store(), epochs, 48, seed=4, b200=b200, serializer=ser),
+                      expect or {}))
 
     for cadence in ("step", "round"):
         for mode in ("twoshot", "oneshot", "nvls", "ring", "nccl"):
@@ -88,6 +89,14 @@ def main():
         # unaligned layer widths (300, 120, 10): the pieces that cannot leave as TMA stores are cast and pushed
         ar(f"ar-{tile}-wire16-unaligned-step", model, 10, {"sync_every": "step", "tile_dtype": tile}, expect={"wire": "bf16"})
         ar(f"ar-{tile}-wire32-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "wire_dtype": "f32"}, expect={"wire": "f32"})
+    # compressed wire of the reference's cadence: dense f16 / bf16 values, and the sparse serializer whose (index, f16)
+    # lists are what crosses NVLink (the run must report fewer bytes than the dense 16-bit wire moves)
+    from orchestra.serializer import SparseSerializer
+    ar("ar-wire-f16-round", model, 10, {"sync_every": "round", "wire_dtype": "f16"}, expect={"wire": "f16"})
+    ar("ar-wire-bf16-round", model, 10, {"sync_every": "round", "wire_dtype": "bf16"}, expect={"wire": "bf16"})
+    ar("ar-wire-sparse-round", model, 10, {"sync_every": "round"}, expect={"wire": "f16+sparse"}, ser=SparseSerializer(0.1))
+    ps("ps-wire-sparse-round", model, 10, {"sync_every": "round", "colocate": True, "sharding": "even"}, expect={"wire": "f16+sparse"},
+       ser=SparseSerializer(0.1))
     if world >= 2:
         ps("ps-pure-servers-layer-round", model, 10, {}, opt=lambda: GradientDescent(0.2), nserv=1, nworkers=world - 1)
         ps("ps-pure-servers-wire16-step", model12, 16, {"sync_every": "step"}, opt=lambda: GradientDescent(0.2), nserv=1,
@@ -140,8 +149,10 @@ def main():
             # Bounds: about ten times the deviations these cases show. Asynchronous pushes land in a different order on
             # GPUs than in the oracle's rank order, Adam divides by sqrt(v), bf16 tiles round the operands, and after a
             # switch the re-scattered data is batched differently: those cases get the wider bound.
-            loose = any(k in name for k in ("async", "adam", "switch", "bf16", "wire16"))
+            loose = any(k in name for k in ("async", "adam", "switch", "bf16", "wire16", "wire-"))
             met_ok = all(met.get(k) == v for k, v in expect.items())
+            if "sparse" in name and world > 1:
+                met_ok = met_ok and met.get("wire_bytes_per_round", 1e30) < met.get("wire_dense16_bytes_per_round", 0)
             # (after a loss-triggered switch the promoted rank's rows are re-scattered: the remaining workers batch
             # them differently from the oracle's workers, and Adam amplifies that: its own, wider bound)
             lim_l, lim_w = (0.3, 0.2) if name == "switch-round" else ((0.08, 0.03) if loose else (0.05, 2e-2))
@@ -149,7 +160,8 @@ def main():
             report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "loss": [float(lg[0]), float(lg[-1])] if same_len else [],
                             "nvls": met.get("nvls"), "mode": met.get("sync_mode"), "wire": met.get("wire"),
                             "wire_push": met.get("wire_push"), "switched": met.get("switched"), "push": met.get("grad_push"),
-                            "stage": met.get("grad_stage"), "expect_ok": bool(met_ok)}
+                            "stage": met.get("grad_stage"), "expect_ok": bool(met_ok),
+                            "wire_bytes": met.get("wire_bytes_per_round"), "dense16_bytes": met.get("wire_dense16_bytes_per_round")}
             ok = ok and good
         dist.barrier()
     if rank == 0:
