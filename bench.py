@@ -179,6 +179,8 @@ def main() -> None:
                     help="diagnostic: run the steps uncaptured with CUDA events around compute / exchange / refresh and add "
                          "their mean durations (phase_ms) to the line; such a line is not a benchmark value")
     ap.add_argument("--strategy", default=None, help="override the config's strategy: ar | psN | ssN (N server ranks)")
+    ap.add_argument("--switch-window", type=int, default=None, help="strategy switch: window (steps) of the gradient-norm test")
+    ap.add_argument("--switch-threshold", type=float, default=None, help="strategy switch: relative-change threshold")
     ap.add_argument("--no-baseline", action="store_true", help="do not run the NCCL + cuBLAS arm after ours (vs_baseline: null)")
     ap.add_argument("--wire", default=None, choices=("auto", "f32", "f16", "bf16"), help="gradient wire between GPUs")
     args = ap.parse_args()
@@ -209,6 +211,10 @@ def main() -> None:
         cfg["phase_timing"] = True
     if args.wire:
         cfg["wire"] = args.wire
+    if args.switch_window:
+        SWITCH["window"] = args.switch_window
+    if args.switch_threshold is not None:
+        SWITCH["threshold"] = args.switch_threshold
     W, K = max(3, args.warmup), args.steps
     sys.path.insert(0, os.path.join(ROOT, "baseline"))
     import torch_nccl
@@ -267,6 +273,18 @@ def main() -> None:
                     "device_ms_per_step": e["bench_ms"] / K},
             "gpu_launches": int(m["launches_per_step"]) * K,
         }
+        if cfg["strategy"].startswith("ss"):
+            # the two phases of the strategy switch, from the per-step CUDA events of the device-resident run: all-reduce
+            # before the promoted ranks became servers, parameter server after (steps next to the switch itself left out)
+            sm, at = m.get("step_ms") or [], m.get("switched_at_step")
+            out["switch"] = {"metric": SWITCH["metric"], "window": SWITCH["window"], "threshold": SWITCH["threshold"],
+                             "switched_at_step": at}
+            if at and len(sm) > at + 6 and at > 8:
+                pre, post = sm[5:at - 2], sm[at + 3:]
+                workers_after = world - min(int(cfg["strategy"][2:] or 2), world)
+                out["switch"].update(pre_ms_per_step=sum(pre) / len(pre), post_ms_per_step=sum(post) / len(post),
+                                     pre_samples_per_s=gb / (sum(pre) / len(pre) / 1e3),
+                                     post_samples_per_s=cfg["batch"] * workers_after / (sum(post) / len(post) / 1e3))
         if base:
             out["baseline"] = {"impl": base["impl"], "what": "same model / strategy / batch / wire with NCCL + cuBLAS (baseline/torch_nccl.py), "
                                "run in this invocation right after ours", "value": base["value"], "ms_per_step": base["ms_per_step"],

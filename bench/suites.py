@@ -165,6 +165,7 @@ def main():
     ap.add_argument("--epochs", type=int, default=4)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=1)
+    ap.add_argument("--only", default="", help="comma-separated substrings: run only the suite rows whose label contains one of them")
     ap.add_argument("--out", default=os.path.join(ROOT, "bench", "results"))
     a = ap.parse_args()
     import torch
@@ -179,6 +180,8 @@ def main():
     with open(os.path.join(a.out, "history.jsonl"), "a") as hist:
         for model_name in (("lenet5", "nielsen") if a.model == "both" else (a.model,)):
             for label, strategy, workers, servers, extra in suites(a.suite, n_nodes):
+                if a.only and not any(k in label for k in a.only.split(",")):
+                    continue
                 for rep in range(a.repeats):
                     if a.suite == "published":      # the models' recipes: benchmarks/issue/suites.py:148-178
                         extra = dict(extra, lr=0.05 if model_name == "lenet5" else 0.1)

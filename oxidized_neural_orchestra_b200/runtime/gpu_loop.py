@@ -275,6 +275,7 @@ def do_switch(r) -> None:
         r.engine, r.feeder, r.widx = None, None, None
     r._set_ownership(ranges, remaining, opt, "async" if is_async else "fused", spec["store"] == "wild")
     r.switched = True
+    r.switched_at_step = len(r.step_events)
     if r.world > 1:
         dist.barrier(group=r.group)
     if r.rank == 0:

@@ -299,7 +299,8 @@ def run(r) -> dict:
     metrics = {
         "step_ms": ms, "steps": len(evs), "step_wall": r.step_wall, "launches_per_step": r.launches_per_step,
         "h2d_bytes_per_step": r.feeder.h2d_bytes_per_step if r.feeder is not None else 0,
-        "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched, "sync_mode": r.sync_mode,
+        "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched,
+        "switched_at_step": getattr(r, "switched_at_step", None), "sync_mode": r.sync_mode,
         "nvls": bool(r.use_nvls and r.win.mc_ptr),
         # what travels between GPUs: the 16-bit wire applies to the fused kernels of step cadence
         "wire": (r.wire16 if (r.wire16 is not None and r.sync_mode in ("fused", "oneshot")) else "f32") if r.world > 1 else "none",
