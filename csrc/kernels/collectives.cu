@@ -232,8 +232,8 @@ __device__ __forceinline__ void chunk_bounds4(long long n4, int nranks, int c, l
   hi = lo + base + (c < rem ? 1 : 0);
 }
 
-__global__ void __launch_bounds__(512) ring_kernel(const OnoRing a) {
-  const int N = a.nranks, r = a.rank, blk = blockIdx.x;
+__device__ void ring_body(const OnoRing& a, const int blk) {
+  const int N = a.nranks, r = a.rank;
   const int prev = (r + N - 1) % N, next = (r + 1) % N;
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
@@ -350,6 +350,23 @@ __global__ void __launch_bounds__(512) ring_kernel(const OnoRing a) {
     if ((!ok || !fin) && a.status) atomicCAS(a.status, 0, ONO_ERR_TIMEOUT_PEER_FLAG);
     a.epoch[blk] = base + 2u * N;
   }
+}
+
+__global__ void __launch_bounds__(512) ring_kernel(const OnoRing a) { ring_body(a, blockIdx.x); }
+
+// Every rank of the ring as one cooperative launch on one GPU (grid.y = rank): the blocks really wait on one another
+// through the same flags, only the wires are missing. For single-GPU tests of the ring protocol.
+__global__ void __launch_bounds__(512) ring_kernel_emulated(const OnoRingEmu e) {
+  OnoRing a;
+  const int r = blockIdx.y;
+  a.nranks = e.nranks; a.rank = r; a.nblocks = e.nblocks; a.n = e.n;
+  a.g = e.g[r];
+  for (int q = 0; q < ONO_MAX_RANKS; ++q) { a.acc[q] = e.acc[q]; a.flags[q] = e.flags[q]; }
+  a.epoch = e.epoch[r];
+  a.p = e.p[r]; a.m = e.m[r]; a.v = e.v[r]; a.adam_pows = e.adam_pows; a.p_bf16 = e.p_bf16[r];
+  a.kind = e.kind; a.lr = e.lr; a.mu = e.mu; a.b1 = e.b1; a.b2 = e.b2; a.eps = e.eps;
+  a.status = e.status; a.timeout_ns = e.timeout_ns;
+  ring_body(a, blockIdx.x);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -569,6 +586,18 @@ extern "C" int ono_ring_allreduce(const OnoRing* r, ono_stream_t st) {
   return check_launch("ring_allreduce");
 }
 
+extern "C" int ono_ring_allreduce_emulated(const OnoRingEmu* r, ono_stream_t st) {
+  if (!r || r->nranks < 1 || r->nranks > ONO_MAX_RANKS || r->nblocks < 1 || r->n <= 0) {
+    set_error("bad ring args%s", "", 0, 0);
+    return -1;
+  }
+  OnoRingEmu copy = *r;
+  void* args[] = {&copy};
+  cudaError_t e = cudaLaunchCooperativeKernel((void*)ring_kernel_emulated, dim3(r->nblocks, r->nranks), dim3(512), args, 0, (cudaStream_t)st);
+  if (e != cudaSuccess) { set_error("cooperative launch failed: %s", cudaGetErrorString(e), 0, 0); return -7; }
+  return 0;
+}
+
 extern "C" int ono_pingpong(int role, unsigned int* my_flag, unsigned int* peer_flag, int rounds, unsigned int base,
                             unsigned long long* rtt, int* status, ono_stream_t st) {
   pingpong_kernel<<<1, 1, 0, (cudaStream_t)st>>>(role, my_flag, peer_flag, rounds, base, rtt, status);
@@ -586,6 +615,7 @@ extern "C" int ono_sizeof(int which) {
     case 5: return (int)sizeof(OnoPsAsync);
     case 6: return (int)sizeof(OnoRing);
     case 7: return (int)sizeof(OnoStagePull);
+    case 8: return (int)sizeof(OnoRingEmu);
     default: return -1;
   }
 }

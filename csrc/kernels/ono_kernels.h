@@ -286,6 +286,19 @@ typedef struct OnoRing {
   int* status; unsigned long long timeout_ns;
 } OnoRing;
 int ono_ring_allreduce(const OnoRing* r, ono_stream_t stream);
+// All ranks of the ring as one cooperative launch on ONE GPU (grid.y = rank), every rank with its own buffers: for
+// single-GPU tests of the ring protocol (the flags are the same; the launch fails cleanly if the grid is not co-resident).
+typedef struct OnoRingEmu {
+  int nranks, nblocks;
+  long long n;
+  const float* g[ONO_MAX_RANKS];
+  float* acc[ONO_MAX_RANKS]; unsigned int* flags[ONO_MAX_RANKS]; unsigned int* epoch[ONO_MAX_RANKS];
+  float* p[ONO_MAX_RANKS]; float* m[ONO_MAX_RANKS]; float* v[ONO_MAX_RANKS]; void* p_bf16[ONO_MAX_RANKS];
+  const float* adam_pows;
+  int kind; float lr, mu, b1, b2, eps;
+  int* status; unsigned long long timeout_ns;
+} OnoRingEmu;
+int ono_ring_allreduce_emulated(const OnoRingEmu* r, ono_stream_t stream);
 
 // Staged reduce-scatter: while backward is still running, a few SMs copy the peers' finished gradient ranges (those this
 // rank owns) from their windows into local staging buffers with bulk async copies through shared memory; the fused

@@ -76,6 +76,7 @@ def _declare(lib) -> None:
         "ono_sync_step_emulated": [C.POINTER(OnoSync), vp],
         "ono_ps_async_step": [C.POINTER(OnoPsAsync), vp],
         "ono_ring_allreduce": [C.POINTER(OnoRing), vp],
+        "ono_ring_allreduce_emulated": [vp, vp],
         "ono_pingpong": [ci, vp, vp, ci, C.c_uint, vp, vp, vp],
         "ono_push_add": [vp, vp, ll, vp],
         "ono_cast16": [vp, vp, ll, ci, vp],
@@ -91,7 +92,7 @@ def _declare(lib) -> None:
     lib.ono_num_sms.restype = ci
     lib.ono_sizeof.argtypes = [ci]
     lib.ono_sizeof.restype = ci
-    for i, st in enumerate((OnoGemm, OnoLoss, OnoOptim, OnoRows, OnoSync, OnoPsAsync, OnoRing, OnoStagePull)):
+    for i, st in enumerate((OnoGemm, OnoLoss, OnoOptim, OnoRows, OnoSync, OnoPsAsync, OnoRing, OnoStagePull, OnoRingEmu)):
         if lib.ono_sizeof(i) != C.sizeof(st):
             raise RuntimeError(f"ABI mismatch for {st.__name__}: C {lib.ono_sizeof(i)} vs ctypes {C.sizeof(st)}")
 
@@ -221,5 +222,16 @@ class OnoRing(C.Structure):
         ("p_bf16", C.c_void_p),
         ("kind", C.c_int), ("lr", C.c_float), ("mu", C.c_float), ("b1", C.c_float), ("b2", C.c_float),
         ("eps", C.c_float),
+        ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+    ]
+
+
+class OnoRingEmu(C.Structure):
+    _fields_ = [
+        ("nranks", C.c_int), ("nblocks", C.c_int), ("n", C.c_longlong),
+        ("g", C.c_void_p * MAX_RANKS), ("acc", C.c_void_p * MAX_RANKS), ("flags", C.c_void_p * MAX_RANKS),
+        ("epoch", C.c_void_p * MAX_RANKS), ("p", C.c_void_p * MAX_RANKS), ("m", C.c_void_p * MAX_RANKS),
+        ("v", C.c_void_p * MAX_RANKS), ("p_bf16", C.c_void_p * MAX_RANKS), ("adam_pows", C.c_void_p),
+        ("kind", C.c_int), ("lr", C.c_float), ("mu", C.c_float), ("b1", C.c_float), ("b2", C.c_float), ("eps", C.c_float),
         ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
     ]

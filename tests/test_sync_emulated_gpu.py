@@ -160,3 +160,63 @@ def test_sixteen_bit_gradient_windows(fmt, kind):
         assert status[r].item() == 0
         assert (p[r].double() - ref_p).abs().max().item() < (2e-3 if kind == "adam" else 1e-5), f"rank {r}"
         assert (pb[r].float() - p[r]).abs().max().item() <= 2 ** -7 * p[r].abs().max().item()
+
+
+@pytest.mark.parametrize("kind", ["sgd", "momentum", "adam"])
+@pytest.mark.parametrize("nranks", [2, 3, 4, 8])
+def test_ring_all_reduce_protocol(kind, nranks):
+    """The ring kernel (reduce-scatter + optimizer on the owned chunk + all-gather of fresh parameters, chunked like
+    worker/src/middlewares/mod.rs:15-59) with every rank in one cooperative launch: each block pipeline waits on its
+    neighbours' step flags exactly as it does over NVLink."""
+    import ctypes as C
+
+    from oxidized_neural_orchestra_b200.ops import _lib
+    from oxidized_neural_orchestra_b200.ops.elementwise import OPT_KIND, adam_tick
+
+    lib = _lib.load()
+    torch.manual_seed(5)
+    n, nblocks = 50_000, 3
+    npad = (n + 3) // 4 * 4
+    z = lambda dt=torch.float32, m=npad: torch.zeros(m, device="cuda", dtype=dt)
+    g, acc, p, m, v = ([z() for _ in range(nranks)] for _ in range(5))
+    pb = [z(torch.bfloat16) for _ in range(nranks)]
+    flags = [z(torch.int32, 2 * nblocks) for _ in range(nranks)]
+    epoch = [z(torch.int32, nblocks) for _ in range(nranks)]
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+    pows = torch.ones(2, device="cuda")
+    p0 = torch.randn(npad, device="cuda")
+    for t in p:
+        t.copy_(p0)
+    e = _lib.OnoRingEmu()
+    e.nranks, e.nblocks, e.n = nranks, nblocks, npad
+    for r in range(nranks):
+        e.g[r], e.acc[r], e.flags[r], e.epoch[r] = g[r].data_ptr(), acc[r].data_ptr(), flags[r].data_ptr(), epoch[r].data_ptr()
+        e.p[r], e.m[r], e.v[r], e.p_bf16[r] = p[r].data_ptr(), m[r].data_ptr(), v[r].data_ptr(), pb[r].data_ptr()
+    e.adam_pows, e.kind, e.lr, e.mu, e.b1, e.b2, e.eps = pows.data_ptr(), OPT_KIND[kind], 0.05, 0.9, 0.9, 0.999, 1e-8
+    e.status, e.timeout_ns = status.data_ptr(), 2_000_000_000
+    ref_p, ref_m, ref_v = p0.double().clone(), torch.zeros(npad, device="cuda").double(), torch.zeros(npad, device="cuda").double()
+    b1t = b2t = 1.0
+    for step in range(3):       # the flags are epoch-stamped: later calls run on what the earlier ones left
+        gs = [torch.randn(npad, device="cuda") for _ in range(nranks)]
+        for r in range(nranks):
+            g[r].copy_(gs[r])
+        if kind == "adam":
+            adam_tick(pows, 0.9, 0.999)
+        _lib.check(lib.ono_ring_allreduce_emulated(C.byref(e), _lib.stream_ptr()), "ono_ring_allreduce_emulated")
+        avg = sum(t.double() for t in gs) / nranks
+        if kind == "sgd":
+            ref_p -= 0.05 * avg
+        elif kind == "momentum":
+            ref_m = 0.9 * ref_m + avg
+            ref_p -= 0.05 * ref_m
+        else:
+            b1t *= 0.9; b2t *= 0.999
+            ref_m = 0.9 * ref_m + 0.1 * avg
+            ref_v = 0.999 * ref_v + 0.001 * avg * avg
+            ref_p -= 0.05 * math.sqrt(1 - b2t) / (1 - b1t) * ref_m / (ref_v.sqrt() + 1e-8)
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    for r in range(nranks):
+        assert (p[r].double() - ref_p).abs().max().item() < (1e-3 if kind == "adam" else 1e-4), f"rank {r}"
+        assert torch.equal(p[r], p[0])                      # every replica ends with the same bits
+        assert (pb[r].float() - p[r]).abs().max().item() <= 2 ** -7 * p[r].abs().max().item()
