@@ -3,6 +3,9 @@
 //   orchestui                                       interactive: menu -> config paths -> dashboard
 //   orchestui --render-once <model.json> <training.json> [--size WxH] [--no-save]
 //                                                   run to completion without a terminal and print the last frame
+//   orchestui --script "<keys>" [--size WxH]        drive the interactive screens from a key script instead of a terminal
+//                                                   (tokens: <enter> <esc> <up> <down> <left> <right> <tab> <bs> <wait> <dump>);
+//                                                   every <dump> prints the current frame as plain text
 //
 // Screen flow and panels follow the reference's terminal UI (orchestui/src/ui/screens/mod.rs:21-57,
 // orchestui/src/app/run.rs:41-70): a menu, a configuration screen with two path prompts (ghost text shows
@@ -12,6 +15,7 @@
 // `safetensors/<adjective>_<term>.safetensors` (orchestui/src/ui/screens/training.rs:480-493) - that
 // directory of auto-named checkpoints is the trained-model repository. Events are consumed without
 // blocking the UI (training.rs:302-347).
+#include <dirent.h>
 #include <sys/stat.h>
 
 #include <chrono>
@@ -79,6 +83,7 @@ struct Dashboard {
   std::vector<float> params;
   std::string stop_reason, error, saved_to;
   bool finished = false, switched = false, stop_requested = false;
+  mutable unsigned frame = 0;      // drives the flow animation of the topology panel
   std::chrono::steady_clock::time_point t0 = std::chrono::steady_clock::now();
   double elapsed_s = 0;
 
@@ -155,37 +160,73 @@ struct Dashboard {
     return path;
   }
 
+  // Topology panel (orchestui/src/ui/components/topology.rs:46-630): the nodes of the current strategy and the traffic
+  // between them, animated while training runs. Ring: the workers in tour order with a packet circulating (reduce-scatter
+  // then all-gather). Parameter server: servers above, workers below, residuals going up and parameters coming down.
   void draw_topology(Canvas& c, int x, int y, int w, int h) const {
     c.box(x, y, w, h, "topology");
-    const std::string algo = plan.is_object() ? plan.at("algorithm").as_string() : "";
-    const bool ps_now = algo == "parameter_server" || switched;
-    int row = y + 1;
-    auto line = [&](const std::string& s, int color = DEFAULT) { if (row < y + h - 1) c.text(x + 2, row++, s, color, false, w - 4); };
     if (!plan.is_object()) return;
+    const std::string algo = plan.at("algorithm").as_string();
+    const bool ps_now = algo == "parameter_server" || switched;
+    const bool live = !finished;
+    const int ix = x + 2, iw = w - 4, iy = y + 1, ih = h - 2;
+    if (iw < 12 || ih < 3) return;
+    std::vector<size_t> wr, sr;
+    for (auto& wk : plan.at("workers").items()) wr.push_back((size_t)wk.at("rank").as_u64());
+    if (const Json* sv = plan.find("servers")) for (auto& s_ : sv->items()) sr.push_back((size_t)s_.at("rank").as_u64());
     if (!ps_now) {
-      std::string ring;
-      for (auto& wk : plan.at("workers").items()) ring += fmt("w%llu → ", wk.at("rank").as_u64());
-      if (!ring.empty()) ring += fmt("w%llu", plan.at("workers")[0].at("rank").as_u64());
-      line("ring all-reduce (order of the tour)", CYAN);
-      line(ring);
-      line("reduce-scatter ⟶ all-gather ⟶ average ⟶ optimizer on every replica", GREY);
-      if (algo == "strategy_switch") line("watching the plateau test: switch promotes servers", YELLOW);
-    } else {
-      line(switched ? "parameter server (after the switch)" : "parameter server", CYAN);
-      std::string servers, wk;
-      if (const Json* sv = plan.find("servers"))
-        for (auto& s : sv->items()) servers += fmt("[S%llu] ", s.at("rank").as_u64());
-      for (auto& w_ : plan.at("workers").items()) {
-        const size_t r = (size_t)w_.at("rank").as_u64();
-        bool is_server = false;
-        if (const Json* sv = plan.find("servers"))
-          for (auto& s : sv->items()) is_server = is_server || s.at("rank").as_u64() == r;
-        if (!(switched && is_server && !training.b200.colocate)) wk += fmt("(w%zu) ", r);
+      c.text(ix, iy, "ring all-reduce", CYAN, false, iw);
+      // nodes laid out on the two long sides of a rectangle, in tour order, arrows along the perimeter
+      const size_t n = wr.size();
+      const size_t top_n = (n + 1) / 2, bot_n = n - top_n;
+      const int step = std::max(5, iw / (int)std::max<size_t>(top_n, 1));
+      const int ty = iy + 1, by_ = std::min(iy + ih - 2, iy + 3);
+      std::vector<std::pair<int, int>> pos(n);
+      for (size_t i = 0; i < top_n; ++i) pos[i] = {ix + (int)i * step, ty};
+      for (size_t i = 0; i < bot_n; ++i) pos[top_n + i] = {ix + (int)(top_n - 1 - i) * step - (top_n > bot_n && i == 0 ? 0 : 0), by_};
+      const size_t phase = n ? (frame / 2) % (2 * n) : 0;        // 2n hops per round: n-1 scatter, n-1 gather, 2 for the update
+      for (size_t i = 0; i < n; ++i) {
+        const bool hot = live && (phase % n) == i;
+        c.text(pos[i].first, pos[i].second, fmt("w%zu", wr[i]), hot ? YELLOW : DEFAULT, hot, 4);
+        const size_t j = (i + 1) % n;
+        if (n > 1 && pos[i].second == pos[j].second) {
+          const int a = std::min(pos[i].first, pos[j].first) + 3, b = std::max(pos[i].first, pos[j].first) - 1;
+          for (int q = a; q <= b; ++q) c.put(q, pos[i].second, pos[i].first < pos[j].first ? "→" : "←", hot ? YELLOW : GREY);
+        } else if (n > 1) {
+          for (int q = std::min(pos[i].second, pos[j].second) + 1; q < std::max(pos[i].second, pos[j].second); ++q)
+            c.put(pos[i].first + 1, q, pos[i].second < pos[j].second ? "↓" : "↑", hot ? YELLOW : GREY);
+        }
       }
-      line("servers: " + servers, GREEN);
-      line("   ⇅ push residual / pull parameters (every worker ↔ every server)", GREY);
-      line("workers: " + wk);
+      if (ih >= 5)
+        c.text(ix, iy + ih - 1, !live ? "idle" : phase < n ? "reduce-scatter: partial sums travel the ring" : "all-gather: fresh parameters travel the ring",
+               GREY, false, iw);
+      if (algo == "strategy_switch" && ih >= 6) c.text(ix, iy + ih - 2, "plateau test armed: switch promotes servers", YELLOW, false, iw);
+    } else {
+      c.text(ix, iy, switched ? "parameter server (after the switch)" : "parameter server", CYAN, false, iw);
+      std::vector<size_t> pure_workers;
+      for (size_t r : wr) {
+        const bool is_server = std::find(sr.begin(), sr.end(), r) != sr.end();
+        if (!(is_server && !training.b200.colocate)) pure_workers.push_back(r);
+      }
+      const int sstep = std::max(6, iw / (int)std::max<size_t>(sr.size(), 1)), wstep = std::max(5, iw / (int)std::max<size_t>(pure_workers.size(), 1));
+      const int sy = iy + 1, wy = std::min(iy + ih - 2, iy + 4);
+      for (size_t i = 0; i < sr.size(); ++i) c.text(ix + (int)i * sstep, sy, fmt("[S%zu]", sr[i]), GREEN, true, 6);
+      const bool push = (frame / 3) % 2 == 0;
+      for (size_t i = 0; i < pure_workers.size(); ++i) {
+        const int wx = ix + (int)i * wstep;
+        c.text(wx, wy, fmt("(w%zu)", pure_workers[i]), DEFAULT, false, 6);
+        if (live) {
+          const int span = wy - sy - 1;
+          if (span > 0) {
+            const int at = push ? wy - 1 - (int)(frame % (unsigned)span) : sy + 1 + (int)(frame % (unsigned)span);
+            c.put(wx + 2, at, push ? "↑" : "↓", push ? YELLOW : CYAN);
+          }
+        }
+      }
+      if (ih >= 6)
+        c.text(ix, iy + ih - 1, !live ? "idle" : push ? "push: residuals to the owners of each shard" : "pull: fresh parameters to every worker", GREY, false, iw);
     }
+    ++frame;
   }
 
   void draw(Canvas& c) const {
@@ -279,20 +320,74 @@ struct Field {
   std::string label, value, ghost;
 };
 
-int interactive() {
-  Terminal term;
-  if (!term.is_tty()) {
+// The trained-model repository: every *.safetensors under ./safetensors with its size and tensors.
+struct RepoEntry {
+  std::string name;
+  long long bytes = 0;
+  std::vector<std::string> tensors;      // "layer_0.weight [784, 128]"
+};
+
+std::vector<RepoEntry> scan_repository() {
+  std::vector<RepoEntry> out;
+  DIR* d = ::opendir("safetensors");
+  if (!d) return out;
+  while (dirent* e = ::readdir(d)) {
+    const std::string n = e->d_name;
+    if (n.size() < 13 || n.substr(n.size() - 12) != ".safetensors") continue;
+    RepoEntry r;
+    r.name = n;
+    struct stat st{};
+    if (::stat(("safetensors/" + n).c_str(), &st) == 0) r.bytes = (long long)st.st_size;
+    try {
+      for (auto& t : load_safetensors("safetensors/" + n)) {
+        std::string shape;
+        for (size_t i = 0; i < t.shape.size(); ++i) shape += (i ? ", " : "") + std::to_string(t.shape[i]);
+        r.tensors.push_back(t.name + " [" + shape + "]");
+      }
+    } catch (const std::exception& ex) { r.tensors.push_back(std::string("unreadable: ") + ex.what()); }
+    out.push_back(std::move(r));
+  }
+  ::closedir(d);
+  std::sort(out.begin(), out.end(), [](const RepoEntry& a, const RepoEntry& b) { return a.name < b.name; });
+  return out;
+}
+
+// Inline examples of the two documents, one pair per strategy (the configuration screen cycles through them).
+struct Example { const char* title; std::vector<const char*> lines; };
+const Example kExamples[] = {
+  {"all-reduce on four GPUs, bf16 tiles, one exchange per step",
+   {"model.json     { \"layers\": [ { \"dense\": { \"output_size\": 4096, \"init\": \"kaiming\", \"act_fn\": { \"relu\": { \"slope\": 0.0 } } } },",
+    "                               { \"dense\": { \"output_size\": 10, \"init\": \"xavier_uniform\", \"act_fn\": \"softmax\" } } ] }",
+    "training.json  { \"addrs\": [\"gpu:0\", \"gpu:1\", \"gpu:2\", \"gpu:3\"], \"algorithm\": \"all_reduce\",",
+    "                 \"dataset\": { \"src\": { \"local\": { \"samples_path\": \"x.bin\", \"labels_path\": \"y.bin\" } }, \"x_size\": 784, \"y_size\": 10 },",
+    "                 \"optimizer\": { \"adam\": { \"lr\": 0.001 } }, \"loss_fn\": \"cross_entropy\", \"batch_size\": 1024, \"max_epochs\": 10,",
+    "                 \"b200\": { \"sync_every\": \"step\", \"tile_dtype\": \"bf16\" } }"}},
+  {"parameter server: two servers, blocking store, barrier synchroniser",
+   {"training.json  { \"addrs\": [\"host-a:4000\", \"host-b:4000\", \"host-c:4000\", \"host-d:4000\"],",
+    "                 \"algorithm\": { \"parameter_server\": { \"nservers\": 2, \"synchronizer\": \"barrier\", \"store\": \"blocking\" } },",
+    "                 \"optimizer\": { \"gradient_descent_with_momentum\": { \"lr\": 0.01, \"mu\": 0.9 } }, \"offline_epochs\": 0,",
+    "                 \"serializer\": { \"sparse_capable\": { \"r\": 0.01 } }, … }"}},
+  {"strategy switch: all-reduce until the loss plateaus, then two ranks become servers",
+   {"training.json  { \"addrs\": [\"cpu:0\", \"cpu:1\", \"cpu:2\", \"cpu:3\"],",
+    "                 \"algorithm\": { \"strategy_switch\": { \"nservers\": 2, \"synchronizer\": \"barrier\", \"store\": \"blocking\" } },",
+    "                 \"early_stopping\": { \"tolerance\": 1e-4 }, \"b200\": { \"switch_window\": 6, \"switch_threshold\": 0.01 }, … }"}},
+};
+
+int interactive(Console& term) {
+  if (!term.usable()) {
     std::fputs("orchestui needs a terminal (or use --render-once <model.json> <training.json>)\n", stderr);
     return 2;
   }
-  enum Screen { MENU, CONFIG, TRAINING } screen = MENU;
-  int menu_sel = 0, field_sel = 0;
+  enum Screen { MENU, CONFIG, TRAINING, REPOSITORY } screen = MENU;
+  int menu_sel = 0, field_sel = 0, repo_sel = 0, example = 0;
   Field fields[2] = {{"model config", "", "model.json"}, {"training config", "", "training.json"}};
   std::string config_error;
   std::unique_ptr<Dashboard> dash;
+  std::vector<RepoEntry> repo;
   enum Popup { NONE, CONFIRM_STOP, CONFIRM_QUIT, SAVE_AS } pop = NONE;
   std::string save_path;
   const char* menu_items[] = {"Start training", "Repository", "Quit"};
+  const int n_examples = (int)(sizeof kExamples / sizeof *kExamples);
   while (true) {
     int W, H;
     term.size(W, H);
@@ -302,6 +397,19 @@ int interactive() {
       c.text(W / 2 - 18, H / 2 - 4, "distributed training on B200 ranks", CYAN, true);
       for (int i = 0; i < 3; ++i) c.text(W / 2 - 10, H / 2 - 1 + i, std::string(i == menu_sel ? "› " : "  ") + menu_items[i], i == menu_sel ? GREEN : DEFAULT, i == menu_sel);
       c.text(2, H - 2, "↑/↓ select   enter confirm   q quit", GREY);
+    } else if (screen == REPOSITORY) {
+      c.box(0, 0, W, H, "trained-model repository · ./safetensors");
+      if (repo.empty()) c.text(4, 3, "no saved models yet: a finished run is saved here under a generated name", GREY, false, W - 8);
+      const int list_w = std::max(30, W * 2 / 5);
+      for (int i = 0; i < (int)repo.size() && i < H - 6; ++i)
+        c.text(3, 2 + i, fmt("%s %-28s %9.1f KB", i == repo_sel ? "›" : " ", repo[(size_t)i].name.c_str(), (double)repo[(size_t)i].bytes / 1024.0),
+               i == repo_sel ? GREEN : DEFAULT, i == repo_sel, list_w);
+      if (!repo.empty()) {
+        const RepoEntry& r = repo[(size_t)repo_sel];
+        c.box(list_w + 4, 1, W - list_w - 6, H - 4, r.name);
+        for (int i = 0; i < (int)r.tensors.size() && i < H - 7; ++i) c.text(list_w + 6, 2 + i, r.tensors[(size_t)i], DEFAULT, false, W - list_w - 10);
+      }
+      c.text(2, H - 2, "↑/↓ select   esc back", GREY);
     } else if (screen == CONFIG) {
       c.box(0, 0, W, H, "configuration");
       for (int i = 0; i < 2; ++i) {
@@ -310,12 +418,14 @@ int interactive() {
         if (fields[i].value.empty()) c.text(6, 5 + 4 * i, fields[i].ghost, GREY, false, W - 12);
         else c.text(6, 5 + 4 * i, fields[i].value, DEFAULT, false, W - 12);
       }
-      c.text(4, 12, "model.json    { \"layers\": [ { \"dense\": { \"output_size\": 128, \"init\": \"kaiming\", \"act_fn\": { \"relu\": { \"slope\": 0.0 } } } }, … ] }", GREY, false, W - 8);
-      c.text(4, 13, "training.json { \"addrs\": [\"gpu:0\", …] | [\"host:port\", …] | [\"cpu:0\", …], \"algorithm\": \"all_reduce\" | { \"parameter_server\": {…} }, … }", GREY, false, W - 8);
-      if (!config_error.empty()) c.text(4, 15, config_error, RED, true, W - 8);
-      c.text(2, H - 2, "tab/↑/↓ switch field   enter start   esc back", GREY);
+      const Example& ex = kExamples[example];
+      c.text(4, 12, fmt("example %d/%d: %s", example + 1, n_examples, ex.title), CYAN, true, W - 8);
+      for (size_t i = 0; i < ex.lines.size() && 13 + (int)i < H - 4; ++i) c.text(4, 13 + (int)i, ex.lines[i], GREY, false, W - 8);
+      if (!config_error.empty()) c.text(4, H - 4, config_error, RED, true, W - 8);
+      c.text(2, H - 2, "tab/↑/↓ switch field   ←/→ other example   enter start   esc back", GREY);
     } else {
       dash->pump(0);
+      if (dash->finished) term.finished_now();
       if (dash->finished && dash->saved_to.empty() && dash->stop_reason != "error" && !dash->params.empty()) dash->save("");
       dash->draw(c);
       if (pop == CONFIRM_STOP) popup(c, "stop training", {"Stop after the current round?", "", "[y] yes    [n] no"});
@@ -324,20 +434,32 @@ int interactive() {
     }
     term.write(c.ansi());
     const int k = term.read_key(screen == TRAINING ? 100 : 250);
+    if (term.wants_dump()) {
+      std::cout << "=== frame ===\n" << c.plain();
+      std::cout.flush();
+      continue;
+    }
     if (k == KEY_NONE) continue;
+    if (k == 'Q') return 0;                     // the end of a key script
     if (screen == MENU) {
       if (k == KEY_UP) menu_sel = (menu_sel + 2) % 3;
       else if (k == KEY_DOWN) menu_sel = (menu_sel + 1) % 3;
       else if (k == 'q') return 0;
       else if (k == KEY_ENTER) {
         if (menu_sel == 0) { screen = CONFIG; config_error.clear(); }
-        else if (menu_sel == 1) config_error = "trained models are kept under ./safetensors/";
+        else if (menu_sel == 1) { repo = scan_repository(); repo_sel = 0; screen = REPOSITORY; }
         else return 0;
       }
+    } else if (screen == REPOSITORY) {
+      if (k == KEY_ESC || k == 'q') screen = MENU;
+      else if (k == KEY_UP && !repo.empty()) repo_sel = (repo_sel + (int)repo.size() - 1) % (int)repo.size();
+      else if (k == KEY_DOWN && !repo.empty()) repo_sel = (repo_sel + 1) % (int)repo.size();
     } else if (screen == CONFIG) {
       Field& f = fields[field_sel];
       if (k == KEY_ESC) screen = MENU;
       else if (k == KEY_TAB || k == KEY_UP || k == KEY_DOWN) field_sel ^= 1;
+      else if (k == KEY_LEFT) example = (example + n_examples - 1) % n_examples;
+      else if (k == KEY_RIGHT) example = (example + 1) % n_examples;
       else if (k == KEY_BACKSPACE) { if (!f.value.empty()) f.value.pop_back(); }
       else if (k == KEY_ENTER) {
         try {
@@ -375,10 +497,17 @@ int main(int argc, char** argv) {
   try {
     if (argc >= 2 && std::strcmp(argv[1], "--render-once") == 0) return render_once(argc, argv);
     if (argc >= 2 && (std::strcmp(argv[1], "-h") == 0 || std::strcmp(argv[1], "--help") == 0)) {
-      std::puts("usage: orchestui | orchestui --render-once <model.json> <training.json> [--size WxH] [--no-save]");
+      std::puts("usage: orchestui | orchestui --render-once <model.json> <training.json> [--size WxH] [--no-save] | orchestui --script \"<keys>\" [--size WxH]");
       return 0;
     }
-    return interactive();
+    if (argc >= 3 && std::strcmp(argv[1], "--script") == 0) {
+      int W = 110, H = 34;
+      for (int i = 3; i + 1 < argc; ++i) if (std::strcmp(argv[i], "--size") == 0) std::sscanf(argv[i + 1], "%dx%d", &W, &H);
+      ScriptConsole sc(argv[2], W, H);
+      return interactive(sc);
+    }
+    Terminal term;
+    return interactive(term);
   } catch (const std::exception& e) {
     std::fprintf(stderr, "orchestui: %s\n", e.what());
     return 1;

@@ -137,7 +137,65 @@ class Canvas {
   std::vector<Cell> cells_;
 };
 
-class Terminal {
+// Where the UI reads keys and sends frames: a real terminal, or a script of keys (tests, demos).
+class Console {
+ public:
+  virtual ~Console() = default;
+  virtual bool usable() const = 0;
+  virtual void size(int& w, int& h) const = 0;
+  virtual void write(const std::string& frame) = 0;
+  virtual int read_key(int timeout_ms) = 0;
+  // A script may ask for the current frame to be printed (plain text) or wait for the run to finish.
+  virtual bool wants_dump() { return false; }
+  virtual bool waiting_for_finish() const { return false; }
+  virtual void finished_now() {}
+};
+
+// Keys from a string: printable characters as themselves, and the tokens <enter> <esc> <up> <down> <left> <right> <tab>
+// <bs> <wait> (hold further keys until the running session has finished) <dump> (print the frame drawn after the
+// previous key). Frames are not written anywhere else; the script ends with an implicit quit.
+class ScriptConsole final : public Console {
+ public:
+  ScriptConsole(const std::string& script, int w, int h) : w_(w), h_(h) {
+    for (size_t i = 0; i < script.size();) {
+      if (script[i] == '<') {
+        const size_t e = script.find('>', i);
+        const std::string tok = e == std::string::npos ? "" : script.substr(i + 1, e - i - 1);
+        int k = -1;
+        if (tok == "enter") k = KEY_ENTER; else if (tok == "esc") k = KEY_ESC; else if (tok == "up") k = KEY_UP;
+        else if (tok == "down") k = KEY_DOWN; else if (tok == "left") k = KEY_LEFT; else if (tok == "right") k = KEY_RIGHT;
+        else if (tok == "tab") k = KEY_TAB; else if (tok == "bs") k = KEY_BACKSPACE; else if (tok == "wait") k = -2; else if (tok == "dump") k = -3;
+        if (k != -1) { keys_.push_back(k); i = e + 1; continue; }
+      }
+      keys_.push_back((unsigned char)script[i++]);
+    }
+  }
+  bool usable() const override { return true; }
+  void size(int& w, int& h) const override { w = w_; h = h_; }
+  void write(const std::string&) override {}
+  int read_key(int timeout_ms) override {
+    if (waiting_) { ::usleep((useconds_t)std::min(timeout_ms, 50) * 1000); return KEY_NONE; }
+    while (pos_ < keys_.size()) {
+      const int k = keys_[pos_++];
+      if (k == -2) { waiting_ = true; return KEY_NONE; }
+      if (k == -3) { dump_ = true; return KEY_NONE; }
+      return k;
+    }
+    return exhausted_++ < 3 ? KEY_NONE : 'Q';     // a few more frames, then the hard quit key
+  }
+  bool wants_dump() override { const bool d = dump_; dump_ = false; return d; }
+  bool waiting_for_finish() const override { return waiting_; }
+  void finished_now() override { waiting_ = false; }
+
+ private:
+  int w_, h_;
+  std::vector<int> keys_;
+  size_t pos_ = 0;
+  int exhausted_ = 0;
+  bool waiting_ = false, dump_ = false;
+};
+
+class Terminal final : public Console {
  public:
   Terminal() {
     tty_ = ::isatty(STDIN_FILENO) && ::isatty(STDOUT_FILENO);
@@ -157,12 +215,13 @@ class Terminal {
     ::tcsetattr(STDIN_FILENO, TCSAFLUSH, &saved_);
   }
   bool is_tty() const { return tty_; }
-  void size(int& w, int& h) const {
+  bool usable() const override { return tty_; }
+  void size(int& w, int& h) const override {
     winsize ws{};
     if (tty_ && ::ioctl(STDOUT_FILENO, TIOCGWINSZ, &ws) == 0 && ws.ws_col > 0) { w = ws.ws_col; h = ws.ws_row; }
     else { w = 100; h = 32; }
   }
-  void write(const std::string& s) const {
+  void write(const std::string& s) override {
     size_t off = 0;
     while (off < s.size()) {
       ssize_t k = ::write(STDOUT_FILENO, s.data() + off, s.size() - off);
@@ -171,7 +230,7 @@ class Terminal {
     }
   }
   // Next key (printable ASCII as itself) or KEY_NONE after `timeout_ms`.
-  int read_key(int timeout_ms) const {
+  int read_key(int timeout_ms) override {
     pollfd pf{STDIN_FILENO, POLLIN, 0};
     if (::poll(&pf, 1, timeout_ms) <= 0) return KEY_NONE;
     unsigned char c;

@@ -168,3 +168,30 @@ def test_orchestui_renders_the_dashboard_and_autosaves_into_the_model_repository
     from orchestra import _orchestra as core
 
     assert sum(np.asarray(t[2]).size for t in core.load_safetensors(str(saved[0]))) == 53
+
+
+def test_orchestui_interactive_screens_driven_by_a_key_script(bins, tmp_path):
+    """The interactive path without a terminal: menu -> configuration (examples carousel, typed paths) -> dashboard with
+    the animated topology -> stop / save pop-ups -> repository screen listing the saved models."""
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, ["cpu:0", "cpu:1", "cpu:2"], algorithm="all_reduce")
+    script = ("<dump>"                                   # the menu
+              "<enter><right><dump>"                     # configuration screen, second example
+              f"{os.path.basename(mp)}<tab>{os.path.basename(tp)}<dump><enter>"
+              "<wait><dump>"                             # dashboard after the run has finished (auto-saved)
+              "w<bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs>"
+              "<bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs><bs>safetensors/mine.safetensors<dump><enter>"
+              "m<down><enter><dump><esc>"                # back to the menu, repository screen
+              "<down><enter>")                           # quit
+    r = subprocess.run([bins["orchestui"], "--script", script, "--size", "120x34"], capture_output=True, text=True, timeout=120,
+                       cwd=tmp_path)
+    assert r.returncode == 0, r.stderr[-2000:]
+    frames = r.stdout.split("=== frame ===\n")[1:]
+    assert len(frames) == 6
+    menu, config, typed, dash, saveas, repo = frames
+    assert "Start training" in menu and "Repository" in menu
+    assert "example 2/3" in config and "parameter_server" in config
+    assert os.path.basename(mp) in typed and os.path.basename(tp) in typed
+    assert "finished: max_epochs" in dash and "ring all-reduce" in dash and "w0" in dash and "w2" in dash and "→" in dash
+    assert "save model" in saveas and "mine.safetensors" in saveas
+    assert "trained-model repository" in repo and "mine.safetensors" in repo and "layer_0.weight [6, 5]" in repo
+    assert (tmp_path / "safetensors" / "mine.safetensors").exists() and len(list((tmp_path / "safetensors").glob("*.safetensors"))) == 2
