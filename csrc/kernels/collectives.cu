@@ -232,6 +232,8 @@ __device__ __forceinline__ void chunk_bounds4(long long n4, int nranks, int c, l
   hi = lo + base + (c < rem ? 1 : 0);
 }
 
+constexpr int RING_UNROLL = 4;
+
 __device__ void ring_body(const OnoRing& a, const int blk) {
   const int N = a.nranks, r = a.rank;
   const int prev = (r + N - 1) % N, next = (r + 1) % N;
@@ -291,11 +293,23 @@ __device__ void ring_body(const OnoRing& a, const int blk) {
     if (!ok) break;
     long long lo, hi;
     slice(c, lo, hi);
-    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      const float4 x = ld_global_v4_volatile(theirs + i);
-      float4 y = mine[i];
-      y.x += x.x; y.y += x.y; y.z += x.z; y.w += x.w;
-      mine[i] = y;
+    // four peer loads in flight per thread before the first use: one block per SM has to keep its share of the link busy
+    for (long long i0 = lo + threadIdx.x; i0 < hi; i0 += (long long)blockDim.x * RING_UNROLL) {
+      float4 x[RING_UNROLL];
+#pragma unroll
+      for (int u = 0; u < RING_UNROLL; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < hi) x[u] = ld_global_v4_volatile(theirs + i);
+      }
+#pragma unroll
+      for (int u = 0; u < RING_UNROLL; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < hi) {
+          float4 y = mine[i];
+          y.x += x[u].x; y.y += x[u].y; y.z += x[u].z; y.w += x[u].w;
+          mine[i] = y;
+        }
+      }
     }
     if (s < N - 2) publish();
   }
@@ -332,11 +346,22 @@ __device__ void ring_body(const OnoRing& a, const int blk) {
     if (!ok) break;
     long long lo, hi;
     slice(c, lo, hi);
-    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      const float4 p = ld_global_v4_volatile(theirs + i);
-      mine[i] = p;
-      *(reinterpret_cast<float4*>(a.p) + i) = p;
-      if (pb) *(reinterpret_cast<uint2*>(pb) + i) = pack_bf16x4(p);
+    for (long long i0 = lo + threadIdx.x; i0 < hi; i0 += (long long)blockDim.x * RING_UNROLL) {
+      float4 x[RING_UNROLL];
+#pragma unroll
+      for (int u = 0; u < RING_UNROLL; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < hi) x[u] = ld_global_v4_volatile(theirs + i);
+      }
+#pragma unroll
+      for (int u = 0; u < RING_UNROLL; ++u) {
+        const long long i = i0 + (long long)u * blockDim.x;
+        if (i < hi) {
+          mine[i] = x[u];
+          *(reinterpret_cast<float4*>(a.p) + i) = x[u];
+          if (pb) *(reinterpret_cast<uint2*>(pb) + i) = pack_bf16x4(x[u]);
+        }
+      }
     }
     if (s < N - 2) publish();
   }

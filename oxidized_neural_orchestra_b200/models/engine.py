@@ -59,8 +59,12 @@ class GpuEngine:
     def __init__(self, layers: list[dict], *, batch_size: int, tile_dtype: str, loss: str,
                  params: torch.Tensor, grads: torch.Tensor, params_bf16: torch.Tensor | None = None,
                  leaky_relu_exact: bool = True, device=None, bias_from_shadow: bool = False,
-                 input_grad: bool = False):
+                 input_grad: bool = False, final: bool = True):
         self.bias_from_shadow = bias_from_shadow
+        # final = False: a dense block in the middle of a network (convolutions follow). Its last layer then writes its
+        # activation into ``out_act`` like any inner layer, and backward starts from ``d[-1]``, which whoever consumes
+        # ``out_act`` fills with the gradient w.r.t. that layer's pre-activation.
+        self.final = final
         self.input_grad = input_grad  # also produce d[0], the gradient w.r.t. the input batch
         self.max_ctas = 0             # CTAs a GEMM of this engine may use (0 = one per SM); lowered while other kernels need SMs
         self.push = None              # weight-gradient tiles added into the owners' f32 accumulators (see backward)
@@ -93,7 +97,9 @@ class GpuEngine:
             raise ValueError("flat parameter/gradient buffers are too small")
         # softmax on the last layer is fused into the loss kernel; on any other layer it is a row-wise pass of its own
         # after the GEMM (forward) and before the next GEMM's operand is formed (Jacobian-vector product in backward)
-        self.softmax_last = self.plans[-1].act == "softmax"
+        self.softmax_last = self.final and self.plans[-1].act == "softmax"
+        if not self.final and self.plans[-1].act in ("softmax", "gelu"):
+            raise NotImplementedError("a dense layer followed by a convolution needs a relu / sigmoid / tanh / linear activation")
         self._alloc()
 
     # ------------------------------------------------------------------------------------------
@@ -125,6 +131,7 @@ class GpuEngine:
         if not self.mn:
             self.at = [z(feats[i], ldB, f32) for i in range(len(feats) - 1)]
             self.dt = [None] + [z(feats[i], ldB, f32) for i in range(1, len(feats))]
+        self.out_act = None if self.final else z(B, self.lds[-1], cd)
         self.ybuf = z(B, _up(feats[-1]), f32)
         self.loss_sum = torch.zeros(1, device=dev, dtype=torch.float64)
         self.correct = torch.zeros(1, device=dev, dtype=torch.int32)
@@ -212,7 +219,7 @@ class GpuEngine:
     def forward(self, nrows: int, stream=None) -> int:
         L, n = self.plans, 0
         for l, pl in enumerate(L):
-            last = l == len(L) - 1
+            last = l == len(L) - 1 and self.final
             a_in = self.a[l][:nrows, :pl.in_features]
             inner_softmax = pl.act == "softmax" and not last
             act = None if (pl.act == "softmax") else pl.act
@@ -230,6 +237,8 @@ class GpuEngine:
                 continue
             if last:
                 kw["out"] = self.logits[:nrows, :pl.out_features]
+            elif l == len(L) - 1:      # a block in the middle of a network: the activation goes to whoever follows
+                kw["out_bf16" if self.bf16 else "out"] = self.out_act[:nrows, :pl.out_features]
             elif self.bf16:
                 kw["out_bf16"] = self.a[l + 1][:nrows, :pl.out_features]
                 if self.zpre[l + 1] is not None:

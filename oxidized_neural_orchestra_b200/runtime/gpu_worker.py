@@ -236,14 +236,12 @@ class GpuRank:
         else:
             self.W = self.C.clone()
             self.g = torch.zeros_like(self.C)
-        if any(l["kind"] != "dense" for l in layers):
-            from ..models.conv_engine import ConvNetEngine as Engine
-        else:
-            Engine = GpuEngine
-        self.engine = Engine(layers, batch_size=B, tile_dtype=self.tile, loss=self.loss_kind, params=self.W,
-                             grads=self.g, params_bf16=self.shadow,
-                             leaky_relu_exact=self.b200.get("leaky_relu_exact", True),
-                             bias_from_shadow=self.cadence == "step")
+        from ..models.conv_engine import make_engine
+
+        self.engine = make_engine(layers, batch_size=B, tile_dtype=self.tile, loss=self.loss_kind, params=self.W,
+                                  grads=self.g, params_bf16=self.shadow,
+                                  leaky_relu_exact=self.b200.get("leaky_relu_exact", True),
+                                  bias_from_shadow=self.cadence == "step")
         self.feeder = BatchFeeder(xs, ys, self.x_size, self.y_size, B, self.dev, self.seed,
                                   device_resident=self.b200.get("data", "host") == "device")
         self.loss_pin = [torch.zeros(1, dtype=torch.float64).pin_memory() for _ in range(2)]

@@ -175,3 +175,71 @@ def test_direct_single_channel_kernels_match_conv2d(dtype, shape):
     assert torch.equal(gk, again_k) and torch.equal(gb, again_b)      # fixed summation order
     CV.conv1_wgrad(g, Fo, x, dy, gk, gb, beta=1.0)                     # accumulate
     assert (gk - 2 * kr.grad.view(Fo, K, K)).abs().max().item() <= 2 * wtol
+
+
+STAGED = [
+    dict(kind="dense", **{"in": 40, "out": 2 * 6 * 6}, act=("tanh", 1.0)),
+    dict(kind="conv", input_dim=[2, 6, 6], kernel_dim=[4, 2, 3], stride=1, padding=1, act=("relu", 0.0)),
+    dict(kind="pool", input_dim=[4, 6, 6], filter_size=2, stride=2, padding=0, act=None),
+    dict(kind="dense", **{"in": 4 * 3 * 3, "out": 18}, act=("sigmoid", 1.0)),
+    dict(kind="pool", input_dim=[2, 3, 3], filter_size=3, stride=1, padding=1, act=None),
+    dict(kind="conv", input_dim=[2, 3, 3], kernel_dim=[3, 2, 2], stride=1, padding=0, act=("tanh", 1.0)),
+    dict(kind="dense", **{"in": 3 * 2 * 2, "out": 5}, act=("softmax", 0.0)),
+]
+
+
+def _staged_ref(params, x, y):
+    off, ps = 0, []
+
+    def take(shape):
+        nonlocal off
+        n = int(np.prod(shape))
+        t = params[off:off + n].view(*shape).clone().requires_grad_(True)
+        off += n
+        ps.append(t)
+        return t
+
+    B = x.shape[0]
+    w, b = take((40, 72)), take((72,))
+    a = torch.tanh(x @ w + b).view(B, 2, 6, 6)
+    k, b = take((4, 2, 3, 3)), take((4,))
+    a = F.max_pool2d(torch.relu(F.conv2d(a, k, b, padding=1)), 2, 2).reshape(B, -1)
+    w, b = take((36, 18)), take((18,))
+    a = torch.sigmoid(a @ w + b).view(B, 2, 3, 3)
+    a = F.max_pool2d(F.pad(a, (1, 1, 1, 1)), 3, 1)          # zero padding takes part in the max (max_pooling.rs:47-157)
+    k, b = take((3, 2, 2, 2)), take((3,))
+    a = torch.tanh(F.conv2d(a, k, b)).reshape(B, -1)
+    w, b = take((12, 5)), take((5,))
+    p = torch.softmax(a @ w + b, 1)
+    L = -(y * torch.log(p.clamp_min(1.1920929e-07))).sum() / p.numel()
+    L.backward()
+    return L.item(), torch.cat([t.grad.reshape(-1) for t in ps])
+
+
+@pytest.mark.parametrize("tile", ["tf32", "bf16"])
+def test_layer_kinds_in_any_order_dense_before_conv_and_several_alternations(tile):
+    """dense -> conv -> pool -> dense -> pool -> conv -> dense: the chained-unit engine against autograd."""
+    from oxidized_neural_orchestra_b200.models.conv_engine import StagedEngine, make_engine
+
+    torch.manual_seed(1)
+    n = 41 * 72 + (4 * 18 + 4) + 37 * 18 + (3 * 8 + 3) + 13 * 5
+    npad = (n + 15) // 16 * 16
+    params = torch.zeros(npad, device="cuda")
+    params[:n] = torch.randn(n, device="cuda") * 0.3
+    grads = torch.zeros(npad, device="cuda")
+    pb = params.to(torch.bfloat16) if tile == "bf16" else None
+    B = 20
+    eng = make_engine(STAGED, batch_size=B, tile_dtype=tile, loss="cross_entropy", params=params, grads=grads, params_bf16=pb)
+    assert isinstance(eng, StagedEngine) and eng.n_params == n
+    eng.refresh()
+    x = torch.rand(B, 40, device="cuda")
+    y = F.one_hot(torch.randint(0, 5, (B,), device="cuda"), 5).float()
+    eng.step(x, y, B)
+    torch.cuda.synchronize()
+    assert eng.status.item() == 0
+    pref = pb.float() if tile == "bf16" else params
+    ref_loss, ref_g = _staged_ref(pref[:n], x.to(torch.bfloat16).float() if tile == "bf16" else x, y)
+    tol = 8e-2 if tile == "bf16" else 2e-2
+    assert abs(eng.loss_sum.item() - ref_loss) <= tol * abs(ref_loss)
+    err = (grads[:n] - ref_g).abs().max().item()
+    assert err <= tol * ref_g.abs().max().item(), (err, ref_g.abs().max().item())
