@@ -55,6 +55,10 @@ struct GemmDev {
   long long slab_elems;    // M * slab_ld
   int slab_ld;
   OnoApply apply;          // optimizer applied to the result tile in the epilogue (apply.p != nullptr)
+  const unsigned int* gate;          // flags that must reach *gate_target before the first operand load (nullptr: none)
+  const unsigned int* gate_target;
+  int gate_stride;
+  unsigned int gate_mask;
 };
 
 template <int BN>
@@ -306,6 +310,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if (p.gate) {
+        // the operands are still being delivered (e.g. fresh weights arriving from their owners): wait, bounded, for every
+        // selected flag, then order the TMA (async proxy) reads behind the acquire
+        const uint32_t want = *p.gate_target;
+        for (int i = 0; i < 32 && ok; ++i)
+          if (((p.gate_mask >> i) & 1u) && !wait_flag_ge(p.gate + (size_t)i * p.gate_stride, want, budget)) {
+            fail(p, abortp, ONO_ERR_TIMEOUT_PEER_FLAG);
+            ok = false;
+          }
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       for (int work = unit; work < total_work && ok; work += units) {
         const int tile = work / SPLITS, split = work % SPLITS;
         const int m0 = (tile % num_m) * TILE_M + (int)crank * BM;
@@ -932,7 +947,11 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   p.M = g->M; p.N = g->N; p.K = g->K;
   p.epi = g->epi;
   p.status = g->status;
-  p.timeout_ns = 2000000000ull;
+  p.timeout_ns = g->timeout_ns ? g->timeout_ns : 2000000000ull;
+  if (g->gate) {
+    if (!g->gate_target || !g->gate_mask || g->gate_stride < 0) { set_error("gate needs a target word and a flag mask%s", ""); return -1; }
+    p.gate = g->gate; p.gate_target = g->gate_target; p.gate_stride = g->gate_stride; p.gate_mask = g->gate_mask;
+  }
   CUtensorMap ta, tb;
   int rc = make_operand(&p.a, &ta, g->A, esize, g->a_major, g->M, g->K, g->lda, 128);
   if (rc) return rc;

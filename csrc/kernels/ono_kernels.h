@@ -81,6 +81,15 @@ typedef struct OnoGemm {
   OnoEpilogue epi;
   int* status;     // device int, set non-zero on an in-kernel timeout; may be null
   OnoApply apply;  // optimizer fused into the epilogue (apply.p == NULL: off)
+  // Gate on the operands: the TMA producer does not load anything before every selected flag word has reached the target
+  // (gate[i * gate_stride] >= *gate_target for every i with bit i of gate_mask set; a bounded acquire wait: on a timeout the
+  // kernel records an error in *status and returns without having loaded). Lets a GEMM be queued before another GPU has
+  // finished delivering its weights (the parameter pull of a layer hides behind the layers before it). gate == NULL: off.
+  const unsigned int* gate;
+  const unsigned int* gate_target;
+  int gate_stride;
+  unsigned int gate_mask;
+  unsigned long long timeout_ns;   // budget of every wait inside the kernel (0 = 2 s)
   float* workspace;           // split-K slabs, 16-byte aligned; NULL = a static buffer of the library, which GEMMs that overlap
   long long workspace_elems;  // on the device would share: give each stream its own workspace. Size in floats.
 } OnoGemm;

@@ -37,7 +37,8 @@ class OnoGemm(C.Structure):
         ("A", C.c_void_p), ("B", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
         ("lda", C.c_int), ("ldb", C.c_int), ("dtype", C.c_int), ("a_major", C.c_int),
         ("b_major", C.c_int), ("bn", C.c_int), ("max_ctas", C.c_int), ("split_k", C.c_int), ("pair", C.c_int), ("epi", OnoEpilogue),
-        ("status", C.c_void_p), ("apply", OnoApply), ("workspace", C.c_void_p), ("workspace_elems", C.c_longlong),
+        ("status", C.c_void_p), ("apply", OnoApply), ("gate", C.c_void_p), ("gate_target", C.c_void_p),
+        ("gate_stride", C.c_int), ("gate_mask", C.c_uint), ("timeout_ns", C.c_ulonglong), ("workspace", C.c_void_p), ("workspace_elems", C.c_longlong),
     ]
 
 

@@ -60,7 +60,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
          aux: torch.Tensor | None = None, dact: str | None = None, dact_param: float = 0.0,
          relu_quirk: bool = False, alpha: float = 1.0, beta: float = 0.0, bn: int = 0,
          max_ctas: int = 0, split_k: int = 0, pair: int = 0, reduce_out: bool = False, out_f16: torch.Tensor | None = None,
-         apply: dict | None = None, status: torch.Tensor | None = None, stream=None) -> None:
+         apply: dict | None = None, gate: tuple | None = None, timeout_ns: int = 0, status: torch.Tensor | None = None,
+         stream=None) -> None:
     """Launch one GEMM. All tensors must be 2-D, on the current CUDA device, with unit inner stride.
 
     ``split_k``: 0 lets the library decide (a shape with a handful of output tiles and a long reduction, e.g. 342 x 128 x
@@ -70,6 +71,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
 
     ``out_f16``: like ``out_bf16`` but the values are IEEE f16 (a 16-bit gradient wire in the reference's format). Either
     16-bit output may be a view of a peer GPU's window: aligned tiles then leave through TMA stores over NVLink.
+
+    ``gate``: ``(flags, target, stride, mask)``: the kernel loads no operand before ``flags[i * stride] >= target[0]`` for every
+    bit ``i`` of ``mask`` (int32 device tensors; a bounded wait: on a timeout ``status`` becomes non-zero and the kernel returns
+    without output). Used to queue a layer's GEMM while its weights are still arriving from their owners.
 
     ``apply``: optimizer applied by the epilogue to the tile it has just computed (the weight gradient of a layer this
     rank owns outright), which is then never written to memory: ``dict(p=, m=, v=, p_bf16=, kind=, lr=, mu=, b1=, b2=,
@@ -166,4 +171,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn_major: bool = False, b_mn_maj
     e.relu_quirk = int(relu_quirk)
     e.alpha, e.beta = alpha, beta
     g.status = _ptr(status)
+    g.timeout_ns = timeout_ns
+    if gate is not None:
+        flags, target, stride, mask = gate
+        g.gate, g.gate_target, g.gate_stride, g.gate_mask = flags.data_ptr(), target.data_ptr(), stride, mask
     _lib.check(lib.ono_gemm(C.byref(g), _lib.stream_ptr(stream)), "ono_gemm")

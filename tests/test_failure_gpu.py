@@ -88,3 +88,51 @@ def test_async_server_lock_that_is_never_released_gives_up():
     torch.cuda.synchronize()
     assert status.item() == 0 and torch.allclose(master, torch.full((n,), -1.0, device="cuda"))
     assert locks.sum().item() == 0
+
+
+def test_gemm_operand_gate_opens_late_or_runs_out_and_the_context_survives():
+    """The GEMM's producer waits (bounded) for flag words before its first operand load: the form in which a layer's GEMM is
+    queued while its weights are still arriving. Flags already there: it runs. Flags set later from another stream: it runs
+    once they are. A flag that nothing sets: the wait runs out, the status word says so, nothing is written, and the next
+    launch on the same context works."""
+    from oxidized_neural_orchestra_b200.ops.gemm import gemm
+
+    torch.manual_seed(0)
+    a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(192, 128, device="cuda", dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    flags = torch.zeros(32, device="cuda", dtype=torch.int32)
+    target = torch.tensor([3], device="cuda", dtype=torch.int32)
+    status = torch.zeros(1, device="cuda", dtype=torch.int32)
+
+    def run(out, timeout_ns, stream=None):
+        gemm(a, b, out=out, gate=(flags, target, 4, 0b101), timeout_ns=timeout_ns, status=status, stream=stream)
+
+    flags[0], flags[8] = 3, 7                       # both selected words (index 0 and 2, stride 4) at or past the target
+    out = torch.zeros(256, 192, device="cuda")
+    run(out, 50_000_000)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
+    # opened late, from another stream, while the kernel is already waiting
+    flags[8] = 2
+    out2 = torch.zeros(256, 192, device="cuda")
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    run(out2, 2_000_000_000)
+    with torch.cuda.stream(side):
+        torch.cuda._sleep(20_000_000)               # ~10 ms of spinning on the side stream first
+        flags[8:9].fill_(3)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and torch.equal(out2, out)
+    # never opened: the wait gives up after its budget
+    flags[8] = 1
+    out3 = torch.full((256, 192), 9.0, device="cuda")
+    run(out3, 30_000_000)
+    torch.cuda.synchronize()
+    assert status.item() == 5                       # ONO_ERR_TIMEOUT_PEER_FLAG
+    assert bool((out3 == 9.0).all())
+    status.zero_()
+    flags[8] = 3
+    run(out3, 30_000_000)
+    torch.cuda.synchronize()
+    assert status.item() == 0 and torch.equal(out3, out)
