@@ -377,6 +377,7 @@ Json B200Config::to_json() const {
   o.set("tile_dtype", tile_dtype);
   o.set("wire_dtype", wire_dtype);
   o.set("wgrad_apply", wgrad_apply);
+  o.set("param_pull", param_pull);
   o.set("shard_layout", shard_layout);
   o.set("switch_check_every", Json((unsigned long long)switch_check_every));
   o.set("allreduce", allreduce);
@@ -428,6 +429,7 @@ B200Config B200Config::from_json(const Json& j) {
   str("data", c.data, {"host", "device"});
   str("grad_push", c.grad_push, {"auto", "on", "off", "reduce", "direct"});
   str("wgrad_apply", c.wgrad_apply, {"auto", "off"});
+  str("param_pull", c.param_pull, {"auto", "kernel", "staged"});
   str("shard_layout", c.shard_layout, {"striped", "contiguous"});
   if (const Json* v = j.find("switch_check_every")) c.switch_check_every = nonzero(*v, "b200.switch_check_every");
   str("grad_stage", c.grad_stage, {"auto", "on", "off"});

@@ -70,6 +70,7 @@ class GpuEngine:
         self.push = None              # weight-gradient tiles added into the owners' f32 accumulators (see backward)
         self.wire16 = None            # weight-gradient tiles stored as 16-bit values into the owners' slabs
         self.apply_plan = None        # optimizer applied by the weight-gradient GEMM's epilogue, per layer
+        self.gates = None             # per layer: flags its forward GEMM waits on before it loads the layer's weights
         if tile_dtype not in ("tf32", "bf16"):
             raise ValueError("tile_dtype must be 'tf32' or 'bf16'")
         self.dev = device or params.device
@@ -224,6 +225,8 @@ class GpuEngine:
             inner_softmax = pl.act == "softmax" and not last
             act = None if (pl.act == "softmax") else pl.act
             kw = dict(bias=self.b_view(l), act=act, act_param=pl.act_param, status=self.status, stream=stream)
+            if self.gates is not None and self.gates.get(l) is not None:
+                kw["gate"] = self.gates[l]      # the layer's weights may still be arriving from their owners
             if inner_softmax:
                 o = pl.out_features
                 kw["out"] = self.soft_tmp[l + 1][:nrows, :o]

@@ -92,10 +92,13 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
             torch.cuda.nvtx.range_push(name)
 
     mark("compute")
-    if with_sync and r.wire_copies:
+    if with_sync and r.pull_staged:
+        n += r.pull_publish(st)          # last step's fresh parameters travel while this step's first layers already run
+    if with_sync and (r.wire_copies or r.pull_staged):
         # 16-bit gradients leave for their owners layer by layer on the communication stream (copy engines) while the
         # layers below are still in backward; the fused kernel starts once the last transfer has been issued and done
-        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st, after_layer=lambda l: r.wire_ship(l, st))
+        n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st,
+                    after_layer=(lambda l: r.wire_ship(l, st)) if r.wire_copies else None)
         st.wait_stream(r.comm_stream)
     else:
         n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
@@ -219,7 +222,13 @@ def do_switch(r) -> None:
     """All-reduce -> parameter server in place: the promoted ranks adopt the ranges they will own
     (every replica already holds the full vector), optimizer state restarts, and their data is
     re-scattered to the remaining workers (node/src/router.rs:305-341, worker/src/builder.rs:165-200)."""
+    if r.pull_staged:           # the last step's parameters have not been published yet: do it before ownership changes
+        with torch.cuda.stream(r.stream):
+            r.pull_publish(r.stream)
+            r.stream.wait_stream(r.comm_stream)
     torch.cuda.synchronize(r.dev)
+    if r.world > 1:
+        dist.barrier(group=r.group)
     acts = r.plan["switch"]["post_actions"]
     promoted = [a["rank"] for a in acts if a["action"] == "upgrade"]
     remaining = [a["rank"] for a in acts if a["action"] == "switch"]

@@ -53,6 +53,7 @@ class GpuRank:
         self.use_nvls = False
         self.push_active = self.stage_active = self.wire16_push = self.apply_active = False
         self.wire_copies, self.wire_transport = None, "staged"
+        self.pull_staged, self.pull_plan = False, None
         self.buckets, self.bucket_after, self.stage_buckets, self.stage_after = [], {}, [], {}
         self.stream = torch.cuda.Stream(device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
@@ -139,6 +140,13 @@ class GpuRank:
                       not self.push and self.wire16 is None)
         if self.stage:
             lay.add("stage_ready", self.world * _lib.STAGE_BUCKETS, torch.int32)
+        # Staged parameter pull (bf16 tiles, every rank an owner): owners publish their fresh shadow slices with copy
+        # engines at the start of the next step, layer by layer, and announce each layer in the consumers' flag tables;
+        # the forward GEMM of a layer waits (bounded) for its flags, so the pull hides behind the layers before it.
+        self.pull_wanted = (self.push16 and self.wire_transport == "staged" and self.tile == "bf16" and
+                            self.b200.get("param_pull", "auto") != "kernel")
+        if self.pull_wanted:
+            lay.add("pull_ready", self.world * _lib.STAGE_BUCKETS, torch.int32)
         self.ring_wanted = self.b200.get("allreduce") == "ring" and self.algorithm != "parameter_server"
         if self.ring_wanted:
             lay.add("ring_acc", self.n_pad, torch.float32)
@@ -418,6 +426,49 @@ class GpuRank:
         self.wire_copies = copies if any(copies.values()) else None
         return {"f16": self.wire16 == "f16", "w": w, "cast": cast}
 
+    def _build_pull(self):
+        """Per layer (forward order): the copy-engine transfers that publish this rank's slices of the layer's bf16 shadow
+        in every peer's window, and the gate the layer's forward GEMM waits on (one flag per owner, set to the step number
+        once that owner's slices of the layer have been delivered)."""
+        lay, win = self.layout, self.win
+        sh0 = lay.offset("params_bf16")
+        plan = []
+        for li, pl in enumerate(self.engine.plans):
+            lo_l, hi_l = pl.w_off, pl.b_off + pl.out_features
+            cps = []
+            for b, e in self.own[self.rank]:
+                a0, a1 = max(b, lo_l), min(e, hi_l)
+                if a1 > a0:
+                    for q in range(self.world):
+                        if q != self.rank:
+                            cps.append((win.ptrs[q] + sh0 + 2 * a0, win.ptrs[self.rank] + sh0 + 2 * a0, 2 * (a1 - a0)))
+            plan.append(cps)
+        self.pull_plan = plan
+        if getattr(self, "pull_step", None) is None:
+            self.pull_step = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.pull_flag_arr = (C.c_void_p * self.world)(*win.peer_ptrs(lay.offset("pull_ready")))
+        ready = lay.tensor(win, "pull_ready")
+        mask = (1 << self.world) - 1
+        self.engine.gates = {li: (ready[li:], self.pull_step, _lib.STAGE_BUCKETS, mask) for li in range(len(plan))}
+
+    def pull_publish(self, stream) -> int:
+        """Start of a step: advance the step number, then (communication stream, ordered after it) ship every layer's
+        fresh slices to the peers and announce the layer. Returns the number of launches and transfers."""
+        lib = _lib.load()
+        _lib.check(lib.ono_stage_tick(self.pull_step.data_ptr(), _lib.stream_ptr(stream)), "ono_stage_tick")
+        ev = torch.cuda.Event()
+        ev.record(stream)
+        self.comm_stream.wait_event(ev)
+        cs = _lib.stream_ptr(self.comm_stream)
+        n = 1
+        for li, cps in enumerate(self.pull_plan):
+            for dst, src, nbytes in cps:
+                _lib.check(lib.ono_copy_async(dst, src, nbytes, cs), "ono_copy_async")
+            _lib.check(lib.ono_stage_signal(self.pull_flag_arr, self.world, self.rank, li, self.pull_step.data_ptr(), cs),
+                       "ono_stage_signal")
+            n += len(cps) + 1
+        return n
+
     def wire_ship(self, l: int, stream) -> int:
         """Ship layer l's finished 16-bit gradients to their owners: copy-engine transfers on the communication stream,
         ordered after the kernels that produced them. Returns the number of transfers."""
@@ -520,6 +571,14 @@ class GpuRank:
             dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.group)
             engines_need_f32 = bool(flag.item() > 0)
         self.f32_everywhere = engines_need_f32
+        n_layers = len([l for l in self.plan["layers"] if l["n_params"] > 0])
+        self.pull_staged = bool(self.pull_wanted and self.wire16_push and mode == "fused" and not engines_need_f32 and
+                                all(len(rs) > 0 for rs in self.own) and set(workers) == set(range(W)) and
+                                n_layers <= _lib.STAGE_BUCKETS and self.engine is not None)
+        self.pull_staged = self._all_ranks_agree(self.pull_staged) if self.pull_wanted else False
+        self.pull_plan = None
+        if self.engine is not None and isinstance(self.engine, GpuEngine):
+            self.engine.gates = None
         if mode in ("fused", "oneshot"):
             s = _lib.OnoSync()
             oneshot = mode == "oneshot"
@@ -530,6 +589,9 @@ class GpuRank:
                       for r, p in enumerate(win.peer_ptrs(lay.offset("params_bf16")))]
             else:
                 pb = [None] * W
+            if self.pull_staged:       # the fused kernel refreshes this rank's own copies only; the pull travels separately
+                pf = [p if r == self.rank else None for r, p in enumerate(pf)]
+                pb = [p if r == self.rank else None for r, p in enumerate(pb)]
             nvls = self.use_nvls and win.mc_ptr != 0 and W > 1
             algo = 1 if nvls else 0
             g_region = self.grad_region
@@ -571,8 +633,8 @@ class GpuRank:
                         opt=opt, divide=not wild, timeout_ns=10_000_000_000,
                         g_mc=(win.mc(lay.offset(("wire16" if self.compress else "slab16") if g_dtype else g_region)) or None)
                         if algo == 1 else None,
-                        p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
-                        p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
+                        p_mc_f32=(win.mc(lay.offset("params")) or None) if (engines_need_f32 and not self.pull_staged) else None,
+                        p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if (self.tile == "bf16" and not self.pull_staged) else None)
             S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
                          v=self.v_loc.data_ptr(), state_off=0, adam_pows=self.adam_pows.data_ptr(),
                          epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
@@ -587,6 +649,8 @@ class GpuRank:
                     self.engine.push = self._build_push()
             if self.wire16_push and self.engine is not None:
                 self.engine.wire16 = self._build_wire16()
+            if self.pull_staged:
+                self._build_pull()
             self.sync_struct = s
             self._build_buckets()
             self._build_stage(workers)
