@@ -227,6 +227,7 @@ class GpuEngine:
             kw = dict(bias=self.b_view(l), act=act, act_param=pl.act_param, status=self.status, stream=stream)
             if self.gates is not None and self.gates.get(l) is not None:
                 kw["gate"] = self.gates[l]      # the layer's weights may still be arriving from their owners
+                kw["timeout_ns"] = 10_000_000_000   # the same patience as the fused kernel's barriers: a rank may start late
             if inner_softmax:
                 o = pl.out_features
                 kw["out"] = self.soft_tmp[l + 1][:nrows, :o]
