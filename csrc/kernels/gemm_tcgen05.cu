@@ -702,15 +702,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 constexpr long long SPLIT_SCRATCH_ELEMS = 4ll << 20;
 __device__ float g_split_scratch[SPLIT_SCRATCH_ELEMS];
 
-__global__ void __launch_bounds__(128) gemm_finish_kernel(const float* slabs, long long slab_elems, int nslabs, int ld, int M,
+// One block per 32 x 32 tile of the result, eight warps: warp w adds the slabs w, w + 8, w + 16, ... (a lane owns one row of
+// the tile, eight 16-byte loads per slab), the eight partial sums are then added in warp order through shared memory, and
+// warp 0 runs the epilogue. The order of every addition is fixed, so the result does not depend on timing.
+__global__ void __launch_bounds__(256) gemm_finish_kernel(const float* slabs, long long slab_elems, int nslabs, int ld, int M,
                                                           int N, const OnoEpilogue e) {
-  const int m = blockIdx.x * 128 + threadIdx.x;
+  __shared__ float part[7][32][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 32 + lane;
   const int n0 = blockIdx.y * 32;
   float v[32];
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = 0.f;
   if (m < M) {
-    for (int sidx = 0; sidx < nslabs; ++sidx) {
+    for (int sidx = warp; sidx < nslabs; sidx += 8) {
       const float* src = slabs + (size_t)sidx * slab_elems + (size_t)m * ld + n0;
 #pragma unroll
       for (int j = 0; j < 32; j += 4)
@@ -719,6 +724,17 @@ __global__ void __launch_bounds__(128) gemm_finish_kernel(const float* slabs, lo
           v[j] += q.x; v[j + 1] += q.y; v[j + 2] += q.z; v[j + 3] += q.w;
         }
     }
+  }
+  if (warp > 0) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) part[warp - 1][lane][j] = v[j];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+#pragma unroll 1
+  for (int w = 0; w < 7; ++w) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] += part[w][lane][j];
   }
   epilogue_chunk(e, v, m, n0, M, N, 0);
 }
@@ -1088,8 +1104,8 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
   };
   rc = run();
   if (rc || !two_pass) return rc;
-  const dim3 fgrid((g->M + 127) / 128, (g->N + 31) / 32);
-  gemm_finish_kernel<<<fgrid, 128, 0, stream>>>(p.slabs, p.slab_elems, p.split_k, p.slab_ld, g->M, g->N, g->epi);
+  const dim3 fgrid((g->M + 31) / 32, (g->N + 31) / 32);
+  gemm_finish_kernel<<<fgrid, 256, 0, stream>>>(p.slabs, p.slab_elems, p.split_k, p.slab_ld, g->M, g->N, g->epi);
   if (cudaGetLastError() != cudaSuccess) { set_error("gemm_finish launch failed%s", ""); return -7; }
   return 0;
 }

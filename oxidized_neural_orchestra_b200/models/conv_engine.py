@@ -218,9 +218,8 @@ class ConvNetEngine:
                     n += 2
                 # weight gradient: K = every output pixel of the batch, tiny output -> split-K
                 tmp = d["gk_tmp"]
-                tmp.zero_()
-                # one work unit per SM: every unit ends with a tile of atomic adds, so more splits than that only add
-                # atomics (a fixed 128 splits cost 0.04 ms per step on the three-layer 28 x 28 benchmark network)
+                # one work unit per SM: every split writes its partial product into a slab of its own and a finishing pass
+                # adds the slabs in order (run-to-run deterministic), so more splits than SMs only add slabs
                 kb = -(-Mout // (64 if self.bf16 else 32))
                 tiles = -(-F // 128) * (1 if ckk <= 128 else -(-ckk // 128))
                 split = max(1, min(kb, -(-self.sms // tiles)))
@@ -233,7 +232,7 @@ class ConvNetEngine:
                 gk = self.grads[d["off"]:d["off"] + F * ckk]
                 cv.operand_grad_to_kernel(F, d["C"], d["K"], tmp[:, :ckk], gk, beta=1.0 if accumulate else 0.0, stream=stream)
                 ew.colsum(dy, self.grads[d["off"] + F * ckk:d["off"] + d["n"]], beta=1.0 if accumulate else 0.0, stream=stream)
-                n += 4
+                n += 4      # split GEMM + finishing pass, permutation, bias column sums
             else:
                 if prev is None:
                     continue

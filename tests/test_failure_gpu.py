@@ -101,7 +101,9 @@ def test_gemm_operand_gate_opens_late_or_runs_out_and_the_context_survives():
     a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
     b = torch.randn(192, 128, device="cuda", dtype=torch.bfloat16)
     ref = a.float() @ b.float().t()
-    flags = torch.zeros(32, device="cuda", dtype=torch.int32)
+    # the flag words live in pinned host memory here, so that the host itself can open the gate while the kernel waits (on a
+    # GPU rank they are words of the rank's window that the owners' signal kernels write)
+    flags = torch.zeros(32, dtype=torch.int32).pin_memory()
     target = torch.tensor([3], device="cuda", dtype=torch.int32)
     status = torch.zeros(1, device="cuda", dtype=torch.int32)
 
@@ -113,15 +115,14 @@ def test_gemm_operand_gate_opens_late_or_runs_out_and_the_context_survives():
     run(out, 50_000_000)
     torch.cuda.synchronize()
     assert status.item() == 0 and (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item()
-    # opened late, from another stream, while the kernel is already waiting
+    # opened late, by the host, while the kernel is already waiting
     flags[8] = 2
     out2 = torch.zeros(256, 192, device="cuda")
-    side = torch.cuda.Stream()
     torch.cuda.synchronize()
-    run(out2, 2_000_000_000)
-    with torch.cuda.stream(side):
-        torch.cuda._sleep(20_000_000)               # ~10 ms of spinning on the side stream first
-        flags[8:9].fill_(3)
+    run(out2, 5_000_000_000)
+    time.sleep(0.05)
+    assert not torch.cuda.current_stream().query()          # still waiting at the gate
+    flags[8] = 3
     torch.cuda.synchronize()
     assert status.item() == 0 and torch.equal(out2, out)
     # never opened: the wait gives up after its budget
