@@ -298,6 +298,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int total_tiles = num_m * num_n;
   const int KB = (p.K + BK - 1) / BK;
   const uint64_t budget = p.timeout_ns;
+  // with a gate the producer may legitimately spend its whole budget before the first load: the roles behind it wait longer,
+  // so that a gate that never opens is reported as such and not as a stalled pipeline
+  const uint64_t cbudget = p.gate ? 2 * budget + 1000000ull : budget;
   // split-K: a work item is (tile, split); split s reduces k-blocks [s*KB_PER, min(KB, (s+1)*KB_PER))
   // and adds its partial product to the output with atomics (the host guarantees no split is empty).
   const int SPLITS = p.split_k > 1 ? p.split_k : 1;
@@ -374,7 +377,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int kb0 = split * KB_PER, kb1 = min(KB, kb0 + KB_PER);
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
-        if (!mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1u, abortp, budget)) {
+        if (!mbar_wait_bounded(&tmem_empty_bar[buf], acc_phase ^ 1u, abortp, cbudget)) {
           fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_EMPTY);
           ok = false;
           break;
@@ -382,7 +385,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, budget)) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abortp, cbudget)) {
             fail(p, abortp, ONO_ERR_TIMEOUT_FULL);
             ok = false;
             break;
@@ -418,7 +421,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // Make sure no MMA is still running before TMEM is released.
       if (PAIR) umma_commit_pair(&drain_bar);
       else umma_commit(&drain_bar);
-      mbar_wait_bounded(&drain_bar, 0, abortp, ok ? budget : 1000000ull);
+      mbar_wait_bounded(&drain_bar, 0, abortp, ok ? cbudget : 1000000ull);
     }
   } else {
     // ---------------- epilogue warps 0..3 (TMEM lanes 32*warp .. 32*warp+31) ----------------
@@ -479,7 +482,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int n0 = (work / num_m) * BN;
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
-        const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget);
+        const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, cbudget);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
           ok = false;
@@ -492,7 +495,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const int nc = n0 + c * 32;
           if (nc >= p.N) break;
           const int b = (int)(done % nbuf);
-          const bool landed = mbar_wait_bounded(&bars[b], (uint32_t)((done / nbuf) & 1), abortp, budget);
+          const bool landed = mbar_wait_bounded(&bars[b], (uint32_t)((done / nbuf) & 1), abortp, cbudget);
           if (!__all_sync(0xffffffffu, landed)) {
             if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_FULL);
             ok = false;
@@ -565,7 +568,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int n0 = (tile / num_m) * BN;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
-      const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, budget);
+      const bool got = mbar_wait_bounded(&tmem_full_bar[buf], acc_phase, abortp, cbudget);
       if (!__all_sync(0xffffffffu, got)) {
         if (lane == 0) fail(p, abortp, ONO_ERR_TIMEOUT_TMEM_FULL);
         ok = false;

@@ -488,9 +488,21 @@ class GpuRank:
         e = self.engine
         kind = {"sgd": "sgd", "momentum": "momentum", "adam": "adam"}[opt.kind]
         cand = []
+        # Only where the GEMM takes the form that moves the master / state / shadow tiles with TMA (bf16 CTA pairs on
+        # 256-column tiles, SGD or momentum, a batch that fits the two-stage operand ring): 8192 x 8192 x 512 takes 0.27 ms
+        # that way against 0.35 ms for the plain GEMM plus the separate pass. The register form (tf32 tiles, Adam) is
+        # faster than its two separate kernels in isolation but slower inside the step (wide MLP, Adam: 1.20 ms against
+        # 1.08 ms per step), so those layers keep the separate fused pass.
+        B = self.trainer["batch_size"]
+        sms = _lib.load().ono_num_sms()
         for li, pl in enumerate(e.plans):
             i, o = pl.in_features, pl.out_features
-            if o % 4 == 0 and (self.C.data_ptr() + 4 * pl.w_off) % 16 == 0 and i * o >= 1 << 16:
+            tma_form = (e.bf16 and opt.kind in ("sgd", "momentum") and i >= 256 and B <= 2048 and o % 8 == 0 and
+                        -(-i // 128) * -(-o // 256) >= sms * 3 // 4 and
+                        (e.w_copy_needed[li] or self.shadow is None or (self.shadow.data_ptr() + 2 * pl.w_off) % 16 == 0))
+            if os.environ.get("ONO_WGRAD_APPLY") == "force":      # every layer either form can take (tests of both forms)
+                tma_form = o % 4 == 0 and i * o >= 1 << 16
+            if tma_form and (self.C.data_ptr() + 4 * pl.w_off) % 16 == 0:
                 cand.append((i * o, li))
         cand.sort(reverse=True)
 

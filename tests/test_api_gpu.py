@@ -237,10 +237,12 @@ def test_periodic_checkpoints_load_back_and_continue_the_run(tmp_path):
 
 @pytest.mark.parametrize("tile", ["bf16", "tf32"])
 @pytest.mark.parametrize("opt", [GradientDescentWithMomentum(0.1, 0.9), Adam(0.005), GradientDescent(0.2)])
-def test_optimizer_in_the_weight_gradient_epilogue_matches_the_separate_pass(tile, opt):
+def test_optimizer_in_the_weight_gradient_epilogue_matches_the_separate_pass(tile, opt, monkeypatch):
     """On one GPU the weight-gradient GEMMs update master, state and shadow in their epilogues; the run must follow the
     run whose optimizer is the separate fused pass (same arithmetic per element, only the GEMM's f32 result is not
-    rounded through memory in between: the two are equal to rounding)."""
+    rounded through memory in between: the two are equal to rounding). The runtime only chooses this for layers large
+    enough for the TMA form; here it is forced onto a small model so that both epilogue forms are exercised."""
+    monkeypatch.setenv("ONO_WGRAD_APPLY", "force")
     xs, ys = _data(n=256, x=512, y=16, seed=4)
     model = Sequential([Dense(1024, XavierUniform(), GELU()), Dense(512, XavierUniform(), ReLU(0.0)),
                         Dense(16, XavierUniform(), Softmax())])
