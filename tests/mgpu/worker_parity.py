@@ -69,11 +69,11 @@ def main():
         ar(f"bf16-ar-{mode}-step", model, 10, {"sync_every": "step", "tile_dtype": "bf16", "allreduce": mode})
     # the parameter pull of bf16 all-owner layouts: published by copy engines under the next forward (gated GEMMs), or from
     # the fused kernel
-    ar("bf16-ar-pull-staged-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16"}, expect={"param_pull": "staged"})
-    ar("bf16-ar-pull-kernel-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16", "param_pull": "kernel"},
-       expect={"param_pull": "kernel"})
-    ar("bf16-ar-pull-staged-adam-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16"}, opt=lambda: Adam(0.002),
+    ar("bf16-ar-pull-staged-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16", "param_pull": "staged"},
        expect={"param_pull": "staged"})
+    ar("bf16-ar-pull-kernel-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16"}, expect={"param_pull": "kernel"})
+    ar("bf16-ar-pull-staged-adam-step", model12, 16, {"sync_every": "step", "tile_dtype": "bf16", "param_pull": "staged"},
+       opt=lambda: Adam(0.002), expect={"param_pull": "staged"})
     ps("bf16-ps-colocated-even-step", model, 10, {"sync_every": "step", "tile_dtype": "bf16", "colocate": True, "sharding": "even"})
     # 16-bit gradient wire in step cadence, both formats: 16-bit tiles written by the GEMM epilogues and shipped to the
     # owners' slabs by copy engines during backward (push, staged), stored into the owners' slabs by the epilogues
