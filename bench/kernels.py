@@ -97,6 +97,8 @@ def cmd_wgrad(a):
     fl = 2.0 * M * N * K
     flush = torch.empty(64 << 20, device="cuda")
     for name, fn in forms.items():
+        if a.form and name != a.form:
+            continue
         for _ in range(3):
             fn()
         ms = _time(fn, a.iters, flush=flush if M * N * 4 < (256 << 20) else None)
@@ -277,6 +279,7 @@ def main():
     wg.add_argument("--k", type=int, default=512); wg.add_argument("--dtype", default="bf16")
     wg.add_argument("--opt", default="momentum"); wg.add_argument("--pair", type=int, default=0, choices=(-1, 0, 1))
     wg.add_argument("--iters", type=int, default=10)
+    wg.add_argument("--form", default="", help="run one output form only: store_f32 | store_bf16 | apply | store_f32+optimizer_pass")
     s = sub.add_parser("sync")
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
