@@ -100,6 +100,7 @@ class Session {
   virtual void stop() = 0;                                         // StopAfterEpoch to every worker
   virtual std::vector<float> final_params() = 0;                   // after the `complete` event
   virtual bool switched() const { return false; }
+  virtual Json run_metrics() const { return Json::object(); }      // what the ranks reported about the run, if anything
 };
 
 class LocalSession final : public Session {
@@ -173,6 +174,7 @@ class RemoteSession final : public Session {
       job.set("world", Json((unsigned long long)addrs.size()));
       job.set("master_addr", master_addr);
       job.set("master_port", master_port);
+      job.set("plan", plan);          // every node works from the orchestrator's plan (roles, ranges, partitions), not from its own
       Json spec = Json::object();
       spec.set("spec", job);
       chs_[r]->send_command(Json::tagged("create_node", spec));
@@ -216,6 +218,7 @@ class RemoteSession final : public Session {
     return false;
   }
   const Json& metrics() const { return metrics_; }
+  Json run_metrics() const override { return metrics_.is_object() ? metrics_ : Json::object(); }
 
  private:
   void push(TrainingEvent ev) {

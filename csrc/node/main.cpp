@@ -8,6 +8,8 @@
 // probe (`stats_request`, node/src/stat_service.rs:69-152) and `create_node`. The rank it is asked to be
 // runs
 //   * in this process, on the C++ engine, when the session has a single CPU rank;
+//   * in this process as well, as one rank of a TCP mesh between the nodes (node/net_rank.hpp), when the session has
+//     several CPU ranks and uses all-reduce or the barrier / blocking parameter server;
 //   * otherwise in a child rank process (the PyTorch + CUDA runtime, one per GPU) that this node starts
 //     on a loopback port and to which it relays the session's frames in both directions, so that a GPU
 //     fault or an out-of-memory in the rank never takes the listener down.
@@ -22,6 +24,7 @@
 #include <thread>
 
 #include "core/session.hpp"
+#include "node/net_rank.hpp"
 
 using namespace ono;
 using Clock = std::chrono::steady_clock;
@@ -176,6 +179,65 @@ void run_local_rank(wire::Channel& ch, const Json& job, std::vector<float> xs, s
   }
 }
 
+// ---- one of several CPU ranks, in this process, talking to the other nodes over TCP -----------------------------
+void run_net_rank(wire::Channel& ch, const Json& job, const Json& plan, const TrainingConfig& training, int listen_fd,
+                  const std::string& node_id, std::vector<float> xs, std::vector<float> ys) {
+  const size_t rank = (size_t)job.at("rank").as_u64();
+  std::atomic<bool> stop{false}, finished{false};
+  std::mutex mu;                       // events leave through the channel from the rank's thread and from this one
+  std::vector<float> params;
+  std::string failure;
+  auto send_event = [&](const TrainingEvent& ev) {
+    Json e = Json::object();
+    e.set("kind", ev.kind);
+    e.set("worker", Json((unsigned long long)ev.worker));
+    Json l = Json::array();
+    for (double v : ev.losses) l.push(Json(v));
+    e.set("losses", l);
+    e.set("text", ev.text);
+    std::lock_guard<std::mutex> lk(mu);
+    ch.send_command(Json::tagged("event", e));
+  };
+  std::thread worker([&] {
+    try {
+      NetRank r(plan, training, rank, listen_fd, node_id, std::move(xs), std::move(ys), send_event, stop);
+      params = r.run();
+    } catch (const std::exception& e) {
+      failure = e.what();
+      logf(1, "rank %zu failed: %s", rank, e.what());
+      try {
+        send_event(TrainingEvent{"error", 0, {}, std::string("rank ") + std::to_string(rank) + ": " + e.what()});
+        send_event(TrainingEvent{"complete", 0, {}, "error"});
+      } catch (const std::exception&) {}
+    }
+    finished = true;
+    try {
+      std::lock_guard<std::mutex> lk(mu);
+      ch.send_command(Json("done"));
+    } catch (const std::exception&) {}
+  });
+  try {
+    while (true) {
+      wire::Message m;
+      try { m = ch.recv(200); } catch (const wire::WireTimeout&) { continue; }
+      if (m.is_command("stop_after_epoch") || m.is_command("abort")) stop = true;
+      else if (m.is_command("request_params")) {
+        while (!finished) std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        {
+          std::lock_guard<std::mutex> lk(mu);
+          ch.send_floats(wire::KIND_PARAMS, params.data(), params.size());
+        }
+        Json met = Json::object();
+        met.set("switched", false);
+        met.set("data_plane", "native tcp mesh");
+        send_event(TrainingEvent{"metrics", 0, {}, met.dump()});
+      } else if (m.is_command("disconnect")) break;
+    }
+  } catch (const std::exception& e) { logf(1, "orchestrator stream ended: %s", e.what()); }
+  stop = true;
+  worker.join();
+}
+
 // ---- any other rank: a child rank process behind a relay ---------------------------------------------------
 void run_child_rank(wire::Channel& up, const Options& opt, const wire::Channel::RawFrame& create_frame) {
   int port = 0;
@@ -272,9 +334,33 @@ void session(wire::Channel& ch, int listen_fd, const std::string& node_id, const
         ch.recv_dataset(xs, ys);
         logf(2, "single CPU rank in this process (%zu samples)", job.at("training").at("dataset").at("x_size").as_u64() ? xs.size() / job.at("training").at("dataset").at("x_size").as_u64() : 0);
         run_local_rank(ch, job, std::move(xs), std::move(ys));
-      } else {
-        run_child_rank(ch, opt, f);
+        return;
       }
+      if (opt.device == "cpu" && std::getenv("ONO_CPU_RANKS_IN_PYTHON") == nullptr) {
+        // several CPU ranks: this process is one of them if the strategy is one the native mesh covers
+        const ModelConfig model = ModelConfig::from_json(job.at("model"));
+        TrainingConfig training = TrainingConfig::from_json(job.at("training"));
+        // the same plan on every node: uniform latencies, or the measured ones the orchestrator passed along
+        std::map<std::string, std::map<std::string, uint64_t>> stats;
+        if (const Json* st = job.find("stats"); st && st->is_object()) {
+          for (auto& a : training.addrs) stats[a];
+          for (auto& [addr, peers] : st->members())
+            for (auto& [peer, rtt] : peers.members()) stats[addr][peer] = rtt.as_u64();
+        }
+        bool measured = false;
+        for (auto& kv : stats) measured = measured || !kv.second.empty();
+        Json plan = job.find("plan") && job.at("plan").is_object()
+                        ? job.at("plan")
+                        : adapt_configs(model, training, measured ? Calculator(std::move(stats)) : Calculator::uniform(training.addrs));
+        if (NetRank::supports(plan, training)) {
+          std::vector<float> xs, ys;
+          ch.recv_dataset(xs, ys);
+          logf(2, "rank %llu of %zu in this process (native TCP mesh)", (unsigned long long)job.at("rank").as_u64(), world);
+          run_net_rank(ch, job, plan, training, listen_fd, node_id, std::move(xs), std::move(ys));
+          return;
+        }
+      }
+      run_child_rank(ch, opt, f);
       return;
     }
   }

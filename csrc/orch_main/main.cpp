@@ -103,6 +103,7 @@ int main(int argc, char** argv) {
     for (double v : progress.history()) h.push(Json(v));
     out.set("loss_history", h);
     out.set("switched", session->switched());
+    out.set("metrics", session->run_metrics());
     if (!raw_events) std::cout << out.dump() << std::endl;
     return 0;
   } catch (const std::exception& e) {

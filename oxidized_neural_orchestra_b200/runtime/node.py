@@ -36,7 +36,8 @@ def run_rank(job: dict, xs: np.ndarray, ys: np.ndarray, emit, stop_event, device
     from orchestra import _orchestra as core
 
     rank, world = job["rank"], job["world"]
-    plan = json.loads(core.adapt_configs(json.dumps(job["model"]), json.dumps(job["training"]), json.dumps(job.get("stats") or {}) if job.get("stats") else ""))
+    plan = job.get("plan") or json.loads(core.adapt_configs(json.dumps(job["model"]), json.dumps(job["training"]),
+                                                          json.dumps(job.get("stats") or {}) if job.get("stats") else ""))
     own_group = False
     if world > 1 and not dist.is_initialized():
         import datetime
@@ -305,7 +306,7 @@ class RemoteHandle:
                 raise ConnectionError(f"{addr} answered as {ch.peer_entity}, expected a node")
             self._chs.append(ch)
         for rank, ch in enumerate(self._chs):
-            job = {"model": model_cfg, "training": training_cfg, "rank": rank, "world": len(addrs), "stats": stats,
+            job = {"model": model_cfg, "training": training_cfg, "rank": rank, "world": len(addrs), "stats": stats, "plan": plan,
                    "master_addr": "127.0.0.1" if master_addr in ("localhost", "127.0.0.1") else master_addr,
                    "master_port": master_port}
             ch.send_command({"create_node": {"spec": job}})

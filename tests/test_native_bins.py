@@ -195,3 +195,35 @@ def test_orchestui_interactive_screens_driven_by_a_key_script(bins, tmp_path):
     assert "save model" in saveas and "mine.safetensors" in saveas
     assert "trained-model repository" in repo and "mine.safetensors" in repo and "layer_0.weight [6, 5]" in repo
     assert (tmp_path / "safetensors" / "mine.safetensors").exists() and len(list((tmp_path / "safetensors").glob("*.safetensors"))) == 2
+
+
+def test_several_cpu_ranks_run_natively_over_a_tcp_mesh_between_the_nodes(bins, cxx_nodes, tmp_path):
+    """Three ono-node processes, each one CPU rank on the C++ engine, exchanging gradients over TCP among themselves
+    (no rank process, no gloo): parameter server with two co-located... servers and the reference's f16 gradient wire,
+    checked against the in-process cluster running the same plan."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import Adam
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync
+
+    for b200 in ({}, {"wire_dtype": "f16"}):
+        mp, tp, model, tr, xs, ys = _configs(tmp_path, cxx_nodes, algorithm={"parameter_server": {
+            "nservers": 1, "synchronizer": "barrier", "store": "blocking"}})
+        cfg = json.loads(open(tp).read())
+        cfg["b200"] = b200
+        cfg["early_stopping"] = None
+        open(tp, "w").write(json.dumps(cfg))
+        got = _run_orchestrator(bins, mp, tp)
+        m = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+        ref = orchestrate(m, orchestra.parameter_server([f"cpu:{i}" for i in range(3)], 1, InlineDataset(xs, ys, 6, 3), Adam(0.05),
+                                                        CrossEntropy(), BarrierSync(), BlockingStore(), tr["max_epochs"], 5, seed=3,
+                                                        b200=b200 or None)).wait(quiet=True)
+        assert got["stop_reason"] == "max_epochs"
+        assert np.allclose(got["loss_history"], ref.loss_history(), rtol=1e-5)
+        assert got.get("metrics", {}).get("data_plane") == "native tcp mesh"
