@@ -55,7 +55,69 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
   if (a.kind == 2 && L.adam_pows) s.adam_step = a.lr * sqrtf(1.0f - L.adam_pows[1]) / (1.0f - L.adam_pows[0]);
 
   double sq = 0.0;
-  if (ok) {
+  // 16-bit gradient windows whose ranges are multiples of 8 elements (the staged push lays shares out that way): one
+  // 16-byte load per worker and thread brings eight gradients, and the fresh bf16 parameters leave as one 16-byte store
+  // per thread (a full 512-byte line per warp over NVLink, P2P or multicast) instead of two 8-byte ones.
+  bool wide8 = a.g_dtype != 0 && a.algo != 1;
+  for (int ri = 0; ri < L.n_ranges && wide8; ++ri) wide8 = ((L.ranges[ri].begin | L.ranges[ri].end) & 7) == 0;
+  if (ok && wide8) {
+    const int f16 = a.g_dtype == 2;
+    const long long stride = (long long)a.nblocks * blockDim.x;
+    for (int ri = 0; ri < L.n_ranges; ++ri) {
+      const long long b8 = L.ranges[ri].begin >> 3, e8 = L.ranges[ri].end >> 3;
+      for (long long i8 = b8 + (long long)blk * blockDim.x + threadIdx.x; i8 < e8; i8 += stride) {
+        float4 g0 = make_float4(0.f, 0.f, 0.f, 0.f), g1 = g0;
+#pragma unroll
+        for (int q = 0; q < ONO_MAX_RANKS; ++q)      // fixed rank order
+          if (q < a.nranks && ((workers >> q) & 1u)) {
+            const uint4 w = ld_relaxed_sys_v4_b32(reinterpret_cast<const uint4*>(a.g[q]) + i8);
+            const float4 x0 = unpack16x4(make_uint2(w.x, w.y), f16), x1 = unpack16x4(make_uint2(w.z, w.w), f16);
+            g0.x += x0.x; g0.y += x0.y; g0.z += x0.z; g0.w += x0.w;
+            g1.x += x1.x; g1.y += x1.y; g1.z += x1.z; g1.w += x1.w;
+          }
+        const long long i4 = i8 << 1;
+        const long long si = (i8 << 3) - L.state_off;
+        float4 p0 = __ldcs(reinterpret_cast<const float4*>(L.p_master) + i4), p1 = __ldcs(reinterpret_cast<const float4*>(L.p_master) + i4 + 1);
+        float4 m0 = make_float4(0.f, 0.f, 0.f, 0.f), m1 = m0, v0 = m0, v1 = m0;
+        if (a.kind >= 1) { m0 = __ldcs(reinterpret_cast<const float4*>(L.m + si)); m1 = __ldcs(reinterpret_cast<const float4*>(L.m + si) + 1); }
+        if (a.kind == 2) { v0 = __ldcs(reinterpret_cast<const float4*>(L.v + si)); v1 = __ldcs(reinterpret_cast<const float4*>(L.v + si) + 1); }
+        p0 = opt_apply4(s, p0, g0, m0, v0);
+        p1 = opt_apply4(s, p1, g1, m1, v1);
+        if (L.sumsq) {
+          const float q0 = g0.x * g0.x + g0.y * g0.y + g0.z * g0.z + g0.w * g0.w, q1 = g1.x * g1.x + g1.y * g1.y + g1.z * g1.z + g1.w * g1.w;
+          sq += (double)(q0 + q1) * (double)(s.gs * s.gs);
+        }
+        if (a.kind >= 1) { __stcs(reinterpret_cast<float4*>(L.m + si), m0); __stcs(reinterpret_cast<float4*>(L.m + si) + 1, m1); }
+        if (a.kind == 2) { __stcs(reinterpret_cast<float4*>(L.v + si), v0); __stcs(reinterpret_cast<float4*>(L.v + si) + 1, v1); }
+        __stcs(reinterpret_cast<float4*>(L.p_master) + i4, p0);
+        __stcs(reinterpret_cast<float4*>(L.p_master) + i4 + 1, p1);
+        if (a.algo != 0) {
+          if (a.p_mc_f32) {
+            multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4, p0);
+            multimem_st_v4(reinterpret_cast<float4*>(a.p_mc_f32) + i4 + 1, p1);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < ONO_MAX_RANKS; ++q)
+            if (q < a.nranks && a.p_out_f32[q] && a.p_out_f32[q] != L.p_master) {
+              *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4) = p0;
+              *(reinterpret_cast<float4*>(a.p_out_f32[q]) + i4 + 1) = p1;
+            }
+        }
+        const uint2 lo = pack_bf16x4(p0), hi = pack_bf16x4(p1);
+        const uint4 pb = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        if (a.algo != 0 && a.p_mc_bf16) {
+          multimem_st_bf16x8(reinterpret_cast<uint4*>(a.p_mc_bf16) + i8, pb);
+        } else {
+#pragma unroll
+          for (int q = 0; q < ONO_MAX_RANKS; ++q)
+            if (q < a.nranks && a.p_out_bf16[q]) *(reinterpret_cast<uint4*>(a.p_out_bf16[q]) + i8) = pb;
+        }
+        if (a.zero_grad && ((workers >> rank) & 1u))
+          *(reinterpret_cast<uint4*>(const_cast<float*>(a.g[rank])) + i8) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  } else if (ok) {
     // Two float4 per thread and iteration, all loads issued before the first use, so that enough
     // bytes are in flight per SM to cover HBM / NVLink latency.
     constexpr int U = 2;

@@ -353,6 +353,17 @@ __device__ __forceinline__ uint2 ld_relaxed_sys_v2(const uint2* p) {
   asm volatile("ld.relaxed.sys.global.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
+// Eight 16-bit values (16 bytes) from memory another GPU may have written.
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4_b32(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// NVLS: eight bf16 values (16 bytes) delivered to every GPU of the multicast group.
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc_ptr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 // NVLS: the sum over every GPU of four 16-bit floats (bf16, or f16), accumulated in f32 inside the switch.
 __device__ __forceinline__ uint2 multimem_ld_reduce_add_16x4(const uint2* mc_ptr, int f16) {
   uint2 v;

@@ -105,16 +105,18 @@ def test_layer_granular_ranges():
 
 @pytest.mark.parametrize("fmt", ["bf16", "f16"])
 @pytest.mark.parametrize("kind", ["momentum", "adam"])
-def test_sixteen_bit_gradient_windows(fmt, kind):
+@pytest.mark.parametrize("n,align", [(70004, 4), (70016, 8)])
+def test_sixteen_bit_gradient_windows(fmt, kind, n, align):
     """Four ranks whose gradient windows hold 16-bit values (the wire format of step cadence): the owners sum them in f32
-    in rank order, average, apply the optimizer and publish f32 + bf16 parameters."""
+    in rank order, average, apply the optimizer and publish f32 + bf16 parameters. Ranges cut at multiples of 8 take the
+    kernel's 16-byte path (eight gradients per load, eight bf16 parameters per store), the others its 8-byte path."""
     from oxidized_neural_orchestra_b200.ops import _lib
     from oxidized_neural_orchestra_b200.ops.elementwise import adam_tick, cast16
     from oxidized_neural_orchestra_b200.parallel import sync as S
     from oxidized_neural_orchestra_b200.parallel.sync import even_ranges
 
     torch.manual_seed(3)
-    N, n, nblocks = 4, 70004, 4
+    N, nblocks = 4, 4
     dt = torch.float16 if fmt == "f16" else torch.bfloat16
     g16 = [torch.zeros(n, device="cuda", dtype=dt) for _ in range(N)]
     p0 = torch.randn(n, device="cuda")
@@ -126,7 +128,7 @@ def test_sixteen_bit_gradient_windows(fmt, kind):
     epoch = [torch.zeros(nblocks, device="cuda", dtype=torch.int32) for _ in range(N)]
     status = [torch.zeros(1, device="cuda", dtype=torch.int32) for _ in range(N)]
     pows = torch.ones(2, device="cuda")
-    ranges = even_ranges(n, list(range(N)), N)
+    ranges = even_ranges(n, list(range(N)), N, align=align)
     s = _lib.OnoSync()
     S.fill_sync(s, nranks=N, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=[t.data_ptr() for t in g16],
                 p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[t.data_ptr() for t in pb],
