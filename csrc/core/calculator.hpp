@@ -42,48 +42,67 @@ class Graph {
   size_t size_ = 0;
 };
 
-// Exact minimum Hamiltonian cycle starting at vertex 0 (tsp.rs:15-37). Empty if none exists.
+// Exact minimum Hamiltonian cycle starting at vertex 0 (what tsp.rs:15-37 computes). Empty if none exists.
 // A single vertex yields {0}: a ring of one rank (the reference returns an empty tour there, which
 // would leave an all-reduce run with no workers).
+//
+// Bottom-up Held-Karp over one flat table: `cost[S * n + v]` is the cheapest way to leave v, visit every
+// vertex outside the visited set S and return to 0. Supersets are numerically larger than their subsets,
+// so one descending sweep over S has every successor ready; there is no recursion and no memo lookup.
+// Only sets that contain vertex 0 (odd S) are reachable. Among equal costs the lowest next vertex wins,
+// which is the order the reference's search settles ties in, so the ring order matches it on an
+// equidistant fabric.
 template <class W>
 std::vector<size_t> travelling_salesman_cycle(const Graph<W>& g) {
   const size_t n = g.len();
   if (n == 0 || n >= 64) return {};
   if (n == 1) return {0};
-  const size_t states = n * (size_t(1) << n);
-  std::vector<std::optional<W>> mem(states);
-  std::vector<std::optional<size_t>> parent(states);
-  std::vector<char> done(states, 0);
-  // iterative DFS would obscure the recurrence; n is at most a few dozen ranks, depth is n.
-  struct Rec {
-    const Graph<W>& g; size_t n;
-    std::vector<std::optional<W>>& mem; std::vector<std::optional<size_t>>& parent; std::vector<char>& done;
-    std::optional<W> run(size_t visited, size_t v) {
-      const size_t i = visited * n + v;
-      if (done[i]) return mem[i];
-      if ((size_t)__builtin_popcountll(visited) == n) return g.weight(v, 0);
+  if (n > 20) {
+    // The exact table needs n * 2^n entries; past 20 ranks take the nearest unvisited neighbour instead.
+    std::vector<size_t> path{0};
+    uint64_t seen = 1;
+    while (path.size() < n) {
+      std::optional<W> best;
+      size_t pick = n;
       for (size_t w = 1; w < n; ++w) {
-        const size_t bit = size_t(1) << w;
-        if (visited & bit) continue;
-        auto wt = g.weight(v, w);
-        if (!wt) continue;
-        auto cost = run(visited | bit, w);
-        if (!cost) continue;
-        const W total = *wt + *cost;
-        if (!mem[i] || total < *mem[i]) { mem[i] = total; parent[i] = w; }
+        if (seen >> w & 1) continue;
+        const auto step = g.weight(path.back(), w);
+        if (step && (!best || *step < *best)) { best = step; pick = w; }
       }
-      done[i] = 1;
-      return mem[i];
+      if (pick == n) return {};
+      seen |= uint64_t(1) << pick;
+      path.push_back(pick);
     }
-  } rec{g, n, mem, parent, done};
-  if (!rec.run(1, 0)) return {};
+    return g.weight(path.back(), 0) ? path : std::vector<size_t>{};
+  }
+  constexpr uint8_t kNone = 0xff;
+  const size_t full = (size_t(1) << n) - 1;
+  std::vector<W> cost((full + 1) * n);
+  std::vector<uint8_t> next((full + 1) * n, kNone);     // next vertex on the best way home, kNone: no way
+  std::vector<char> reach((full + 1) * n, 0);
+  for (size_t v = 1; v < n; ++v)
+    if (auto home = g.weight(v, 0)) { cost[full * n + v] = *home; reach[full * n + v] = 1; }
+  for (size_t S = full - 2; S >= 1 && S <= full; S -= 2) {            // odd sets only, descending
+    for (size_t v = 0; v < n; ++v) {
+      if (!(S >> v & 1) || (v == 0 && S != 1)) continue;            // the walk stands on v; 0 only at the start
+      const size_t at = S * n + v;
+      for (size_t w = 1; w < n; ++w) {
+        if (S >> w & 1) continue;
+        const size_t to = (S | size_t(1) << w) * n + w;
+        const auto step = g.weight(v, w);
+        if (!step || !reach[to]) continue;
+        const W total = *step + cost[to];
+        if (!reach[at] || total < cost[at]) { cost[at] = total; next[at] = (uint8_t)w; reach[at] = 1; }
+      }
+    }
+    if (S == 1) break;
+  }
+  if (!reach[1 * n + 0]) return {};
   std::vector<size_t> path{0};
-  size_t visited = 1, v = 0;
-  while (path.size() < n) {
-    const size_t w = *parent[visited * n + v];
-    visited |= size_t(1) << w;
-    path.push_back(w);
-    v = w;
+  for (size_t S = 1, v = 0; path.size() < n;) {
+    v = next[S * n + v];
+    S |= size_t(1) << v;
+    path.push_back(v);
   }
   return path;
 }
