@@ -532,8 +532,48 @@ __global__ void __launch_bounds__(256) rows_vec_kernel(const OnoRows r) {
   }
 }
 
+// Row gather out of pinned host memory (the batch feeder's host-to-device path). The loads cross PCIe, so what counts is
+// bytes in flight, not threads: a few blocks, each thread with four independent 16-byte loads outstanding (24 blocks x 256
+// threads x 64 bytes = 384 KB in flight, several times the bandwidth-delay product of a Gen5 x16 link). Kept this small on
+// purpose: the kernel runs on the copy stream beside the training step, and a grid of thousands of blocks stalled on PCIe
+// would fill the SMs' thread slots and hold back the persistent GEMM CTAs of the step it is supposed to hide behind.
+constexpr int ROWS_HOST_BLOCKS = 24;
+__global__ void __launch_bounds__(256) rows_host_kernel(const OnoRows r) {
+  const int w4 = r.W >> 2;
+  const long long total = (long long)r.R * w4, stride = (long long)gridDim.x * blockDim.x;
+  constexpr int U = 4;
+  for (long long base = (long long)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += stride * U) {
+    float4 v[U];
+    long long at[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long e = base + u * stride;
+      at[u] = -1;
+      if (e < total) {
+        const int row = (int)(e / w4), c4 = (int)(e - (long long)row * w4);
+        v[u] = *reinterpret_cast<const float4*>(r.src + (size_t)r.idx[row] * r.ld_src + 4 * c4);
+        at[u] = (long long)row * r.ld_dst + 4 * c4;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (at[u] >= 0) *reinterpret_cast<float4*>(r.dst_f32 + at[u]) = v[u];
+  }
+}
+
+static bool is_host_memory(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeHost;
+}
+
 extern "C" int ono_rows(const OnoRows* r, ono_stream_t st) {
   if (!r || !r->src || r->R <= 0 || r->W <= 0) { set_error("bad rows args%s", "", 0, 0); return -1; }
+  if (r->idx && r->dst_f32 && !r->dst_bf16 && !r->dstT_f32 && !r->dstT_bf16 && r->W % 4 == 0 && r->ld_src % 4 == 0 &&
+      r->ld_dst % 4 == 0 && (((uintptr_t)r->src | (uintptr_t)r->dst_f32) & 15) == 0 && is_host_memory(r->src)) {
+    rows_host_kernel<<<ROWS_HOST_BLOCKS, 256, 0, (cudaStream_t)st>>>(*r);
+    return launch_ok("rows");
+  }
   const bool vec = !r->idx && !r->dst_bf16 && !r->dstT_bf16 && (r->dst_f32 || r->dstT_f32) && r->R % 4 == 0 && r->W % 4 == 0 &&
                    r->ld_src % 4 == 0 && (!r->dst_f32 || r->ld_dst % 4 == 0) && (!r->dstT_f32 || r->ld_dstT % 4 == 0) &&
                    (((uintptr_t)r->src | (uintptr_t)r->dst_f32 | (uintptr_t)r->dstT_f32) & 15) == 0 && (long long)r->R * r->W >= (1 << 16);

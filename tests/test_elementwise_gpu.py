@@ -104,6 +104,22 @@ def test_rows_gather_cast_transpose_and_colsum():
     assert abs(ss.item() - (src.double() ** 2).sum().item()) < 1e-6 * ss.item()
 
 
+@pytest.mark.parametrize("width", [784, 10, 8192])
+def test_rows_gather_from_pinned_host_memory(width):
+    """The batch feeder's path: the kernel reads the selected rows straight out of pinned host memory (a few blocks with
+    16-byte loads when the rows allow it, the generic kernel otherwise)."""
+    from oxidized_neural_orchestra_b200.ops import elementwise as ew
+
+    torch.manual_seed(1)
+    src = torch.randn(300, width).pin_memory()
+    idx = torch.randperm(300)[:77].to(torch.int32).cuda()
+    dst = torch.full((80, width), -7.0, device="cuda")
+    ew.rows(src, idx=idx, n_rows=77, dst=dst)
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:77].cpu(), src[idx.cpu().long()])
+    assert torch.all(dst[77:] == -7.0)
+
+
 def test_philox_init_is_shard_independent_and_distributed_right():
     from oxidized_neural_orchestra_b200.ops import elementwise as ew
 
