@@ -146,7 +146,9 @@ def cmd_sync_emulated(a):
     R, n = a.emulate_ranks, a.elems
     torch.manual_seed(0)
     z = lambda dt=torch.float32: torch.zeros(n, device="cuda", dtype=dt)
-    g, p, m, v = [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)]
+    wire = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[a.wire]
+    g, p, m, v = [z(wire) for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)], [z() for _ in range(R)]
+    pb = [z(torch.bfloat16) for _ in range(R)] if a.bf16_shadow else [None] * R
     for t in g:
         t.normal_(0, 1e-3)
     nblocks = max(1, min(_lib.load().ono_num_sms() // R, n // 4 // 1024))
@@ -156,9 +158,11 @@ def cmd_sync_emulated(a):
     pows = torch.full((2,), 0.5, device="cuda")
     s = _lib.OnoSync()
     S.fill_sync(s, nranks=R, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=[t.data_ptr() for t in g],
-                p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[None] * R, flag_ptrs=[t.data_ptr() for t in flags],
+                p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[None if t is None else t.data_ptr() for t in pb],
+                flag_ptrs=[t.data_ptr() for t in flags],
                 worker_mask=(1 << R) - 1, member_mask=(1 << R) - 1, n_workers=R, opt=S.OptimizerCfg(kind=a.opt, lr=0.01, mu=0.9))
-    ranges = S.even_ranges(n, list(range(R)), R)
+    s.g_dtype = {"f32": 0, "bf16": 1, "f16": 2}[a.wire]
+    ranges = S.even_ranges(n, list(range(R)), R, align=8)
     for r in range(R):
         S.fill_local(s.loc[r], p_master=p[r].data_ptr(), m=m[r].data_ptr(), v=v[r].data_ptr(), state_off=0,
                      adam_pows=pows.data_ptr(), epoch=epoch[r].data_ptr(), ranges=ranges[r], status=status.data_ptr())
@@ -166,8 +170,9 @@ def cmd_sync_emulated(a):
         S.launch_sync(s, emulated=True)
     ms = _time(lambda: S.launch_sync(s, emulated=True), a.iters)
     assert status.item() == 0
-    per = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + 4 * R + 4 * R     # owner state + R gradient reads + R parameter writes
-    rec = {"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "ms": ms,
+    # owner state + R gradient reads + R parameter writes (f32, and bf16 with the shadow)
+    per = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + g[0].element_size() * R + 4 * R + (2 * R if a.bf16_shadow else 0)
+    rec = {"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "wire": a.wire, "ms": ms,
            "GBs_local_hbm": per * n / ms / 1e6, "blocks_per_rank": nblocks}
     if a.checksum:      # bits of every rank's parameters and optimizer state: equal between runs (fixed summation order)
         import hashlib
@@ -284,6 +289,7 @@ def main():
     s.add_argument("--elems", type=int, default=64 << 20); s.add_argument("--opt", default="adam")
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
     s.add_argument("--emulate-ranks", type=int, default=0, help="run R ranks as one cooperative launch on this GPU")
+    s.add_argument("--wire", default="f32", choices=("f32", "bf16", "f16"), help="with --emulate-ranks: format of the gradient windows")
     s.add_argument("--checksum", action="store_true", help="with --emulate-ranks: print a hash of the resulting state")
     w = sub.add_parser("sweep")
     w.add_argument("--max-bytes", type=int, default=1 << 30)
