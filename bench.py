@@ -106,6 +106,8 @@ def build_run(cfg: dict, n_gpus: int, steps_total: int, data_mode: str, seed: in
         b200["grad_push"] = cfg["grad_push"]
     if cfg.get("grad_stage"):
         b200["grad_stage"] = cfg["grad_stage"]
+    if cfg.get("pre_reduce"):
+        b200["pre_reduce"] = cfg["pre_reduce"]
     if cfg.get("phase_timing"):
         b200["phase_timing"] = True
     if cfg.get("wire"):
@@ -174,6 +176,8 @@ def main() -> None:
     ap.add_argument("--push", default=None, choices=("on", "off", "auto", "direct", "reduce"),
                     help="gradient push: auto/on = 16-bit tiles + copy engines, direct = epilogue stores into the owner's window, "
                          "reduce = f32 reduce-adds, off = the fused kernel pulls")
+    ap.add_argument("--pre-reduce", default=None, choices=("auto", "off"),
+                    help="fewer owners than ranks: ranks that own nothing sum a part of each owner's share (default auto)")
     ap.add_argument("--stage", default=None, choices=("on", "off", "auto"), help="staged reduce-scatter during backward")
     ap.add_argument("--phases", action="store_true",
                     help="diagnostic: run the steps uncaptured with CUDA events around compute / exchange / refresh and add "
@@ -207,6 +211,8 @@ def main() -> None:
         cfg["grad_push"] = args.push
     if args.stage:
         cfg["grad_stage"] = args.stage
+    if args.pre_reduce:
+        cfg["pre_reduce"] = args.pre_reduce
     if args.phases:
         cfg["phase_timing"] = True
     if args.wire:
@@ -264,6 +270,7 @@ def main() -> None:
                        "optimizer": cfg["opt"][0], "l2": l2_note,
                        "sync": m["sync_mode"], "wire": m.get("wire"), "wire_push": bool(m.get("wire_push", False)),
                        "wire_transport": m.get("wire_transport"), "param_pull": m.get("param_pull"),
+                       "pre_reduce": bool(m.get("pre_reduce", False)),
                        "wgrad_apply": bool(m.get("wgrad_apply", False)),
                        "grad_push": bool(m.get("grad_push", False)), "grad_stage": bool(m.get("grad_stage", False))},
             "clocks": clocks,

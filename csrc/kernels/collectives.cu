@@ -76,6 +76,11 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
             g1.x += x1.x; g1.y += x1.y; g1.z += x1.z; g1.w += x1.w;
           }
         const long long i4 = i8 << 1;
+        if (L.fwd) {      // pre-reduction for the owner: the f32 sums travel, the owner's second launch does the rest
+          *(reinterpret_cast<float4*>(L.fwd) + i4) = g0;
+          *(reinterpret_cast<float4*>(L.fwd) + i4 + 1) = g1;
+          continue;
+        }
         const long long si = (i8 << 3) - L.state_off;
         float4 p0 = __ldcs(reinterpret_cast<const float4*>(L.p_master) + i4), p1 = __ldcs(reinterpret_cast<const float4*>(L.p_master) + i4 + 1);
         float4 m0 = make_float4(0.f, 0.f, 0.f, 0.f), m1 = m0, v0 = m0, v1 = m0;
@@ -117,6 +122,8 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
           *(reinterpret_cast<uint4*>(const_cast<float*>(a.g[rank])) + i8) = make_uint4(0u, 0u, 0u, 0u);
       }
     }
+  } else if (ok && L.fwd) {
+    if (threadIdx.x == 0 && L.status) atomicCAS(L.status, 0, ONO_ERR_BAD_ARG);   // pre-reduction needs the 16-byte path
   } else if (ok) {
     // Two float4 per thread and iteration, all loads issued before the first use, so that enough
     // bytes are in flight per SM to cover HBM / NVLink latency.
@@ -497,6 +504,13 @@ static int validate_sync(const OnoSync* s) {
   }
   if (s->algo == 1 && !s->g_mc) { set_error("NVLS needs multicast addresses%s", "", 0, 0); return -1; }
   if (s->g_dtype < 0 || s->g_dtype > 2) { set_error("g_dtype must be 0 (f32), 1 (bf16) or 2 (f16)%s", "", 0, 0); return -1; }
+  for (int r = 0; r < s->nranks; ++r) {
+    const OnoSyncLocal& L = s->loc[r];
+    if (!L.fwd) continue;
+    bool ok = s->g_dtype != 0 && s->algo != 1 && (((uintptr_t)L.fwd) & 15) == 0;
+    for (int i = 0; i < L.n_ranges && ok; ++i) ok = ((L.ranges[i].begin | L.ranges[i].end) & 7) == 0;
+    if (!ok) { set_error("pre-reduction needs 16-bit windows, peer loads and ranges cut at multiples of 8%s", "", 0, 0); return -1; }
+  }
   return 0;
 }
 

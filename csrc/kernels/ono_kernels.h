@@ -233,6 +233,12 @@ typedef struct OnoSyncLocal {
   unsigned int* epoch;    // [nblocks] barrier epochs of this rank (device, zero-initialised)
   double* sumsq;          // optional: += sum of squares of the averaged gradient over owned ranges
   int* status;            // optional error word
+  // Pre-reduction for another owner (16-bit gradient windows only, ranges cut at multiples of 8): when set, this rank
+  // does not own its ranges; it sums the workers' 16-bit slabs over them in f32, in rank order, and stores the sums here
+  // (the owner's f32 gradient vector, indexed globally, possibly over NVLink). No optimizer, no parameter stores. The
+  // owner then finishes those ranges from its own f32 vector in a second launch. Halves (or better) the bytes that
+  // converge on an owner when there are fewer owners than workers.
+  float* fwd;
   int n_ranges;
   OnoRange ranges[ONO_MAX_RANGES];
 } OnoSyncLocal;

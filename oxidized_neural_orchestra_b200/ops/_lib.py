@@ -180,7 +180,7 @@ class OnoSyncLocal(C.Structure):
     _fields_ = [
         ("p_master", C.c_void_p), ("m", C.c_void_p), ("v", C.c_void_p), ("state_off", C.c_longlong),
         ("adam_pows", C.c_void_p), ("epoch", C.c_void_p), ("sumsq", C.c_void_p), ("status", C.c_void_p),
-        ("n_ranges", C.c_int), ("ranges", OnoRange * MAX_RANGES),
+        ("fwd", C.c_void_p), ("n_ranges", C.c_int), ("ranges", OnoRange * MAX_RANGES),
     ]
 
 

@@ -34,6 +34,42 @@ def even_ranges(n: int, owners: list[int], nranks: int, align: int = 4) -> list[
     return out
 
 
+def pre_reduce_plan(own: list[list[tuple[int, int]]], max_ranges: int):
+    """Fewer owners than ranks (a parameter server with 4 servers on 8 GPUs): every worker's 16-bit gradients of an
+    owner's share converge on that owner, (N-1)/S of the vector through one GPU's links, while the ranks that own nothing
+    receive nothing. Those ranks become reducers: each owner keeps 1/(k+1) of every range it owns and hands one such part
+    to each of its k idle partners; the workers ship a part's gradients to whoever reduces it, the partner sums the slabs in
+    f32 in rank order and stores the sums into the owner's f32 gradient vector (first launch of the exchange), and the
+    owner finishes those parts from its own memory (second launch). Same sums, same order, same result; the bytes that
+    arrive at any one GPU during backward drop by the factor k+1.
+
+    Returns ``(reduce_at, finish_at, fwd_to)``: per rank the ranges whose slabs it sums in the first launch; per owner
+    the ranges it finishes in the second; partner rank -> owner rank. ``None`` when the layout does not allow it (no idle
+    ranks, idle ranks not a multiple of the owners, a range not cut at multiples of 8, range tables too long)."""
+    owners = [r for r, rs in enumerate(own) if rs]
+    idle = [r for r, rs in enumerate(own) if not rs]
+    if not owners or not idle or len(idle) % len(owners):
+        return None
+    k = len(idle) // len(owners)
+    reduce_at, finish_at, fwd = [[] for _ in own], [[] for _ in own], {}
+    for j, o in enumerate(owners):
+        partners = idle[j * k:(j + 1) * k]
+        for h in partners:
+            fwd[h] = o
+        for b, e in own[o]:
+            if b % 8 or e % 8:
+                return None
+            cuts = [b] + [b + ((e - b) * t // (k + 1)) // 64 * 64 for t in range(1, k + 1)] + [e]
+            for t, r in enumerate([o] + partners):
+                if cuts[t + 1] > cuts[t]:
+                    reduce_at[r].append((cuts[t], cuts[t + 1]))
+            if e > cuts[1]:
+                finish_at[o].append((cuts[1], e))
+    if any(len(rs) > max_ranges for rs in reduce_at + finish_at):
+        return None
+    return reduce_at, finish_at, fwd
+
+
 def layer_ranges(layer_offsets: list[tuple[int, int, int]], nranks: int) -> list[list[tuple[int, int]]]:
     """``(owner_rank, begin, end)`` per layer -> merged ranges per rank (layer-granular sharding)."""
     out: list[list[tuple[int, int]]] = [[] for _ in range(nranks)]
@@ -81,11 +117,16 @@ def fill_sync(s: "_lib.OnoSync", *, nranks: int, rank: int, n: int, nblocks: int
 
 def fill_local(loc: "_lib.OnoSyncLocal", *, p_master: int, m: int | None, v: int | None, state_off: int,
                adam_pows: int | None, epoch: int, ranges: list[tuple[int, int]], sumsq: int | None = None,
-               status: int | None = None) -> None:
+               status: int | None = None, fwd: int | None = None) -> None:
+    """``fwd``: this rank pre-reduces its ranges for another owner: the f32 sums of the workers' 16-bit slabs go to that
+    address (the owner's f32 gradient vector) and nothing else happens on them (ranges must be multiples of 8)."""
     if len(ranges) > _lib.MAX_RANGES:
         raise ValueError(f"at most {_lib.MAX_RANGES} ranges per rank")
+    if fwd and any(b % 8 or e % 8 for b, e in ranges):
+        raise ValueError("pre-reduced ranges must be multiples of 8 elements")
     loc.p_master, loc.m, loc.v, loc.state_off = p_master, m, v, state_off
     loc.adam_pows, loc.epoch, loc.sumsq, loc.status = adam_pows, epoch, sumsq, status
+    loc.fwd = fwd
     loc.n_ranges = len(ranges)
     for i, (b, e) in enumerate(ranges):
         if b % 4:

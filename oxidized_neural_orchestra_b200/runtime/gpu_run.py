@@ -306,6 +306,7 @@ def run(r) -> dict:
         "wire": (r.wire16 if (r.wire16 is not None and r.sync_mode in ("fused", "oneshot")) else "f32") if r.world > 1 else "none",
         "wire_push": bool(r.wire16_push), "wire_transport": r.wire_transport if r.wire16_push else None,
         "wgrad_apply": bool(r.apply_active), "param_pull": "staged" if r.pull_staged else "kernel",
+        "pre_reduce": bool(getattr(r, "fwd_to", None)),
     }
     if r.phase_timing:
         metrics["phase_ms"] = getattr(r, "phase_ms_last", {})     # means over the steps of the last record

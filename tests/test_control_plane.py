@@ -260,3 +260,33 @@ def test_ownership_boundaries_snap_to_row_blocks_for_pushed_gradients():
                 if b == w0 or b == w0 + i * o or (w0 < b < w0 + i * o and (b - w0) % (128 * o) == 0):
                     ok = True
             assert ok, (owners, b)
+
+
+def test_pre_reduce_plan_splits_every_owned_range_among_owner_and_idle_partners():
+    """Four owners on eight ranks: every owned range is cut in two at a multiple of 64, the owner sums the first part and its
+    idle partner the second; together the parts tile the owned ranges exactly. Layouts that do not allow it return None."""
+    from oxidized_neural_orchestra_b200.parallel.sync import pre_reduce_plan
+
+    layers = [(0, 8192 * 64 + 64), (8192 * 64 + 64, 8192 * 64 + 64 + 1000 * 64 + 1000)]
+    own = [[] for _ in range(8)]
+    for b, e in layers:                       # striped: a quarter of every layer per owner (ranks 0..3)
+        cuts = [b + (e - b) * j // 4 // 64 * 64 for j in range(4)] + [e]
+        for o in range(4):
+            own[o].append((cuts[o], cuts[o + 1]))
+    reduce_at, finish_at, fwd = pre_reduce_plan(own, 16)
+    assert fwd == {4: 0, 5: 1, 6: 2, 7: 3}
+    for o in range(4):
+        parts = sorted(reduce_at[o] + reduce_at[o + 4])
+        assert [p[0] for p in parts[::2]] == [b for b, _ in own[o]] and [p[1] for p in parts[1::2]] == [e for _, e in own[o]]
+        assert all(parts[i][1] == parts[i + 1][0] for i in range(0, len(parts), 2))      # the two parts of a range meet
+        assert finish_at[o] == reduce_at[o + 4] and all(b % 64 == 0 for b, _ in finish_at[o])
+        mine, theirs = sum(e - b for b, e in reduce_at[o]), sum(e - b for b, e in reduce_at[o + 4])
+        assert abs(mine - theirs) <= 64 * len(own[o])
+    # one owner, three idle ranks: four parts per range
+    reduce_at, finish_at, fwd = pre_reduce_plan([[(0, 4096)], [], [], []], 16)
+    assert reduce_at == [[(0, 1024)], [(1024, 2048)], [(2048, 3072)], [(3072, 4096)]] and finish_at[0] == [(1024, 4096)]
+    assert fwd == {1: 0, 2: 0, 3: 0}
+    assert pre_reduce_plan([[(0, 512)], [(512, 1024)]], 16) is None                  # nobody idle
+    assert pre_reduce_plan([[(0, 512)], [(512, 1024)], []], 16) is None              # idle ranks do not divide among the owners
+    assert pre_reduce_plan([[(0, 1004)], []], 16) is None                            # a range end that is not a multiple of 8
+    assert pre_reduce_plan([[(i * 64, i * 64 + 64) for i in range(0, 40, 2)], []], 16) is None   # range table too long

@@ -164,6 +164,80 @@ def test_sixteen_bit_gradient_windows(fmt, kind, n, align):
         assert (pb[r].float() - p[r]).abs().max().item() <= 2 ** -7 * p[r].abs().max().item()
 
 
+@pytest.mark.parametrize("kind", ["momentum", "adam"])
+def test_pre_reduction_by_non_owner_ranks(kind):
+    """Two owners, two ranks that own nothing: each owner keeps half of its share and the other half is summed by its
+    helper, whose f32 sums land in the owner's f32 gradient vector; a second launch lets the owner finish that half from
+    its own memory. The result is that of the one-launch exchange (same summation order, same scale)."""
+    from oxidized_neural_orchestra_b200.ops import _lib
+    from oxidized_neural_orchestra_b200.ops.elementwise import adam_tick
+    from oxidized_neural_orchestra_b200.parallel import sync as S
+
+    torch.manual_seed(11)
+    N, n, nblocks = 4, 1 << 16, 4
+    q = n // 4
+    owned = [[(0, 2 * q)], [(2 * q, n)], [], []]
+    first = [[(0, q)], [(2 * q, 3 * q)], [(q, 2 * q)], [(3 * q, n)]]      # who sums which quarter in the first launch
+    helper_of = {2: 0, 3: 1}
+    z = lambda dt=torch.float32: torch.zeros(n, device="cuda", dtype=dt)
+    p0 = torch.randn(n, device="cuda")
+
+    def run(split: bool):
+        g16 = [z(torch.bfloat16) for _ in range(N)]
+        G = [torch.full((n,), 7.0, device="cuda") for _ in range(N)]       # stale values the helpers must overwrite
+        p, pb = [p0.clone() for _ in range(N)], [z(torch.bfloat16) for _ in range(N)]
+        m, v = [z() for _ in range(N)], [z() for _ in range(N)]
+        flags = [torch.zeros(nblocks * 8, device="cuda", dtype=torch.int32) for _ in range(N)]
+        epoch = [torch.zeros(nblocks, device="cuda", dtype=torch.int32) for _ in range(N)]
+        status = [torch.zeros(1, device="cuda", dtype=torch.int32) for _ in range(N)]
+        pows = torch.ones(2, device="cuda")
+        opt = S.OptimizerCfg(kind=kind, lr=0.05, mu=0.9)
+
+        def make(g_ptrs, g_dtype, ranges, members, workers, fwd=None):
+            s = _lib.OnoSync()
+            S.fill_sync(s, nranks=N, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=g_ptrs, p_f32_ptrs=[t.data_ptr() for t in p],
+                        p_bf16_ptrs=[t.data_ptr() for t in pb], flag_ptrs=[t.data_ptr() for t in flags], worker_mask=workers,
+                        member_mask=members, n_workers=N, opt=opt)
+            s.g_dtype = g_dtype
+            for r in range(N):
+                S.fill_local(s.loc[r], p_master=p[r].data_ptr(), m=m[r].data_ptr(), v=v[r].data_ptr(), state_off=0,
+                             adam_pows=pows.data_ptr(), epoch=epoch[r].data_ptr(), ranges=ranges[r], status=status[r].data_ptr(),
+                             fwd=(fwd or {}).get(r))
+            return s
+
+        every = (1 << N) - 1
+        slabs = [t.data_ptr() for t in g16]
+        if split:
+            launches = [make(slabs, 1, first, every, every, fwd={h: G[o].data_ptr() for h, o in helper_of.items()})]
+            for o in (0, 1):        # the owner alone finishes its helper's quarter from its own f32 vector
+                rest = [[] for _ in range(N)]
+                rest[o] = first[2 + o]
+                launches.append(make([t.data_ptr() for t in G], 0, rest, 1 << o, 1 << o))
+        else:
+            launches = [make(slabs, 1, owned, every, every)]
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        for step in range(3):
+            for r in range(N):
+                g16[r].copy_((torch.randn(n, device="cuda", generator=gen) * 0.01).to(torch.bfloat16))
+            if kind == "adam":
+                adam_tick(pows, 0.9, 0.999)
+            for s in launches:
+                S.launch_sync(s, emulated=True)
+        torch.cuda.synchronize()
+        assert all(t.item() == 0 for t in status)
+        return p, pb, m
+
+    p_a, pb_a, m_a = run(False)
+    p_b, pb_b, m_b = run(True)
+    for r in range(N):
+        # same summation order and scale in both forms; the two code paths may contract multiply-adds differently
+        assert (p_a[r] - p_b[r]).abs().max().item() <= 1e-6, f"rank {r}"
+        assert torch.equal(pb_b[r], p_b[r].to(torch.bfloat16)), f"rank {r}"
+        assert torch.equal(p_b[r], p_b[0]), f"rank {r}"
+    assert (m_a[0] - m_b[0]).abs().max().item() <= 1e-6 and (m_a[1] - m_b[1]).abs().max().item() <= 1e-6
+    assert (p_b[0] - p0).abs().max().item() > 1e-4
+
+
 @pytest.mark.parametrize("kind", ["sgd", "momentum", "adam"])
 @pytest.mark.parametrize("nranks", [2, 3, 4, 8])
 def test_ring_all_reduce_protocol(kind, nranks):
