@@ -176,7 +176,7 @@ def main() -> None:
     ap.add_argument("--push", default=None, choices=("on", "off", "auto", "direct", "reduce"),
                     help="gradient push: auto/on = 16-bit tiles + copy engines, direct = epilogue stores into the owner's window, "
                          "reduce = f32 reduce-adds, off = the fused kernel pulls")
-    ap.add_argument("--pre-reduce", default=None, choices=("auto", "off"),
+    ap.add_argument("--pre-reduce", default=None, choices=("auto", "on", "off"),
                     help="fewer owners than ranks: ranks that own nothing sum a part of each owner's share (default auto)")
     ap.add_argument("--stage", default=None, choices=("on", "off", "auto"), help="staged reduce-scatter during backward")
     ap.add_argument("--phases", action="store_true",

@@ -432,7 +432,7 @@ B200Config B200Config::from_json(const Json& j) {
   str("wgrad_apply", c.wgrad_apply, {"auto", "off"});
   str("param_pull", c.param_pull, {"auto", "kernel", "staged"});
   str("shard_layout", c.shard_layout, {"striped", "contiguous"});
-  str("pre_reduce", c.pre_reduce, {"auto", "off"});
+  str("pre_reduce", c.pre_reduce, {"auto", "on", "off"});
   if (const Json* v = j.find("switch_check_every")) c.switch_check_every = nonzero(*v, "b200.switch_check_every");
   str("grad_stage", c.grad_stage, {"auto", "on", "off"});
   if (const Json* v = j.find("switch_window")) { c.switch_window = nonzero(*v, "b200.switch_window"); if (c.switch_window < 2) throw InvalidConfig("b200.switch_window must be at least 2"); }

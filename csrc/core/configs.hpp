@@ -114,7 +114,7 @@ struct B200Config {
                                           // ("reduce": add f32 tiles into the owner's accumulator instead)
   std::string shard_layout = "striped";   // "striped" | "contiguous": equal shares as one slice of every layer per owner (GPU ranks, staged 16-bit push) or as one run
   std::string param_pull = "auto";        // "auto" | "kernel" | "staged": fresh parameters reach the other GPUs from the fused kernel, or by copy engines under the next forward
-  std::string pre_reduce = "auto";        // "auto" | "off": with fewer owners than ranks, ranks that own nothing sum a part of each owner's share and forward f32 sums
+  std::string pre_reduce = "auto";        // "auto" (4 GPUs and more) | "on" | "off": with fewer owners than ranks, ranks that own nothing sum a part of each owner's share and forward f32 sums
   std::string wgrad_apply = "auto";       // "auto" | "off": on one GPU the weight-gradient GEMMs apply the optimizer in their epilogues
   size_t switch_check_every = 10;         // step cadence: steps between two evaluations of the gradient-norm switch metric
   double comm_timeout_s = 300.0;          // a collective or device wait that exceeds this ends the run with an error

@@ -235,8 +235,9 @@ typedef struct OnoSyncLocal {
   int* status;            // optional error word
   // Pre-reduction for another owner (16-bit gradient windows only, ranges cut at multiples of 8): when set, this rank
   // does not own its ranges; it sums the workers' 16-bit slabs over them in f32, in rank order, and stores the sums here
-  // (the owner's f32 gradient vector, indexed globally, possibly over NVLink). No optimizer, no parameter stores. The
-  // owner then finishes those ranges from its own f32 vector in a second launch. Halves (or better) the bytes that
+  // (an f32 vector indexed globally: this rank's own, from where a copy engine carries them to the owner, or the
+  // owner's over NVLink). No optimizer, no parameter stores. The owner then finishes those ranges from its own f32
+  // vector in a second launch. Halves (or better) the bytes that
   // converge on an owner when there are fewer owners than workers.
   float* fwd;
   int n_ranges;

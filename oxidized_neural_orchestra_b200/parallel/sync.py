@@ -39,8 +39,8 @@ def pre_reduce_plan(own: list[list[tuple[int, int]]], max_ranges: int):
     owner's share converge on that owner, (N-1)/S of the vector through one GPU's links, while the ranks that own nothing
     receive nothing. Those ranks become reducers: each owner keeps 1/(k+1) of every range it owns and hands one such part
     to each of its k idle partners; the workers ship a part's gradients to whoever reduces it, the partner sums the slabs in
-    f32 in rank order and stores the sums into the owner's f32 gradient vector (first launch of the exchange), and the
-    owner finishes those parts from its own memory (second launch). Same sums, same order, same result; the bytes that
+    f32 in rank order (first launch of the exchange), a copy engine carries the f32 sums into the owner's f32 gradient
+    vector, and the owner finishes those parts from its own memory (second launch). Same sums, same order, same result; the bytes that
     arrive at any one GPU during backward drop by the factor k+1.
 
     Returns ``(reduce_at, finish_at, fwd_to)``: per rank the ranges whose slabs it sums in the first launch; per owner

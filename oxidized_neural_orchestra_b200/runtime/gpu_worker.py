@@ -347,6 +347,12 @@ class GpuRank:
         dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
         return bool(flag.item() > 0)
 
+    def _plan_pre_reduce(self) -> None:
+        """Ranks that own nothing take a part of every owner's share to sum (see ``parallel.sync.pre_reduce_plan``)."""
+        plan_ = S.pre_reduce_plan(self.own, _lib.MAX_RANGES)
+        if plan_ is not None:
+            self.reduce_at, self.finish_at, self.fwd_to = plan_
+
     def _stripe(self, ranges):
         """Equal shares laid out as one slice of every layer per owner instead of one contiguous run of layers.
 
@@ -398,7 +404,7 @@ class GpuRank:
             i, o = pl.in_features, pl.out_features
             aligned = o % 8 == 0 and pl.w_off % 8 == 0
             pieces, casts, cps = [], [], []
-            for owner, rs in enumerate(self.own):
+            for owner, rs in enumerate(self.own if direct_transport else self.reduce_at):    # staged: whoever sums the range
                 for lo, hi in rs:
                     a0, a1 = max(lo, pl.w_off), min(hi, pl.b_off + o)      # the layer's whole block: weights then bias
                     if a1 > a0 and owner != self.rank and not direct_transport:
@@ -549,6 +555,12 @@ class GpuRank:
         if self.push_active or (self.wire16_push and self.wire_transport == "direct"):
             ranges = self._snap_to_row_blocks(ranges)
         self.own = snap_ranges(ranges, self.n_pad)
+        # who sums the 16-bit slabs of which range: the owners themselves, unless ranks that own nothing take a part of it
+        self.reduce_at, self.finish_at, self.fwd_to = self.own, None, {}
+        pre = self.b200.get("pre_reduce", "auto")
+        if self.wire16_push and self.wire_transport == "staged" and mode == "fused" and (pre == "on" or (pre == "auto" and W >= 4)):
+            # (on two GPUs the forwarded f32 sums weigh more than the 16-bit slabs they save: measured slower there)
+            self._plan_pre_reduce()
         self.buckets, self.bucket_after = [], {}
         self.stage_buckets, self.stage_after, self.stage_active = [], {}, False
         if self.engine is not None:
@@ -650,11 +662,30 @@ class GpuRank:
                         if algo == 1 else None,
                         p_mc_f32=(win.mc(lay.offset("params")) or None) if (engines_need_f32 and not self.pull_staged) else None,
                         p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if (self.tile == "bf16" and not self.pull_staged) else None)
-            S.fill_local(s.loc[self.rank], p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(),
-                         v=self.v_loc.data_ptr(), state_off=0, adam_pows=self.adam_pows.data_ptr(),
-                         epoch=self.epoch_words.data_ptr(), ranges=self.own[self.rank],
-                         sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None,
-                         status=self.sync_status.data_ptr())
+            local = dict(p_master=self.C.data_ptr(), m=self.m_loc.data_ptr(), v=self.v_loc.data_ptr(), state_off=0,
+                         adam_pows=self.adam_pows.data_ptr(), epoch=self.epoch_words.data_ptr(),
+                         sumsq=self.sumsq.data_ptr() if self.grad_norm_switch else None, status=self.sync_status.data_ptr())
+            self.sync_struct2, self.fwd_copies = None, []
+            if self.fwd_to:
+                # first launch: owners update the part they reduce themselves, their partners forward f32 sums of theirs;
+                # second launch: the owners finish the forwarded parts from their own f32 gradient vector
+                # (the partner writes its sums into its OWN f32 gradient vector and a copy engine carries them to the owner
+                # between the two launches: stores issued by SMs over NVLink reached ~320 GB/s here, the copy engine 770)
+                f32_ptrs = win.peer_ptrs(lay.offset(self.grad_region))
+                mine = self.rank in self.fwd_to
+                S.fill_local(s.loc[self.rank], ranges=self.reduce_at[self.rank], fwd=f32_ptrs[self.rank] if mine else None, **local)
+                self.fwd_copies = [(f32_ptrs[self.fwd_to[self.rank]] + 4 * b, f32_ptrs[self.rank] + 4 * b, 4 * (e - b))
+                                   for b, e in self.reduce_at[self.rank]] if mine else []
+                s2 = _lib.OnoSync()
+                S.fill_sync(s2, nranks=W, rank=self.rank, n=self.n_pad, nblocks=self.nblocks, algo=algo, g_ptrs=f32_ptrs,
+                            p_f32_ptrs=pf, p_bf16_ptrs=pb, flag_ptrs=win.flag_ptrs, worker_mask=1 << self.rank,
+                            member_mask=allmask, n_workers=len(workers), opt=opt, divide=not wild, timeout_ns=10_000_000_000,
+                            p_mc_f32=(win.mc(lay.offset("params")) or None) if engines_need_f32 else None,
+                            p_mc_bf16=(win.mc(lay.offset("params_bf16")) or None) if self.tile == "bf16" else None)
+                S.fill_local(s2.loc[self.rank], ranges=self.finish_at[self.rank], **local)
+                self.sync_struct2 = s2
+            else:
+                S.fill_local(s.loc[self.rank], ranges=self.own[self.rank], **local)
             s.g_dtype = g_dtype
             if self.compress and self.sparse_r is not None:
                 s.zero_grad = 1
@@ -884,6 +915,12 @@ class GpuRank:
         if self.sync_mode in ("fused", "oneshot"):
             S.launch_sync(self.sync_struct, stream=stream)
             n += 1
+            if getattr(self, "sync_struct2", None) is not None:
+                lib, sp = _lib.load(), _lib.stream_ptr(stream)
+                for dst, src, nbytes in self.fwd_copies:       # a partner's sums travel to their owner; owners have none
+                    _lib.check(lib.ono_copy_async(dst, src, nbytes, sp), "ono_copy_async")
+                S.launch_sync(self.sync_struct2, stream=stream)
+                n += 1 + len(self.fwd_copies)
         elif self.sync_mode == "async":
             if self.widx is not None and self.rank in self.sync_workers:
                 a = self.async_struct

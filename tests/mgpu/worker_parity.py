@@ -84,6 +84,10 @@ def main():
             ar(f"ar-{tile}-wire16-{fmt}-push-step", model12, 16, dict(base), expect={"wire": fmt, "wire_push": True, "wire_transport": "staged"})
             ps(f"ps-{tile}-wire16-{fmt}-push-step", model12, 16, dict(base, colocate=True, sharding="even"),
                expect={"wire": fmt, "wire_push": True})
+        # fewer owners than ranks: the idle ranks sum a part of each owner's share and a copy engine forwards the f32 sums
+        ps(f"ps-{tile}-wire16-prereduce-step", model12, 16, dict(sync_every="step", tile_dtype=tile, colocate=True, sharding="even",
+                                                               pre_reduce="on"),
+           expect={"wire": "bf16", "wire_push": True, "pre_reduce": True})
         ar(f"ar-{tile}-wire16-direct-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "direct"},
            expect={"wire": "bf16", "wire_push": True, "wire_transport": "direct"})
         ps(f"ps-{tile}-wire16-direct-step", model12, 16, {"sync_every": "step", "tile_dtype": tile, "grad_push": "direct",
@@ -108,6 +112,8 @@ def main():
         ps("ps-pure-servers-layer-round", model, 10, {}, opt=lambda: GradientDescent(0.2), nserv=1, nworkers=world - 1)
         ps("ps-pure-servers-wire16-step", model12, 16, {"sync_every": "step"}, opt=lambda: GradientDescent(0.2), nserv=1,
            nworkers=world - 1, expect={"wire": "bf16", "wire_push": True})
+        ps("ps-pure-servers-wire16-prereduce-step", model12, 16, {"sync_every": "step", "pre_reduce": "on"},
+           opt=lambda: GradientDescent(0.2), nserv=1, nworkers=world - 1, expect={"wire": "bf16", "wire_push": True, "pre_reduce": True})
         ps("ps-async-wild-round", model, 10, {}, opt=lambda: GradientDescent(0.05), nserv=1, sync=NonBlockingSync, store=WildStore,
            nworkers=world - 1)
         cases.append(("switch-round", model, lambda a: orchestra.strategy_switch(
