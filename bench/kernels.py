@@ -158,11 +158,12 @@ def cmd_sync_emulated(a):
     pows = torch.full((2,), 0.5, device="cuda")
     s = _lib.OnoSync()
     S.fill_sync(s, nranks=R, rank=0, n=n, nblocks=nblocks, algo=0, g_ptrs=[t.data_ptr() for t in g],
-                p_f32_ptrs=[t.data_ptr() for t in p], p_bf16_ptrs=[None if t is None else t.data_ptr() for t in pb],
+                p_f32_ptrs=[None if a.f32_master_only else t.data_ptr() for t in p],
+                p_bf16_ptrs=[None if t is None else t.data_ptr() for t in pb],
                 flag_ptrs=[t.data_ptr() for t in flags],
                 worker_mask=(1 << R) - 1, member_mask=(1 << R) - 1, n_workers=R, opt=S.OptimizerCfg(kind=a.opt, lr=0.01, mu=0.9))
     s.g_dtype = {"f32": 0, "bf16": 1, "f16": 2}[a.wire]
-    ranges = S.even_ranges(n, list(range(R)), R, align=8)
+    ranges = S.even_ranges(n, list(range(R)), R, align=a.range_align)
     for r in range(R):
         S.fill_local(s.loc[r], p_master=p[r].data_ptr(), m=m[r].data_ptr(), v=v[r].data_ptr(), state_off=0,
                      adam_pows=pows.data_ptr(), epoch=epoch[r].data_ptr(), ranges=ranges[r], status=status.data_ptr())
@@ -171,7 +172,8 @@ def cmd_sync_emulated(a):
     ms = _time(lambda: S.launch_sync(s, emulated=True), a.iters)
     assert status.item() == 0
     # owner state + R gradient reads + R parameter writes (f32, and bf16 with the shadow)
-    per = {"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + g[0].element_size() * R + 4 * R + (2 * R if a.bf16_shadow else 0)
+    per = ({"sgd": 8, "momentum": 16, "adam": 24}[a.opt] + g[0].element_size() * R + (0 if a.f32_master_only else 4 * R)
+           + (2 * R if a.bf16_shadow else 0))
     rec = {"kernel": f"sync_kernel_emulated({R} ranks, one GPU)", "elems": n, "opt": a.opt, "wire": a.wire, "ms": ms,
            "GBs_local_hbm": per * n / ms / 1e6, "blocks_per_rank": nblocks}
     if a.checksum:      # bits of every rank's parameters and optimizer state: equal between runs (fixed summation order)
@@ -290,6 +292,10 @@ def main():
     s.add_argument("--bf16-shadow", action="store_true"); s.add_argument("--iters", type=int, default=20)
     s.add_argument("--emulate-ranks", type=int, default=0, help="run R ranks as one cooperative launch on this GPU")
     s.add_argument("--wire", default="f32", choices=("f32", "bf16", "f16"), help="with --emulate-ranks: format of the gradient windows")
+    s.add_argument("--f32-master-only", action="store_true", help="with --emulate-ranks: f32 parameters stay with their owner, only "
+                   "the bf16 shadow goes to every rank (bf16-tile engines; lets 16-bit windows take the 16-byte path)")
+    s.add_argument("--range-align", type=int, default=8, help="with --emulate-ranks: owned ranges are cut at multiples of this many "
+                   "elements (8: the kernel's 16-byte path for 16-bit windows; 4: its 8-byte path)")
     s.add_argument("--checksum", action="store_true", help="with --emulate-ranks: print a hash of the resulting state")
     w = sub.add_parser("sweep")
     w.add_argument("--max-bytes", type=int, default=1 << 30)

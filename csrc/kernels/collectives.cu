@@ -58,7 +58,16 @@ __device__ void sync_body(const OnoSync& a, const int rank, const int blk) {
   // 16-bit gradient windows whose ranges are multiples of 8 elements (the staged push lays shares out that way): one
   // 16-byte load per worker and thread brings eight gradients, and the fresh bf16 parameters leave as one 16-byte store
   // per thread (a full 512-byte line per warp over NVLink, P2P or multicast) instead of two 8-byte ones.
+  // Not when f32 parameters leave for other GPUs: a thread's two float4 would go out as two stores that each fill half a
+  // 32-byte sector, twice the packets over NVLink (measured: the tf32 MLP on four GPUs lost 13 %); that case keeps the
+  // 8-byte path, whose stores are contiguous across the warp.
   bool wide8 = a.g_dtype != 0 && a.algo != 1;
+  if (!L.fwd) {
+    if (a.algo != 0) wide8 = wide8 && !a.p_mc_f32;
+    else
+      for (int q = 0; q < ONO_MAX_RANKS; ++q)
+        if (q < a.nranks && q != rank && a.p_out_f32[q] && a.p_out_f32[q] != L.p_master) wide8 = false;
+  }
   for (int ri = 0; ri < L.n_ranges && wide8; ++ri) wide8 = ((L.ranges[ri].begin | L.ranges[ri].end) & 7) == 0;
   if (ok && wide8) {
     const int f16 = a.g_dtype == 2;

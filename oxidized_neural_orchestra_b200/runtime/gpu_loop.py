@@ -99,7 +99,10 @@ def _batch_body(r, slot: int, nrows: int, with_sync: bool) -> int:
         # layers below are still in backward; the fused kernel starts once the last transfer has been issued and done
         n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st,
                     after_layer=(lambda l: r.wire_ship(l, st)) if r.wire_copies else None)
-        st.wait_stream(r.comm_stream)
+        for cs in (r.push_streams_used() if r.wire_copies else []):
+            st.wait_stream(cs)
+        if r.pull_staged:
+            st.wait_stream(r.comm_stream)
     else:
         n += e.step(f.dev_x[slot], f.dev_y[slot], nrows, stream=st)
     mark("exchange")

@@ -57,6 +57,9 @@ class GpuRank:
         self.buckets, self.bucket_after, self.stage_buckets, self.stage_after = [], {}, [], {}
         self.stream = torch.cuda.Stream(device=device)
         self.comm_stream = torch.cuda.Stream(device=device)
+        # the staged gradient push may spread its transfers over several streams (one copy engine each), by destination
+        self.push_streams = [self.comm_stream] + [torch.cuda.Stream(device=device)
+                                                  for _ in range(max(0, int(os.environ.get("ONO_PUSH_STREAMS", "1")) - 1))]
         wspec = plan["workers"][self.widx if self.widx is not None else 0]["spec"]
         self.trainer = wspec["trainer"]
         self.max_epochs = self.trainer["max_epochs"]
@@ -409,7 +412,7 @@ class GpuRank:
                     a0, a1 = max(lo, pl.w_off), min(hi, pl.b_off + o)      # the layer's whole block: weights then bias
                     if a1 > a0 and owner != self.rank and not direct_transport:
                         off = 2 * (self.rank * self.n_pad + a0)
-                        cps.append((self.win.ptrs[owner] + slab0 + off, self.win.ptrs[self.rank] + slab0 + off, 2 * (a1 - a0)))
+                        cps.append((self.win.ptrs[owner] + slab0 + off, self.win.ptrs[self.rank] + slab0 + off, 2 * (a1 - a0), owner))
                     a0, a1 = max(lo, pl.w_off), min(hi, pl.w_off + i * o)
                     if a1 > a0 and direct_transport:
                         if aligned:
@@ -486,11 +489,19 @@ class GpuRank:
             return 0
         ev = torch.cuda.Event()
         ev.record(stream)
-        self.comm_stream.wait_event(ev)
-        lib, cs = _lib.load(), _lib.stream_ptr(self.comm_stream)
-        for dst, src, nbytes in cps:
-            _lib.check(lib.ono_copy_async(dst, src, nbytes, cs), "ono_copy_async")
+        lib, k = _lib.load(), len(self.push_streams)
+        for cs in {self.push_streams[owner % k] for _, _, _, owner in cps}:
+            cs.wait_event(ev)
+        for dst, src, nbytes, owner in cps:
+            _lib.check(lib.ono_copy_async(dst, src, nbytes, _lib.stream_ptr(self.push_streams[owner % k])), "ono_copy_async")
         return len(cps)
+
+    def push_streams_used(self):
+        """The streams the staged gradient push issues transfers on (the step joins them before the exchange)."""
+        if not self.wire_copies:
+            return []
+        k = len(self.push_streams)
+        return list({self.push_streams[owner % k] for cps in self.wire_copies.values() for _, _, _, owner in cps})
 
     def _build_apply(self, opt, n_workers: int, wild: bool):
         """Layers whose weight-gradient GEMM applies the optimizer itself, and the ranges left to the fused kernel."""
