@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstdint>
 #include <cstring>
 #include <numeric>
 #include <stdexcept>
@@ -13,45 +14,152 @@
 namespace ono::oracle {
 
 // ---- small dense kernels (row-major) ----------------------------------------------------------
+// The hot loops are plain C++ written so that the compiler vectorises them (unit-stride updates and `omp simd` reductions),
+// compiled once per instruction-set level and picked at load time by the CPU that runs them: a node binary built on one
+// machine runs on another. Summation order inside a dot product therefore depends on the vector width; every comparison
+// against this engine allows for rounding.
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__) && !defined(ONO_NO_CLONES)
+#define ONO_HOT __attribute__((target_clones("arch=x86-64-v4", "arch=x86-64-v3", "default")))
+#else
+#define ONO_HOT
+#endif
+
+// c[0..n) += a * b[0..n)
+#define ONO_AXPY(c, a, b, n)                             \
+  _Pragma("omp simd") for (size_t j_ = 0; j_ < (n); ++j_) (c)[j_] += (a) * (b)[j_]
+
 // C[M,N] (+)= A[M,K] * B[K,N]
-static void gemm_nn(const float* A, const float* B, float* C, size_t M, size_t N, size_t K, bool accumulate) {
+ONO_HOT static void gemm_nn(const float* A, const float* B, float* C, size_t M, size_t N, size_t K, bool accumulate) {
   if (!accumulate) std::fill(C, C + M * N, 0.f);
   for (size_t i = 0; i < M; ++i) {
     float* c = C + i * N;
-    for (size_t k = 0; k < K; ++k) {
+    size_t k = 0;
+    for (; k + 4 <= K; k += 4) {       // four rows of B per pass over c: a quarter of the loads and stores of c
+      const float a0 = A[i * K + k], a1 = A[i * K + k + 1], a2 = A[i * K + k + 2], a3 = A[i * K + k + 3];
+      if (a0 == 0.f && a1 == 0.f && a2 == 0.f && a3 == 0.f) continue;
+      const float *b0 = B + k * N, *b1 = b0 + N, *b2 = b1 + N, *b3 = b2 + N;
+#pragma omp simd
+      for (size_t j = 0; j < N; ++j) c[j] += a0 * b0[j] + a1 * b1[j] + a2 * b2[j] + a3 * b3[j];
+    }
+    for (; k < K; ++k) {
       const float a = A[i * K + k];
       if (a == 0.f) continue;
       const float* b = B + k * N;
-      for (size_t j = 0; j < N; ++j) c[j] += a * b[j];
+      ONO_AXPY(c, a, b, N);
     }
   }
 }
 // C[K,N] += A[M,K]^T * D[M,N]
-static void gemm_tn_acc(const float* A, const float* D, float* C, size_t M, size_t N, size_t K) {
-  for (size_t i = 0; i < M; ++i) {
+ONO_HOT static void gemm_tn_acc(const float* A, const float* D, float* C, size_t M, size_t N, size_t K) {
+  size_t i = 0;
+  for (; i + 4 <= M; i += 4) {         // four samples per pass over a row of C
+    const float *d0 = D + i * N, *d1 = d0 + N, *d2 = d1 + N, *d3 = d2 + N;
+    for (size_t k = 0; k < K; ++k) {
+      const float a0 = A[i * K + k], a1 = A[(i + 1) * K + k], a2 = A[(i + 2) * K + k], a3 = A[(i + 3) * K + k];
+      if (a0 == 0.f && a1 == 0.f && a2 == 0.f && a3 == 0.f) continue;
+      float* c = C + k * N;
+#pragma omp simd
+      for (size_t j = 0; j < N; ++j) c[j] += a0 * d0[j] + a1 * d1[j] + a2 * d2[j] + a3 * d3[j];
+    }
+  }
+  for (; i < M; ++i) {
     const float* d = D + i * N;
     for (size_t k = 0; k < K; ++k) {
       const float a = A[i * K + k];
       if (a == 0.f) continue;
       float* c = C + k * N;
-      for (size_t j = 0; j < N; ++j) c[j] += a * d[j];
+      ONO_AXPY(c, a, d, N);
     }
   }
 }
+ONO_HOT static float dot(const float* a, const float* b, size_t n) {
+  float s = 0.f;
+#pragma omp simd reduction(+ : s)
+  for (size_t j = 0; j < n; ++j) s += a[j] * b[j];
+  return s;
+}
 // C[M,K] = D[M,N] * W[K,N]^T
-static void gemm_nt(const float* D, const float* W, float* C, size_t M, size_t N, size_t K) {
+ONO_HOT static void gemm_nt(const float* D, const float* W, float* C, size_t M, size_t N, size_t K) {
   for (size_t i = 0; i < M; ++i) {
     const float* d = D + i * N;
     for (size_t k = 0; k < K; ++k) {
       const float* w = W + k * N;
       float s = 0.f;
+#pragma omp simd reduction(+ : s)
       for (size_t j = 0; j < N; ++j) s += d[j] * w[j];
       C[i * K + k] = s;
     }
   }
 }
+// Convolution backward for one sample. dcol[ckk, npix] = K[F, ckk]^T delta[F, npix]
+ONO_HOT static void conv_dcol(const float* kernels, const float* delta, float* dcol, size_t F, size_t ckk, size_t npix) {
+  std::fill(dcol, dcol + ckk * npix, 0.f);
+  for (size_t f = 0; f < F; ++f) {
+    const float* dd = delta + f * npix;
+    for (size_t q = 0; q < ckk; ++q) {
+      const float kv = kernels[f * ckk + q];
+      if (kv == 0.f) continue;
+      float* dc = dcol + q * npix;
+      ONO_AXPY(dc, kv, dd, npix);
+    }
+  }
+}
+// dK[F, ckk] += delta[F, npix] col[ckk, npix]^T ; db[F] += row sums of delta
+ONO_HOT static void conv_dk(const float* delta, const float* col, float* dk, float* db, size_t F, size_t ckk, size_t npix) {
+  for (size_t f = 0; f < F; ++f) {
+    const float* dd = delta + f * npix;
+    for (size_t q = 0; q < ckk; ++q) {
+      const float* cc = col + q * npix;
+      float s = 0.f;
+#pragma omp simd reduction(+ : s)
+      for (size_t i = 0; i < npix; ++i) s += dd[i] * cc[i];
+      dk[f * ckk + q] += s;
+    }
+    float sb = 0.f;
+#pragma omp simd reduction(+ : sb)
+    for (size_t i = 0; i < npix; ++i) sb += dd[i];
+    db[f] += sb;
+  }
+}
 
 // ---- activations ------------------------------------------------------------------------------
+// exp and tanh as branch-free float code the compiler vectorises (Cephes-style range reduction and polynomials, a few ulp
+// from libm): a LeNet-5 sample runs ~6 500 of them, which cost as much as its convolutions when taken one libm call at a time.
+static inline float exp_poly(float x) {
+  x = std::min(88.f, std::max(-87.f, x));
+  const float n = std::nearbyint(x * 1.44269504088896341f);
+  const float r = (x - n * 0.693359375f) - n * -2.12194440e-4f;
+  float p = 1.9875691500e-4f;
+  p = p * r + 1.3981999507e-3f;
+  p = p * r + 8.3334519073e-3f;
+  p = p * r + 4.1665795894e-2f;
+  p = p * r + 1.6666665459e-1f;
+  p = p * r + 5.0000001201e-1f;
+  const float e = p * r * r + r + 1.f;
+  int32_t bits = ((int32_t)n + 127) << 23;
+  float scale;
+  std::memcpy(&scale, &bits, 4);
+  return e * scale;
+}
+ONO_HOT static void act_sigmoid(float* y, size_t n, float amp) {
+#pragma omp simd
+  for (size_t i = 0; i < n; ++i) y[i] = amp / (1.f + exp_poly(-y[i]));
+}
+ONO_HOT static void act_tanh(float* y, size_t n, float amp) {
+#pragma omp simd
+  for (size_t i = 0; i < n; ++i) {
+    const float x = y[i], ax = std::fabs(x), z = x * x;
+    float small = -5.70498872745e-3f;
+    small = small * z + 2.06390887954e-2f;
+    small = small * z - 5.37397155531e-2f;
+    small = small * z + 1.33314422036e-1f;
+    small = small * z - 3.33332819422e-1f;
+    small = small * z * x + x;
+    const float big = std::copysign(1.f - 2.f / (exp_poly(2.f * ax) + 1.f), x);
+    y[i] = amp * (ax < 0.625f ? small : big);
+  }
+}
+
 ActFn ActFn::from_spec(const Json& j) {
   ActFn a;
   if (j.is_null()) return a;
@@ -72,8 +180,8 @@ ActFn ActFn::from_spec(const Json& j) {
 void Layer::apply_act(std::vector<float>& y, size_t B, size_t width) {
   switch (act.kind) {
     case Act::None: break;
-    case Act::Sigmoid: for (auto& v : y) v = act.param / (1.f + std::exp(-v)); break;
-    case Act::Tanh: for (auto& v : y) v = act.param * std::tanh(v); break;
+    case Act::Sigmoid: act_sigmoid(y.data(), y.size(), act.param); break;
+    case Act::Tanh: act_tanh(y.data(), y.size(), act.param); break;
     case Act::ReLU: for (auto& v : y) v = std::max(v, act.param * v); break;
     case Act::Gelu:
       pre_ = y;
@@ -147,6 +255,7 @@ class Dense final : public Layer {
     float* gb = grad + in_ * out_;
     for (size_t i = 0; i < B; ++i)
       for (size_t j = 0; j < out_; ++j) gb[j] += d[i * out_ + j];
+    if (!need_dx) { dx.clear(); return; }
     dx.resize(B * in_);
     gemm_nt(d.data(), params, dx.data(), B, out_, in_);  // dX = d W^T
   }
@@ -184,52 +293,50 @@ class Conv2d final : public Layer {
   void backward(const float* params, float* grad, std::vector<float>& d, size_t B, std::vector<float>& dx) override {
     act_backward(d, B, out_size());
     const size_t ckk = C_ * K_ * K_, npix = OH_ * OW_;
-    dx.assign(B * in_size(), 0.f);
+    if (need_dx) dx.assign(B * in_size(), 0.f);
+    else dx.clear();
     dcol_.resize(ckk * npix);
     float* gb = grad + F_ * ckk;
     for (size_t b = 0; b < B; ++b) {
       const float* db = d.data() + b * out_size();
       // col_delta = K^T delta  -> col2im scatter-add (conv2d.rs:161-172, 240-266)
-      std::fill(dcol_.begin(), dcol_.end(), 0.f);
-      for (size_t f = 0; f < F_; ++f)
-        for (size_t q = 0; q < ckk; ++q) {
-          const float kv = params[f * ckk + q];
-          if (kv == 0.f) continue;
-          float* dc = dcol_.data() + q * npix;
-          const float* dd = db + f * npix;
-          for (size_t i = 0; i < npix; ++i) dc[i] += kv * dd[i];
-        }
-      col2im(dx.data() + b * in_size());
+      if (need_dx) {
+        conv_dcol(params, db, dcol_.data(), F_, ckk, npix);
+        col2im(dx.data() + b * in_size());
+      }
       // dK += delta col^T (conv2d.rs:174-180)
       im2col(x_.data() + b * in_size());
-      for (size_t f = 0; f < F_; ++f) {
-        const float* dd = db + f * npix;
-        for (size_t q = 0; q < ckk; ++q) {
-          const float* cc = col_.data() + q * npix;
-          float s = 0.f;
-          for (size_t i = 0; i < npix; ++i) s += dd[i] * cc[i];
-          grad[f * ckk + q] += s;
-        }
-        float sb = 0.f;
-        for (size_t i = 0; i < npix; ++i) sb += dd[i];
-        gb[f] += sb;
-      }
+      conv_dk(db, col_.data(), grad, gb, F_, ckk, npix);
     }
   }
 
  private:
+  // Output columns [lo, hi) of a row whose input column ox * S + kx - P falls inside the image.
+  void valid_span(size_t kx, size_t& lo, size_t& hi) const {
+    lo = kx >= P_ ? 0 : (P_ - kx + S_ - 1) / S_;
+    const long last = (long)W_ - 1 + (long)P_ - (long)kx;          // largest ox * S allowed
+    hi = last < 0 ? 0 : std::min(OW_, (size_t)last / S_ + 1);
+    if (lo > hi) lo = hi;
+  }
   void im2col(const float* x) {
     const size_t npix = OH_ * OW_;
     for (size_t c = 0; c < C_; ++c)
       for (size_t ky = 0; ky < K_; ++ky)
         for (size_t kx = 0; kx < K_; ++kx) {
           float* row = col_.data() + ((c * K_ + ky) * K_ + kx) * npix;
+          size_t lo, hi;
+          valid_span(kx, lo, hi);
           for (size_t oy = 0; oy < OH_; ++oy) {
             const long iy = (long)(oy * S_ + ky) - (long)P_;
-            for (size_t ox = 0; ox < OW_; ++ox) {
-              const long ix = (long)(ox * S_ + kx) - (long)P_;
-              row[oy * OW_ + ox] = (iy >= 0 && iy < (long)H_ && ix >= 0 && ix < (long)W_) ? x[(c * H_ + iy) * W_ + ix] : 0.f;
+            float* r = row + oy * OW_;
+            if (iy < 0 || iy >= (long)H_) { std::fill(r, r + OW_, 0.f); continue; }
+            std::fill(r, r + lo, 0.f);
+            if (hi > lo) {
+              const float* src = x + (c * H_ + iy) * W_ + (lo * S_ + kx - P_);   // lo * S + kx >= P inside the span
+              if (S_ == 1) std::copy(src, src + (hi - lo), r + lo);
+              else for (size_t ox = lo; ox < hi; ++ox) r[ox] = src[(ox - lo) * S_];
             }
+            std::fill(r + hi, r + OW_, 0.f);
           }
         }
   }
@@ -239,14 +346,15 @@ class Conv2d final : public Layer {
       for (size_t ky = 0; ky < K_; ++ky)
         for (size_t kx = 0; kx < K_; ++kx) {
           const float* row = dcol_.data() + ((c * K_ + ky) * K_ + kx) * npix;
+          size_t lo, hi;
+          valid_span(kx, lo, hi);
           for (size_t oy = 0; oy < OH_; ++oy) {
             const long iy = (long)(oy * S_ + ky) - (long)P_;
-            if (iy < 0 || iy >= (long)H_) continue;
-            for (size_t ox = 0; ox < OW_; ++ox) {
-              const long ix = (long)(ox * S_ + kx) - (long)P_;
-              if (ix < 0 || ix >= (long)W_) continue;
-              dx[(c * H_ + iy) * W_ + ix] += row[oy * OW_ + ox];
-            }
+            if (iy < 0 || iy >= (long)H_ || hi <= lo) continue;
+            float* dst = dx + (c * H_ + iy) * W_ + (lo * S_ + kx - P_);
+            const float* r = row + oy * OW_ + lo;
+            if (S_ == 1) { for (size_t t = 0; t < hi - lo; ++t) dst[t] += r[t]; }
+            else for (size_t t = 0; t < hi - lo; ++t) dst[t * S_] += r[t];
           }
         }
   }
@@ -342,6 +450,7 @@ Sequential::Sequential(const Json& layer_specs, size_t x_size, bool leaky_relu_e
     layers_.push_back(std::move(l));
   }
   if (layers_.empty()) throw std::runtime_error("model must have at least one layer");
+  layers_.front()->need_dx = false;
   outs_.resize(layers_.size());
 }
 

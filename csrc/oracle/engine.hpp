@@ -42,6 +42,7 @@ class Layer {
   virtual void backward(const float* params, float* grad, std::vector<float>& d, size_t B, std::vector<float>& dx) = 0;
   ActFn act;
   bool leaky_relu_exact = true;  // false reproduces relu.rs:41-45 (d := slope * a where a <= 0)
+  bool need_dx = true;           // false for a model's first layer: nobody consumes the gradient w.r.t. the input
 
  protected:
   void apply_act(std::vector<float>& y, size_t B, size_t width);

@@ -33,7 +33,7 @@ CUDA_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",
 ]
-CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"]
+CXX_FLAGS = ["-O3", "-fopenmp-simd", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"]
 
 
 def _newer(src: Path, dst: Path, extra: list[Path]) -> bool:
@@ -133,7 +133,9 @@ def build_bins(force: bool = False, sanitize: str | None = None, only: tuple | N
     ``bin/<sanitize>/`` for the host-side race and memory checks of the C++ runtime (control plane, sessions,
     dynamic barrier, codec); the reference runs no sanitizer in CI (.github/workflows/test.yml:29-30)."""
     bindir = BINDIR if sanitize is None else BINDIR / sanitize
-    flags = CXX_FLAGS if sanitize is None else ["-O1", "-g1", "-fno-omit-frame-pointer", *CXX_FLAGS[1:], *SANITIZERS[sanitize]]
+    # (sanitizer builds: no per-ISA clones of the hot loops, their load-time resolvers run before the sanitizer runtime is up)
+    flags = CXX_FLAGS if sanitize is None else ["-O1", "-g1", "-fno-omit-frame-pointer", "-DONO_NO_CLONES", *CXX_FLAGS[1:],
+                                                *SANITIZERS[sanitize]]
     cxx = CXX
     if sanitize is not None:
         cxx = sanitizer_cxx(sanitize)
