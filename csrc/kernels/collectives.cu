@@ -661,12 +661,14 @@ extern "C" int ono_stage_pull(const OnoStagePull* s, ono_stream_t st) {
   }
   for (int r = 0; r < s->n_ranges; ++r)
     if (s->ranges[r].begin % 4) { set_error("stage_pull ranges must begin at multiples of 4 elements%s", "", 0, 0); return -1; }
-  static bool attr = false;
+  static bool attr_dev[64] = {false};     // a function attribute belongs to the device it was set on
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("bad device%s", "", 0, 0); return -6; }
   const int smem = PULL_SLOTS * PULL_CHUNK + 128;
-  if (!attr) {
+  if (!attr_dev[dev]) {
     cudaError_t e = cudaFuncSetAttribute(stage_pull_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute(stage_pull): %s", cudaGetErrorString(e), 0, 0); return -6; }
-    attr = true;
+    attr_dev[dev] = true;
   }
   stage_pull_kernel<<<s->nblocks, 32, smem, (cudaStream_t)st>>>(*s);
   return check_launch("stage_pull");

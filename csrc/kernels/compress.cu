@@ -244,8 +244,13 @@ using namespace ono;
 
 extern "C" int ono_sparse_threshold(const float* x, long long n, float r, unsigned long long seed, float* thr_out, ono_stream_t st) {
   if (!x || n <= 0 || !thr_out || r < 0.f || r > 1.f) { set_error("bad sparse_threshold args%s", "", 0, 0); return -1; }
-  static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(sparse_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SAMPLE_MAX * 4); attr = true; }
+  static bool attr_dev[64] = {false};     // a function attribute belongs to the device it was set on
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("bad device%s", "", 0, 0); return -6; }
+  if (!attr_dev[dev]) {
+    cudaFuncSetAttribute(sparse_threshold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SAMPLE_MAX * 4);
+    attr_dev[dev] = true;
+  }
   sparse_threshold_kernel<<<1, 1024, SPARSE_SAMPLE_MAX * 4, (cudaStream_t)st>>>(x, n, r, seed, thr_out);
   return done("sparse_threshold");
 }

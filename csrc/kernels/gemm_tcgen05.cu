@@ -1006,7 +1006,7 @@ extern "C" int ono_gemm(const OnoGemm* g, ono_stream_t stream_) {
     const long long tiles0 = (long long)((g->M + (pair ? 255 : 127)) / (pair ? 256 : 128)) * ((g->N + bn - 1) / bn);
     const long long ldn = ((long long)g->N + 3) / 4 * 4;
     int want = g->split_k > 1 ? g->split_k : 0;
-    if (g->split_k == 0 && !ap.p && !e.reduce_out && !pair && tiles0 * 8 <= num_sms() && KBh >= 32)
+    if (g->split_k == 0 && !ap.p && !e.reduce_out && !pair && tiles0 * 8 <= num_sms() && KBh >= 16)
       want = (int)std::min<long long>(KBh / 4, num_sms() / tiles0);
     if (want > KBh) want = KBh;
     if (want >= 2) {
