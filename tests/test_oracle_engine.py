@@ -200,3 +200,19 @@ def test_conv_pool_dense_network_learns_symbols():
     assert losses[-1] < 0.01
     loss, acc = tr.evaluate(p, syms.reshape(-1), np.eye(3, dtype=np.float32).reshape(-1))
     assert acc == 1.0
+
+
+@pytest.mark.parametrize("kind", ["tanh", "sigmoid"])
+def test_vectorised_activations_stay_within_a_few_ulp_of_libm(kind):
+    """tanh and sigmoid are branch-free polynomial code (vectorised per instruction-set level); their values must stay
+    within a few float ulp of the exact function over the whole useful range, including the switch-over at |x| = 0.625,
+    large arguments and zero."""
+    n = 4096
+    x = np.concatenate([np.linspace(-30, 30, n - 9), [0.0, -0.0, 0.625, -0.625, 0.6249999, 1e-6, -1e-6, 88.0, -88.0]]).astype(np.float32)
+    n = x.size
+    params = np.concatenate([np.eye(n, dtype=np.float32).reshape(-1), np.zeros(n, np.float32)])   # identity weights, no bias
+    y, _ = _run([_spec("dense", dim=[n, n], act_fn={kind: {"amp": 1.0}})], n, params, x.reshape(1, n), np.zeros((1, n), np.float32))
+    exact = np.tanh(x.astype(np.float64)) if kind == "tanh" else 1.0 / (1.0 + np.exp(-x.astype(np.float64)))
+    err = np.abs(y.reshape(-1).astype(np.float64) - exact)
+    assert err.max() <= 4 * np.finfo(np.float32).eps, (err.max(), x[err.argmax()])
+    assert y.reshape(-1)[n - 9] == (0.0 if kind == "tanh" else 0.5)
