@@ -278,6 +278,12 @@ void LocalCluster::build_servers(const Json& server_list, const std::vector<std:
     const size_t nw = (size_t)spec.at("nworkers").as_u64();
     if (spec.at("store").as_string() == "wild") s.store = std::make_unique<WildStore>(std::move(shard), opt);
     else s.store = std::make_unique<BlockingStore>(std::move(shard), opt, nw);
+    if (!inline_params && (opts_.init_m.size() == n_params_ || opts_.init_v.size() == n_params_)) {
+      std::vector<float> m, v;       // this shard's slice of the saved moments
+      if (opts_.init_m.size() == n_params_) gather_ranges(opts_.init_m, s.ranges, m);
+      if (opts_.init_v.size() == n_params_) gather_ranges(opts_.init_v, s.ranges, v);
+      s.store->optimizer().load_state(m.empty() ? nullptr : m.data(), v.empty() ? nullptr : v.data(), opts_.init_b1t, opts_.init_b2t);
+    }
     if (spec.at("synchronizer").is_string()) s.sync = std::make_unique<NonBlockingSync>();
     else s.sync = std::make_unique<BarrierSync>(nw);
     servers_.push_back(std::move(s));
@@ -285,12 +291,24 @@ void LocalCluster::build_servers(const Json& server_list, const std::vector<std:
   }
 }
 
+void LocalCluster::note_epochs(size_t done) {
+  std::lock_guard<std::mutex> lk(policy_mu_);
+  final_state_.epochs = std::max(final_state_.epochs, opts_.start_epoch + done);
+}
+
 void LocalCluster::gather_final_from_servers() {
   final_params_.assign(n_params_, 0.f);
+  final_state_.m.assign(n_params_, 0.f);
+  final_state_.v.assign(n_params_, 0.f);
   for (auto& s : servers_) {
     std::vector<float> shard(s.store->len());
     s.store->pull_params(shard.data());
     scatter_ranges(shard, s.ranges, final_params_);
+    const Optimizer& o = s.store->optimizer();
+    if (!o.m().empty()) scatter_ranges(o.m(), s.ranges, final_state_.m);
+    if (!o.v().empty()) scatter_ranges(o.v(), s.ranges, final_state_.v);
+    final_state_.b1t = o.b1t();
+    final_state_.b2t = o.b2t();
   }
 }
 
@@ -300,6 +318,19 @@ void LocalCluster::all_reduce_worker(size_t w) {
   std::vector<float>& params = ar_params_[w];
   std::vector<float> scratch = params, residual(n_params_, 0.f), grad;
   Optimizer opt(trainer.optimizer_spec(), n_params_);
+  if (opts_.init_m.size() == n_params_ || opts_.init_v.size() == n_params_)
+    opt.load_state(opts_.init_m.size() == n_params_ ? opts_.init_m.data() : nullptr,
+                   opts_.init_v.size() == n_params_ ? opts_.init_v.data() : nullptr, opts_.init_b1t, opts_.init_b2t);
+  struct Keep {      // worker 0's replica is the run's result (session.rs:371-412); so is its optimizer state
+    LocalCluster& c; Optimizer& o; size_t w, n;
+    ~Keep() {
+      if (w != 0) return;
+      c.final_state_.m = o.m().empty() ? std::vector<float>(n, 0.f) : o.m();
+      c.final_state_.v = o.v().empty() ? std::vector<float>(n, 0.f) : o.v();
+      c.final_state_.b1t = o.b1t();
+      c.final_state_.b2t = o.b2t();
+    }
+  } keep{*this, opt, w, n_params_};
   while (true) {
     TrainResult res = trainer.train(scratch.data(), residual.data());
     const auto d = report_losses(w, res.losses);
@@ -317,6 +348,7 @@ void LocalCluster::all_reduce_worker(size_t w) {
     scratch = params;                                   // all_reduce.rs:131-132
     if (res.is_last) break;
   }
+  note_epochs(trainer.epochs_done());
 }
 
 void LocalCluster::ps_worker(size_t w, RoundTrainer& trainer, std::vector<float>& params) {
@@ -346,6 +378,7 @@ void LocalCluster::ps_worker(size_t w, RoundTrainer& trainer, std::vector<float>
     if (res.is_last) break;
   }
   for (auto& s : servers_) s.sync->leave(*s.store);
+  note_epochs(trainer.epochs_done());
   ClusterEvent ev;
   ev.kind = "worker_done";
   ev.worker = w;
@@ -368,6 +401,7 @@ void LocalCluster::run_all() {
       std::vector<std::vector<float>> params(nworkers_, std::vector<float>(n_params_, 0.f));
       for (size_t w = 0; w < nworkers_; ++w)
         trainers.push_back(std::make_unique<RoundTrainer>(workers[w].at("spec").at("trainer"), std::move(parts[w]), opts_.leaky_relu_exact));
+      for (auto& t : trainers) t->set_epoch_base(opts_.start_epoch);
       for (size_t w = 0; w < nworkers_; ++w)
         threads_.emplace_back([this, w, &trainers, &params] {
           try { ps_worker(w, *trainers[w], params[w]); }
@@ -383,6 +417,7 @@ void LocalCluster::run_all() {
       trainers_.clear();
       for (size_t w = 0; w < nworkers_; ++w)
         trainers_.push_back(std::make_unique<RoundTrainer>(workers[w].at("spec").at("trainer"), parts[w], opts_.leaky_relu_exact));
+      for (auto& t : trainers_) t->set_epoch_base(opts_.start_epoch);
       ring_bufs_.assign(nworkers_, nullptr);
       ring_grads_.assign(nworkers_, nullptr);
       ring_msgs_.assign(nworkers_, {});
@@ -445,6 +480,7 @@ void LocalCluster::run_all() {
           // builder.rs:179-181 rebuilds the trainer, restarting the epoch counter; carrying it over
           // is this runtime's default
           if (!opts_.switch_resets_progress) trainers.back()->set_epochs_done(trainers_[w]->epochs_done());
+          trainers.back()->set_epoch_base(opts_.start_epoch);
         }
         bool work_left = false;
         for (auto& t : trainers) work_left = work_left || t->epochs_done() < t->max_epochs();

@@ -32,6 +32,7 @@ class Store {
   virtual void accumulate(const float* grad, size_t n) = 0;
   virtual void update_params() = 0;
   virtual void pull_params(float* out) = 0;
+  virtual Optimizer& optimizer() = 0;
 };
 
 // Two gradient accumulators flipped by the single updater; update = mean over workers, optimizer,
@@ -43,6 +44,7 @@ class BlockingStore final : public Store {
   void accumulate(const float* grad, size_t n) override;
   void update_params() override;
   void pull_params(float* out) override;
+  Optimizer& optimizer() override { return opt_; }
 
  private:
   std::vector<float> params_, acc_[2];
@@ -62,6 +64,7 @@ class WildStore final : public Store {
   void accumulate(const float* grad, size_t n) override;
   void update_params() override {}
   void pull_params(float* out) override;
+  Optimizer& optimizer() override { return opt_; }
 
  private:
   std::vector<float> params_;
@@ -107,6 +110,17 @@ struct ClusterOptions {
   double sparse_r = 0.0;
   bool leaky_relu_exact = true;
   bool switch_resets_progress = false;
+  // Optimizer state to start from (global parameter order; empty = fresh state) and the number of epochs the saved
+  // run had done (offsets the shuffle sequence). The reference has no such thing: it exports weights only.
+  std::vector<float> init_m, init_v;
+  float init_b1t = 1.f, init_b2t = 1.f;
+  size_t start_epoch = 0;
+};
+
+struct ClusterState {              // optimizer state at the end of a run, global parameter order
+  std::vector<float> m, v;
+  float b1t = 1.f, b2t = 1.f;
+  size_t epochs = 0;
 };
 
 class LocalCluster {
@@ -121,6 +135,7 @@ class LocalCluster {
   void join();
   bool finished() const { return finished_.load(); }
   const std::vector<float>& final_params() const { return final_params_; }
+  const ClusterState& final_state() const { return final_state_; }
   const std::string& stop_reason() const { return stop_reason_; }
   bool switched() const { return switched_.load(); }
 
@@ -138,6 +153,7 @@ class LocalCluster {
   SessionPolicy::Decision report_losses(size_t w, const std::vector<double>& losses);
   void build_servers(const Json& server_list, const std::vector<std::vector<float>>* inline_params);
   void gather_final_from_servers();
+  void note_epochs(size_t done);
 
   Json plan_;
   Dataset data_;
@@ -154,6 +170,7 @@ class LocalCluster {
   std::atomic<bool> stop_{false}, finished_{false}, switched_{false};
   std::string stop_reason_ = "max_epochs";
   std::vector<float> final_params_;
+  ClusterState final_state_;
   std::vector<Server> servers_;
   // all-reduce shared state
   std::vector<std::vector<float>*> ring_bufs_;          // each worker's residual (scatter) buffer

@@ -527,6 +527,12 @@ void Optimizer::reset() {
   b1t_ = b2t_ = 1.f;
 }
 
+void Optimizer::load_state(const float* m, const float* v, float b1t, float b2t) {
+  if (m && !m_.empty()) std::copy(m, m + m_.size(), m_.begin());
+  if (v && !v_.empty()) std::copy(v, v + v_.size(), v_.begin());
+  if (spec_.kind == OptimizerSpec::Adam) { b1t_ = b1t; b2t_ = b2t; }
+}
+
 void Optimizer::step(float* p, const float* g, size_t n) {
   const auto& s = spec_;
   if (s.kind == OptimizerSpec::GradientDescent) {
@@ -640,7 +646,7 @@ TrainResult RoundTrainer::train(float* params, float* residual) {
   const size_t n = data_.rows(), P = model_.n_params();
   if (n == 0) throw std::runtime_error("empty epoch: the worker has no samples");
   for (size_t e = 0; e < todo; ++e) {
-    data_.shuffle(seed_, epoch_);
+    data_.shuffle(seed_, epoch_base_ + epoch_);
     double total = 0.0;
     size_t batches = 0;
     for (size_t lo = 0; lo < n; lo += batch_size_) {

@@ -90,6 +90,13 @@ class Optimizer {
   void step(float* params, const float* grad, size_t n);  // n must equal the constructed size
   const OptimizerSpec& spec() const { return spec_; }
   void reset();
+  // The state a later run needs to continue exactly here (empty vectors where the optimizer keeps none).
+  const std::vector<float>& m() const { return m_; }
+  const std::vector<float>& v() const { return v_; }
+  float b1t() const { return b1t_; }
+  float b2t() const { return b2t_; }
+  // m / v: n floats each, or null to leave the moment as it is; ignored where the optimizer keeps none.
+  void load_state(const float* m, const float* v, float b1t, float b2t);
 
  private:
   OptimizerSpec spec_;
@@ -133,6 +140,12 @@ class RoundTrainer {
   Dataset& dataset() { return data_; }
   Sequential& model() { return model_; }
   void set_epochs_done(size_t e) { epoch_ = e; }
+  // A resumed run continues the shuffle sequence of the saved one. Every epoch permutes the order the previous epoch
+  // left, so the permutations of the epochs already done are replayed on the fresh partition first.
+  void set_epoch_base(size_t e) {
+    for (size_t k = 0; k < e; ++k) data_.shuffle(seed_, k);
+    epoch_base_ = e;
+  }
   // Mean loss and accuracy (arg-max match) of `params` over a dataset; used for evaluation.
   std::pair<double, double> evaluate(const float* params, const Dataset& d, size_t batch = 256);
 
@@ -141,7 +154,7 @@ class RoundTrainer {
   Dataset data_;
   Loss loss_ = Loss::Mse;
   OptimizerSpec opt_;
-  size_t batch_size_ = 1, max_epochs_ = 1, offline_epochs_ = 0, epoch_ = 0;
+  size_t batch_size_ = 1, max_epochs_ = 1, offline_epochs_ = 0, epoch_ = 0, epoch_base_ = 0;
   uint64_t seed_ = 0;
   std::vector<float> grad_, delta_;
 };

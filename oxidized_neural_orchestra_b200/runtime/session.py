@@ -37,11 +37,29 @@ class CpuHandle:
         ser = training_cfg.get("serializer", "base")
         sparse = isinstance(ser, dict)
         self.n_workers = len(plan["workers"])
+        # Resume (additive to the reference, which exports weights only): the weights come through the plan
+        # (`b200.init_from` becomes inline parameter generators), the optimizer state and the position in the shuffle
+        # sequence from the sidecar a previous run wrote (`b200.state_path`, CPU or GPU ranks: same file).
+        state, start_epoch = None, int(b.get("start_epoch", -1))
+        self._state_path = b.get("state_path") or None
+        self._n_params = int(plan.get("n_params") or sum(l["n_params"] for l in plan["layers"]))
+        self._opt_kind = next(iter(training_cfg["optimizer"])) if isinstance(training_cfg.get("optimizer"), dict) else "?"
+        if b.get("init_state_from"):
+            from ..utils.state import load_state
+
+            state = load_state(b["init_state_from"], self._n_params)
+            if start_epoch < 0:
+                start_epoch = int(state["meta"].get("epochs", 0))
         self._cluster = core.LocalCluster(json.dumps(plan), xs, ys, x_size, y_size,
                                           wire="f16" if b.get("wire_dtype") == "f16" else "f32",
                                           sparse=sparse, sparse_r=ser["sparse_capable"]["r"] if sparse else 0.0,
                                           leaky_relu_exact=b.get("leaky_relu_exact", True),
-                                          switch_resets_progress=b.get("switch_resets_progress", False))
+                                          switch_resets_progress=b.get("switch_resets_progress", False),
+                                          init_m=None if state is None else np.ascontiguousarray(state["m"], dtype=np.float32),
+                                          init_v=None if state is None else np.ascontiguousarray(state["v"], dtype=np.float32),
+                                          init_b1t=1.0 if state is None else float(state["adam_pows"][0]),
+                                          init_b2t=1.0 if state is None else float(state["adam_pows"][1]),
+                                          start_epoch=max(0, start_epoch))
         self._cluster.start()
         self._done = False
 
@@ -59,6 +77,12 @@ class CpuHandle:
 
     def result(self):
         self._cluster.join()
+        if self._state_path:
+            from ..utils.state import save_state
+
+            st = self._cluster.final_state()
+            save_state(self._state_path, st["m"], st["v"], np.asarray(st["adam_pows"], dtype=np.float32),
+                       optimizer=self._opt_kind, epochs=int(st["epochs"]), n_params=self._n_params)
         return self._cluster.final_params(), {"switched": self._cluster.switched()}
 
 

@@ -219,3 +219,40 @@ def test_warm_start_from_a_saved_checkpoint(tmp_path):
         bad = Sequential([Dense(7, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
         orchestrate(bad, orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), GradientDescent(0.1), CrossEntropy(), 1, 5,
                                               b200={"init_from": str(ckpt)}))
+
+
+@pytest.mark.parametrize("strategy", ["all_reduce", "parameter_server"])
+@pytest.mark.parametrize("opt_name", ["momentum", "adam"])
+def test_cpu_ranks_resume_with_optimizer_state(tmp_path, strategy, opt_name):
+    """Weights + optimizer state + shuffle position on CPU ranks: 3 + 3 epochs give what 6 epochs give, and without the
+    state they do not. The sidecar is the file GPU ranks write and read (utils/state.py)."""
+    from oxidized_neural_orchestra_b200.utils.state import load_state
+
+    xs, ys = _data(n=48, x=6, y=3, seed=5)
+    model = _model()
+    opt = (lambda: GradientDescentWithMomentum(0.2, 0.9)) if opt_name == "momentum" else (lambda: Adam(0.01))
+    addrs = ["cpu:0", "cpu:1"]
+
+    def run(epochs, **b200):
+        ds = InlineDataset(xs, ys, 6, 3)
+        if strategy == "all_reduce":
+            tr = orchestra.all_reduce(addrs, ds, opt(), CrossEntropy(), epochs, 8, seed=4, b200=b200 or None)
+        else:
+            tr = orchestra.parameter_server(addrs, 2, ds, opt(), CrossEntropy(), BarrierSync(), BlockingStore(), epochs, 8, seed=4,
+                                            b200={"colocate": True, **b200})
+        return orchestrate(model, tr).wait(quiet=True)
+
+    whole = run(6)
+    ckpt, state = tmp_path / "m.safetensors", tmp_path / "m.state.safetensors"
+    half = run(3, state_path=str(state))
+    half.save_safetensors(ckpt)
+    st = load_state(str(state), len(half.weights_array()))
+    assert st["meta"]["epochs"] == "3" and np.abs(st["m"]).max() > 0
+    assert (st["v"].max() > 0) == (opt_name == "adam")
+    resumed = run(3, init_from=str(ckpt), init_state_from=str(state))
+    cold = run(3, init_from=str(ckpt), start_epoch=3)
+    err_resumed = np.abs(resumed.weights_array() - whole.weights_array()).max()
+    err_cold = np.abs(cold.weights_array() - whole.weights_array()).max()
+    assert err_resumed < 1e-6, err_resumed
+    assert err_cold > 20 * max(err_resumed, 1e-7), (err_cold, err_resumed)
+    assert np.allclose(resumed.loss_history(), whole.loss_history()[3:], rtol=1e-5, atol=1e-7)
