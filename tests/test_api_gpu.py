@@ -211,6 +211,40 @@ def test_resume_with_optimizer_state_continues_the_uninterrupted_run(tmp_path):
     assert np.allclose(resumed.loss_history(), whole.loss_history()[3:], rtol=1e-4, atol=1e-6)
 
 
+def test_state_sidecar_moves_between_gpu_and_cpu_ranks(tmp_path):
+    """The optimizer-state file is the same for both kinds of rank: three epochs on a GPU rank, then three more on a CPU rank
+    from its weights + state land where six epochs on the GPU rank land (up to tf32 tiles against f32 loops), and clearly
+    closer than a continuation that drops the state."""
+    from orchestra.optimizers import GradientDescentWithMomentum
+
+    xs, ys = _data(n=128, x=32, y=12)
+    model = Sequential([Dense(24, XavierUniform(), ReLU(0.0)), Dense(12, XavierUniform(), Softmax())])
+
+    def run(addr, epochs, **b200):
+        if addr.startswith("gpu"):
+            b200 = {"sync_every": "step", **b200}
+        tr = orchestra.all_reduce([addr], InlineDataset(xs, ys, 32, 12), GradientDescentWithMomentum(0.5, 0.9), CrossEntropy(), epochs, 128, seed=4, b200=b200 or None)
+        return orchestrate(model, tr).wait(quiet=True)
+
+    # one batch per epoch (batch = the whole set): the step and the round cadence coincide and the batch order cannot differ
+    whole = run("gpu:0", 6)
+    ckpt, state = tmp_path / "m.safetensors", tmp_path / "m.state.safetensors"
+    half = run("gpu:0", 3, state_path=str(state))
+    half.save_safetensors(ckpt)
+    resumed = run("cpu:0", 3, init_from=str(ckpt), init_state_from=str(state))
+    cold = run("cpu:0", 3, init_from=str(ckpt), start_epoch=3)
+    err_resumed = np.abs(resumed.weights_array() - whole.weights_array()).max()
+    err_cold = np.abs(cold.weights_array() - whole.weights_array()).max()
+    assert err_resumed < 2e-3, err_resumed
+    assert err_cold > 5 * err_resumed, (err_cold, err_resumed)
+    # and back: the CPU rank's state continues on the GPU rank
+    state2, ckpt2 = tmp_path / "c.state.safetensors", tmp_path / "c.safetensors"
+    chalf = run("cpu:0", 3, state_path=str(state2))
+    chalf.save_safetensors(ckpt2)
+    back = run("gpu:0", 3, init_from=str(ckpt2), init_state_from=str(state2))
+    assert np.abs(back.weights_array() - whole.weights_array()).max() < 2e-3
+
+
 def test_periodic_checkpoints_load_back_and_continue_the_run(tmp_path):
     from orchestra.optimizers import Adam
 
