@@ -106,7 +106,58 @@ PUBLISHED = {
 }
 
 
+class NodeProcesses:
+    """`n` native node processes (`bin/ono-node`, one CPU rank each) listening on loopback ports: the deployment the
+    reference's numbers come from (one node per container on one host, its README "benchmarks"), minus the containers."""
+
+    def __init__(self, n: int):
+        import socket
+        import subprocess
+
+        exe = os.path.join(ROOT, "bin", "ono-node")
+        if not os.path.exists(exe):
+            raise SystemExit("bin/ono-node is missing: python -m oxidized_neural_orchestra_b200.build")
+        self.procs, self.addrs = [], []
+        env = dict(os.environ, ONO_LOG="warn", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        for _ in range(n):
+            with socket.socket() as sk:
+                sk.bind(("127.0.0.1", 0))
+                port = sk.getsockname()[1]
+            self.procs.append(subprocess.Popen([exe, "--port", str(port), "--device", "cpu"], env=env))
+            self.addrs.append(f"127.0.0.1:{port}")
+        deadline = time.time() + 60
+        for a in self.addrs:
+            host, port = a.rsplit(":", 1)
+            while True:
+                try:
+                    socket.create_connection((host, int(port)), timeout=0.5).close()
+                    break
+                except OSError:
+                    if time.time() > deadline:
+                        self.close()
+                        raise SystemExit(f"node {a} did not start listening")
+                    time.sleep(0.05)
+
+    def close(self):
+        for p in self.procs:
+            p.kill()
+        for p in self.procs:
+            p.wait(timeout=30)
+
+
 def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, epochs, batch):
+    if prefix == "tcp":
+        extra = dict(extra)
+        n = workers + (servers if extra.get("pure_servers") else 0)
+        nodes = NodeProcesses(n)
+        try:
+            return run_one(model_name, label, strategy, workers, servers, dict(extra, _addrs=nodes.addrs), "node", data, epochs, batch)
+        finally:
+            nodes.close()
+    return _run_one(model_name, label, strategy, workers, servers, extra, prefix, data, epochs, batch)
+
+
+def _run_one(model_name, label, strategy, workers, servers, extra, prefix, data, epochs, batch):
     import orchestra
     from mnist_models import lenet5, nielsen
     from orchestra import orchestrate
@@ -121,7 +172,7 @@ def run_one(model_name, label, strategy, workers, servers, extra, prefix, data, 
     pure = extra.pop("pure_servers", False)
     batch = extra.pop("batch", batch)
     lr = extra.pop("lr", 0.5)
-    addrs = [f"{prefix}:{i}" for i in range(workers + (servers if pure else 0))]
+    addrs = extra.pop("_addrs", None) or [f"{prefix}:{i}" for i in range(workers + (servers if pure else 0))]
     ds = InlineDataset(xtr, ytr, 784, 10)
     common = dict(max_epochs=epochs, batch_size=batch, seed=42, **extra)
     b200 = {"colocate": True} if (prefix == "gpu" and not pure) else None
@@ -160,7 +211,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--suite", default="strategies")
     ap.add_argument("--model", default="both", choices=("lenet5", "nielsen", "both"))
-    ap.add_argument("--nodes", default=None, choices=("gpu", "cpu"))
+    ap.add_argument("--nodes", default=None, choices=("gpu", "cpu", "tcp"),
+                    help="gpu: one rank per local GPU; cpu: in-process rank threads; tcp: one native ono-node process per node on "
+                         "loopback ports (the reference's deployment without the containers)")
     ap.add_argument("--rows", type=int, default=4096)
     ap.add_argument("--epochs", type=int, default=4)
     ap.add_argument("--batch", type=int, default=64)

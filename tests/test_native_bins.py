@@ -5,6 +5,7 @@ import os
 import shutil
 import socket
 import subprocess
+import sys
 import time
 
 import numpy as np
@@ -227,3 +228,20 @@ def test_several_cpu_ranks_run_natively_over_a_tcp_mesh_between_the_nodes(bins, 
         assert got["stop_reason"] == "max_epochs"
         assert np.allclose(got["loss_history"], ref.loss_history(), rtol=1e-5)
         assert got.get("metrics", {}).get("data_plane") == "native tcp mesh"
+
+
+def test_published_rows_run_on_native_node_processes(bins, tmp_path):
+    """`bench/suites.py --nodes tcp`: one ono-node process per node on loopback ports, the orchestrator's session over
+    them, a throughput table against the reference's published figures."""
+    out = tmp_path / "pub"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench", "suites.py"), "--suite", "published", "--nodes", "tcp", "--model", "lenet5",
+                        "--rows", "192", "--epochs", "2", "--only", "AR 3w offline 0 b64,PS blocking 3w+2s", "--out", str(out)],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    table = (out / "published_tcp.md").read_text()
+    rows = [l for l in table.splitlines() if l.startswith("| lenet5 |")]
+    assert len(rows) == 2 and "| 9675 |" in rows[0] and "| 9970 |" in rows[1]
+    recs = [json.loads(l) for l in (out / "history.jsonl").read_text().splitlines()]
+    assert all(rec["epochs"] == 2 and rec["samples_per_sec"] > 0 and np.isfinite(rec["final_loss"]) for rec in recs)
+    assert [rec["nodes"] for rec in recs] == [3, 5]
+
