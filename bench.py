@@ -284,7 +284,7 @@ def main() -> None:
             # before the promoted ranks became servers, parameter server after (steps next to the switch itself left out)
             sm, at = m.get("step_ms") or [], m.get("switched_at_step")
             out["switch"] = {"metric": SWITCH["metric"], "window": SWITCH["window"], "threshold": SWITCH["threshold"],
-                             "switched_at_step": at}
+                             "switched_at_step": at, "declined": bool(m.get("switch_declined", False))}
             if at and len(sm) > at + 6 and at > 8:
                 pre, post = sm[5:at - 2], sm[at + 3:]
                 workers_after = world - min(int(cfg["strategy"][2:] or 2), world)

@@ -225,6 +225,12 @@ def do_switch(r) -> None:
     """All-reduce -> parameter server in place: the promoted ranks adopt the ranges they will own
     (every replica already holds the full vector), optimizer state restarts, and their data is
     re-scattered to the remaining workers (node/src/router.rs:305-341, worker/src/builder.rs:165-200)."""
+    if not any(a["action"] == "switch" for a in r.plan["switch"]["post_actions"]):
+        # every rank would be promoted and nobody would be left to train (as many servers as nodes): the run stays in
+        # all-reduce; the same decision on every rank, since all of them read it from the plan
+        r.switch_declined = True        # reported in the run's metrics; the test is not repeated
+        r.grad_norm_switch = False
+        return
     if r.pull_staged:           # the last step's parameters have not been published yet: do it before ownership changes
         with torch.cuda.stream(r.stream):
             r.pull_publish(r.stream)

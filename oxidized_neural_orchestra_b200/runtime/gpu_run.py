@@ -269,7 +269,7 @@ def run(r) -> dict:
             _checkpoint(r, r.first_epoch + epoch)
         if decision == 1:
             break
-        if decision == 2 and r.algorithm == "strategy_switch" and not r.switched:
+        if decision == 2 and r.algorithm == "strategy_switch" and not r.switched and not getattr(r, "switch_declined", False):
             with tracer.span("strategy_switch", epoch=epoch):
                 L.do_switch(r)
             pending = [False, False]
@@ -300,7 +300,8 @@ def run(r) -> dict:
         "step_ms": ms, "steps": len(evs), "step_wall": r.step_wall, "launches_per_step": r.launches_per_step,
         "h2d_bytes_per_step": r.feeder.h2d_bytes_per_step if r.feeder is not None else 0,
         "d2h_bytes_per_step": 8 if r.feeder is not None else 0, "switched": r.switched,
-        "switched_at_step": getattr(r, "switched_at_step", None), "sync_mode": r.sync_mode,
+        "switched_at_step": getattr(r, "switched_at_step", None), "switch_declined": bool(getattr(r, "switch_declined", False)),
+        "sync_mode": r.sync_mode,
         "nvls": bool(r.use_nvls and r.win.mc_ptr),
         # what travels between GPUs: the 16-bit wire applies to the fused kernels of step cadence
         "wire": (r.wire16 if (r.wire16 is not None and r.sync_mode in ("fused", "oneshot")) else "f32") if r.world > 1 else "none",
