@@ -174,11 +174,14 @@ def _run_one(model_name, label, strategy, workers, servers, extra, prefix, data,
     lr = extra.pop("lr", 0.5)
     addrs = extra.pop("_addrs", None) or [f"{prefix}:{i}" for i in range(workers + (servers if pure else 0))]
     ds = InlineDataset(xtr, ytr, 784, 10)
+    wire = extra.pop("wire", None)
     common = dict(max_epochs=epochs, batch_size=batch, seed=42, **extra)
     b200 = {"colocate": True} if (prefix == "gpu" and not pure) else None
+    if wire:        # the reference always ships gradients as f16 (comms/src/handles/compressor.rs:104-118)
+        b200 = dict(b200 or {}, wire_dtype=wire)
     opt, loss = GradientDescent(lr), CrossEntropy()   # the loss is normalised by batch x classes (cross_entropy.rs:35-47)
     if strategy == "ar":
-        cfg = orchestra.all_reduce(addrs, ds, opt, loss, **common)
+        cfg = orchestra.all_reduce(addrs, ds, opt, loss, **(dict(common, b200=b200) if b200 else common))
     else:
         sync = NonBlockingSync() if strategy == "ps_async" else BarrierSync()
         fn = orchestra.strategy_switch if strategy == "ss" else orchestra.parameter_server
@@ -218,6 +221,7 @@ def main():
     ap.add_argument("--epochs", type=int, default=4)
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--repeats", type=int, default=1)
+    ap.add_argument("--wire", default=None, choices=("f16", "bf16", "f32"), help="gradient wire (b200.wire_dtype); the reference's is f16")
     ap.add_argument("--only", default="", help="comma-separated substrings: run only the suite rows whose label contains one of them")
     ap.add_argument("--out", default=os.path.join(ROOT, "bench", "results"))
     a = ap.parse_args()
@@ -238,6 +242,8 @@ def main():
                 for rep in range(a.repeats):
                     if a.suite == "published":      # the models' recipes: benchmarks/issue/suites.py:148-178
                         extra = dict(extra, lr=0.05 if model_name == "lenet5" else 0.1)
+                    if a.wire:
+                        extra = dict(extra, wire=a.wire)
                     rec = run_one(model_name, label, strategy, workers, servers, extra, prefix, data, a.epochs, a.batch)
                     if rec is None:
                         continue
