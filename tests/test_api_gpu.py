@@ -245,6 +245,25 @@ def test_state_sidecar_moves_between_gpu_and_cpu_ranks(tmp_path):
     assert np.abs(back.weights_array() - whole.weights_array()).max() < 2e-3
 
 
+def test_switch_that_would_leave_no_worker_is_declined():
+    """A strategy switch on one GPU would promote the only rank to a server and leave nobody to train (the reference's
+    planner needs more workers than servers): the run says so in its metrics and keeps training in all-reduce."""
+    from orchestra.optimizers import Adam
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync
+
+    xs, ys = _data(n=96, x=32, y=12)
+    model = Sequential([Dense(24, XavierUniform(), ReLU(0.0)), Dense(12, XavierUniform(), Softmax())])
+    tr = orchestra.strategy_switch(["gpu:0"], 1, InlineDataset(xs, ys, 32, 12), Adam(0.01), CrossEntropy(), BarrierSync(), BlockingStore(),
+                                   6, 32, seed=4, b200={"sync_every": "step", "switch_metric": "grad_norm", "switch_window": 2,
+                                                        "switch_threshold": 10.0, "switch_check_every": 2})
+    m = orchestrate(model, tr).wait(quiet=True)
+    met = m.metrics()
+    assert met["switch_declined"] is True and not met["switched"] and met["switched_at_step"] is None
+    hist = m.loss_history()
+    assert len(hist) == 6 and hist[-1] < hist[0]
+
+
 def test_periodic_checkpoints_load_back_and_continue_the_run(tmp_path):
     from orchestra.optimizers import Adam
 
