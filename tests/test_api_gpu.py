@@ -255,7 +255,7 @@ def test_switch_that_would_leave_no_worker_is_declined():
     xs, ys = _data(n=96, x=32, y=12)
     model = Sequential([Dense(24, XavierUniform(), ReLU(0.0)), Dense(12, XavierUniform(), Softmax())])
     tr = orchestra.strategy_switch(["gpu:0"], 1, InlineDataset(xs, ys, 32, 12), Adam(0.01), CrossEntropy(), BarrierSync(), BlockingStore(),
-                                   6, 32, seed=4, b200={"sync_every": "step", "switch_metric": "grad_norm", "switch_window": 2,
+                                   6, 32, seed=4, b200={"sync_every": "step", "colocate": True, "switch_metric": "grad_norm", "switch_window": 2,
                                                         "switch_threshold": 10.0, "switch_check_every": 2})
     m = orchestrate(model, tr).wait(quiet=True)
     met = m.metrics()
