@@ -40,6 +40,15 @@ void BlockingStore::pull_params(float* out) {
   std::copy(params_.begin(), params_.end(), out);
 }
 
+void BlockingStore::snapshot(std::vector<float>& params, std::vector<float>& m, std::vector<float>& v, float& b1t, float& b2t) {
+  std::lock_guard<std::mutex> lk(mu_);
+  params = params_;
+  m = opt_.m();
+  v = opt_.v();
+  b1t = opt_.b1t();
+  b2t = opt_.b2t();
+}
+
 WildStore::WildStore(std::vector<float> params, const OptimizerSpec& opt) : params_(std::move(params)), opt_(opt, params_.size()) {}
 
 void WildStore::accumulate(const float* grad, size_t n) {
@@ -51,6 +60,15 @@ void WildStore::accumulate(const float* grad, size_t n) {
 void WildStore::pull_params(float* out) {
   std::lock_guard<std::mutex> lk(mu_);
   std::copy(params_.begin(), params_.end(), out);
+}
+
+void WildStore::snapshot(std::vector<float>& params, std::vector<float>& m, std::vector<float>& v, float& b1t, float& b2t) {
+  std::lock_guard<std::mutex> lk(mu_);
+  params = params_;
+  m = opt_.m();
+  v = opt_.v();
+  b1t = opt_.b1t();
+  b2t = opt_.b2t();
 }
 
 // ---- synchronizers ----------------------------------------------------------------------------
@@ -73,6 +91,7 @@ void NonBlockingSync::step(Store& store, const float* grad, size_t n, float* par
 // ---- cluster plumbing -------------------------------------------------------------------------
 LocalCluster::LocalCluster(Json plan, Dataset data, ClusterOptions opts)
     : plan_(std::move(plan)), data_(std::move(data)), opts_(std::move(opts)) {
+  ckpt_mark_ = opts_.checkpoint_every ? opts_.start_epoch / opts_.checkpoint_every : 0;
   n_params_ = (size_t)plan_.at("n_params").as_u64();
   nworkers_ = plan_.at("workers").size();
   if (const Json* s = plan_.find("seed"); s && !s->is_null()) seed_ = s->as_u64();
@@ -296,6 +315,51 @@ void LocalCluster::note_epochs(size_t done) {
   final_state_.epochs = std::max(final_state_.epochs, opts_.start_epoch + done);
 }
 
+void LocalCluster::maybe_checkpoint(size_t epochs_done, const std::vector<float>* replica, const Optimizer* replica_opt) {
+  const size_t every = opts_.checkpoint_every;
+  if (every == 0) return;
+  const size_t at = opts_.start_epoch + epochs_done, mark = at / every;
+  if (mark <= ckpt_mark_) return;
+  ckpt_mark_ = mark;
+  Checkpoint c;
+  c.state.epochs = at;
+  if (replica) {                 // all-reduce: every replica holds the whole model and its own (identical) optimizer
+    c.params = *replica;
+    c.state.m = replica_opt->m().empty() ? std::vector<float>(n_params_, 0.f) : replica_opt->m();
+    c.state.v = replica_opt->v().empty() ? std::vector<float>(n_params_, 0.f) : replica_opt->v();
+    c.state.b1t = replica_opt->b1t();
+    c.state.b2t = replica_opt->b2t();
+  } else {                       // parameter server: the shards are authoritative
+    c.params.assign(n_params_, 0.f);
+    c.state.m.assign(n_params_, 0.f);
+    c.state.v.assign(n_params_, 0.f);
+    std::vector<float> p, m, v;
+    for (auto& s : servers_) {
+      s.store->snapshot(p, m, v, c.state.b1t, c.state.b2t);
+      scatter_ranges(p, s.ranges, c.params);
+      if (!m.empty()) scatter_ranges(m, s.ranges, c.state.m);
+      if (!v.empty()) scatter_ranges(v, s.ranges, c.state.v);
+    }
+  }
+  {
+    std::lock_guard<std::mutex> lk(ckpt_mu_);
+    ckpts_.push_back(std::move(c));
+  }
+  ClusterEvent ev;
+  ev.kind = "checkpoint";
+  ev.text = std::to_string(at);
+  emit(std::move(ev));
+}
+
+bool LocalCluster::pop_checkpoint(std::vector<float>& params, ClusterState& state) {
+  std::lock_guard<std::mutex> lk(ckpt_mu_);
+  if (ckpts_.empty()) return false;
+  params = std::move(ckpts_.front().params);
+  state = std::move(ckpts_.front().state);
+  ckpts_.pop_front();
+  return true;
+}
+
 void LocalCluster::gather_final_from_servers() {
   final_params_.assign(n_params_, 0.f);
   final_state_.m.assign(n_params_, 0.f);
@@ -346,6 +410,7 @@ void LocalCluster::all_reduce_worker(size_t w) {
     ring_all_reduce(w, residual, grad);
     opt.step(params.data(), grad.data(), n_params_);  // all_reduce.rs:126
     scratch = params;                                   // all_reduce.rs:131-132
+    if (w == 0) maybe_checkpoint(trainer.epochs_done(), &params, &opt);
     if (res.is_last) break;
   }
   note_epochs(trainer.epochs_done());
@@ -375,6 +440,9 @@ void LocalCluster::ps_worker(size_t w, RoundTrainer& trainer, std::vector<float>
       ++si;
     }
     report_losses(w, res.losses);
+    // (with the barrier synchroniser every server has taken this round's update from every worker by now and cannot
+    // take the next before this worker pushes again: the copy is one consistent round)
+    if (w == ps_leader_) maybe_checkpoint(trainer.epochs_done(), nullptr, nullptr);
     if (res.is_last) break;
   }
   for (auto& s : servers_) s.sync->leave(*s.store);
@@ -485,6 +553,7 @@ void LocalCluster::run_all() {
         bool work_left = false;
         for (auto& t : trainers) work_left = work_left || t->epochs_done() < t->max_epochs();
         if (work_left && !stop_.load()) {
+          ps_leader_ = remaining.front();
           for (size_t k = 0; k < remaining.size(); ++k)
             threads_.emplace_back([this, k, &remaining, &trainers, &params] {
               try { ps_worker(remaining[k], *trainers[k], params[k]); }

@@ -33,6 +33,8 @@ class Store {
   virtual void update_params() = 0;
   virtual void pull_params(float* out) = 0;
   virtual Optimizer& optimizer() = 0;
+  // Parameters and optimizer state of the shard as one consistent copy (taken under the store's lock).
+  virtual void snapshot(std::vector<float>& params, std::vector<float>& m, std::vector<float>& v, float& b1t, float& b2t) = 0;
 };
 
 // Two gradient accumulators flipped by the single updater; update = mean over workers, optimizer,
@@ -45,6 +47,7 @@ class BlockingStore final : public Store {
   void update_params() override;
   void pull_params(float* out) override;
   Optimizer& optimizer() override { return opt_; }
+  void snapshot(std::vector<float>& params, std::vector<float>& m, std::vector<float>& v, float& b1t, float& b2t) override;
 
  private:
   std::vector<float> params_, acc_[2];
@@ -65,6 +68,7 @@ class WildStore final : public Store {
   void update_params() override {}
   void pull_params(float* out) override;
   Optimizer& optimizer() override { return opt_; }
+  void snapshot(std::vector<float>& params, std::vector<float>& m, std::vector<float>& v, float& b1t, float& b2t) override;
 
  private:
   std::vector<float> params_;
@@ -115,6 +119,10 @@ struct ClusterOptions {
   std::vector<float> init_m, init_v;
   float init_b1t = 1.f, init_b2t = 1.f;
   size_t start_epoch = 0;
+  // Every `checkpoint_every` epochs (counted from the saved run's first epoch) the leading worker takes a copy of the
+  // parameters and the optimizer state and announces it with a "checkpoint" event; the host fetches it with
+  // pop_checkpoint() and writes the files. 0 = never.
+  size_t checkpoint_every = 0;
 };
 
 struct ClusterState {              // optimizer state at the end of a run, global parameter order
@@ -136,6 +144,8 @@ class LocalCluster {
   bool finished() const { return finished_.load(); }
   const std::vector<float>& final_params() const { return final_params_; }
   const ClusterState& final_state() const { return final_state_; }
+  // The oldest checkpoint not fetched yet (see ClusterOptions::checkpoint_every); false if there is none.
+  bool pop_checkpoint(std::vector<float>& params, ClusterState& state);
   const std::string& stop_reason() const { return stop_reason_; }
   bool switched() const { return switched_.load(); }
 
@@ -154,6 +164,8 @@ class LocalCluster {
   void build_servers(const Json& server_list, const std::vector<std::vector<float>>* inline_params);
   void gather_final_from_servers();
   void note_epochs(size_t done);
+  // Called by the leading worker between rounds, when no update is in flight on its side.
+  void maybe_checkpoint(size_t epochs_done, const std::vector<float>* replica, const Optimizer* replica_opt);
 
   Json plan_;
   Dataset data_;
@@ -171,6 +183,10 @@ class LocalCluster {
   std::string stop_reason_ = "max_epochs";
   std::vector<float> final_params_;
   ClusterState final_state_;
+  struct Checkpoint { std::vector<float> params; ClusterState state; };
+  std::mutex ckpt_mu_;
+  std::deque<Checkpoint> ckpts_;
+  size_t ckpt_mark_ = 0, ps_leader_ = 0;
   std::vector<Server> servers_;
   // all-reduce shared state
   std::vector<std::vector<float>*> ring_bufs_;          // each worker's residual (scatter) buffer

@@ -104,7 +104,7 @@ struct PyCluster {
   std::unique_ptr<oracle::LocalCluster> c;
   PyCluster(const std::string& plan_json, const farray& xs, const farray& ys, size_t x_size, size_t y_size,
             const std::string& wire, bool sparse, double r, bool exact, bool resets, py::object init_m, py::object init_v,
-            float init_b1t, float init_b2t, size_t start_epoch) {
+            float init_b1t, float init_b2t, size_t start_epoch, size_t checkpoint_every) {
     oracle::ClusterOptions o;
     o.wire = wire;
     o.sparse = sparse;
@@ -116,6 +116,7 @@ struct PyCluster {
     o.init_b1t = init_b1t;
     o.init_b2t = init_b2t;
     o.start_epoch = start_epoch;
+    o.checkpoint_every = checkpoint_every;
     c = std::make_unique<oracle::LocalCluster>(Json::parse(plan_json), make_dataset(xs, ys, x_size, y_size), o);
   }
   py::object next_event(int timeout_ms) {
@@ -180,12 +181,12 @@ PYBIND11_MODULE(_orchestra, m) {
       .def_property_readonly("epochs_done", [](PyRoundTrainer& t) { return t.t.epochs_done(); });
   py::class_<PyCluster>(m, "LocalCluster")
       .def(py::init<const std::string&, const farray&, const farray&, size_t, size_t, const std::string&, bool, double, bool, bool,
-                    py::object, py::object, float, float, size_t>(),
+                    py::object, py::object, float, float, size_t, size_t>(),
            py::arg("plan_json"), py::arg("samples"), py::arg("labels"), py::arg("x_size"), py::arg("y_size"),
            py::arg("wire") = "f32", py::arg("sparse") = false, py::arg("sparse_r") = 0.0,
            py::arg("leaky_relu_exact") = true, py::arg("switch_resets_progress") = false,
            py::arg("init_m") = py::none(), py::arg("init_v") = py::none(), py::arg("init_b1t") = 1.0f, py::arg("init_b2t") = 1.0f,
-           py::arg("start_epoch") = 0)
+           py::arg("start_epoch") = 0, py::arg("checkpoint_every") = 0)
       .def("start", [](PyCluster& c) { c.c->start(); })
       .def("request_stop", [](PyCluster& c) { c.c->request_stop(); })
       .def("next_event", &PyCluster::next_event, py::arg("timeout_ms") = 100)
@@ -194,6 +195,18 @@ PYBIND11_MODULE(_orchestra, m) {
       .def("switched", [](PyCluster& c) { return c.c->switched(); })
       .def("stop_reason", [](PyCluster& c) { return c.c->stop_reason(); })
       .def("final_params", [](PyCluster& c) { return to_np(c.c->final_params()); })
+      .def("pop_checkpoint", [](PyCluster& c) -> py::object {
+        std::vector<float> params;
+        oracle::ClusterState st;
+        if (!c.c->pop_checkpoint(params, st)) return py::none();
+        py::dict d;
+        d["params"] = to_np(params);
+        d["m"] = to_np(st.m);
+        d["v"] = to_np(st.v);
+        d["adam_pows"] = py::make_tuple(st.b1t, st.b2t);
+        d["epochs"] = st.epochs;
+        return d;
+      })
       .def("final_state", [](PyCluster& c) {
         const auto& st = c.c->final_state();
         py::dict d;

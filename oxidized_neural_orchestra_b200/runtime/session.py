@@ -59,7 +59,9 @@ class CpuHandle:
                                           init_v=None if state is None else np.ascontiguousarray(state["v"], dtype=np.float32),
                                           init_b1t=1.0 if state is None else float(state["adam_pows"][0]),
                                           init_b2t=1.0 if state is None else float(state["adam_pows"][1]),
-                                          start_epoch=max(0, start_epoch))
+                                          start_epoch=max(0, start_epoch),
+                                          checkpoint_every=int(b.get("checkpoint_every", 0) or 0) if b.get("checkpoint_path") else 0)
+        self._plan, self._ckpt_pattern = plan, b.get("checkpoint_path") or None
         self._cluster.start()
         self._done = False
 
@@ -71,9 +73,27 @@ class CpuHandle:
             ev = self._cluster.next_event(200)
             if ev is None:
                 continue
+            if ev["kind"] == "checkpoint":       # the leading worker took a copy of the model and its optimizer state
+                self._write_checkpoints()
+                continue
             if ev["kind"] == "complete":
+                self._write_checkpoints()
                 self._done = True
             yield ev
+
+    def _write_checkpoints(self):
+        """Periodic checkpoints (`b200.checkpoint_path` / `checkpoint_every`): weights in the reference's layout plus the
+        optimizer-state sidecar, the files GPU ranks write; the sidecar is complete before the weights file appears."""
+        from ..utils.state import checkpoint_paths, layers_from_plan, save_state, save_tensors, weight_tensors
+
+        while self._ckpt_pattern:
+            c = self._cluster.pop_checkpoint()
+            if c is None:
+                break
+            path, side = checkpoint_paths(self._ckpt_pattern, int(c["epochs"]))
+            save_state(side, c["m"], c["v"], np.asarray(c["adam_pows"], dtype=np.float32), optimizer=self._opt_kind,
+                       epochs=int(c["epochs"]), n_params=self._n_params)
+            save_tensors(path, weight_tensors(layers_from_plan(self._plan), np.asarray(c["params"], dtype=np.float32)))
 
     def result(self):
         self._cluster.join()

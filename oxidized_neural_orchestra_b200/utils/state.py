@@ -51,6 +51,28 @@ def weight_tensors(engine_layers: list[dict], params: np.ndarray) -> list:
     return out
 
 
+def layers_from_plan(plan: dict) -> list[dict]:
+    """The layer descriptions ``weight_tensors`` needs, straight from a plan's LayerSpec documents."""
+    out = []
+    for l in plan["layers"]:
+        (kind, body), = l["spec"].items()
+        if kind == "dense":
+            out.append({"kind": "dense", "in": body["dim"][0], "out": body["dim"][1]})
+        elif kind == "conv":
+            out.append({"kind": "conv", "kernel_dim": body["kernel_dim"]})
+        else:
+            out.append({"kind": "pool"})
+    return out
+
+
+def checkpoint_paths(pattern: str, epochs_done: int) -> tuple[str, str]:
+    """Weights file and state sidecar of a periodic checkpoint: ``{epoch}`` in the pattern is replaced, else
+    ``.epoch<N>`` is appended; the sidecar sits beside the weights as ``<base>.state.safetensors``."""
+    path = pattern.replace("{epoch}", str(epochs_done)) if "{epoch}" in pattern else f"{pattern}.epoch{epochs_done}"
+    base = path[:-len(".safetensors")] if path.endswith(".safetensors") else path
+    return path, base + ".state.safetensors"
+
+
 def save_tensors(path: str, tensors: list, meta: dict | None = None, sort: bool = True) -> None:
     """Write (name, f32 array) pairs as a safetensors file (no metadata block unless ``meta`` is given). Entries are
     laid out in name order, like the core exporter (csrc/core/codec.cpp) and the reference's, so the files are equal

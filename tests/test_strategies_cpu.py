@@ -256,3 +256,32 @@ def test_cpu_ranks_resume_with_optimizer_state(tmp_path, strategy, opt_name):
     assert err_resumed < 1e-6, err_resumed
     assert err_cold > 20 * max(err_resumed, 1e-7), (err_cold, err_resumed)
     assert np.allclose(resumed.loss_history(), whole.loss_history()[3:], rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("strategy", ["all_reduce", "parameter_server"])
+def test_cpu_ranks_write_periodic_checkpoints_that_continue_the_run(tmp_path, strategy):
+    """`checkpoint_path` / `checkpoint_every` on CPU ranks: weights + state files every two epochs, and a run resumed
+    from the middle one ends where the uninterrupted run ends."""
+    xs, ys = _data(n=48, x=6, y=3, seed=5)
+    model = _model()
+    addrs = ["cpu:0", "cpu:1"]
+
+    def run(epochs, **b200):
+        ds = InlineDataset(xs, ys, 6, 3)
+        if strategy == "all_reduce":
+            tr = orchestra.all_reduce(addrs, ds, Adam(0.01), CrossEntropy(), epochs, 8, seed=4, b200=b200 or None)
+        else:
+            tr = orchestra.parameter_server(addrs, 2, ds, Adam(0.01), CrossEntropy(), BarrierSync(), BlockingStore(), epochs, 8, seed=4,
+                                            b200={"colocate": True, **b200})
+        return orchestrate(model, tr).wait(quiet=True)
+
+    pat = str(tmp_path / "ck_{epoch}.safetensors")
+    whole = run(6, checkpoint_path=pat, checkpoint_every=2)
+    files = sorted(p.name for p in tmp_path.iterdir())
+    assert files == ["ck_2.safetensors", "ck_2.state.safetensors", "ck_4.safetensors", "ck_4.state.safetensors",
+                     "ck_6.safetensors", "ck_6.state.safetensors"]
+    last = np.concatenate([np.asarray(t[2]).reshape(-1) for t in sorted(
+        core.load_safetensors(str(tmp_path / "ck_6.safetensors")), key=lambda t: (int(t[0].split("_")[1].split(".")[0]), t[0].endswith("bias")))])
+    assert np.allclose(last, whole.weights_array(), atol=1e-7)
+    resumed = run(2, init_from=str(tmp_path / "ck_4.safetensors"), init_state_from=str(tmp_path / "ck_4.state.safetensors"))
+    assert np.abs(resumed.weights_array() - whole.weights_array()).max() < 1e-6
