@@ -216,3 +216,41 @@ def test_vectorised_activations_stay_within_a_few_ulp_of_libm(kind):
     err = np.abs(y.reshape(-1).astype(np.float64) - exact)
     assert err.max() <= 4 * np.finfo(np.float32).eps, (err.max(), x[err.argmax()])
     assert y.reshape(-1)[n - 9] == (0.0 if kind == "tanh" else 0.5)
+
+
+def _gate(bits, fn):
+    xs = np.array([[(i >> (bits - 1 - b)) & 1 for b in range(bits)] for i in range(1 << bits)], dtype=np.float32)
+    ys = np.array([fn(r) for r in xs.astype(int)], dtype=np.float32)
+    return xs.reshape(-1), ys
+
+
+_SIG = {"sigmoid": {"amp": 1.0}}
+_SMALL_NETS = {
+    # test_sequential_dense.rs:21-69 (y = x + 1 with one 1 -> 1 dense layer, lr 0.1, 100 epochs, batch 4)
+    "linear": (np.array([0, 1, 2, 3], np.float32), np.array([1, 2, 3, 4], np.float32), 1, [(1, 1, None)], 0.1, 4, 100, 1e-3),
+    # :71-124 (AND of two inputs, 2 -> 1 sigmoid)
+    "and2": (*_gate(2, lambda r: float(r.all())), 2, [(2, 1, _SIG)], 1.0, 4, 6000, 0.01),
+    # :126-188 (AND of three inputs, 3 -> 2 -> 1 sigmoid)
+    "and3": (*_gate(3, lambda r: float(r.all())), 3, [(3, 2, _SIG), (2, 1, _SIG)], 1.0, 8, 8000, 0.01),
+    # :250-323 (parity of four inputs, 4 -> 8 -> 3 -> 1 sigmoid)
+    "xor4": (*_gate(4, lambda r: float(r.sum() % 2)), 4, [(4, 8, _SIG), (8, 3, _SIG), (3, 1, _SIG)], 1.0, 16, 20000, 0.02),
+}
+
+
+@pytest.mark.parametrize("name", sorted(_SMALL_NETS))
+def test_small_networks_of_the_reference_converge(name):
+    """The reference's dense convergence topologies (machine_learning/src/test/test_sequential_dense.rs), which there run
+    without an assertion: here the full-batch MSE must fall below a bound within the epoch budget."""
+    xs, ys, x_size, dims, lr, batch, epochs, bound = _SMALL_NETS[name]
+    layers = [_spec("dense", dim=[i, o], act_fn=a) for i, o, a in dims]
+    spec = _trainer_spec(layers, x_size, 1, "mse", {"gradient_descent": {"learning_rate": lr}}, batch, epochs)
+    tr = core.RoundTrainer(json.dumps(spec), xs, ys)
+    rng = np.random.default_rng(3)
+    p, r = (rng.standard_normal(tr.n_params) * 0.7).astype(np.float32), np.zeros(tr.n_params, np.float32)
+    loss = float("inf")
+    for _ in range(epochs):
+        p, r, losses, last = tr.train(p, r)
+        loss = losses[-1]
+        if loss < bound or last:
+            break
+    assert loss < bound, (name, loss)
