@@ -31,7 +31,9 @@ class NetRank {
   static bool supports(const Json& plan, const TrainingConfig& training) {
     const std::string algo = plan.at("algorithm").as_string();
     if (algo == "strategy_switch") return false;
-    if (training.serializer.sparse) return false;
+    // the sparse serializer: natively for the parameter server (one thresholded message per worker and server shard, as in
+    // comms/src/sparse); the ring all-reduce re-encodes at every hop and stays with the rank processes
+    if (training.serializer.sparse && algo != "parameter_server") return false;
     if (algo == "parameter_server")
       for (auto& s : plan.at("servers").items()) {
         const Json& sp = s.at("spec");
@@ -47,6 +49,8 @@ class NetRank {
         emit_(std::move(emit)), stop_(stop), addrs_(training.addrs) {
     n_ = (size_t)plan_.at("n_params").as_u64();
     f16_wire_ = training.b200.wire_dtype == "f16";
+    sparse_ = training.serializer.sparse;
+    sparse_r_ = training.serializer.r;
     exact_ = training.b200.leaky_relu_exact;
     timeout_ms_ = (int)std::min(3.6e6, training.b200.comm_timeout_s * 1000.0);
     for (auto& w : plan_.at("workers").items()) worker_ranks_.push_back((size_t)w.at("rank").as_u64());
@@ -70,10 +74,13 @@ class NetRank {
     own_.assign(world_, {});
     Json opt_spec;
     if (plan_.at("algorithm").as_string() == "parameter_server") {
+      server_index_.assign(world_, 0);
+      size_t si = 0;
       for (auto& s : plan_.at("servers").items()) {
         const size_t r = (size_t)s.at("rank").as_u64();
         for (auto& rg : s.at("ranges").items()) own_[r].push_back({(size_t)rg[0].as_u64(), (size_t)rg[1].as_u64()});
         opt_spec = s.at("spec").at("optimizer");
+        server_index_[r] = si++;
       }
     } else {
       const size_t base = n_ / world_, rem = n_ % world_;
@@ -114,7 +121,8 @@ class NetRank {
         losses = tr.losses;
         if (losses.size() > nep) losses.resize(nep);
       }
-      exchange();
+      if (sparse_) exchange_sparse();
+      else exchange();
       epoch += nep;
       const int decision = decide(losses, nep, reason);
       if (decision == 1) break;
@@ -244,7 +252,14 @@ class NetRank {
       for (float& v : sums[k]) v /= (float)nw;
       opts_[k].step(C_.data() + rg.first, sums[k].data(), sums[k].size());
     }
-    // publish the fresh ranges
+    publish();
+    std::fill(R_.begin(), R_.end(), 0.f);
+  }
+
+  // Every owner sends its fresh ranges to everybody; afterwards every rank holds the whole updated vector.
+  void publish() {
+    std::exception_ptr send_err;
+    std::vector<float> buf;
     std::thread sender2([&] {
       try {
         for (size_t q = 0; q < world_; ++q)
@@ -262,7 +277,78 @@ class NetRank {
     sender2.join();
     if (send_err) std::rethrow_exception(send_err);
     W_ = C_;
-    std::fill(R_.begin(), R_.end(), 0.f);
+  }
+
+  // The sparse serializer (comms/src/handles/compressor.rs:71-98, comms/src/sparse/protocol.rs): per worker and server one
+  // message over the server's whole shard (its ranges concatenated): the entries at or above a sampled-quantile
+  // threshold as (offset, run of f16) records, or the dense f16 encoding when that is not larger. What was sent leaves
+  // the worker's residual, the rest waits for a later round (worker/src/middlewares/server_cluster.rs:85-104).
+  void exchange_sparse() {
+    const bool me_worker = widx_ >= 0;
+    const size_t nw = worker_ranks_.size();
+    auto shard_len = [&](size_t q) { size_t n = 0; for (auto& rg : own_[q]) n += rg.second - rg.first; return n; };
+    std::map<size_t, Compressed> out;
+    std::vector<float> g;
+    if (me_worker)
+      for (size_t q = 0; q < world_; ++q) {
+        if (own_[q].empty()) continue;
+        g.clear();
+        for (auto& rg : own_[q]) g.insert(g.end(), R_.begin() + (long)rg.first, R_.begin() + (long)rg.second);
+        Compressed c = compress_gradient(g.data(), g.size(), true, sparse_r_, seed_ + 31 * (uint64_t)widx_ + server_index_[q]);
+        for (auto& rg : own_[q])
+          for (size_t i = rg.first; i < rg.second; ++i)
+            if (!c.sparse || std::fabs(R_[i]) >= c.threshold) R_[i] = 0.f;
+        out[q] = std::move(c);
+      }
+    auto decode = [&](bool sparse, const uint8_t* bytes, size_t len, size_t n, std::vector<float>& dst) {
+      if (sparse) {
+        dst.assign(n, 0.f);
+        sparse_lift(dst, bytes, len);
+        dst.resize(n, 0.f);
+      } else {
+        if (len != 2 * n) throw wire::WireError("a peer sent an f16 shard of the wrong length");
+        dst.resize(n);
+        for (size_t i = 0; i < n; ++i) dst[i] = f16_to_f32((uint16_t)(bytes[2 * i] | (bytes[2 * i + 1] << 8)));
+      }
+    };
+    std::exception_ptr send_err;
+    std::thread sender([&] {
+      try {
+        for (auto& kv : out) {
+          if (kv.first == rank_) continue;
+          wire::Channel::RawFrame f;
+          f.kind = kv.second.sparse ? 2 : 1;
+          f.body.assign(reinterpret_cast<const char*>(kv.second.bytes.data()), kv.second.bytes.size());
+          peers_.at(kv.first).send_raw(f);
+        }
+      } catch (...) { send_err = std::current_exception(); }
+    });
+    const size_t mine = shard_len(rank_);
+    std::vector<float> sum(mine, 0.f), buf;
+    if (mine) {
+      if (me_worker) {
+        const Compressed& c = out.at(rank_);
+        decode(c.sparse, c.bytes.data(), c.bytes.size(), mine, sum);
+      }
+      for (size_t q = 0; q < world_; ++q) {      // fixed order of additions: peers in rank order
+        if (q == rank_ || !is_worker(q)) continue;
+        wire::Message m = peers_.at(q).recv(timeout_ms_);
+        if (m.kind != 1 && m.kind != 2) throw wire::WireError("unexpected message during the gradient exchange");
+        decode(m.kind == 2, reinterpret_cast<const uint8_t*>(m.raw.data()), m.raw.size(), mine, buf);
+        for (size_t i = 0; i < mine; ++i) sum[i] += buf[i];
+      }
+    }
+    sender.join();
+    if (send_err) std::rethrow_exception(send_err);
+    size_t at = 0;
+    for (size_t k = 0; k < own_[rank_].size(); ++k) {
+      const Range rg = own_[rank_][k];
+      const size_t len = rg.second - rg.first;
+      for (size_t i = 0; i < len; ++i) sum[at + i] /= (float)nw;
+      opts_[k].step(C_.data() + rg.first, sum.data() + at, len);
+      at += len;
+    }
+    publish();
   }
 
   // All ranks learn every rank's losses and stop flag and run the same policy on them.
@@ -329,7 +415,9 @@ class NetRank {
   std::map<size_t, wire::Channel> peers_;
   std::vector<float> C_, W_, R_;
   uint64_t seed_ = 0;
-  bool f16_wire_ = false, exact_ = true;
+  bool f16_wire_ = false, exact_ = true, sparse_ = false;
+  double sparse_r_ = 0.0;
+  std::vector<size_t> server_index_;
 };
 
 }  // namespace ono

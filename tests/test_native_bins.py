@@ -228,6 +228,26 @@ def test_several_cpu_ranks_run_natively_over_a_tcp_mesh_between_the_nodes(bins, 
         assert got["stop_reason"] == "max_epochs"
         assert np.allclose(got["loss_history"], ref.loss_history(), rtol=1e-5)
         assert got.get("metrics", {}).get("data_plane") == "native tcp mesh"
+    # the sparse serializer on the same mesh: thresholded (offset, f16 run) messages per worker and server shard, unsent
+    # entries stay in the workers' residuals; same thresholds (same seeds) as the in-process cluster
+    from orchestra.serializer import SparseSerializer
+
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, cxx_nodes, algorithm={"parameter_server": {
+        "nservers": 1, "synchronizer": "barrier", "store": "blocking"}})
+    cfg = json.loads(open(tp).read())
+    cfg["serializer"] = {"sparse_capable": {"r": 0.3}}
+    cfg["early_stopping"] = None
+    open(tp, "w").write(json.dumps(cfg))
+    got = _run_orchestrator(bins, mp, tp)
+    m = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+    ref = orchestrate(m, orchestra.parameter_server([f"cpu:{i}" for i in range(3)], 1, InlineDataset(xs, ys, 6, 3), Adam(0.05),
+                                                    CrossEntropy(), BarrierSync(), BlockingStore(), tr["max_epochs"], 5, seed=3,
+                                                    serializer=SparseSerializer(0.3))).wait(quiet=True)
+    dense = orchestrate(m, orchestra.parameter_server([f"cpu:{i}" for i in range(3)], 1, InlineDataset(xs, ys, 6, 3), Adam(0.05),
+                                                      CrossEntropy(), BarrierSync(), BlockingStore(), tr["max_epochs"], 5, seed=3)).wait(quiet=True)
+    assert got.get("metrics", {}).get("data_plane") == "native tcp mesh"
+    assert np.allclose(got["loss_history"], ref.loss_history(), rtol=1e-5)
+    assert not np.array_equal(ref.loss_history(), dense.loss_history())      # the serializer does change the run
 
 
 def test_published_rows_run_on_native_node_processes(bins, tmp_path):
@@ -245,3 +265,38 @@ def test_published_rows_run_on_native_node_processes(bins, tmp_path):
     assert all(rec["epochs"] == 2 and rec["samples_per_sec"] > 0 and np.isfinite(rec["final_loss"]) for rec in recs)
     assert [rec["nodes"] for rec in recs] == [3, 5]
 
+
+def test_sparse_serializer_runs_natively_between_node_processes(bins, cxx_nodes, tmp_path):
+    """A model large enough for the thresholded (offset, f16 run) encoding to beat the dense one: the node processes ship
+    those records over the TCP mesh, servers lift them, workers keep what they did not send; the run equals the in-process
+    cluster's (same thresholds from the same seeds) and differs from a run without the serializer."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+    from orchestra.serializer import SparseSerializer
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync
+
+    rng = np.random.default_rng(1)
+    xs = rng.random((60, 6)).astype(np.float32)
+    ys = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 60)]
+    model = Sequential([Dense(64, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+
+    def run(addrs, ser):
+        tr = orchestra.parameter_server(addrs, 1, InlineDataset(xs, ys, 6, 3), GradientDescent(0.5), CrossEntropy(), BarrierSync(),
+                                        BlockingStore(), 6, 10, seed=3, serializer=ser)
+        return orchestrate(model, tr).wait(quiet=True)
+
+    native = run(cxx_nodes, SparseSerializer(0.05))
+    inproc = run([f"cpu:{i}" for i in range(3)], SparseSerializer(0.05))
+    dense = run([f"cpu:{i}" for i in range(3)], None)
+    assert (native.metrics() or {}).get("data_plane") == "native tcp mesh"
+    assert np.allclose(native.loss_history(), inproc.loss_history(), rtol=1e-5)
+    assert np.abs(native.weights_array() - inproc.weights_array()).max() < 1e-5
+    # with 5 % of the entries per message the run is visibly not the dense one
+    assert np.abs(np.asarray(inproc.loss_history()) - np.asarray(dense.loss_history())).max() > 1e-4
