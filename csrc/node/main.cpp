@@ -198,10 +198,12 @@ void run_net_rank(wire::Channel& ch, const Json& job, const Json& plan, const Tr
     std::lock_guard<std::mutex> lk(mu);
     ch.send_command(Json::tagged("event", e));
   };
+  std::atomic<bool> switched{false};
   std::thread worker([&] {
     try {
       NetRank r(plan, training, rank, listen_fd, node_id, std::move(xs), std::move(ys), send_event, stop);
       params = r.run();
+      switched = r.switched();
     } catch (const std::exception& e) {
       failure = e.what();
       logf(1, "rank %zu failed: %s", rank, e.what());
@@ -228,7 +230,7 @@ void run_net_rank(wire::Channel& ch, const Json& job, const Json& plan, const Tr
           ch.send_floats(wire::KIND_PARAMS, params.data(), params.size());
         }
         Json met = Json::object();
-        met.set("switched", false);
+        met.set("switched", switched.load());
         met.set("data_plane", "native tcp mesh");
         send_event(TrainingEvent{"metrics", 0, {}, met.dump()});
       } else if (m.is_command("disconnect")) break;

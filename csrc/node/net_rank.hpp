@@ -13,6 +13,9 @@
 #pragma once
 #include <atomic>
 #include <cmath>
+#include <mutex>
+#include <deque>
+#include <condition_variable>
 #include <functional>
 #include <map>
 #include <memory>
@@ -30,15 +33,30 @@ class NetRank {
 
   static bool supports(const Json& plan, const TrainingConfig& training) {
     const std::string algo = plan.at("algorithm").as_string();
-    if (algo == "strategy_switch") return false;
+    if (algo == "strategy_switch") {
+      // all-reduce first, then the promoted ranks become servers in place (see do_switch); the sparse serializer would
+      // have to be re-encoded at every ring hop of the first phase and stays with the rank processes
+      if (training.serializer.sparse) return false;
+      for (auto& a : plan.at("switch").at("post_actions").items()) {
+        if (a.at("action").as_string() != "upgrade") continue;
+        const Json& sp = a.at("spec");
+        const bool barrier = sp.at("synchronizer").is_string() ? sp.at("synchronizer").as_string() == "barrier"
+                                                                : sp.at("synchronizer").find("barrier") != nullptr;
+        if (barrier && sp.at("store").as_string() != "blocking") return false;
+      }
+      return true;
+    }
     // the sparse serializer: natively for the parameter server (one thresholded message per worker and server shard, as in
     // comms/src/sparse); the ring all-reduce re-encodes at every hop and stays with the rank processes
     if (training.serializer.sparse && algo != "parameter_server") return false;
     if (algo == "parameter_server")
       for (auto& s : plan.at("servers").items()) {
         const Json& sp = s.at("spec");
-        if (sp.at("synchronizer").is_string() ? sp.at("synchronizer").as_string() != "barrier" : !sp.at("synchronizer").find("barrier")) return false;
-        if (sp.at("store").as_string() != "blocking") return false;
+        const bool barrier = sp.at("synchronizer").is_string() ? sp.at("synchronizer").as_string() == "barrier"
+                                                                : sp.at("synchronizer").find("barrier") != nullptr;
+        // barrier + blocking store: one averaged update per round; non-blocking synchroniser (either store): every push is
+        // applied on arrival. A wild store behind a barrier stays with the rank processes.
+        if (barrier && sp.at("store").as_string() != "blocking") return false;
       }
     return true;
   }
@@ -67,9 +85,17 @@ class NetRank {
       d.labels = std::move(ys);
       trainer_ = std::make_unique<oracle::RoundTrainer>(wspec, std::move(d), exact_);
     }
+    active_.assign(worker_ranks_.size(), 1);
+    resets_progress_ = training.b200.switch_resets_progress;
+    ar_phase_ = plan_.at("algorithm").as_string() != "parameter_server";
     policy_ = std::make_unique<SessionPolicy>(worker_ranks_.size());
     if (const Json* es = plan_.find("early_stopping"); es && !es->is_null())
       policy_->enable_early_stopping((size_t)es->at("window").as_u64(), es->at("tolerance").as_double());
+    if (plan_.at("algorithm").as_string() == "strategy_switch") {
+      const Json& sw = plan_.at("switch");
+      policy_->enable_switch((size_t)sw.at("window").as_u64(), sw.at("threshold").as_double());
+      can_switch_ = true;
+    }
     // ownership table and the optimizer of every owned range
     own_.assign(world_, {});
     Json opt_spec;
@@ -81,6 +107,9 @@ class NetRank {
         for (auto& rg : s.at("ranges").items()) own_[r].push_back({(size_t)rg[0].as_u64(), (size_t)rg[1].as_u64()});
         opt_spec = s.at("spec").at("optimizer");
         server_index_[r] = si++;
+        const Json& sy = s.at("spec").at("synchronizer");
+        async_ = !(sy.is_string() ? sy.as_string() == "barrier" : sy.find("barrier") != nullptr);
+        wild_ = s.at("spec").at("store").as_string() == "wild";
       }
     } else {
       const size_t base = n_ / world_, rem = n_ % world_;
@@ -95,6 +124,8 @@ class NetRank {
     const oracle::OptimizerSpec os = oracle::OptimizerSpec::from_spec(opt_spec);
     for (auto& rg : own_[rank_]) opts_.emplace_back(os, rg.second - rg.first);
   }
+
+  bool switched() const { return switched_; }
 
   // Runs the session to its end; the return value is the final parameter vector (every rank holds it).
   std::vector<float> run() {
@@ -121,12 +152,31 @@ class NetRank {
         losses = tr.losses;
         if (losses.size() > nep) losses.resize(nep);
       }
-      if (sparse_) exchange_sparse();
-      else exchange();
-      epoch += nep;
-      const int decision = decide(losses, nep, reason);
-      if (decision == 1) break;
+      if (ar_phase_) {
+        // all-reduce workers report first and exchange afterwards (worker/src/workers/all_reduce.rs:57-135): a round
+        // that ends in a stop or a switch is not applied
+        epoch += nep;
+        const int decision = decide(losses, nep, reason);
+        if (decision == 1) break;
+        if (decision == 2 && can_switch_) {
+          can_switch_ = false;
+          do_switch();
+          if (resets_progress_) {            // worker/src/builder.rs:179-181: the rebuilt trainer starts its epochs again
+            epoch = 0;
+            max_epochs_ = new_max_epochs_;
+          }
+          continue;
+        }
+        exchange();
+      } else {
+        if (async_) exchange_async();
+        else if (sparse_) exchange_sparse();
+        else exchange();
+        epoch += nep;
+        if (decide(losses, nep, reason) == 1) break;
+      }
     }
+    if (async_) publish();      // every rank ends with the owners' final ranges
     TrainingEvent done{"complete", 0, {}, reason};
     emit_(done);
     for (auto& p : peers_) p.second.close();
@@ -187,7 +237,90 @@ class NetRank {
     }
   }
 
-  bool is_worker(size_t r) const { return std::find(worker_ranks_.begin(), worker_ranks_.end(), r) != worker_ranks_.end(); }
+  bool is_worker(size_t r) const {
+    for (size_t i = 0; i < worker_ranks_.size(); ++i)
+      if (worker_ranks_[i] == r) return active_[i] != 0;
+    return false;
+  }
+  size_t n_active() const { return (size_t)std::count(active_.begin(), active_.end(), (char)1); }
+
+  // All-reduce -> parameter server in place (orchestrator/src/sessions/event_listener.rs:171-219, node/src/router.rs:305-341,
+  // worker/src/builder.rs:165-200): the promoted ranks keep the ranges the plan gives them out of the replica every rank
+  // holds, stop training and hand their samples to the remaining workers in equal parts; optimizer state restarts.
+  void do_switch() {
+    const Json& acts = plan_.at("switch").at("post_actions");
+    std::vector<size_t> promoted, remaining;           // worker indices
+    for (size_t w = 0; w < worker_ranks_.size(); ++w)
+      (acts[w].at("action").as_string() == "upgrade" ? promoted : remaining).push_back(w);
+    if (rank_ == 0) {
+      emit_(TrainingEvent{"switch", 0, {}, ""});
+      for (size_t w : promoted) emit_(TrainingEvent{"upgrading", w, {}, ""});
+    }
+    // the promoted ranks' samples, in equal parts, to the remaining workers (appended in the order of the promoted)
+    oracle::Dataset mine;
+    if (trainer_) mine = trainer_->dataset();
+    const size_t done = trainer_ ? trainer_->epochs_done() : 0;
+    for (size_t w : promoted) {
+      const size_t pr = worker_ranks_[w];
+      if (pr == rank_) {
+        auto pieces = mine.partition(remaining.size());
+        for (size_t k = 0; k < remaining.size(); ++k) {
+          const size_t to = worker_ranks_[remaining[k]];
+          if (to == rank_) continue;
+          peers_.at(to).send_floats(wire::KIND_PARAMS, pieces[k].samples.data(), pieces[k].samples.size());
+          peers_.at(to).send_floats(wire::KIND_PARAMS, pieces[k].labels.data(), pieces[k].labels.size());
+        }
+      } else if (widx_ >= 0 && acts[(size_t)widx_].at("action").as_string() != "upgrade") {
+        wire::Message mx = peers_.at(pr).recv(timeout_ms_), my = peers_.at(pr).recv(timeout_ms_);
+        if (mx.kind != wire::KIND_PARAMS || my.kind != wire::KIND_PARAMS) throw wire::WireError("expected a dataset part from a promoted rank");
+        oracle::Dataset part;
+        part.x_size = mine.x_size;
+        part.y_size = mine.y_size;
+        part.samples = std::move(mx.floats);
+        part.labels = std::move(my.floats);
+        mine.append(part);
+      }
+    }
+    // new ownership, fresh optimizer state
+    own_.assign(world_, {});
+    server_index_.assign(world_, 0);
+    Json opt_spec;
+    for (size_t w : promoted) {
+      const Json& a = acts[w];
+      const size_t r = worker_ranks_[w];
+      for (auto& rg : a.at("ranges").items()) own_[r].push_back({(size_t)rg[0].as_u64(), (size_t)rg[1].as_u64()});
+      server_index_[r] = (size_t)a.at("server_index").as_u64();
+      opt_spec = a.at("spec").at("optimizer");
+      const Json& sy = a.at("spec").at("synchronizer");
+      async_ = !(sy.is_string() ? sy.as_string() == "barrier" : sy.find("barrier") != nullptr);
+      wild_ = a.at("spec").at("store").as_string() == "wild";
+      active_[w] = 0;
+      policy_->worker_left(w);
+    }
+    opts_.clear();
+    const oracle::OptimizerSpec os = oracle::OptimizerSpec::from_spec(opt_spec);
+    for (auto& rg : own_[rank_]) opts_.emplace_back(os, rg.second - rg.first);
+    // the remaining workers train on with their enlarged partitions; the promoted ranks only serve
+    if (widx_ >= 0 && !active_[(size_t)widx_]) {
+      trainer_.reset();
+      widx_ = -1;
+    } else if (widx_ >= 0) {
+      const Json& ts = acts[(size_t)widx_].at("trainer_spec");
+      trainer_ = std::make_unique<oracle::RoundTrainer>(ts, std::move(mine), exact_);
+      if (!resets_progress_) trainer_->set_epochs_done(done);
+      offline_ = (size_t)ts.at("offline_epochs").as_u64();
+    }
+    for (size_t w : remaining) {
+      const Json& ts = acts[w].at("trainer_spec");
+      new_max_epochs_ = (size_t)ts.at("max_epochs").as_u64();
+      offline_ = (size_t)ts.at("offline_epochs").as_u64();
+    }
+    ar_phase_ = false;
+    W_ = C_;
+    std::fill(R_.begin(), R_.end(), 0.f);
+    if (rank_ == 0)
+      for (size_t w : promoted) emit_(TrainingEvent{"upgraded", w, {}, ""});
+  }
 
   void send_range(wire::Channel& ch, const float* p, size_t n, bool f16) {
     if (!f16) { ch.send_floats(wire::KIND_PARAMS, p, n); return; }
@@ -218,7 +351,7 @@ class NetRank {
   // Residuals to the owners, averaged update at the owners, fresh parameters to everybody.
   void exchange() {
     const bool me_worker = widx_ >= 0;
-    const size_t nw = worker_ranks_.size();
+    const size_t nw = n_active();
     // a sender thread keeps the sockets draining while this thread receives: nobody blocks on a full send buffer
     std::exception_ptr send_err;
     std::thread sender([&] {
@@ -285,7 +418,7 @@ class NetRank {
   // the worker's residual, the rest waits for a later round (worker/src/middlewares/server_cluster.rs:85-104).
   void exchange_sparse() {
     const bool me_worker = widx_ >= 0;
-    const size_t nw = worker_ranks_.size();
+    const size_t nw = n_active();
     auto shard_len = [&](size_t q) { size_t n = 0; for (auto& rg : own_[q]) n += rg.second - rg.first; return n; };
     std::map<size_t, Compressed> out;
     std::vector<float> g;
@@ -351,6 +484,172 @@ class NetRank {
     publish();
   }
 
+  // Non-blocking synchroniser (parameter_server/src/synchronization/non_blocking.rs; wild store: storage/wild/shard.rs:43-58):
+  // an owner applies every worker's push on arrival, alone (blocking store: divided by the number of workers; wild store:
+  // as it is), and answers that worker with its shard as it stands then. Three threads per rank and round: a receiver that
+  // reads every peer socket and never sends (it applies pushes and files replies), a transmitter that does all the
+  // sending in order, and this thread, which encodes its own pushes and waits for both. A receiver that also sent could
+  // block on a full socket while its peer does the same.
+  void exchange_async() {
+    const bool me_worker = widx_ >= 0;
+    const size_t nw = n_active();
+    auto shard_len = [&](size_t q) { size_t n = 0; for (auto& rg : own_[q]) n += rg.second - rg.first; return n; };
+    const size_t mine = shard_len(rank_);
+    struct Frame { size_t peer; wire::Channel::RawFrame f; };
+    std::mutex tx_mu, shard_mu;
+    std::condition_variable tx_cv;
+    std::deque<Frame> tx_q;
+    bool tx_stop = false;
+    std::exception_ptr tx_err, rx_err;
+    auto enqueue = [&](size_t peer, wire::Channel::RawFrame f) {
+      { std::lock_guard<std::mutex> lk(tx_mu); tx_q.push_back(Frame{peer, std::move(f)}); }
+      tx_cv.notify_one();
+    };
+    std::thread tx([&] {
+      try {
+        for (;;) {
+          Frame fr;
+          {
+            std::unique_lock<std::mutex> lk(tx_mu);
+            tx_cv.wait(lk, [&] { return tx_stop || !tx_q.empty(); });
+            if (tx_q.empty()) return;
+            fr = std::move(tx_q.front());
+            tx_q.pop_front();
+          }
+          peers_.at(fr.peer).send_raw(fr.f);
+        }
+      } catch (...) { tx_err = std::current_exception(); }
+    });
+    auto floats_frame = [](uint32_t kind, const float* p, size_t n) {
+      wire::Channel::RawFrame f;
+      f.kind = kind;
+      f.body.assign(reinterpret_cast<const char*>(p), n * sizeof(float));
+      return f;
+    };
+    // one push, applied alone
+    auto apply = [&](const std::vector<float>& grad, std::vector<float>& fresh) {
+      std::lock_guard<std::mutex> lk(shard_mu);
+      size_t at = 0;
+      fresh.clear();
+      std::vector<float> g;
+      for (size_t k = 0; k < own_[rank_].size(); ++k) {
+        const Range rg = own_[rank_][k];
+        const size_t len = rg.second - rg.first;
+        g.assign(grad.begin() + (long)at, grad.begin() + (long)(at + len));
+        if (!wild_) for (float& v : g) v /= (float)nw;
+        opts_[k].step(C_.data() + rg.first, g.data(), len);
+        fresh.insert(fresh.end(), C_.begin() + (long)rg.first, C_.begin() + (long)rg.second);
+        at += len;
+      }
+    };
+    auto decode = [&](const wire::Message& m, size_t n, std::vector<float>& dst) {
+      if (m.kind == wire::KIND_PARAMS) {
+        if (m.floats.size() != n) throw wire::WireError("a peer sent a shard of the wrong length");
+        dst = m.floats;
+      } else if (m.kind == 2) {
+        dst.assign(n, 0.f);
+        sparse_lift(dst, reinterpret_cast<const uint8_t*>(m.raw.data()), m.raw.size());
+        dst.resize(n, 0.f);
+      } else if (m.kind == 1) {
+        if (m.raw.size() != 2 * n) throw wire::WireError("a peer sent an f16 shard of the wrong length");
+        dst.resize(n);
+        for (size_t i = 0; i < n; ++i)
+          dst[i] = f16_to_f32((uint16_t)((unsigned char)m.raw[2 * i] | ((unsigned char)m.raw[2 * i + 1] << 8)));
+      } else throw wire::WireError("unexpected message during the gradient exchange");
+    };
+    // What this rank still expects from each peer this round: a push (the peer is a worker and I own a shard) and / or an
+    // answer (the peer owns a shard and I am a worker). A peer that has delivered both is not read any further: its next
+    // frames belong to the loss exchange that follows.
+    std::map<size_t, int> want_push, want_reply;
+    size_t pushes_left = 0, replies_left = 0;
+    for (auto& p : peers_) {
+      const size_t q = p.first;
+      want_push[q] = (mine && is_worker(q)) ? 1 : 0;
+      want_reply[q] = (me_worker && !own_[q].empty()) ? 1 : 0;
+      pushes_left += (size_t)want_push[q];
+      replies_left += (size_t)want_reply[q];
+    }
+    std::thread rx([&] {
+      try {
+        std::vector<float> grad, fresh;
+        while (pushes_left + replies_left > 0) {
+          std::vector<pollfd> pfs;
+          std::vector<size_t> who;
+          for (auto& p : peers_)
+            if (want_push[p.first] + want_reply[p.first] > 0) { pfs.push_back(pollfd{p.second.fd(), POLLIN, 0}); who.push_back(p.first); }
+          int r;
+          do { r = ::poll(pfs.data(), pfs.size(), timeout_ms_); } while (r < 0 && errno == EINTR);
+          if (r <= 0) throw wire::WireError("timed out during the asynchronous exchange");
+          for (size_t i = 0; i < pfs.size(); ++i) {
+            if (!(pfs[i].revents & (POLLIN | POLLHUP | POLLERR))) continue;
+            const size_t q = who[i];
+            wire::Message m = peers_.at(q).recv(timeout_ms_);
+            if (m.kind == wire::KIND_DATACHUNK) {       // an owner's answer: its shard after my push
+              size_t at = 0;
+              if (m.floats.size() != shard_len(q) || want_reply[q] == 0) throw wire::WireError("unexpected shard from a peer");
+              want_reply[q] = 0;
+              for (auto& rg : own_[q]) {
+                std::copy(m.floats.begin() + (long)at, m.floats.begin() + (long)(at + rg.second - rg.first), W_.begin() + (long)rg.first);
+                at += rg.second - rg.first;
+              }
+              --replies_left;
+            } else {                                     // a worker's push for my shard
+              if (want_push[q] == 0) throw wire::WireError("unexpected push from a peer");
+              want_push[q] = 0;
+              decode(m, mine, grad);
+              apply(grad, fresh);
+              enqueue(q, floats_frame(wire::KIND_DATACHUNK, fresh.data(), fresh.size()));
+              --pushes_left;
+            }
+          }
+        }
+      } catch (...) { rx_err = std::current_exception(); }
+    });
+    // my own pushes
+    std::vector<float> g, dec, fresh;
+    try {
+      if (me_worker)
+        for (size_t q = 0; q < world_; ++q) {
+          if (own_[q].empty()) continue;
+          g.clear();
+          for (auto& rg : own_[q]) g.insert(g.end(), R_.begin() + (long)rg.first, R_.begin() + (long)rg.second);
+          Compressed c;
+          const bool coded = sparse_ || f16_wire_;
+          if (coded) c = compress_gradient(g.data(), g.size(), sparse_, sparse_r_, seed_ + 31 * (uint64_t)widx_ + server_index_[q]);
+          for (auto& rg : own_[q])
+            for (size_t i = rg.first; i < rg.second; ++i)
+              if (!coded || !c.sparse || std::fabs(R_[i]) >= c.threshold) R_[i] = 0.f;
+          if (q == rank_) {          // my own shard: applied here, under the same lock the receiver takes
+            if (coded) {
+              wire::Message m;
+              m.kind = c.sparse ? 2 : 1;
+              m.raw.assign(reinterpret_cast<const char*>(c.bytes.data()), c.bytes.size());
+              decode(m, mine, dec);
+            } else dec = g;
+            apply(dec, fresh);
+            size_t at = 0;
+            for (auto& rg : own_[rank_]) {
+              std::copy(fresh.begin() + (long)at, fresh.begin() + (long)(at + rg.second - rg.first), W_.begin() + (long)rg.first);
+              at += rg.second - rg.first;
+            }
+          } else if (coded) {
+            wire::Channel::RawFrame f;
+            f.kind = c.sparse ? 2 : 1;
+            f.body.assign(reinterpret_cast<const char*>(c.bytes.data()), c.bytes.size());
+            enqueue(q, std::move(f));
+          } else {
+            enqueue(q, floats_frame(wire::KIND_PARAMS, g.data(), g.size()));
+          }
+        }
+    } catch (...) { rx_err = rx_err ? rx_err : std::current_exception(); }
+    rx.join();
+    { std::lock_guard<std::mutex> lk(tx_mu); tx_stop = true; }
+    tx_cv.notify_one();
+    tx.join();
+    if (rx_err) std::rethrow_exception(rx_err);
+    if (tx_err) std::rethrow_exception(tx_err);
+  }
+
   // All ranks learn every rank's losses and stop flag and run the same policy on them.
   int decide(const std::vector<double>& losses, size_t nl, std::string& reason) {
     std::vector<float> mine(nl + 1, std::nanf(""));
@@ -392,10 +691,12 @@ class NetRank {
         }
       if (rank_ == 0) emit_(TrainingEvent{"losses", wi, ls, ""});
       const int d = (int)policy_->on_losses(wi, ls.data(), ls.size());
-      decision = std::max(decision, d == 2 ? 0 : d);
+      if (d == 1) decision = 1;
+      else if (d == 2 && decision == 0) decision = 2;
     }
     if (stop_req) { reason = "stopped"; return 1; }
     if (decision == 1) reason = "early_stopping";
+    if (decision == 2) switched_ = true;
     return decision;
   }
 
@@ -415,7 +716,10 @@ class NetRank {
   std::map<size_t, wire::Channel> peers_;
   std::vector<float> C_, W_, R_;
   uint64_t seed_ = 0;
-  bool f16_wire_ = false, exact_ = true, sparse_ = false;
+  bool f16_wire_ = false, exact_ = true, sparse_ = false, async_ = false, wild_ = false;
+  bool can_switch_ = false, resets_progress_ = false, switched_ = false, ar_phase_ = false;
+  size_t new_max_epochs_ = 1;
+  std::vector<char> active_;
   double sparse_r_ = 0.0;
   std::vector<size_t> server_index_;
 };

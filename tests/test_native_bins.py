@@ -300,3 +300,75 @@ def test_sparse_serializer_runs_natively_between_node_processes(bins, cxx_nodes,
     assert np.abs(native.weights_array() - inproc.weights_array()).max() < 1e-5
     # with 5 % of the entries per message the run is visibly not the dense one
     assert np.abs(np.asarray(inproc.loss_history()) - np.asarray(dense.loss_history())).max() > 1e-4
+
+
+@pytest.mark.parametrize("store", ["blocking", "wild"])
+def test_non_blocking_parameter_server_runs_natively_between_node_processes(bins, cxx_nodes, tmp_path, store):
+    """Non-blocking synchroniser on node processes: every push is applied on arrival, alone, and answered with the owner's
+    shard as it stands then (blocking store: divided by the number of workers; wild store: applied as it is). The order of
+    arrival is not fixed, so the check is that the run ends, learns, and stayed on the native data plane."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescent
+    from orchestra.serializer import SparseSerializer
+    from orchestra.store import BlockingStore, WildStore
+    from orchestra.sync import NonBlockingSync
+
+    rng = np.random.default_rng(2)
+    labels = rng.integers(0, 3, 90)
+    xs = (np.eye(3, dtype=np.float32)[labels] @ rng.random((3, 6)).astype(np.float32) + 0.1 * rng.random((90, 6)).astype(np.float32))
+    ys = np.eye(3, dtype=np.float32)[labels]
+    model = Sequential([Dense(32, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+    for ser, b200 in ((None, None), (None, {"wire_dtype": "f16"}), (SparseSerializer(0.1), None)):
+        tr = orchestra.parameter_server(cxx_nodes, 1, InlineDataset(xs, ys, 6, 3), GradientDescent(0.2 if store == "wild" else 0.6),
+                                        CrossEntropy(), NonBlockingSync(), WildStore() if store == "wild" else BlockingStore(), 12, 15,
+                                        seed=3, serializer=ser, b200=b200)
+        m = orchestrate(model, tr).wait(quiet=True)
+        hist = m.loss_history()
+        assert (m.metrics() or {}).get("data_plane") == "native tcp mesh"
+        assert len(hist) == 12 and np.isfinite(hist).all() and hist[-1] < 0.8 * hist[0], hist
+
+
+@pytest.mark.parametrize("sync", ["barrier", "non_blocking"])
+def test_strategy_switch_runs_natively_between_node_processes(bins, cxx_nodes, tmp_path, sync):
+    """All-reduce, then the switch: the promoted node keeps its ranges, stops training and hands its samples to the two
+    remaining workers, which carry on against it as a parameter server; all of it inside the node processes. With the
+    barrier synchroniser the run equals the in-process cluster's."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescentWithMomentum
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync, NonBlockingSync
+
+    rng = np.random.default_rng(4)
+    labels = rng.integers(0, 3, 96)
+    xs = (np.eye(3, dtype=np.float32)[labels] @ rng.random((3, 6)).astype(np.float32) + 0.1 * rng.random((96, 6)).astype(np.float32))
+    ys = np.eye(3, dtype=np.float32)[labels]
+    model = Sequential([Dense(16, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+
+    def run(addrs):
+        tr = orchestra.strategy_switch(addrs, 1, InlineDataset(xs, ys, 6, 3), GradientDescentWithMomentum(0.3, 0.9), CrossEntropy(),
+                                       BarrierSync() if sync == "barrier" else NonBlockingSync(), BlockingStore(), 10, 8, seed=3,
+                                       b200={"switch_window": 2, "switch_threshold": 10.0})
+        return orchestrate(model, tr).wait(quiet=True)
+
+    native = run(cxx_nodes)
+    met = native.metrics() or {}
+    assert met.get("data_plane") == "native tcp mesh" and met.get("switched") is True
+    hist = native.loss_history()
+    assert len(hist) == 10 and np.isfinite(hist).all() and hist[-1] < hist[0]
+    if sync == "barrier":
+        inproc = run([f"cpu:{i}" for i in range(3)])
+        assert (inproc.metrics() or {}).get("switched") is True
+        assert np.allclose(hist, inproc.loss_history(), rtol=1e-5)
+        assert np.abs(native.weights_array() - inproc.weights_array()).max() < 1e-5

@@ -101,3 +101,51 @@ def test_remote_native_rank_over_the_control_channel_is_clean(san, tmp_path):
             node.kill()
             _, err = node.communicate()
     assert "Sanitizer" not in err and "runtime error:" not in err, err[-3000:]
+
+
+def test_native_mesh_between_node_processes_is_clean(san, tmp_path):
+    """Three instrumented node processes exchanging among themselves: the barrier exchange, the sparse serializer, the
+    non-blocking exchange (receiver + transmitter + worker thread per rank, pushes applied under the shard lock) and the
+    strategy switch (re-partition, dataset hand-over, new roles) in place."""
+    kind, bins, env = san
+    ports = []
+    for _ in range(3):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    nodes = [subprocess.Popen([bins["ono-node"], "--port", str(p), "--device", "cpu"], env=env, stderr=subprocess.PIPE, text=True)
+             for p in ports]
+    errs = []
+    try:
+        for p in ports:
+            for _ in range(200):
+                try:
+                    socket.create_connection(("127.0.0.1", p), timeout=0.2).close()
+                    break
+                except OSError:
+                    time.sleep(0.05)
+        addrs = [f"127.0.0.1:{p}" for p in ports]
+        for algorithm, extra in (({"parameter_server": {"nservers": 1, "synchronizer": "barrier", "store": "blocking"}},
+                                  {"serializer": {"sparse_capable": {"r": 0.2}}}),
+                                 ({"parameter_server": {"nservers": 1, "synchronizer": "non_blocking", "store": "blocking"}}, {}),
+                                 ({"parameter_server": {"nservers": 1, "synchronizer": "non_blocking", "store": "wild"}},
+                                  {"b200": {"wire_dtype": "f16"}}),
+                                 ({"strategy_switch": {"nservers": 1, "synchronizer": "non_blocking", "store": "blocking"}},
+                                  {"b200": {"switch_window": 2, "switch_threshold": 10.0}})):
+            mp, tp = _write(tmp_path, addrs, algorithm, extra)
+            r = subprocess.run([bins["ono-orchestrator"], mp, tp, "--quiet"], capture_output=True, text=True, timeout=600, env=env)
+            res = _clean(kind, r)
+            assert res["stop_reason"] == "max_epochs" and len(res["loss_history"]) == 4
+            assert res.get("metrics", {}).get("data_plane") == "native tcp mesh"
+    finally:
+        for n in nodes:
+            n.terminate()
+        for n in nodes:
+            try:
+                _, err = n.communicate(timeout=60)
+            except subprocess.TimeoutExpired:
+                n.kill()
+                _, err = n.communicate()
+            errs.append(err)
+    for err in errs:
+        assert "Sanitizer" not in err and "runtime error:" not in err, err[-3000:]
