@@ -34,9 +34,7 @@ class NetRank {
   static bool supports(const Json& plan, const TrainingConfig& training) {
     const std::string algo = plan.at("algorithm").as_string();
     if (algo == "strategy_switch") {
-      // all-reduce first, then the promoted ranks become servers in place (see do_switch); the sparse serializer would
-      // have to be re-encoded at every ring hop of the first phase and stays with the rank processes
-      if (training.serializer.sparse) return false;
+      // all-reduce first, then the promoted ranks become servers in place (see do_switch)
       for (auto& a : plan.at("switch").at("post_actions").items()) {
         if (a.at("action").as_string() != "upgrade") continue;
         const Json& sp = a.at("spec");
@@ -46,9 +44,9 @@ class NetRank {
       }
       return true;
     }
-    // the sparse serializer: natively for the parameter server (one thresholded message per worker and server shard, as in
-    // comms/src/sparse); the ring all-reduce re-encodes at every hop and stays with the rank processes
-    if (training.serializer.sparse && algo != "parameter_server") return false;
+    // the sparse serializer: one thresholded message per worker and server shard under the parameter server
+    // (exchange_sparse), re-encoded at every hop of the ring under all-reduce (exchange_ring_sparse)
+    if (training.serializer.sparse && algo == "all_reduce" && plan.at("workers").size() < 2) return false;
     if (algo == "parameter_server")
       for (auto& s : plan.at("servers").items()) {
         const Json& sp = s.at("spec");
@@ -167,7 +165,8 @@ class NetRank {
           }
           continue;
         }
-        exchange();
+        if (sparse_) exchange_ring_sparse();
+        else exchange();
       } else {
         if (async_) exchange_async();
         else if (sparse_) exchange_sparse();
@@ -484,6 +483,86 @@ class NetRank {
     publish();
   }
 
+  // The reference's ring all-reduce with the sparse serializer (worker/src/middlewares/worker_ring.rs:112-204,
+  // mod.rs:15-59): n - 1 scatter-reduce hops and n - 1 all-gather hops over near-equal chunks, every hop's chunk encoded
+  // anew (thresholded (offset, f16 run) records, or dense f16 when that is not larger). In the scatter phase what a worker
+  // sent leaves its residual and the rest waits for a later round; in the gather phase a worker keeps of its own copy only
+  // what it sent on. Every worker then divides by n and applies its own optimizer to its replica.
+  void exchange_ring_sparse() {
+    const size_t n = worker_ranks_.size(), w = (size_t)widx_;
+    const size_t next = worker_ranks_[(w + 1) % n], prev = worker_ranks_[(w + n - 1) % n];
+    auto bounds = [&](size_t c, size_t& lo, size_t& hi) {
+      const size_t base = n_ / n, rem = n_ % n;
+      lo = base * c + std::min(c, rem);
+      hi = lo + base + (c < rem ? 1 : 0);
+    };
+    // one hop: my chunk goes to the next worker while the previous worker's arrives
+    auto hop = [&](const Compressed& c, size_t recv_len, std::vector<float>& got) {
+      std::exception_ptr send_err;
+      std::thread sender([&] {
+        try {
+          wire::Channel::RawFrame f;
+          f.kind = c.sparse ? 2 : 1;
+          f.body.assign(reinterpret_cast<const char*>(c.bytes.data()), c.bytes.size());
+          peers_.at(next).send_raw(f);
+        } catch (...) { send_err = std::current_exception(); }
+      });
+      std::exception_ptr recv_err;
+      try {
+        wire::Message m = peers_.at(prev).recv(timeout_ms_);
+        if (m.kind == 2) {
+          got.assign(recv_len, 0.f);
+          sparse_lift(got, reinterpret_cast<const uint8_t*>(m.raw.data()), m.raw.size());
+          got.resize(recv_len, 0.f);
+        } else if (m.kind == 1 && m.raw.size() == 2 * recv_len) {
+          got.resize(recv_len);
+          for (size_t k = 0; k < recv_len; ++k)
+            got[k] = f16_to_f32((uint16_t)((unsigned char)m.raw[2 * k] | ((unsigned char)m.raw[2 * k + 1] << 8)));
+        } else throw wire::WireError("unexpected message during the ring exchange");
+      } catch (...) { recv_err = std::current_exception(); }
+      sender.join();
+      if (recv_err) std::rethrow_exception(recv_err);
+      if (send_err) std::rethrow_exception(send_err);
+    };
+    std::vector<float> grad(n_, 0.f), got;
+    size_t i = w, lo, hi;
+    for (size_t st = 0; st + 1 < n; ++st) {                      // scatter-reduce
+      bounds(i, lo, hi);
+      Compressed c = compress_gradient(R_.data() + lo, hi - lo, true, sparse_r_, seed_ + st * 131 + w);
+      for (size_t k = lo; k < hi; ++k)
+        if (!c.sparse || std::fabs(R_[k]) >= c.threshold) R_[k] = 0.f;
+      i = (i + n - 1) % n;
+      bounds(i, lo, hi);
+      hop(c, hi - lo, got);
+      for (size_t k = lo; k < hi; ++k) R_[k] += got[k - lo];
+    }
+    i = (w + 1) % n;                                              // all-gather
+    bounds(i, lo, hi);
+    std::copy(R_.begin() + (long)lo, R_.begin() + (long)hi, grad.begin() + (long)lo);
+    for (size_t j = 0; j + 1 < n; ++j) {
+      bounds(i, lo, hi);
+      Compressed c = compress_gradient(grad.data() + lo, hi - lo, true, sparse_r_, seed_ + 7919 + j * 131 + w);
+      if (c.sparse) {
+        for (size_t k = lo; k < hi; ++k)
+          if (std::fabs(grad[k]) < c.threshold) grad[k] = 0.f;
+      } else if (j == 0) {
+        std::fill(R_.begin() + (long)lo, R_.begin() + (long)hi, 0.f);
+      }
+      i = (i + n - 1) % n;
+      bounds(i, lo, hi);
+      hop(c, hi - lo, got);
+      std::copy(got.begin(), got.end(), grad.begin() + (long)lo);
+    }
+    const float inv = 1.0f / (float)n;
+    for (float& g : grad) g *= inv;
+    if (!ring_opt_) {
+      const Json& wspec = plan_.at("workers")[w].at("spec").at("trainer");
+      ring_opt_ = std::make_unique<oracle::Optimizer>(oracle::OptimizerSpec::from_spec(wspec.at("optimizer")), n_);
+    }
+    ring_opt_->step(C_.data(), grad.data(), n_);
+    W_ = C_;
+  }
+
   // Non-blocking synchroniser (parameter_server/src/synchronization/non_blocking.rs; wild store: storage/wild/shard.rs:43-58):
   // an owner applies every worker's push on arrival, alone (blocking store: divided by the number of workers; wild store:
   // as it is), and answers that worker with its shard as it stands then. Three threads per rank and round: a receiver that
@@ -711,6 +790,7 @@ class NetRank {
   std::vector<size_t> worker_ranks_;
   std::vector<std::vector<Range>> own_;
   std::vector<oracle::Optimizer> opts_;
+  std::unique_ptr<oracle::Optimizer> ring_opt_;      // the whole-replica optimizer of the ring exchange
   std::unique_ptr<oracle::RoundTrainer> trainer_;
   std::unique_ptr<SessionPolicy> policy_;
   std::map<size_t, wire::Channel> peers_;

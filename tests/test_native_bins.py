@@ -372,3 +372,46 @@ def test_strategy_switch_runs_natively_between_node_processes(bins, cxx_nodes, t
         assert (inproc.metrics() or {}).get("switched") is True
         assert np.allclose(hist, inproc.loss_history(), rtol=1e-5)
         assert np.abs(native.weights_array() - inproc.weights_array()).max() < 1e-5
+
+
+def test_sparse_ring_all_reduce_runs_natively_between_node_processes(bins, cxx_nodes, tmp_path):
+    """The reference's ring with its sparse serializer on node processes: every hop's chunk thresholded and encoded anew,
+    residuals kept at the senders; the run equals the in-process cluster's ring hop for hop (same seeds), also through a
+    strategy switch whose second phase carries the serializer on."""
+    import orchestra
+    from orchestra import Sequential, orchestrate
+    from orchestra.activations import Softmax, Tanh
+    from orchestra.arch import Dense
+    from orchestra.datasets import InlineDataset
+    from orchestra.initialization import XavierUniform
+    from orchestra.loss_fns import CrossEntropy
+    from orchestra.optimizers import GradientDescentWithMomentum
+    from orchestra.serializer import SparseSerializer
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync
+
+    rng = np.random.default_rng(6)
+    labels = rng.integers(0, 3, 96)
+    xs = (np.eye(3, dtype=np.float32)[labels] @ rng.random((3, 6)).astype(np.float32) + 0.1 * rng.random((96, 6)).astype(np.float32))
+    ys = np.eye(3, dtype=np.float32)[labels]
+    model = Sequential([Dense(64, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+    opt = lambda: GradientDescentWithMomentum(0.3, 0.9)
+
+    def ar(addrs, ser):
+        return orchestrate(model, orchestra.all_reduce(addrs, InlineDataset(xs, ys, 6, 3), opt(), CrossEntropy(), 8, 8, seed=3,
+                                                       serializer=ser)).wait(quiet=True)
+
+    def ss(addrs):
+        tr = orchestra.strategy_switch(addrs, 1, InlineDataset(xs, ys, 6, 3), opt(), CrossEntropy(), BarrierSync(), BlockingStore(), 8, 8,
+                                       seed=3, serializer=SparseSerializer(0.05), b200={"switch_window": 2, "switch_threshold": 10.0})
+        return orchestrate(model, tr).wait(quiet=True)
+
+    cpu = [f"cpu:{i}" for i in range(3)]
+    native, inproc, dense = ar(cxx_nodes, SparseSerializer(0.05)), ar(cpu, SparseSerializer(0.05)), ar(cpu, None)
+    assert (native.metrics() or {}).get("data_plane") == "native tcp mesh"
+    assert np.allclose(native.loss_history(), inproc.loss_history(), rtol=1e-5)
+    assert np.abs(native.weights_array() - inproc.weights_array()).max() < 1e-5
+    assert np.abs(np.asarray(inproc.loss_history()) - np.asarray(dense.loss_history())).max() > 1e-4
+    native, inproc = ss(cxx_nodes), ss(cpu)
+    assert (native.metrics() or {}).get("data_plane") == "native tcp mesh" and (native.metrics() or {}).get("switched") is True
+    assert np.allclose(native.loss_history(), inproc.loss_history(), rtol=1e-5)

@@ -105,8 +105,8 @@ def test_remote_native_rank_over_the_control_channel_is_clean(san, tmp_path):
 
 def test_native_mesh_between_node_processes_is_clean(san, tmp_path):
     """Three instrumented node processes exchanging among themselves: the barrier exchange, the sparse serializer, the
-    non-blocking exchange (receiver + transmitter + worker thread per rank, pushes applied under the shard lock) and the
-    strategy switch (re-partition, dataset hand-over, new roles) in place."""
+    non-blocking exchange (receiver + transmitter + worker thread per rank, pushes applied under the shard lock), the
+    strategy switch (re-partition, dataset hand-over, new roles) in place and the sparse ring."""
     kind, bins, env = san
     ports = []
     for _ in range(3):
@@ -131,7 +131,8 @@ def test_native_mesh_between_node_processes_is_clean(san, tmp_path):
                                  ({"parameter_server": {"nservers": 1, "synchronizer": "non_blocking", "store": "wild"}},
                                   {"b200": {"wire_dtype": "f16"}}),
                                  ({"strategy_switch": {"nservers": 1, "synchronizer": "non_blocking", "store": "blocking"}},
-                                  {"b200": {"switch_window": 2, "switch_threshold": 10.0}})):
+                                  {"b200": {"switch_window": 2, "switch_threshold": 10.0}}),
+                                 ("all_reduce", {"serializer": {"sparse_capable": {"r": 0.2}}})):
             mp, tp = _write(tmp_path, addrs, algorithm, extra)
             r = subprocess.run([bins["ono-orchestrator"], mp, tp, "--quiet"], capture_output=True, text=True, timeout=600, env=env)
             res = _clean(kind, r)
