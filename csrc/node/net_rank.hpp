@@ -176,6 +176,17 @@ class NetRank {
       }
     }
     if (async_) publish();      // every rank ends with the owners' final ranges
+    // The orchestrator asks node 0 for the result. All-reduce replicas are the run's result through worker 0's copy
+    // (orchestrator/src/sessions/session.rs:371-412); under the lossy ring they are not bit-equal, so worker 0's copy
+    // travels to rank 0 when another rank hosts that worker.
+    if (ar_phase_ && sparse_ && !worker_ranks_.empty() && worker_ranks_[0] != 0) {
+      if (rank_ == worker_ranks_[0]) peers_.at(0).send_floats(wire::KIND_PARAMS, C_.data(), C_.size());
+      else if (rank_ == 0) {
+        wire::Message m = peers_.at(worker_ranks_[0]).recv(timeout_ms_);
+        if (m.kind != wire::KIND_PARAMS || m.floats.size() != n_) throw wire::WireError("expected worker 0's replica");
+        C_ = std::move(m.floats);
+      }
+    }
     TrainingEvent done{"complete", 0, {}, reason};
     emit_(done);
     for (auto& p : peers_) p.second.close();
