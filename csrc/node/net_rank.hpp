@@ -7,9 +7,16 @@
 // their shards. Decisions (early stop, stop request) are taken by every rank from the same gathered losses, as on the
 // GPU ranks, so no extra messaging is needed.
 //
-// Covered here: all_reduce and parameter_server with the barrier synchroniser and the blocking store. The asynchronous
-// synchroniser, the wild store, the sparse serializer and the strategy switch run in a rank process instead (the caller
-// checks `NetRank::supports`).
+// Covered here (the caller checks `NetRank::supports`):
+//   * all_reduce: the owner-based exchange above; with the sparse serializer the reference's ring itself, every hop's
+//     chunk thresholded and encoded anew (exchange_ring_sparse);
+//   * parameter_server with the barrier synchroniser and the blocking store (exchange), also with the sparse serializer:
+//     one thresholded message per worker and server shard, unsent entries kept by the worker (exchange_sparse);
+//   * parameter_server with the non-blocking synchroniser on either store: every push applied on arrival, alone, and
+//     answered with the shard as it stands (exchange_async);
+//   * strategy_switch: all-reduce first; at the switch the promoted ranks keep their ranges, hand their samples to the
+//     remaining workers and serve (do_switch).
+// A wild store behind a barrier runs in a rank process instead.
 #pragma once
 #include <atomic>
 #include <cmath>
