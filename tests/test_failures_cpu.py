@@ -5,6 +5,7 @@ Reference behaviour being matched: a worker io error ends the session with an er
 (orchestrator/src/sessions/worker_listener.rs:99-104, event_listener.rs:128-132); a departing barrier
 member never deadlocks the others (parameter_server/src/synchronization/barrier.rs:30-38).
 """
+import os
 import threading
 import time
 
@@ -22,6 +23,8 @@ from orchestra.loss_fns import CrossEntropy
 from orchestra.optimizers import GradientDescent
 from oxidized_neural_orchestra_b200.runtime import wire
 from oxidized_neural_orchestra_b200.runtime.launch import spawn_nodes
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_dyn_barrier_survivors_pass_when_a_member_leaves():
@@ -129,3 +132,61 @@ def test_control_channel_reports_a_silent_peer_instead_of_blocking():
     conn.close()
     ch.close()
     lsock.close()
+
+
+@pytest.mark.parametrize("sync", ["barrier", "non_blocking"])
+def test_a_native_node_that_dies_mid_run_ends_the_session_with_an_error(sync):
+    """Native node processes exchanging over their TCP mesh: one of them is killed mid-run; the others' receiver /
+    transmitter threads see the closed socket (or run into the communication time limit), the session reports an
+    error and nothing hangs."""
+    import socket
+    import subprocess
+
+    from orchestra.store import BlockingStore
+    from orchestra.sync import BarrierSync, NonBlockingSync
+
+    exe = os.path.join(ROOT, "bin", "ono-node")
+    if not os.path.exists(exe):
+        pytest.skip("bin/ono-node is not built")
+    ports = []
+    for _ in range(3):
+        with socket.socket() as sk:
+            sk.bind(("127.0.0.1", 0))
+            ports.append(sk.getsockname()[1])
+    procs = [subprocess.Popen([exe, "--port", str(p), "--device", "cpu"], env=dict(os.environ, ONO_LOG="error")) for p in ports]
+    try:
+        for p in ports:
+            for _ in range(200):
+                try:
+                    socket.create_connection(("127.0.0.1", p), timeout=0.2).close()
+                    break
+                except OSError:
+                    time.sleep(0.05)
+        rng = np.random.default_rng(0)
+        xs = rng.random((60, 6), dtype=np.float32)
+        ys = np.eye(3, dtype=np.float32)[rng.integers(0, 3, 60)]
+        model = Sequential([Dense(5, XavierUniform(), Tanh()), Dense(3, XavierUniform(), Softmax())])
+        tr = orchestra.parameter_server([f"127.0.0.1:{p}" for p in ports], 1, InlineDataset(xs, ys, 6, 3), GradientDescent(0.01), CrossEntropy(),
+                                        BarrierSync() if sync == "barrier" else NonBlockingSync(), BlockingStore(), 1_000_000, 5, seed=1,
+                                        b200={"comm_timeout_s": 5.0})
+        s = orchestrate(model, tr)
+        box = {}
+
+        def waiter():
+            try:
+                box["model"] = s.wait(quiet=True)
+            except RuntimeError as e:
+                box["error"] = str(e)
+
+        t = threading.Thread(target=waiter, daemon=True)
+        t.start()
+        time.sleep(1.5)                 # let some rounds go through
+        procs[2].kill()                 # the exact child this test started
+        t.join(timeout=90)
+        assert not t.is_alive(), "the session hung after a node died"
+        assert "error" in box, box
+    finally:
+        for p in procs:
+            p.kill()
+        for p in procs:
+            p.wait(timeout=30)
