@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <fstream>
 #include <numeric>
@@ -236,6 +237,58 @@ std::vector<NamedTensor> load_safetensors(const std::string& path) {
     out.push_back(std::move(nt));
   }
   return out;
+}
+
+void save_state_sidecar(const std::string& path, const StateSidecar& st) {
+  const float pows[2] = {st.b1t, st.b2t};
+  const size_t nm = st.m.size() * 4, nv = st.v.size() * 4;
+  std::string header = "{\"__metadata__\":{\"optimizer\":\"" + st.optimizer + "\",\"epochs\":\"" + std::to_string(st.epochs) +
+                       "\",\"n_params\":\"" + std::to_string(st.m.size()) + "\"}," +
+                       "\"optimizer.m\":{\"dtype\":\"F32\",\"shape\":[" + std::to_string(st.m.size()) + "],\"data_offsets\":[0," + std::to_string(nm) + "]}," +
+                       "\"optimizer.v\":{\"dtype\":\"F32\",\"shape\":[" + std::to_string(st.v.size()) + "],\"data_offsets\":[" + std::to_string(nm) + "," + std::to_string(nm + nv) + "]}," +
+                       "\"optimizer.adam_pows\":{\"dtype\":\"F32\",\"shape\":[2],\"data_offsets\":[" + std::to_string(nm + nv) + "," + std::to_string(nm + nv + 8) + "]}}";
+  while (header.size() % 8) header.push_back(' ');
+  const std::string tmp = path + ".tmp";
+  {
+    std::ofstream f(tmp, std::ios::binary | std::ios::trunc);
+    if (!f) throw std::runtime_error("cannot write " + tmp);
+    uint8_t le[8];
+    const uint64_t hl = header.size();
+    for (int i = 0; i < 8; ++i) le[i] = (uint8_t)(hl >> (8 * i));
+    f.write((const char*)le, 8);
+    f.write(header.data(), (std::streamsize)header.size());
+    f.write((const char*)st.m.data(), (std::streamsize)nm);
+    f.write((const char*)st.v.data(), (std::streamsize)nv);
+    f.write((const char*)pows, 8);
+    f.flush();
+    if (!f) throw std::runtime_error("short write to " + tmp);
+  }
+  if (std::rename(tmp.c_str(), path.c_str()) != 0) throw std::runtime_error("cannot rename " + tmp + " to " + path);
+}
+
+StateSidecar load_state_sidecar(const std::string& path, size_t n_params) {
+  StateSidecar st;
+  for (auto& t : load_safetensors(path)) {
+    if (t.name == "optimizer.m") st.m = std::move(t.data);
+    else if (t.name == "optimizer.v") st.v = std::move(t.data);
+    else if (t.name == "optimizer.adam_pows" && t.data.size() == 2) { st.b1t = t.data[0]; st.b2t = t.data[1]; }
+  }
+  if (st.m.size() != n_params || st.v.size() != n_params)
+    throw std::runtime_error(path + ": state of " + std::to_string(st.m.size()) + " parameters does not fit a model of " + std::to_string(n_params));
+  // the metadata block: strings
+  std::ifstream f(path, std::ios::binary);
+  uint8_t le[8];
+  f.read((char*)le, 8);
+  uint64_t hl = 0;
+  for (int i = 0; i < 8; ++i) hl |= (uint64_t)le[i] << (8 * i);
+  std::string hs(hl, '\0');
+  f.read(hs.data(), (std::streamsize)hl);
+  const Json header = Json::parse(hs);
+  if (const Json* md = header.find("__metadata__")) {
+    if (const Json* e = md->find("epochs"); e && e->is_string()) st.epochs = (size_t)std::strtoull(e->as_string().c_str(), nullptr, 10);
+    if (const Json* o = md->find("optimizer"); o && o->is_string()) st.optimizer = o->as_string();
+  }
+  return st;
 }
 
 // ---- dataset files ----------------------------------------------------------------------------

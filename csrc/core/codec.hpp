@@ -51,6 +51,19 @@ struct NamedTensor {
 void save_safetensors(const std::string& path, const ModelConfig& model, size_t input_size, const std::vector<float>& params);
 std::vector<NamedTensor> load_safetensors(const std::string& path);
 
+// Optimizer-state sidecar of a checkpoint (an addition: the reference exports weights only). A safetensors container with
+// `optimizer.m`, `optimizer.v` F32 [n] in the flat parameter order of the weights file, `optimizer.adam_pows` F32 [2]
+// (running b1^t, b2^t) and string metadata `optimizer`, `epochs`, `n_params`; the same file the Python runtime writes
+// for GPU and CPU ranks. Written to a temporary name and renamed, so a crash never leaves a truncated file.
+struct StateSidecar {
+  std::vector<float> m, v;
+  float b1t = 1.f, b2t = 1.f;
+  size_t epochs = 0;
+  std::string optimizer;
+};
+void save_state_sidecar(const std::string& path, const StateSidecar& st);
+StateSidecar load_state_sidecar(const std::string& path, size_t n_params);
+
 // ---- dataset files ----------------------------------------------------------------------------
 // Converts a .csv/.tsv file to a sibling .bin of packed LE f32 (cached if it exists; a non-numeric
 // first row is skipped as a header). Other extensions are returned unchanged.

@@ -123,9 +123,9 @@ struct B200Config {
   std::string init_from;                  // safetensors checkpoint to start from instead of the initialisers (warm start / resume)
   std::string checkpoint_path;            // GPU ranks: periodic checkpoint (weights here, optimizer state beside it); "{epoch}" is replaced
   long long checkpoint_every = 0;         // epochs between periodic checkpoints (0 = off)
-  std::string state_path;                 // GPU ranks: rank 0 writes the optimizer state (m, v, Adam powers) here at the end of the run
-  long long start_epoch = -1;             // GPU ranks: first epoch number for the shuffle sequence (-1: 0, or the epochs recorded in init_state_from)
-  std::string init_state_from;            // GPU ranks: optimizer state to resume from (a file written through state_path)
+  std::string state_path;                 // GPU ranks and in-process CPU ranks: the optimizer state (m, v, Adam powers) is written here at the end of the run
+  long long start_epoch = -1;             // first epoch number for the shuffle sequence (-1: 0, or the epochs recorded in init_state_from)
+  std::string init_state_from;            // GPU ranks and in-process CPU ranks: optimizer state to resume from (a file written through state_path)
   std::string trace_path;                 // chrome-trace JSON of the run's phases (empty = off)
   std::string metrics_path;               // JSONL, one record per round / step window (empty = off)
   bool present = false;

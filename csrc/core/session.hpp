@@ -113,6 +113,22 @@ class LocalSession final : public Session {
     o.leaky_relu_exact = t.b200.leaky_relu_exact;
     o.switch_resets_progress = t.b200.switch_resets_progress;
     workers_ = plan.at("workers").size();
+    // resume (additive): the weights come through the plan (`b200.init_from`), the optimizer state and the position in
+    // the shuffle sequence from the sidecar a previous run wrote
+    n_params_ = (size_t)plan.at("n_params").as_u64();
+    state_path_ = t.b200.state_path;
+    long long start = t.b200.start_epoch;
+    if (!t.b200.init_state_from.empty()) {
+      StateSidecar st = load_state_sidecar(t.b200.init_state_from, n_params_);
+      o.init_m = std::move(st.m);
+      o.init_v = std::move(st.v);
+      o.init_b1t = st.b1t;
+      o.init_b2t = st.b2t;
+      if (start < 0) start = (long long)st.epochs;
+    }
+    o.start_epoch = start > 0 ? (size_t)start : 0;
+    if (const Json* op = plan.at("workers")[0].at("spec").at("trainer").find("optimizer"); op && op->is_object() && !op->members().empty())
+      opt_kind_ = op->members().at(0).first;
     cluster_ = std::make_unique<oracle::LocalCluster>(plan, std::move(data), o);
     cluster_->start();
   }
@@ -126,12 +142,26 @@ class LocalSession final : public Session {
   void stop() override { cluster_->request_stop(); }
   std::vector<float> final_params() override {
     cluster_->join();
+    if (!state_path_.empty() && !state_written_) {
+      const oracle::ClusterState& cs = cluster_->final_state();
+      StateSidecar st;
+      st.m = cs.m.empty() ? std::vector<float>(n_params_, 0.f) : cs.m;
+      st.v = cs.v.empty() ? std::vector<float>(n_params_, 0.f) : cs.v;
+      st.b1t = cs.b1t;
+      st.b2t = cs.b2t;
+      st.epochs = cs.epochs;
+      st.optimizer = opt_kind_;
+      save_state_sidecar(state_path_, st);
+      state_written_ = true;
+    }
     return cluster_->final_params();
   }
   bool switched() const override { return cluster_->switched(); }
 
  private:
-  size_t workers_ = 0;
+  size_t workers_ = 0, n_params_ = 0;
+  std::string state_path_, opt_kind_;
+  bool state_written_ = false;
   std::unique_ptr<oracle::LocalCluster> cluster_;
 };
 

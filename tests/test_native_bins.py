@@ -415,3 +415,29 @@ def test_sparse_ring_all_reduce_runs_natively_between_node_processes(bins, cxx_n
     native, inproc = ss(cxx_nodes), ss(cpu)
     assert (native.metrics() or {}).get("data_plane") == "native tcp mesh" and (native.metrics() or {}).get("switched") is True
     assert np.allclose(native.loss_history(), inproc.loss_history(), rtol=1e-5)
+
+
+def test_orchestrator_binary_resumes_with_optimizer_state(bins, tmp_path):
+    """`ono-orchestrator` on in-process CPU ranks: `b200.state_path` writes the optimizer-state sidecar (the file the Python
+    runtime writes), and a second run from `--save`d weights + that sidecar continues the first: 3 + 3 epochs give the
+    losses of 6."""
+    from oxidized_neural_orchestra_b200.utils.state import load_state
+
+    mp, tp, model, tr, xs, ys = _configs(tmp_path, ["cpu:0", "cpu:1"], epochs=6)
+    whole = _run_orchestrator(bins, mp, tp)
+
+    def write(epochs, b200):
+        cfg = json.loads(open(tp).read())
+        cfg["max_epochs"], cfg["b200"], cfg["early_stopping"] = epochs, b200, None
+        path = tmp_path / f"t_{epochs}_{len(b200)}.json"
+        path.write_text(json.dumps(cfg))
+        return str(path)
+
+    w, st = str(tmp_path / "half.safetensors"), str(tmp_path / "half.state.safetensors")
+    half = _run_orchestrator(bins, mp, write(3, {"state_path": st}), "--save", w)
+    side = load_state(st, 53)
+    assert side["meta"]["epochs"] == "3" and side["meta"]["optimizer"] == "adam" and np.abs(side["m"]).max() > 0 and side["v"].max() > 0
+    rest = _run_orchestrator(bins, mp, write(3, {"init_from": w, "init_state_from": st}))
+    assert np.allclose(half["loss_history"] + rest["loss_history"], whole["loss_history"], rtol=1e-5)
+    cold = _run_orchestrator(bins, mp, write(3, {"init_from": w, "start_epoch": 3}))
+    assert not np.allclose(cold["loss_history"], whole["loss_history"][3:], rtol=1e-5)
